@@ -1,0 +1,27 @@
+"""SwiGLU: down(silu(gate(x)) · up(x)), gate and up in one product with gate's rows first, silu in 32-bit
+(std/holon_std/ffn/units.py:12-50; std/holon_std/ffn/reference.py:7-12)."""
+from __future__ import annotations
+
+import torch
+
+from .base import BuildContext, Part
+from .linear import Linear
+
+
+class SwiGLU(Part):
+    def __init__(self, ctx: BuildContext, *, inter: int, hidden: int, layer: int = 0) -> None:
+        super().__init__()
+        self.ctx, self.inter = ctx, inter
+        self.gate_up = self.add_child("gate_up", Linear(ctx, "weight", hidden, {
+            "gate_proj.weight": inter, "up_proj.weight": inter}))
+        self.down = self.add_child("down_proj", Linear(ctx, "weight", inter, {"weight": hidden}))
+
+    def loadables(self, prefix: str = ""):
+        for name, p, rows in super().loadables(prefix):
+            yield name.replace(prefix + "gate_up.", prefix, 1), p, rows
+
+    def forward(self, x: torch.Tensor, step) -> torch.Tensor:
+        gu = self.gate_up.forward(x)
+        act = self.ctx.empty(x.shape[0], self.inter)
+        self.ctx.kernels.silu_mul(act, gu)
+        return self.down.forward(act)

@@ -1,0 +1,27 @@
+"""Tiny configurations and small tools shared by the tests."""
+from __future__ import annotations
+
+import torch
+
+from holon_b200.weights import RandomSource, write_model_folder
+
+# Two tiny Qwen3 configurations that differ in every size and option: head counts and groups (2 and 6), head sizes
+# (16 and 48, the second no power of two and heads × head size ≠ hidden), width, layers, vocabulary (256 and 389,
+# the second odd), eps, rotation base, tied or own head.
+TINY_A = dict(architectures=["Qwen3ForCausalLM"], num_hidden_layers=2, hidden_size=64, num_attention_heads=4,
+              num_key_value_heads=2, head_dim=16, intermediate_size=128, vocab_size=256, rope_theta=10000.0,
+              rms_norm_eps=1e-6, tie_word_embeddings=True, max_position_embeddings=128)
+TINY_B = dict(architectures=["Qwen3ForCausalLM"], num_hidden_layers=3, hidden_size=96, num_attention_heads=6,
+              num_key_value_heads=1, head_dim=48, intermediate_size=176, vocab_size=389, rope_theta=1000000.0,
+              rms_norm_eps=1e-5, tie_word_embeddings=False, max_position_embeddings=512)
+TINY = {"a": (TINY_A, 0), "b": (TINY_B, 1)}
+
+
+def make_folder(tmp_path, name: str):
+    config, seed = TINY[name]
+    return write_model_folder(RandomSource(config, seed), tmp_path / f"tiny_{name}")
+
+
+def random_prompt(vocab: int, n: int, seed: int) -> list[int]:
+    g = torch.Generator().manual_seed(seed)
+    return torch.randint(0, vocab, (n,), generator=g).tolist()
