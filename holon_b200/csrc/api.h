@@ -1,0 +1,65 @@
+// The C interface of the kernel library. Every function enqueues work on `stream` and returns at once:
+// 0 on success, HB_ERR_REFUSED for sizes or types a kernel does not take (hb_last_error() says which),
+// HB_ERR_CUDA when the launch itself failed. Pointers are device pointers unless a comment says otherwise.
+// dtype codes: 0 = float32, 1 = bfloat16.
+#pragma once
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define HB_F32 0
+#define HB_BF16 1
+#define HB_ERR_REFUSED 1
+#define HB_ERR_CUDA 2
+
+typedef void* hb_stream;
+
+const char* hb_last_error(void);
+int hb_version(void);
+
+// out[t, :] = float(table[ids[t], :]); ids outside [0, vocab) give a row of zeros.
+int hb_embed(float* out, const void* table, int table_dtype, const int32_t* ids, int tokens, int hidden, int vocab,
+             hb_stream stream);
+
+// Row r reads row t = index ? index[r] : r of h (and of delta when given): v = h[t] + delta[t];
+// out[r] = v * rsqrt(mean(v^2) + eps) * (weight + offset), rounded once. With delta and without index, h[t] = v is
+// written back (h must then be float32). h_dtype may be bfloat16 only without delta (a plain norm).
+int hb_add_rmsnorm(void* out, int out_dtype, void* h, int h_dtype, const void* delta, const void* weight,
+                   int weight_dtype, float eps, float offset, const int32_t* index, int rows, int dim,
+                   hb_stream stream);
+
+// out[t, i] = silu(gate_up[t, i]) * gate_up[t, inter + i], in 32-bit, rounded once.
+int hb_silu_mul(void* out, const void* gate_up, int dtype, int tokens, int inter, hb_stream stream);
+
+// Per token and head: RMSNorm over the head (if weights are given), rounding, rotation of the first rotary_dim
+// dimensions in half-split pairs with cos|sin rows of `table` [max_positions, rotary_dim], rounding. q goes to q_out
+// [tokens, heads, head_dim]; k and v go to kv [pages, 2, kv_heads, page_size, head_dim] at write_index = page *
+// page_size + offset (a negative or out-of-range index skips the token). kv may be null (q only).
+int hb_qk_norm_rope_kv_write(void* q_out, const void* qkv, int dtype, const int32_t* positions, const float* table,
+                             int rotary_dim, int max_positions, const void* q_weight, const void* k_weight,
+                             int weight_dtype, float eps, float offset, void* kv, const int32_t* write_index,
+                             int pages, int page_size, int tokens, int heads, int kv_heads, int head_dim,
+                             hb_stream stream);
+
+// Attention of the step's new rows over the paged cache, any sizes, on CUDA cores with 32-bit arithmetic.
+// Row b owns query rows query_start[b] .. query_start[b+1], the last ones of its kv_len[b] tokens; a query at position
+// p sees keys j <= p, with window > 0 only p - j < window.
+int hb_attention_generic(void* out, const void* q, const void* kv, int dtype, const int32_t* block_table,
+                         int table_stride, const int32_t* row_slot, const int32_t* query_start,
+                         const int32_t* kv_len, int rows, int tokens, int heads, int kv_heads, int head_dim,
+                         int pages, int page_size, float scale, int window, hb_stream stream);
+
+// out[m, n] = sum_k x[m, k] * w[n, k], all float32, sums in a fixed order that does not depend on m's neighbours.
+int hb_gemm_f32(float* out, const float* x, const float* w, int m, int n, int k, hb_stream stream);
+
+// One token per logits row: arg max where temperature is 0, else a draw from softmax(logits / temperature) after the
+// filters (when `filtered`), by inverse CDF in vocabulary order with the uniform of (seed, position).
+int hb_sample(int32_t* tokens, const float* logits, const float* temperature, const int32_t* top_k,
+              const float* top_p, const float* min_p, const int32_t* seed_lo, const int32_t* seed_hi,
+              const int32_t* position, int filtered, int rows, int vocab, hb_stream stream);
+
+#ifdef __cplusplus
+}
+#endif

@@ -1,0 +1,120 @@
+// Embedding gather, RMSNorm with the residual sum folded in, SwiGLU's activation.
+#include <stdarg.h>
+#include <stdio.h>
+
+#include "common.cuh"
+
+static thread_local char g_error[512] = "";
+void hb_set_error(const char* fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_error, sizeof g_error, fmt, ap);
+    va_end(ap);
+}
+extern "C" const char* hb_last_error(void) { return g_error; }
+extern "C" int hb_version(void) { return 1; }
+
+// ---------------------------------------------------------------- embedding
+template <typename T>
+__global__ void embed_kernel(float* __restrict__ out, const T* __restrict__ table, const int32_t* __restrict__ ids,
+                             int hidden, int vocab) {
+    const int t = blockIdx.x;
+    const int id = ids[t];
+    const bool ok = id >= 0 && id < vocab;
+    const T* row = table + (size_t)(ok ? id : 0) * hidden;
+    float* o = out + (size_t)t * hidden;
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) o[i] = ok ? to_f32(row[i]) : 0.f;
+}
+
+extern "C" int hb_embed(float* out, const void* table, int table_dtype, const int32_t* ids, int tokens, int hidden,
+                        int vocab, hb_stream stream) {
+    if (tokens == 0) return 0;
+    cudaStream_t s = (cudaStream_t)stream;
+    const int threads = hidden >= 1024 ? 256 : 128;
+    if (table_dtype == HB_F32) embed_kernel<float><<<tokens, threads, 0, s>>>(out, (const float*)table, ids, hidden, vocab);
+    else if (table_dtype == HB_BF16) embed_kernel<bf16><<<tokens, threads, 0, s>>>(out, (const bf16*)table, ids, hidden, vocab);
+    else HB_REFUSE("embed: table dtype %d", table_dtype);
+    HB_LAUNCH_CHECK("embed");
+    return 0;
+}
+
+// ---------------------------------------------------------------- (add +) RMSNorm
+// One block per output row. The row is kept in shared memory as 32-bit between the two passes.
+template <typename TH, typename TD, typename TW>
+__global__ void add_rmsnorm_kernel(TD* __restrict__ out, TH* h, const TD* __restrict__ delta,
+                                   const TW* __restrict__ weight, float eps, float offset,
+                                   const int32_t* __restrict__ index, int dim) {
+    extern __shared__ float row[];
+    __shared__ float scratch[33];
+    const int r = blockIdx.x;
+    const size_t t = index ? (size_t)index[r] : (size_t)r;
+    TH* hr = h + t * dim;
+    const TD* dr = delta ? delta + t * dim : nullptr;
+    const bool write_back = delta != nullptr && index == nullptr;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < dim; i += blockDim.x) {
+        float v = to_f32(hr[i]);
+        if (dr) v += to_f32(dr[i]);
+        if (write_back) hr[i] = from_f32<TH>(v);
+        row[i] = v;
+        ss += v * v;
+    }
+    const float total = block_sum(ss, scratch);
+    const float rstd = rsqrtf(total / (float)dim + eps);
+    TD* o = out + (size_t)r * dim;
+    for (int i = threadIdx.x; i < dim; i += blockDim.x)
+        o[i] = from_f32<TD>(row[i] * rstd * (to_f32(weight[i]) + offset));
+}
+
+template <typename TH, typename TD, typename TW>
+static int launch_add_rmsnorm(void* out, void* h, const void* delta, const void* weight, float eps, float offset,
+                              const int32_t* index, int rows, int dim, cudaStream_t s) {
+    const size_t smem = (size_t)dim * sizeof(float);
+    auto kernel = add_rmsnorm_kernel<TH, TD, TW>;
+    if (smem > 200 * 1024) HB_REFUSE("rmsnorm: a row of %d values does not fit shared memory (limit 51200)", dim);
+    if (smem > 48 * 1024) HB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    const int threads = dim >= 2048 ? 512 : (dim >= 512 ? 256 : 128);
+    kernel<<<rows, threads, smem, s>>>((TD*)out, (TH*)h, (const TD*)delta, (const TW*)weight, eps, offset, index, dim);
+    HB_LAUNCH_CHECK("add_rmsnorm");
+    return 0;
+}
+
+extern "C" int hb_add_rmsnorm(void* out, int out_dtype, void* h, int h_dtype, const void* delta, const void* weight,
+                              int weight_dtype, float eps, float offset, const int32_t* index, int rows, int dim,
+                              hb_stream stream) {
+    if (rows == 0) return 0;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (h_dtype != HB_F32 && delta) HB_REFUSE("add_rmsnorm: the residual stream must be float32 when a delta is added");
+#define HB_CASE(H, D, W, TH, TD, TW) if (h_dtype == H && out_dtype == D && weight_dtype == W) \
+    return launch_add_rmsnorm<TH, TD, TW>(out, h, delta, weight, eps, offset, index, rows, dim, s);
+    HB_CASE(HB_F32, HB_F32, HB_F32, float, float, float)
+    HB_CASE(HB_F32, HB_BF16, HB_BF16, float, bf16, bf16)
+    HB_CASE(HB_F32, HB_BF16, HB_F32, float, bf16, float)
+    HB_CASE(HB_BF16, HB_BF16, HB_BF16, bf16, bf16, bf16)
+    HB_CASE(HB_BF16, HB_BF16, HB_F32, bf16, bf16, float)
+#undef HB_CASE
+    HB_REFUSE("add_rmsnorm: no kernel for dtypes h=%d out=%d weight=%d", h_dtype, out_dtype, weight_dtype);
+}
+
+// ---------------------------------------------------------------- silu(gate) * up
+template <typename T>
+__global__ void silu_mul_kernel(T* __restrict__ out, const T* __restrict__ gate_up, int inter, size_t total) {
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+        const size_t t = i / inter, c = i % inter;
+        const float g = to_f32(gate_up[t * 2 * inter + c]), u = to_f32(gate_up[t * 2 * inter + inter + c]);
+        out[i] = from_f32<T>(g / (1.f + expf(-g)) * u);
+    }
+}
+
+extern "C" int hb_silu_mul(void* out, const void* gate_up, int dtype, int tokens, int inter, hb_stream stream) {
+    const size_t total = (size_t)tokens * inter;
+    if (total == 0) return 0;
+    cudaStream_t s = (cudaStream_t)stream;
+    const int threads = 256;
+    const int blocks = (int)((total + threads - 1) / threads < 148 * 16 ? (total + threads - 1) / threads : 148 * 16);
+    if (dtype == HB_F32) silu_mul_kernel<float><<<blocks, threads, 0, s>>>((float*)out, (const float*)gate_up, inter, total);
+    else if (dtype == HB_BF16) silu_mul_kernel<bf16><<<blocks, threads, 0, s>>>((bf16*)out, (const bf16*)gate_up, inter, total);
+    else HB_REFUSE("silu_mul: dtype %d", dtype);
+    HB_LAUNCH_CHECK("silu_mul");
+    return 0;
+}

@@ -1,0 +1,104 @@
+// q/k RMSNorm per head + rotation + write of keys and values into the paged cache, one kernel.
+// One warp per (token, head): query heads first, then key heads, then value heads (a plain copy).
+#include "common.cuh"
+
+template <typename T, typename TW>
+__global__ void qk_norm_rope_kv_write_kernel(T* __restrict__ q_out, const T* __restrict__ qkv,
+                                             const int32_t* __restrict__ positions, const float* __restrict__ table,
+                                             int rotary_dim, int max_positions, const TW* __restrict__ q_weight,
+                                             const TW* __restrict__ k_weight, float eps, float offset,
+                                             T* __restrict__ kv, const int32_t* __restrict__ write_index, int pages,
+                                             int page_size, int heads, int kv_heads, int head_dim) {
+    extern __shared__ float smem[];
+    const int warps = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int t = blockIdx.x;
+    const int item = blockIdx.y * warps + warp;
+    const int items = heads + (kv ? 2 * kv_heads : 0);
+    if (item >= items) return;
+    float* y = smem + (size_t)warp * head_dim;
+    const int width = (heads + 2 * kv_heads) * head_dim;
+    const T* src = qkv + (size_t)t * width + (size_t)item * head_dim;       // q heads, k heads, v heads in a row
+
+    T* dst;
+    const TW* weight = nullptr;
+    bool rotate = false;
+    if (item < heads) {
+        dst = q_out + ((size_t)t * heads + item) * head_dim;
+        weight = q_weight;
+        rotate = true;
+    } else {
+        const int w = write_index[t];
+        if (w < 0) return;
+        const int page = w / page_size, off = w % page_size;
+        if (page >= pages) return;
+        const int is_v = item >= heads + kv_heads;
+        const int head = item - heads - (is_v ? kv_heads : 0);
+        dst = kv + ((((size_t)page * 2 + is_v) * kv_heads + head) * page_size + off) * head_dim;
+        weight = is_v ? nullptr : k_weight;
+        rotate = !is_v;
+    }
+    if (!rotate) {                                   // values: copied as they are
+        for (int d = lane; d < head_dim; d += 32) dst[d] = src[d];
+        return;
+    }
+    float ss = 0.f;
+    for (int d = lane; d < head_dim; d += 32) {
+        const float v = to_f32(src[d]);
+        y[d] = v;
+        ss += v * v;
+    }
+    if (weight) {
+        ss = warp_sum(ss);
+        const float rstd = rsqrtf(ss / (float)head_dim + eps);
+        for (int d = lane; d < head_dim; d += 32) y[d] = rounded<T>(y[d] * rstd * (to_f32(weight[d]) + offset));
+    }
+    __syncwarp();
+    const int half = rotary_dim >> 1;
+    int pos = positions[t];
+    pos = pos < 0 ? 0 : (pos >= max_positions ? max_positions - 1 : pos);
+    const float* cs = table + (size_t)pos * rotary_dim;
+    for (int i = lane; i < half; i += 32) {
+        const float a = y[i], b = y[i + half], c = cs[i], s = cs[half + i];
+        dst[i] = from_f32<T>(a * c - b * s);
+        dst[i + half] = from_f32<T>(b * c + a * s);
+    }
+    for (int d = rotary_dim + lane; d < head_dim; d += 32) dst[d] = from_f32<T>(y[d]);
+}
+
+template <typename T, typename TW>
+static int launch(void* q_out, const void* qkv, const int32_t* positions, const float* table, int rotary_dim,
+                  int max_positions, const void* qw, const void* kw, float eps, float offset, void* kv,
+                  const int32_t* write_index, int pages, int page_size, int tokens, int heads, int kv_heads,
+                  int head_dim, cudaStream_t s) {
+    const int warps = 4;
+    const int items = heads + (kv ? 2 * kv_heads : 0);
+    dim3 grid(tokens, (items + warps - 1) / warps);
+    const size_t smem = (size_t)warps * head_dim * sizeof(float);
+    qk_norm_rope_kv_write_kernel<T, TW><<<grid, warps * 32, smem, s>>>(
+        (T*)q_out, (const T*)qkv, positions, table, rotary_dim, max_positions, (const TW*)qw, (const TW*)kw, eps,
+        offset, (T*)kv, write_index, pages, page_size, heads, kv_heads, head_dim);
+    HB_LAUNCH_CHECK("qk_norm_rope_kv_write");
+    return 0;
+}
+
+extern "C" int hb_qk_norm_rope_kv_write(void* q_out, const void* qkv, int dtype, const int32_t* positions,
+                                        const float* table, int rotary_dim, int max_positions, const void* q_weight,
+                                        const void* k_weight, int weight_dtype, float eps, float offset, void* kv,
+                                        const int32_t* write_index, int pages, int page_size, int tokens, int heads,
+                                        int kv_heads, int head_dim, hb_stream stream) {
+    if (tokens == 0) return 0;
+    if (head_dim > 2048) HB_REFUSE("qk_norm_rope_kv_write: head_dim %d is above 2048", head_dim);
+    if (rotary_dim < 0 || rotary_dim > head_dim || (rotary_dim & 1))
+        HB_REFUSE("qk_norm_rope_kv_write: rotary_dim %d must be even and at most head_dim %d", rotary_dim, head_dim);
+    if (rotary_dim && !table) HB_REFUSE("qk_norm_rope_kv_write: a rotation needs its table");
+    if ((q_weight == nullptr) != (k_weight == nullptr)) HB_REFUSE("qk_norm_rope_kv_write: give both norm weights or none");
+    if (kv && !write_index) HB_REFUSE("qk_norm_rope_kv_write: writing the cache needs write_index");
+    cudaStream_t s = (cudaStream_t)stream;
+#define HB_ARGS q_out, qkv, positions, table, rotary_dim, max_positions, q_weight, k_weight, eps, offset, kv, \
+    write_index, pages, page_size, tokens, heads, kv_heads, head_dim, s
+    if (dtype == HB_F32 && weight_dtype == HB_F32) return launch<float, float>(HB_ARGS);
+    if (dtype == HB_BF16 && weight_dtype == HB_BF16) return launch<bf16, bf16>(HB_ARGS);
+    if (dtype == HB_BF16 && weight_dtype == HB_F32) return launch<bf16, float>(HB_ARGS);
+#undef HB_ARGS
+    HB_REFUSE("qk_norm_rope_kv_write: no kernel for dtype %d with weight dtype %d", dtype, weight_dtype);
+}

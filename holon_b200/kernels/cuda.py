@@ -1,0 +1,170 @@
+"""The kernel table of the product path: hand-written CUDA for sm_100a, called through the library's C interface.
+
+Every method takes torch tensors on one CUDA device, checks what the kernel assumes (device, dtype, contiguity,
+shapes) and enqueues the kernel on torch's current stream. There is no other path: a size a kernel refuses raises
+`KernelError` with the kernel's own message. bfloat16 matrix products go to cuBLAS through torch, as the
+reference's go through `torch.nn.functional.linear` (std/holon_std/ops/units.py:223-229); float32 products run
+the library's own true 32-bit kernel.
+"""
+from __future__ import annotations
+
+import ctypes
+
+import torch
+
+from .build import library_path
+
+_CODES = {torch.float32: 0, torch.bfloat16: 1}
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+def _code(t: torch.Tensor) -> int:
+    try:
+        return _CODES[t.dtype]
+    except KeyError:
+        raise KernelError(f"kernels take float32 and bfloat16 tensors, not {t.dtype}") from None
+
+
+class CudaKernels:
+    name = "cuda sm_100a"
+
+    def __init__(self, device) -> None:
+        self.device = torch.device(device)
+        if self.device.type != "cuda":
+            raise KernelError(f"the engine runs on a CUDA device; {self.device} is none")
+        self.path = library_path()
+        self.lib = ctypes.CDLL(str(self.path))
+        self.lib.hb_last_error.restype = ctypes.c_char_p
+        self._fn = {}
+        self.launches = 0
+        self.attention_bf16 = "fast"          # "generic" forces the CUDA-core kernel for bfloat16 too (tests)
+
+    # ------------------------------------------------------------------ plumbing
+    def _call(self, name: str, *args) -> None:
+        fn = self._fn.get(name)
+        if fn is None:
+            fn = self._fn[name] = getattr(self.lib, name)
+            fn.restype = ctypes.c_int
+        code = fn(*args, ctypes.c_void_p(torch.cuda.current_stream(self.device).cuda_stream))
+        self.launches += 1
+        if code:
+            raise KernelError(f"{name}: {self.lib.hb_last_error().decode()}")
+
+    def _check(self, *tensors: torch.Tensor | None) -> None:
+        for t in tensors:
+            if t is None:
+                continue
+            if t.device != self.device:
+                raise KernelError(f"a tensor lives on {t.device}, the kernels run on {self.device}")
+            if not t.is_contiguous():
+                raise KernelError(f"kernels take contiguous tensors; got strides {t.stride()} for shape {tuple(t.shape)}")
+
+    @staticmethod
+    def _p(t: torch.Tensor | None) -> ctypes.c_void_p:
+        return ctypes.c_void_p(t.data_ptr() if t is not None else 0)
+
+    @staticmethod
+    def _i32(t: torch.Tensor | None, what: str) -> ctypes.c_void_p:
+        if t is not None and t.dtype != torch.int32:
+            raise KernelError(f"{what} must be int32, not {t.dtype}")
+        return ctypes.c_void_p(t.data_ptr() if t is not None else 0)
+
+    # ------------------------------------------------------------------ kernels
+    def embed(self, out, table, ids) -> None:
+        self._check(out, table, ids)
+        if out.dtype != torch.float32 or out.shape != (ids.shape[0], table.shape[1]):
+            raise KernelError("embed: out must be float32 [tokens, hidden]")
+        self._call("hb_embed", self._p(out), self._p(table), _code(table), self._i32(ids, "ids"),
+                   ids.shape[0], table.shape[1], table.shape[0])
+
+    def rmsnorm(self, out, x, weight, eps, offset) -> None:
+        self._check(out, x, weight)
+        if out.shape != x.shape or weight.shape != (x.shape[-1],):
+            raise KernelError("rmsnorm: out and x must have one shape, weight [dim]")
+        rows = x.numel() // x.shape[-1]
+        self._call("hb_add_rmsnorm", self._p(out), _code(out), self._p(x), _code(x), self._p(None), self._p(weight),
+                   _code(weight), ctypes.c_float(eps), ctypes.c_float(offset), self._p(None), rows, x.shape[-1])
+
+    def add_rmsnorm(self, out, h, delta, weight, eps, offset, index) -> None:
+        self._check(out, h, delta, weight, index)
+        rows = index.shape[0] if index is not None else h.shape[0]
+        if h.dtype != torch.float32 or out.shape != (rows, h.shape[1]) or weight.shape != (h.shape[1],):
+            raise KernelError("add_rmsnorm: h must be float32 [tokens, dim], out [rows, dim], weight [dim]")
+        if delta is not None and (delta.shape != h.shape or delta.dtype != out.dtype):
+            raise KernelError("add_rmsnorm: delta must have h's shape and out's dtype")
+        self._call("hb_add_rmsnorm", self._p(out), _code(out), self._p(h), 0, self._p(delta), self._p(weight),
+                   _code(weight), ctypes.c_float(eps), ctypes.c_float(offset), self._i32(index, "index"), rows,
+                   h.shape[1])
+
+    def silu_mul(self, out, gate_up) -> None:
+        self._check(out, gate_up)
+        if gate_up.shape != (out.shape[0], 2 * out.shape[1]) or out.dtype != gate_up.dtype:
+            raise KernelError("silu_mul: gate_up must be [tokens, 2 * inter] of out's dtype")
+        self._call("hb_silu_mul", self._p(out), self._p(gate_up), _code(out), out.shape[0], out.shape[1])
+
+    def qk_norm_rope_kv_write(self, q_out, qkv, positions, table, rotary_dim, q_weight, k_weight, eps, offset, kv,
+                              write_index, heads, kv_heads, head_dim) -> None:
+        self._check(q_out, qkv, positions, table, q_weight, k_weight, kv, write_index)
+        t = qkv.shape[0]
+        if qkv.shape != (t, (heads + 2 * kv_heads) * head_dim) or q_out.shape != (t, heads, head_dim) \
+                or q_out.dtype != qkv.dtype:
+            raise KernelError("qk_norm_rope_kv_write: qkv must be [tokens, (heads + 2 kv_heads) head_dim], q_out "
+                              "[tokens, heads, head_dim], of one dtype")
+        if table is not None and (table.dtype != torch.float32 or table.shape[1] != rotary_dim):
+            raise KernelError("qk_norm_rope_kv_write: the rotation table must be float32 [positions, rotary_dim]")
+        if kv is not None and (kv.dtype != qkv.dtype or kv.shape[1:3] != (2, kv_heads) or kv.shape[4] != head_dim):
+            raise KernelError("qk_norm_rope_kv_write: kv must be [pages, 2, kv_heads, page_size, head_dim] of qkv's dtype")
+        self._call("hb_qk_norm_rope_kv_write", self._p(q_out), self._p(qkv), _code(qkv),
+                   self._i32(positions, "positions"), self._p(table), rotary_dim,
+                   table.shape[0] if table is not None else 0, self._p(q_weight), self._p(k_weight),
+                   _code(q_weight) if q_weight is not None else 0, ctypes.c_float(eps), ctypes.c_float(offset),
+                   self._p(kv), self._i32(write_index, "write_index"), kv.shape[0] if kv is not None else 0,
+                   kv.shape[3] if kv is not None else 1, t, heads, kv_heads, head_dim)
+
+    def paged_attention(self, out, q, kv, block_table, rows, scale, window) -> None:
+        self._check(out, q, kv, block_table, rows.row_slot, rows.query_start, rows.kv_len)
+        t, heads, head_dim = q.shape
+        if out.shape != q.shape or kv.dtype != q.dtype or out.dtype != q.dtype or kv.shape[4] != head_dim:
+            raise KernelError("paged_attention: out and q [tokens, heads, head_dim], kv [pages, 2, kv_heads, page_size, "
+                              "head_dim], one dtype")
+        self._attention_generic(out, q, kv, block_table, rows, scale, window)
+
+    def _attention_generic(self, out, q, kv, block_table, rows, scale, window) -> None:
+        t, heads, head_dim = q.shape
+        self._call("hb_attention_generic", self._p(out), self._p(q), self._p(kv), _code(q),
+                   self._i32(block_table, "block_table"), block_table.shape[1], self._i32(rows.row_slot, "row_slot"),
+                   self._i32(rows.query_start, "query_start"), self._i32(rows.kv_len, "kv_len"), rows.n_rows, t,
+                   heads, kv.shape[2], head_dim, kv.shape[0], kv.shape[3], ctypes.c_float(scale), int(window))
+
+    def linear(self, out, x, weight) -> None:
+        self._check(out, x, weight)
+        m, k = x.shape
+        n = weight.shape[0]
+        if weight.shape != (n, k) or out.shape != (m, n) or x.dtype != weight.dtype:
+            raise KernelError(f"linear: x {tuple(x.shape)} · w {tuple(weight.shape)}ᵀ -> out {tuple(out.shape)} do not fit")
+        if x.dtype == torch.float32:
+            if out.dtype != torch.float32:
+                raise KernelError("linear: a float32 product writes float32")
+            self._call("hb_gemm_f32", self._p(out), self._p(x), self._p(weight), m, n, k)
+        elif out.dtype == torch.float32:                 # the head: bfloat16 operands, 32-bit logits
+            torch.mm(x, weight.t(), out_dtype=torch.float32, out=out)
+        else:
+            torch.mm(x, weight.t(), out=out)
+
+    def sample(self, tokens, logits, temperature, top_k, top_p, min_p, seed_lo, seed_hi, position, filtered) -> None:
+        self._check(tokens, logits, temperature, top_k, top_p, min_p, seed_lo, seed_hi, position)
+        r, v = logits.shape
+        if logits.dtype != torch.float32 or tokens.dtype != torch.int32 or tokens.shape[0] < r:
+            raise KernelError("sample: logits float32 [rows, vocab], tokens int32 [rows]")
+        for name, t, dt in (("temperature", temperature, torch.float32), ("top_p", top_p, torch.float32),
+                            ("min_p", min_p, torch.float32), ("top_k", top_k, torch.int32),
+                            ("seed_lo", seed_lo, torch.int32), ("seed_hi", seed_hi, torch.int32),
+                            ("position", position, torch.int32)):
+            if t.dtype != dt or t.shape[0] < r:
+                raise KernelError(f"sample: {name} must be {dt} [rows]")
+        self._call("hb_sample", self._p(tokens), self._p(logits), self._p(temperature), self._p(top_k),
+                   self._p(top_p), self._p(min_p), self._p(seed_lo), self._p(seed_hi), self._p(position),
+                   int(bool(filtered)), r, v)

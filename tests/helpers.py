@@ -1,9 +1,12 @@
 """Tiny configurations and small tools shared by the tests."""
 from __future__ import annotations
 
-import torch
+import json
 
-from holon_b200.weights import RandomSource, write_model_folder
+import torch
+from safetensors.torch import save_file
+
+from holon_b200.weights import RandomSource
 
 # Two tiny Qwen3 configurations that differ in every size and option: head counts and groups (2 and 6), head sizes
 # (16 and 48, the second no power of two and heads × head size ≠ hidden), width, layers, vocabulary (256 and 389,
@@ -17,9 +20,21 @@ TINY_B = dict(architectures=["Qwen3ForCausalLM"], num_hidden_layers=3, hidden_si
 TINY = {"a": (TINY_A, 0), "b": (TINY_B, 1)}
 
 
-def make_folder(tmp_path, name: str):
+def make_folder(tmp_path, name: str, sharpen: float = 2.0, dtype=torch.bfloat16):
+    """A model folder of tiny configuration `name` with seeded random weights. `sharpen` scales the q- and k-norm
+    weights: with unit gains the scores of random weights stay near zero and attention is close to an average over
+    all keys, which hides a wrong mask or a wrong page; scaled gains make single keys stand out."""
     config, seed = TINY[name]
-    return write_model_folder(RandomSource(config, seed), tmp_path / f"tiny_{name}")
+    folder = tmp_path / f"tiny_{name}"
+    folder.mkdir(parents=True, exist_ok=True)
+    tensors = {}
+    for stored, t in RandomSource(config, seed, dtype=dtype).tensors():
+        if stored.endswith(("q_norm.weight", "k_norm.weight")):
+            t = (t.float() * sharpen).to(dtype)
+        tensors[stored] = t.contiguous()
+    (folder / "config.json").write_text(json.dumps(config))
+    save_file(tensors, str(folder / "model.safetensors"))
+    return folder
 
 
 def random_prompt(vocab: int, n: int, seed: int) -> list[int]:

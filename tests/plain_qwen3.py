@@ -37,6 +37,35 @@ def rope_theta(config) -> float:
     return float(params["rope_theta"])
 
 
+# ---------------------------------------------------------------- rounding of a reduced-precision pipeline
+
+_ROUND_TO = None
+
+
+class rounding:
+    """`with rounding(torch.bfloat16): forward(...)` rounds every intermediate result to that type where the
+    reference's bfloat16 pipeline does (each product's output, each norm, the rotation, the attention output, silu and
+    its product, each residual sum: std/holon_std/ops/reference.py:7-30, std/holon_std/ffn/reference.py:12), while
+    the arithmetic inside each function stays 32-bit. The distance of such a run from the exact one is the yardstick
+    for what a bfloat16 engine may differ by: the reference's judge measures an engine against a plain bfloat16 run in
+    the same way (judge/README.md:64-67)."""
+
+    def __init__(self, dtype):
+        self.dtype = dtype
+
+    def __enter__(self):
+        global _ROUND_TO
+        self.before, _ROUND_TO = _ROUND_TO, self.dtype
+
+    def __exit__(self, *exc):
+        global _ROUND_TO
+        _ROUND_TO = self.before
+
+
+def _r(x):
+    return x if _ROUND_TO is None else x.to(_ROUND_TO).to(x.dtype)
+
+
 # ---------------------------------------------------------------- parts
 
 def embedding(ids, table):
@@ -47,7 +76,7 @@ def embedding(ids, table):
 def rms_norm(x, weight, eps):
     """x · rsqrt(mean(x²) + eps) · weight, eps inside the root (std/holon_std/ops/reference.py:7-11)."""
     variance = (x * x).mean(dim=-1, keepdim=True)
-    return x * torch.rsqrt(variance + eps) * weight
+    return _r(x * torch.rsqrt(variance + eps) * weight)
 
 
 def rope(x, positions, theta):
@@ -58,7 +87,7 @@ def rope(x, positions, theta):
     angles = positions.to(torch.float32)[:, None] * inv_freq[None, :]
     cos, sin = angles.cos().to(x.dtype)[:, None, :], angles.sin().to(x.dtype)[:, None, :]
     a, b = x[..., : d // 2], x[..., d // 2:]
-    return torch.cat((a * cos - b * sin, b * cos + a * sin), dim=-1)
+    return _r(torch.cat((a * cos - b * sin, b * cos + a * sin), dim=-1))
 
 
 def causal_attention(q, k, v, window=0):
@@ -74,7 +103,7 @@ def causal_attention(q, k, v, window=0):
     if window:
         hidden = hidden | (pos[:, None] - pos[None, :] >= window)
     probs = scores.masked_fill(hidden, float("-inf")).softmax(dim=-1)
-    return torch.einsum("hqk,khd->qhd", probs, v)
+    return _r(torch.einsum("hqk,khd->qhd", probs, v))
 
 
 def attention_layer(x, w, prefix, config, positions, window=0):
@@ -82,29 +111,29 @@ def attention_layer(x, w, prefix, config, positions, window=0):
     (std/holon_std/mixers/gqa/units.py:234-262, 282-294; recipe.py:47-49 gives q/k-norm the model's eps)."""
     t = x.shape[0]
     hq, hkv, d = config["num_attention_heads"], config["num_key_value_heads"], config["head_dim"]
-    q = (x @ w[prefix + "q_proj.weight"].T).reshape(t, hq, d)
-    k = (x @ w[prefix + "k_proj.weight"].T).reshape(t, hkv, d)
-    v = (x @ w[prefix + "v_proj.weight"].T).reshape(t, hkv, d)
+    q = _r(x @ w[prefix + "q_proj.weight"].T).reshape(t, hq, d)
+    k = _r(x @ w[prefix + "k_proj.weight"].T).reshape(t, hkv, d)
+    v = _r(x @ w[prefix + "v_proj.weight"].T).reshape(t, hkv, d)
     q = rms_norm(q, w[prefix + "q_norm.weight"], config["rms_norm_eps"])
     k = rms_norm(k, w[prefix + "k_norm.weight"], config["rms_norm_eps"])
     q, k = rope(q, positions, rope_theta(config)), rope(k, positions, rope_theta(config))
     o = causal_attention(q, k, v, window)
-    return o.reshape(t, hq * d) @ w[prefix + "o_proj.weight"].T
+    return _r(o.reshape(t, hq * d) @ w[prefix + "o_proj.weight"].T)
 
 
 def swiglu(x, w, prefix):
     """down(silu(gate(x)) · up(x)), no biases (std/holon_std/ffn/units.py:31-50; ffn/reference.py:7-12)."""
-    gate = x @ w[prefix + "gate_proj.weight"].T
-    up = x @ w[prefix + "up_proj.weight"].T
-    return (torch.nn.functional.silu(gate) * up) @ w[prefix + "down_proj.weight"].T
+    gate = _r(x @ w[prefix + "gate_proj.weight"].T)
+    up = _r(x @ w[prefix + "up_proj.weight"].T)
+    return _r(_r(_r(torch.nn.functional.silu(gate)) * up) @ w[prefix + "down_proj.weight"].T)
 
 
 def block(h, w, i, config, positions):
     """Pre-norm residual block: h += mixer(norm(h)); h += ffn(norm(h)) (std/holon_std/blocks/units.py:23-25)."""
     p = f"model.layers.{i}."
     eps = config["rms_norm_eps"]
-    h = h + attention_layer(rms_norm(h, w[p + "input_layernorm.weight"], eps), w, p + "self_attn.", config, positions)
-    return h + swiglu(rms_norm(h, w[p + "post_attention_layernorm.weight"], eps), w, p + "mlp.")
+    h = _r(h + attention_layer(rms_norm(h, w[p + "input_layernorm.weight"], eps), w, p + "self_attn.", config, positions))
+    return _r(h + swiglu(rms_norm(h, w[p + "post_attention_layernorm.weight"], eps), w, p + "mlp."))
 
 
 def forward(config, w, ids):
@@ -116,7 +145,7 @@ def forward(config, w, ids):
         h = block(h, w, i, config, positions)
     h = rms_norm(h, w["model.norm.weight"], config["rms_norm_eps"])
     head = w["model.embed_tokens.weight"] if config.get("tie_word_embeddings", False) else w["lm_head.weight"]
-    return h @ head.T
+    return _r(h @ head.T)
 
 
 # ---------------------------------------------------------------- sampling

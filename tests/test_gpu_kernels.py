@@ -1,0 +1,266 @@
+"""Each CUDA kernel alone against its plain torch twin (tests/ref_kernels.py), at sizes other than the engine's
+tests use: widths and vocabularies that are no power of two, head sizes in steps of 16, odd groups, ragged rows,
+page edges, windows. Where random inputs would average a fault away, one key is made to dominate."""
+from __future__ import annotations
+
+import math
+
+import pytest
+import torch
+
+import plain_qwen3 as plain
+from holon_b200.engine.batch import Rows
+from ref_kernels import RefKernels
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+DTYPES = [torch.float32, torch.bfloat16]
+REF = RefKernels()
+
+
+@pytest.fixture(scope="module")
+def K():
+    from holon_b200.kernels import load_kernels
+    return load_kernels(DEV)
+
+
+def rand(*shape, dtype=torch.float32, seed=0, scale=1.0):
+    g = torch.Generator().manual_seed(seed)
+    return (torch.randn(*shape, generator=g) * scale).to(dtype)
+
+
+def close(got, want, dtype, scale=1.0):
+    tol = (2e-5 if dtype == torch.float32 else 1.6e-2) * scale
+    diff = (got.float().cpu() - want.float()).abs().max().item()
+    assert diff <= tol, f"difference {diff} > {tol}"
+
+
+def test_embed(K):
+    for dtype in DTYPES:
+        table = rand(389, 96, dtype=dtype)
+        ids = torch.tensor([0, 388, 5, 5, 77], dtype=torch.int32)
+        out, want = torch.empty(5, 96, device=DEV), torch.empty(5, 96)
+        K.embed(out, table.to(DEV), ids.to(DEV))
+        REF.embed(want, table, ids)
+        assert torch.equal(out.cpu(), want)
+
+
+@pytest.mark.parametrize("dim", [96, 1000, 4096, 13000])
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_add_rmsnorm(K, dim, dtype):
+    h, delta, w = rand(7, dim, seed=1), rand(7, dim, dtype=dtype, seed=2), (1 + rand(dim, seed=3) * 0.1)
+    for wdt in {dtype, torch.float32}:                   # a norm weight stored in 32 bits stays 32-bit
+        for index in (None, torch.tensor([6, 0, 3], dtype=torch.int32)):
+            for d in (delta, None):
+                hg, hw = h.clone().to(DEV), h.clone()
+                rows = 7 if index is None else 3
+                out, want = torch.empty(rows, dim, dtype=dtype, device=DEV), torch.empty(rows, dim, dtype=dtype)
+                K.add_rmsnorm(out, hg, d.to(DEV) if d is not None else None, w.to(wdt).to(DEV), 1e-5, 0.0,
+                              index.to(DEV) if index is not None else None)
+                REF.add_rmsnorm(want, hw, d, w.to(wdt), 1e-5, 0.0, index)
+                close(out, want, dtype, scale=4)
+                assert torch.allclose(hg.cpu(), hw, atol=1e-6)       # the stream holds the sum (or is untouched)
+    x = rand(5, dim, dtype=dtype, seed=4)
+    out, want = torch.empty_like(x, device=DEV), torch.empty_like(x)
+    K.rmsnorm(out, x.to(DEV), w.to(dtype).to(DEV), 1e-6, 1.0)
+    REF.rmsnorm(want, x, w.to(dtype), 1e-6, 1.0)
+    close(out, want, dtype, scale=8)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_silu_mul(K, dtype):
+    gu = rand(9, 2 * 176, dtype=dtype, scale=3.0)
+    out, want = torch.empty(9, 176, dtype=dtype, device=DEV), torch.empty(9, 176, dtype=dtype)
+    K.silu_mul(out, gu.to(DEV))
+    REF.silu_mul(want, gu)
+    close(out, want, dtype, scale=8)
+
+
+@pytest.mark.parametrize("m,n,k", [(1, 389, 96), (5, 64, 7), (70, 130, 33), (129, 257, 1024), (3, 1000, 4098)])
+def test_gemm_f32(K, m, n, k):
+    x, w = rand(m, k, seed=1), rand(n, k, seed=2)
+    out = torch.empty(m, n, device=DEV)
+    K.linear(out, x.to(DEV), w.to(DEV))
+    want = (x.double() @ w.double().T).float()
+    assert (out.cpu() - want).abs().max().item() <= 3e-6 * math.sqrt(k) * 4
+    # a row's result does not depend on the rows beside it
+    alone = torch.empty(1, n, device=DEV)
+    K.linear(alone, x[m - 1:].contiguous().to(DEV), w.to(DEV))
+    assert torch.equal(alone[0], out[m - 1])
+
+
+@pytest.mark.parametrize("m,n,k", [(1, 389, 96), (9, 1000, 176), (200, 96, 192)])
+def test_linear_bf16(K, m, n, k):
+    x, w = rand(m, k, dtype=torch.bfloat16, seed=1), rand(n, k, dtype=torch.bfloat16, seed=2)
+    want = x.float() @ w.float().T
+    out = torch.empty(m, n, dtype=torch.bfloat16, device=DEV)
+    K.linear(out, x.to(DEV), w.to(DEV))
+    close(out, want, torch.bfloat16, scale=want.abs().max().item())
+    logits = torch.empty(m, n, dtype=torch.float32, device=DEV)          # the head's form: 32-bit out
+    K.linear(logits, x.to(DEV), w.to(DEV))
+    assert (logits.cpu() - want).abs().max().item() <= 1e-3 * want.abs().max().item()
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("heads,kv_heads,head_dim,rotary,page", [(6, 3, 80, 80, 8), (5, 1, 32, 16, 5), (8, 8, 128, 128, 64)])
+def test_qk_norm_rope_kv_write(K, dtype, heads, kv_heads, head_dim, rotary, page):
+    t, pages = 11, 6
+    qkv = rand(t, (heads + 2 * kv_heads) * head_dim, dtype=dtype, seed=5)
+    positions = torch.tensor([0, 1, 2, 40, 41, 7, 8, 9, 10, 11, 299], dtype=torch.int32)
+    inv = 1.0 / (1e4 ** (torch.arange(0, rotary, 2, dtype=torch.float32) / rotary))
+    ang = torch.arange(300, dtype=torch.float32)[:, None] * inv[None]
+    table = torch.cat((ang.cos(), ang.sin()), -1).contiguous()
+    qw, kw = (1 + rand(head_dim, seed=6) * 0.1).to(dtype), (1 + rand(head_dim, seed=7) * 0.1).to(dtype)
+    write = torch.randperm(pages * page, generator=torch.Generator().manual_seed(8))[:t].to(torch.int32)
+    write[3] = -1                                                             # a padded token writes nothing
+    for weights in ((qw, kw), (None, None)):
+        kv = rand(pages, 2, kv_heads, page, head_dim, dtype=dtype, seed=9)   # garbage: untouched cells must stay
+        kvg, q, qg = kv.clone().to(DEV), torch.empty(t, heads, head_dim, dtype=dtype), None
+        qg = torch.empty(t, heads, head_dim, dtype=dtype, device=DEV)
+        g = lambda x: x.to(DEV) if x is not None else None               # noqa: E731
+        K.qk_norm_rope_kv_write(qg, qkv.to(DEV), positions.to(DEV), table.to(DEV), rotary, g(weights[0]),
+                                g(weights[1]), 1e-6, 0.0, kvg, write.to(DEV), heads, kv_heads, head_dim)
+        REF.qk_norm_rope_kv_write(q, qkv, positions, table, rotary, weights[0], weights[1], 1e-6, 0.0, kv, write,
+                                  heads, kv_heads, head_dim)
+        close(qg, q, dtype, scale=8)
+        close(kvg, kv, dtype, scale=8)
+        v_got = kvg.cpu()[:, 1]
+        assert torch.equal(v_got, kv[:, 1])                                   # values are copied bit for bit
+    qg2 = torch.empty(t, heads, head_dim, dtype=dtype, device=DEV)            # a run that only reads the cache
+    K.qk_norm_rope_kv_write(qg2, qkv.to(DEV), positions.to(DEV), table.to(DEV), rotary, None, None, 0.0, 0.0, None,
+                            None, heads, kv_heads, head_dim)
+    assert torch.equal(qg2, qg)
+
+
+def paged_case(heads, kv_heads, head_dim, page, rows_spec, dtype, seed=0, window=0):
+    """rows_spec: (tokens held before the step, new tokens) per row. Pages are handed out in a shuffled order."""
+    g = torch.Generator().manual_seed(seed)
+    need = [-(-(a + b) // page) for a, b in rows_spec]
+    pages = sum(need) + 3
+    order = torch.randperm(pages - 1, generator=g).tolist()
+    slots = len(rows_spec) + 1
+    table = torch.full((slots, max(need) + 1), pages - 1, dtype=torch.int32)
+    kv = torch.randn(pages, 2, kv_heads, page, head_dim, generator=g).to(dtype)
+    at = 0
+    row_slot = torch.randperm(slots, generator=g)[:len(rows_spec)].to(torch.int32)
+    for b, n in enumerate(need):
+        table[row_slot[b], :n] = torch.tensor(order[at:at + n], dtype=torch.int32)
+        at += n
+    qs = torch.tensor([0] + [b for _, b in rows_spec], dtype=torch.int32).cumsum(0).to(torch.int32)
+    kv_len = torch.tensor([a + b for a, b in rows_spec], dtype=torch.int32)
+    t = int(qs[-1])
+    q = torch.randn(t, heads, head_dim, generator=g).to(dtype)
+    n_decode = 0
+    while n_decode < len(rows_spec) and rows_spec[n_decode][1] == 1:
+        n_decode += 1
+    host = Rows(row_slot, qs, kv_len, len(rows_spec), t, n_decode, max(b for _, b in rows_spec), int(kv_len.max()))
+    return q, kv, table, host
+
+
+def on_device(rows):
+    return Rows(rows.row_slot.to(DEV), rows.query_start.to(DEV), rows.kv_len.to(DEV), rows.n_rows, rows.n_tokens,
+                rows.n_decode, rows.max_q, rows.max_kv, rows.query_start.numpy(), rows.kv_len.numpy())
+
+
+GEOMETRIES = [(32, 8, 128, 64), (16, 4, 256, 16), (6, 1, 48, 4), (8, 2, 64, 16), (4, 4, 16, 7), (14, 2, 112, 32)]
+PREFILL_ROWS = [(0, 1), (0, 17), (5, 16), (31, 33), (0, 64), (100, 7), (16, 16), (63, 2), (0, 130)]
+DECODE_ROWS = [(0, 1), (15, 1), (16, 1), (99, 1), (999, 1), (2500, 1), (63, 1), (64, 1)]
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("geometry", GEOMETRIES)
+@pytest.mark.parametrize("kind", ["prefill", "decode", "mixed"])
+@pytest.mark.parametrize("window", [0, 20])
+def test_paged_attention(K, dtype, geometry, kind, window):
+    heads, kv_heads, head_dim, page = geometry
+    spec = {"prefill": PREFILL_ROWS, "decode": DECODE_ROWS, "mixed": DECODE_ROWS[:4] + PREFILL_ROWS[:5]}[kind]
+    q, kv, table, rows = paged_case(heads, kv_heads, head_dim, page, spec, dtype, seed=len(spec) + window)
+    scale = 1 / math.sqrt(head_dim)
+    want = torch.empty_like(q)
+    REF.paged_attention(want, q, kv, table, rows, scale, window)
+    out = torch.full_like(q, float("nan"), device=DEV)
+    K.paged_attention(out, q.to(DEV), kv.to(DEV), table.to(DEV), on_device(rows), scale, window)
+    close(out, want, dtype, scale=4)
+    again = torch.empty_like(out)
+    K.paged_attention(again, q.to(DEV), kv.to(DEV), table.to(DEV), on_device(rows), scale, window)
+    assert torch.equal(out, again)                                            # run to run identical
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("page", [16, 64])
+def test_attention_finds_one_far_key(K, dtype, page):
+    """One key among 700 is made to match the query; the output must be that key's value. The key sits at page edges,
+    at the first and the last position, and, with a window, just inside and just outside it."""
+    heads, kv_heads, head_dim, n = 8, 2, 64, 700
+    scale = 1 / math.sqrt(head_dim)
+    for window in (0, 128):
+        for target in (0, page - 1, page, 5 * page - 1, 5 * page, n - 129, n - 128, n - 2, n - 1):
+            q, kv, table, rows = paged_case(heads, kv_heads, head_dim, page, [(n - 1, 1), (n - 3, 3)], dtype, seed=target)
+            kv.mul_(0.05)
+            for b in range(2):
+                slot = int(rows.row_slot[b])
+                p, off = int(table[slot, target // page]), target % page
+                for t in range(int(rows.query_start[b]), int(rows.query_start[b + 1])):
+                    for h in range(heads):
+                        direction = torch.nn.functional.normalize(q[t, h].float(), dim=0)
+                        q[t, h] = (direction * 8).to(dtype)
+                    kv[p, 0, :, off] = 0
+                for hk in range(kv_heads):                        # the key matches the mean direction of its group
+                    group = q[int(rows.query_start[b]), hk * 4:(hk + 1) * 4].float()
+                    kv[p, 0, hk, off] = (torch.nn.functional.normalize(group.mean(0), dim=0) * 60).to(dtype)
+                    kv[p, 1, hk, off] = 3.0
+            want = torch.empty_like(q)
+            REF.paged_attention(want, q, kv, table, rows, scale, window)
+            out = torch.empty_like(q, device=DEV)
+            K.paged_attention(out, q.to(DEV), kv.to(DEV), table.to(DEV), on_device(rows), scale, window)
+            close(out, want, dtype, scale=4)
+            visible = window == 0 or (n - 1) - target < window
+            first_row = out[0].float().cpu()                      # the decode row, at position n - 1
+            if visible:
+                assert (first_row - 3.0).abs().max() < 0.2, (window, target)
+            else:
+                assert first_row.abs().max() < 1.0, (window, target)
+
+
+def test_sample_greedy_and_temperature(K):
+    v, rows = 1531, 6
+    logits = rand(rows, v, seed=3, scale=2.0)
+    logits[1, 700] = logits[1, 900] = 9.0                         # equal maxima: the lowest index wins
+    logits[5] = logits[2]
+    params = dict(temperature=torch.tensor([0, 0, 0.7, 1.0, 1.3, 0.7]), top_k=torch.zeros(rows, dtype=torch.int32),
+                  top_p=torch.ones(rows), min_p=torch.zeros(rows), seed_lo=torch.tensor([1, 2, 3, 4, 5, 3], dtype=torch.int32),
+                  seed_hi=torch.tensor([0, 0, 9, 0, 1, 9], dtype=torch.int32),
+                  position=torch.tensor([5, 6, 7, 8, 9, 7], dtype=torch.int32))
+    out = torch.empty(rows, dtype=torch.int32, device=DEV)
+    g = {k: t.to(DEV) for k, t in params.items()}
+    K.sample(out, logits.to(DEV), g["temperature"], g["top_k"], g["top_p"], g["min_p"], g["seed_lo"], g["seed_hi"],
+             g["position"], False)
+    got = out.cpu().tolist()
+    assert got[0] == int(logits[0].argmax()) and got[1] == 700
+    for r in range(2, rows):
+        seed = int(params["seed_lo"][r]) | (int(params["seed_hi"][r]) << 32)
+        want = plain.sample(logits[r], float(params["temperature"][r]), seed, int(params["position"][r]))
+        assert got[r] == want
+    assert got[2] == got[5]                                        # same seed, position and logits: same token
+
+
+def test_sample_follows_the_distribution(K):
+    """4096 draws of one row at positions 0..4095, against the plain implementation's float64 distribution, with and
+    without filters: total variation small, filtered-out tokens never drawn."""
+    v, n = 389, 4096
+    row = rand(1, v, seed=11, scale=2.5)
+    logits = row.expand(n, v).contiguous().to(DEV)
+    for temperature, top_k, top_p, min_p in ((0.8, 0, 1.0, 0.0), (1.0, 12, 1.0, 0.0), (1.0, 0, 0.8, 0.0),
+                                             (1.2, 0, 1.0, 0.05), (0.9, 40, 0.9, 0.02)):
+        filtered = bool(top_k or top_p < 1 or min_p > 0)
+        out = torch.empty(n, dtype=torch.int32, device=DEV)
+        full = lambda x, dt: torch.full((n,), x, dtype=dt, device=DEV)   # noqa: E731
+        K.sample(out, logits, full(temperature, torch.float32), full(top_k, torch.int32), full(top_p, torch.float32),
+                 full(min_p, torch.float32), full(1234, torch.int32), full(0, torch.int32),
+                 torch.arange(n, dtype=torch.int32, device=DEV), filtered)
+        probs = plain.distribution(row[0], temperature, top_k, top_p, min_p)
+        counts = torch.bincount(out.cpu().long(), minlength=v).double() / n
+        assert counts[probs == 0].sum() == 0
+        assert 0.5 * (counts - probs).abs().sum() < 0.12
+        for i in range(0, n, 97):                                  # and token by token
+            assert int(out[i]) == plain.draw(probs, plain.uniform(1234, i))
