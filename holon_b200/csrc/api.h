@@ -3,6 +3,7 @@
 // HB_ERR_CUDA when the launch itself failed. Pointers are device pointers unless a comment says otherwise.
 // dtype codes: 0 = float32, 1 = bfloat16.
 #pragma once
+#include <stddef.h>
 #include <stdint.h>
 
 #ifdef __cplusplus
@@ -50,6 +51,23 @@ int hb_attention_generic(void* out, const void* q, const void* kv, int dtype, co
                          int table_stride, const int32_t* row_slot, const int32_t* query_start,
                          const int32_t* kv_len, int rows, int tokens, int heads, int kv_heads, int head_dim,
                          int pages, int page_size, float scale, int window, hb_stream stream);
+
+// bfloat16 attention on tensor cores for rows that bring one token each (rows 0 .. rows - 1 of the batch). The keys of
+// a row are cut into `splits` parts that run side by side; with more than one split, `scratch` must hold
+// hb_attention_decode_scratch_floats(...) floats: the parts' partial results, merged by a second kernel.
+// head_dim: a multiple of 16 up to 256.
+size_t hb_attention_decode_scratch_floats(int rows, int heads, int head_dim, int splits);
+int hb_attention_decode_bf16(void* out, float* scratch, const void* q, const void* kv, const int32_t* block_table,
+                             int table_stride, const int32_t* row_slot, const int32_t* query_start,
+                             const int32_t* kv_len, int rows, int heads, int kv_heads, int head_dim, int pages,
+                             int page_size, float scale, int window, int splits, hb_stream stream);
+
+// bfloat16 attention on tensor cores for rows row0 .. rows - 1, each bringing any number of tokens. q_tiles: at least
+// the sum over these rows of ceil(tokens / 64).
+int hb_attention_prefill_bf16(void* out, const void* q, const void* kv, const int32_t* block_table, int table_stride,
+                              const int32_t* row_slot, const int32_t* query_start, const int32_t* kv_len, int row0,
+                              int rows, int q_tiles, int heads, int kv_heads, int head_dim, int pages, int page_size,
+                              float scale, int window, hb_stream stream);
 
 // out[m, n] = sum_k x[m, k] * w[n, k], all float32, sums in a fixed order that does not depend on m's neighbours.
 int hb_gemm_f32(float* out, const float* x, const float* w, int m, int n, int k, hb_stream stream);

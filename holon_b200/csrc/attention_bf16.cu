@@ -1,0 +1,478 @@
+// bfloat16 paged attention on tensor cores (mma.sync m16n8k16, 32-bit accumulation and softmax).
+//
+// Two kernels share the tile loader and the fragment code:
+//  * decode: rows that bring one token. A CTA owns (row, kv head, split of the keys); the kv head's whole group of
+//    query heads is the 16-row M tile, so keys and values are read once per group. Its four warps take 16 keys each of
+//    every 64-key tile and keep their own running softmax; they are merged in shared memory at the end. With more than
+//    one split the CTA writes (max, sum, unnormalised output) to scratch and a second kernel merges the splits in a
+//    fixed order.
+//  * prefill: rows that bring several tokens (prompt portions). A CTA owns 64 queries of one head, 16 per warp, and
+//    walks the 64-key tiles up to its diagonal (FlashAttention-2 style).
+// Head sizes are multiples of 16 up to 256 (template D_PAD 64 / 128 / 256 with a run-time head_dim inside it); any page
+// size; any group size (groups above 16 heads take several CTAs). Keys outside a row's range are zero-filled on load
+// and masked, so nothing is ever read from a page the row does not hold.
+#include "common.cuh"
+
+#define TILE_N 64
+
+// ---------------------------------------------------------------- small PTX wrappers
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, bool valid) {
+    const int n = valid ? 16 : 0;                  // src-size 0: the 16 bytes are filled with zeros
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(dst), "l"(src), "r"(n));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *(uint32_t*)&v;
+}
+
+// Shared-memory tiles hold rows of D_PAD bf16 = D_PAD/8 chunks of 16 bytes; the chunk index is XOR-ed with the row
+// within each group of 8 chunks so that ldmatrix's 8 rows fall into 8 different bank groups.
+template <int D_PAD> __device__ __forceinline__ int swz(int row, int chunk) {
+    return row * (D_PAD / 8) + ((chunk & ~7) | ((chunk ^ row) & 7));
+}
+
+struct KvView {
+    const bf16* kv;                // [pages, 2, kv_heads, page_size, head_dim]
+    const int32_t* table;          // this row's block-table row
+    int pages, page_size, kv_heads, head_dim, hk;
+};
+
+// Loads keys [tile * 64, tile * 64 + 64) of one kv head into k_s / v_s; keys outside [lo, hi) become zeros.
+template <int D_PAD, int THREADS>
+__device__ __forceinline__ void load_kv_tile(bf16* k_s, bf16* v_s, const KvView& c, int tile, int lo, int hi) {
+    const int chunks = c.head_dim >> 3;                        // 16-byte chunks per key row
+    const long head_stride = (long)c.page_size * c.head_dim;
+    for (int i = threadIdx.x; i < TILE_N * (D_PAD / 8); i += THREADS) {
+        const int r = i / (D_PAD / 8), ch = i % (D_PAD / 8);
+        if (ch >= chunks) continue;                           // columns past head_dim are never read
+        const int j = tile * TILE_N + r;
+        bool valid = j >= lo && j < hi;
+        long off = 0;
+        if (valid) {
+            const int page = c.table[j / c.page_size];
+            valid = page >= 0 && page < c.pages;
+            off = (((long)page * 2) * c.kv_heads + c.hk) * head_stride + (long)(j % c.page_size) * c.head_dim + ch * 8;
+        }
+        const int d = swz<D_PAD>(r, ch) * 8;
+        cp_async16(smem_u32(k_s + d), c.kv + off, valid);
+        cp_async16(smem_u32(v_s + d), c.kv + off + (valid ? (long)c.kv_heads * head_stride : 0), valid);
+    }
+}
+
+// ================================================================ decode
+// grid (rows, kv_heads * m_tiles, splits), 128 threads. m_tiles = ceil(group / 16).
+template <int D_PAD, int STAGES>
+__global__ void __launch_bounds__(128) decode_kernel(
+        bf16* __restrict__ out, float* __restrict__ part_o, float* __restrict__ part_ml, const bf16* __restrict__ q,
+        const bf16* __restrict__ kv, const int32_t* __restrict__ block_table, int table_stride,
+        const int32_t* __restrict__ row_slot, const int32_t* __restrict__ query_start,
+        const int32_t* __restrict__ kv_len, int heads, int kv_heads, int head_dim, int pages, int page_size,
+        float scale_log2, int window, int splits) {
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+    bf16* q_s = (bf16*)smem_raw;                                   // [16][D_PAD]
+    bf16* k_s = q_s + 16 * D_PAD;                                  // [STAGES][64][D_PAD]
+    bf16* v_s = k_s + STAGES * TILE_N * D_PAD;                     // [STAGES][64][D_PAD]
+    const int b = blockIdx.x, split = blockIdx.z;
+    const int group = heads / kv_heads, m_tiles = (group + 15) / 16;
+    const int hk = blockIdx.y / m_tiles, mt = blockIdx.y % m_tiles;
+    const int g0 = mt * 16, g = min(16, group - g0);                // this CTA's query heads: hk * group + g0 + [0, g)
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int t = query_start[b];
+    const int n = kv_len[b];
+    const int lo = window > 0 ? max(0, n - window) : 0;             // the one query sits at position n - 1
+    const int tile_lo = lo / TILE_N, tile_hi = (n + TILE_N - 1) / TILE_N;
+    const int per = (tile_hi - tile_lo + splits - 1) / splits;
+    const int first = tile_lo + split * per, last = min(tile_hi, first + per);
+
+    KvView view{kv, block_table + (size_t)row_slot[b] * table_stride, pages, page_size, kv_heads, head_dim, hk};
+    const int chunks = head_dim >> 3;
+    for (int i = threadIdx.x; i < 16 * (D_PAD / 8); i += 128) {    // the group's queries; rows past g are zeros
+        const int r = i / (D_PAD / 8), ch = i % (D_PAD / 8);
+        const bool valid = r < g && ch < chunks;
+        const bf16* src = q + ((size_t)t * heads + (size_t)hk * group + g0 + (valid ? r : 0)) * head_dim + (valid ? ch * 8 : 0);
+        cp_async16(smem_u32(q_s + swz<D_PAD>(r, ch) * 8), src, valid);
+    }
+#pragma unroll
+    for (int s = 0; s < STAGES - 1; ++s) {
+        if (first + s < last) load_kv_tile<D_PAD, 128>(k_s + s * TILE_N * D_PAD, v_s + s * TILE_N * D_PAD, view, first + s, lo, n);
+        cp_async_commit();
+    }
+
+    float o[D_PAD / 8][4];
+#pragma unroll
+    for (int i = 0; i < D_PAD / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+    float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;      // rows lane/4 and lane/4 + 8
+    const int ksteps = head_dim >> 4;
+
+    for (int tile = first; tile < last; ++tile) {
+        const int stage = (tile - first) % STAGES;
+        cp_async_wait<STAGES - 2>();
+        __syncthreads();
+        if (tile + STAGES - 1 < last) {
+            const int s2 = (tile - first + STAGES - 1) % STAGES;
+            load_kv_tile<D_PAD, 128>(k_s + s2 * TILE_N * D_PAD, v_s + s2 * TILE_N * D_PAD, view, tile + STAGES - 1, lo, n);
+        }
+        cp_async_commit();
+        const bf16* kt = k_s + stage * TILE_N * D_PAD;
+        const bf16* vt = v_s + stage * TILE_N * D_PAD;
+        const int key0 = tile * TILE_N + warp * 16;                 // this warp's 16 keys
+        if (key0 >= n || key0 + 16 <= lo) continue;                 // (uniform per warp; the barrier is above)
+        float s[2][4] = {};
+#pragma unroll
+        for (int ks = 0; ks < D_PAD / 16; ++ks) {
+            if (ks < ksteps) {
+                uint32_t a[4], kb[4];
+                ldmatrix_x4(a, smem_u32(q_s + swz<D_PAD>(lane & 15, ks * 2 + (lane >> 4)) * 8));
+                ldmatrix_x4(kb, smem_u32(kt + swz<D_PAD>(warp * 16 + (lane & 7) + ((lane >> 4) << 3), ks * 2 + ((lane >> 3) & 1)) * 8));
+                mma_bf16(s[0], a, kb[0], kb[1]);
+                mma_bf16(s[1], a, kb[2], kb[3]);
+            }
+        }
+        float mx0 = -INFINITY, mx1 = -INFINITY;
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int j = key0 + nt * 8 + (lane & 3) * 2 + (e & 1);
+                const float v = (j >= lo && j < n) ? s[nt][e] * scale_log2 : -INFINITY;
+                s[nt][e] = v;
+                if (e < 2) mx0 = fmaxf(mx0, v); else mx1 = fmaxf(mx1, v);
+            }
+        mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1)); mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+        mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1)); mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+        const float n0 = fmaxf(m0, mx0), n1 = fmaxf(m1, mx1);
+        const float c0 = n0 == -INFINITY ? 1.f : exp2f(m0 - n0), c1 = n1 == -INFINITY ? 1.f : exp2f(m1 - n1);
+        m0 = n0; m1 = n1;
+        float sum0 = 0.f, sum1 = 0.f;
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt) {
+            s[nt][0] = n0 == -INFINITY ? 0.f : exp2f(s[nt][0] - n0); s[nt][1] = n0 == -INFINITY ? 0.f : exp2f(s[nt][1] - n0);
+            s[nt][2] = n1 == -INFINITY ? 0.f : exp2f(s[nt][2] - n1); s[nt][3] = n1 == -INFINITY ? 0.f : exp2f(s[nt][3] - n1);
+            sum0 += s[nt][0] + s[nt][1]; sum1 += s[nt][2] + s[nt][3];
+        }
+        l0 = l0 * c0 + sum0; l1 = l1 * c1 + sum1;                   // per-lane partial sums; quads are joined at the end
+        uint32_t p[4] = {pack_bf16(s[0][0], s[0][1]), pack_bf16(s[0][2], s[0][3]), pack_bf16(s[1][0], s[1][1]), pack_bf16(s[1][2], s[1][3])};
+#pragma unroll
+        for (int dt = 0; dt < D_PAD / 16; ++dt) {
+            if (dt < ksteps) {
+                o[2 * dt][0] *= c0; o[2 * dt][1] *= c0; o[2 * dt][2] *= c1; o[2 * dt][3] *= c1;
+                o[2 * dt + 1][0] *= c0; o[2 * dt + 1][1] *= c0; o[2 * dt + 1][2] *= c1; o[2 * dt + 1][3] *= c1;
+                uint32_t vb[4];
+                ldmatrix_x4_trans(vb, smem_u32(vt + swz<D_PAD>(warp * 16 + (lane & 7) + (((lane >> 3) & 1) << 3), dt * 2 + (lane >> 4)) * 8));
+                mma_bf16(o[2 * dt], p, vb[0], vb[1]);
+                mma_bf16(o[2 * dt + 1], p, vb[2], vb[3]);
+            }
+        }
+    }
+    cp_async_wait<0>();
+    l0 += __shfl_xor_sync(0xffffffffu, l0, 1); l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
+    l1 += __shfl_xor_sync(0xffffffffu, l1, 1); l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+    __syncthreads();                                                // every warp is done with the tiles: reuse them
+
+    // ---- merge the four warps: [warp][row][D_PAD] floats and [warp][row][2] (max, sum) in the tile memory
+    float* wo = (float*)k_s;
+    float* wml = wo + 4 * 16 * D_PAD;
+    const int r0 = lane >> 2, cq = (lane & 3) * 2;
+#pragma unroll
+    for (int i = 0; i < D_PAD / 8; ++i) {
+        if (i * 8 < head_dim) {
+            if (r0 < g) { wo[(warp * 16 + r0) * D_PAD + i * 8 + cq] = o[i][0]; wo[(warp * 16 + r0) * D_PAD + i * 8 + cq + 1] = o[i][1]; }
+            if (r0 + 8 < g) { wo[(warp * 16 + r0 + 8) * D_PAD + i * 8 + cq] = o[i][2]; wo[(warp * 16 + r0 + 8) * D_PAD + i * 8 + cq + 1] = o[i][3]; }
+        }
+    }
+    if ((lane & 3) == 0) {
+        wml[(warp * 16 + r0) * 2] = m0; wml[(warp * 16 + r0) * 2 + 1] = l0;
+        wml[(warp * 16 + r0 + 8) * 2] = m1; wml[(warp * 16 + r0 + 8) * 2 + 1] = l1;
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < g * head_dim; i += 128) {
+        const int r = i / head_dim, d = i % head_dim;
+        float mm = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) mm = fmaxf(mm, wml[(w * 16 + r) * 2]);
+        float acc = 0.f, l = 0.f;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) {
+            const float mw = wml[(w * 16 + r) * 2];
+            const float f = mw == -INFINITY ? 0.f : exp2f(mw - mm);
+            acc += f * wo[(w * 16 + r) * D_PAD + d];
+            l += f * wml[(w * 16 + r) * 2 + 1];
+        }
+        const int h = hk * group + g0 + r;
+        if (splits == 1) {
+            out[((size_t)t * heads + h) * head_dim + d] = __float2bfloat16_rn(l > 0.f ? acc / l : 0.f);
+        } else {
+            const size_t slot = ((size_t)b * heads + h) * splits + split;
+            part_o[slot * head_dim + d] = acc;
+            if (d == 0) { part_ml[slot * 2] = mm; part_ml[slot * 2 + 1] = l; }
+        }
+    }
+}
+
+// out[t, h, :] = sum_s w_s o_s / sum_s w_s l_s, w_s = 2^(m_s - max m), splits in ascending order.
+__global__ void decode_merge_kernel(bf16* __restrict__ out, const float* __restrict__ part_o,
+                                    const float* __restrict__ part_ml, const int32_t* __restrict__ query_start,
+                                    int heads, int head_dim, int splits) {
+    const int b = blockIdx.x, h = blockIdx.y;
+    const size_t base = ((size_t)b * heads + h) * splits;
+    float mm = -INFINITY;
+    for (int s = 0; s < splits; ++s) mm = fmaxf(mm, part_ml[(base + s) * 2]);
+    const int t = query_start[b];
+    for (int d = threadIdx.x; d < head_dim; d += blockDim.x) {
+        float acc = 0.f, l = 0.f;
+        for (int s = 0; s < splits; ++s) {
+            const float ms = part_ml[(base + s) * 2];
+            const float f = ms == -INFINITY ? 0.f : exp2f(ms - mm);
+            acc += f * part_o[(base + s) * head_dim + d];
+            l += f * part_ml[(base + s) * 2 + 1];
+        }
+        out[((size_t)t * heads + h) * head_dim + d] = __float2bfloat16_rn(l > 0.f ? acc / l : 0.f);
+    }
+}
+
+template <int D_PAD> static size_t decode_smem(int stages) {
+    const size_t tiles = (size_t)(16 + 2 * stages * TILE_N) * D_PAD * sizeof(bf16);
+    const size_t merge = 16 * D_PAD * sizeof(bf16) + (size_t)(4 * 16 * D_PAD + 4 * 16 * 2) * sizeof(float);
+    return tiles > merge ? tiles : merge;
+}
+
+template <int D_PAD, int STAGES>
+static int launch_decode(bf16* out, float* part_o, float* part_ml, const bf16* q, const bf16* kv,
+                         const int32_t* block_table, int table_stride, const int32_t* row_slot,
+                         const int32_t* query_start, const int32_t* kv_len, int rows, int heads, int kv_heads,
+                         int head_dim, int pages, int page_size, float scale, int window, int splits, cudaStream_t s) {
+    auto kernel = decode_kernel<D_PAD, STAGES>;
+    const size_t smem = decode_smem<D_PAD>(STAGES);
+    HB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    const int group = heads / kv_heads, m_tiles = (group + 15) / 16;
+    dim3 grid(rows, kv_heads * m_tiles, splits);
+    kernel<<<grid, 128, smem, s>>>(out, part_o, part_ml, q, kv, block_table, table_stride, row_slot, query_start,
+                                   kv_len, heads, kv_heads, head_dim, pages, page_size,
+                                   scale * 1.4426950408889634f, window, splits);
+    HB_LAUNCH_CHECK("attention_decode");
+    if (splits > 1) {
+        decode_merge_kernel<<<dim3(rows, heads), 128, 0, s>>>(out, part_o, part_ml, query_start, heads, head_dim, splits);
+        HB_LAUNCH_CHECK("attention_decode_merge");
+    }
+    return 0;
+}
+
+extern "C" size_t hb_attention_decode_scratch_floats(int rows, int heads, int head_dim, int splits) {
+    return splits > 1 ? (size_t)rows * heads * splits * (head_dim + 2) : 0;
+}
+
+extern "C" int hb_attention_decode_bf16(void* out, float* scratch, const void* q, const void* kv,
+                                        const int32_t* block_table, int table_stride, const int32_t* row_slot,
+                                        const int32_t* query_start, const int32_t* kv_len, int rows, int heads,
+                                        int kv_heads, int head_dim, int pages, int page_size, float scale, int window,
+                                        int splits, hb_stream stream) {
+    if (rows == 0) return 0;
+    if (head_dim % 16 || head_dim > 256 || head_dim < 16)
+        HB_REFUSE("attention_decode_bf16: head_dim %d is no multiple of 16 up to 256", head_dim);
+    if (kv_heads < 1 || heads % kv_heads) HB_REFUSE("attention_decode_bf16: %d heads, %d kv heads", heads, kv_heads);
+    if (splits < 1 || splits > 64) HB_REFUSE("attention_decode_bf16: %d splits (1 to 64)", splits);
+    if (splits > 1 && !scratch) HB_REFUSE("attention_decode_bf16: more than one split needs scratch memory");
+    if (rows > 65535 * 32) HB_REFUSE("attention_decode_bf16: %d rows", rows);
+    float* part_o = scratch;
+    float* part_ml = scratch ? scratch + (size_t)rows * heads * splits * head_dim : nullptr;
+    cudaStream_t s = (cudaStream_t)stream;
+#define HB_ARGS (bf16*)out, part_o, part_ml, (const bf16*)q, (const bf16*)kv, block_table, table_stride, row_slot, \
+    query_start, kv_len, rows, heads, kv_heads, head_dim, pages, page_size, scale, window, splits, s
+    if (head_dim <= 64) return launch_decode<64, 4>(HB_ARGS);
+    if (head_dim <= 128) return launch_decode<128, 3>(HB_ARGS);
+    return launch_decode<256, 2>(HB_ARGS);
+#undef HB_ARGS
+}
+
+// ================================================================ prefill
+// grid (query tiles, heads), 128 threads; a CTA finds its (row, first query) by walking the rows' tile counts.
+template <int D_PAD>
+__global__ void __launch_bounds__(128) prefill_kernel(
+        bf16* __restrict__ out, const bf16* __restrict__ q, const bf16* __restrict__ kv,
+        const int32_t* __restrict__ block_table, int table_stride, const int32_t* __restrict__ row_slot,
+        const int32_t* __restrict__ query_start, const int32_t* __restrict__ kv_len, int row0, int rows, int heads,
+        int kv_heads, int head_dim, int pages, int page_size, float scale_log2, int window) {
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+    bf16* q_s = (bf16*)smem_raw;                                   // [64][D_PAD]
+    bf16* k_s = q_s + 64 * D_PAD;                                  // [2][64][D_PAD]
+    bf16* v_s = k_s + 2 * TILE_N * D_PAD;
+    __shared__ int s_row, s_q0;
+    if (threadIdx.x == 0) {
+        int left = blockIdx.x, found = -1, q0 = 0;
+        for (int b = row0; b < rows; ++b) {
+            const int tiles = (query_start[b + 1] - query_start[b] + 63) >> 6;
+            if (left < tiles) { found = b; q0 = left * 64; break; }
+            left -= tiles;
+        }
+        s_row = found; s_q0 = q0;
+    }
+    __syncthreads();
+    const int b = s_row;
+    if (b < 0) return;
+    const int h = blockIdx.y, hk = h / (heads / kv_heads);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int t0 = query_start[b] + s_q0, nq = query_start[b + 1] - query_start[b];
+    const int qn = min(64, nq - s_q0);                              // queries in this tile
+    const int n = kv_len[b];
+    const int p0 = n - nq + s_q0;                                   // position of the tile's first query
+    const int hi = min(n, p0 + qn);                                 // keys below hi are visible to someone here
+    const int lo = window > 0 ? max(0, p0 - window + 1) : 0;
+    const int tile_lo = lo / TILE_N, tile_hi = (hi + TILE_N - 1) / TILE_N;
+
+    KvView view{kv, block_table + (size_t)row_slot[b] * table_stride, pages, page_size, kv_heads, head_dim, hk};
+    const int chunks = head_dim >> 3;
+    for (int i = threadIdx.x; i < 64 * (D_PAD / 8); i += 128) {
+        const int r = i / (D_PAD / 8), ch = i % (D_PAD / 8);
+        const bool valid = r < qn && ch < chunks;
+        const bf16* src = q + ((size_t)(t0 + (valid ? r : 0)) * heads + h) * head_dim + (valid ? ch * 8 : 0);
+        cp_async16(smem_u32(q_s + swz<D_PAD>(r, ch) * 8), src, valid);
+    }
+    if (tile_lo < tile_hi) load_kv_tile<D_PAD, 128>(k_s, v_s, view, tile_lo, lo, hi);
+    cp_async_commit();
+
+    float o[D_PAD / 8][4];
+#pragma unroll
+    for (int i = 0; i < D_PAD / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+    float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
+    const int ksteps = head_dim >> 4;
+    const int pos0 = p0 + warp * 16 + (lane >> 2), pos1 = pos0 + 8;  // this lane's two query positions
+
+    for (int tile = tile_lo; tile < tile_hi; ++tile) {
+        const int stage = (tile - tile_lo) & 1;
+        cp_async_wait<0>();
+        __syncthreads();
+        if (tile + 1 < tile_hi)
+            load_kv_tile<D_PAD, 128>(k_s + (stage ^ 1) * TILE_N * D_PAD, v_s + (stage ^ 1) * TILE_N * D_PAD, view, tile + 1, lo, hi);
+        cp_async_commit();
+        const bf16* kt = k_s + stage * TILE_N * D_PAD;
+        const bf16* vt = v_s + stage * TILE_N * D_PAD;
+        const int key0 = tile * TILE_N;
+        if (warp * 16 >= qn) continue;                              // a warp without queries
+        if (key0 > p0 + warp * 16 + 15) continue;                   // every key of the tile is in this warp's future
+        float s[8][4];
+#pragma unroll
+        for (int nt = 0; nt < 8; ++nt) s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.f;
+#pragma unroll
+        for (int ks = 0; ks < D_PAD / 16; ++ks) {
+            if (ks < ksteps) {
+                uint32_t a[4];
+                ldmatrix_x4(a, smem_u32(q_s + swz<D_PAD>(warp * 16 + (lane & 15), ks * 2 + (lane >> 4)) * 8));
+#pragma unroll
+                for (int np = 0; np < 4; ++np) {
+                    uint32_t kb[4];
+                    ldmatrix_x4(kb, smem_u32(kt + swz<D_PAD>(np * 16 + (lane & 7) + ((lane >> 4) << 3), ks * 2 + ((lane >> 3) & 1)) * 8));
+                    mma_bf16(s[2 * np], a, kb[0], kb[1]);
+                    mma_bf16(s[2 * np + 1], a, kb[2], kb[3]);
+                }
+            }
+        }
+        const bool edge = key0 + TILE_N - 1 > p0 + warp * 16 || key0 < lo + 0 || window > 0 || key0 + TILE_N > hi;
+        float mx0 = -INFINITY, mx1 = -INFINITY;
+#pragma unroll
+        for (int nt = 0; nt < 8; ++nt)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                float v = s[nt][e] * scale_log2;
+                if (edge) {
+                    const int j = key0 + nt * 8 + (lane & 3) * 2 + (e & 1);
+                    const int pos = e < 2 ? pos0 : pos1;
+                    const bool seen = j <= pos && j < hi && (window <= 0 || pos - j < window);
+                    if (!seen) v = -INFINITY;
+                }
+                s[nt][e] = v;
+                if (e < 2) mx0 = fmaxf(mx0, v); else mx1 = fmaxf(mx1, v);
+            }
+        mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1)); mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+        mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1)); mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+        const float n0 = fmaxf(m0, mx0), n1 = fmaxf(m1, mx1);
+        const float c0 = n0 == -INFINITY ? 1.f : exp2f(m0 - n0), c1 = n1 == -INFINITY ? 1.f : exp2f(m1 - n1);
+        m0 = n0; m1 = n1;
+        float sum0 = 0.f, sum1 = 0.f;
+#pragma unroll
+        for (int nt = 0; nt < 8; ++nt) {
+            s[nt][0] = n0 == -INFINITY ? 0.f : exp2f(s[nt][0] - n0); s[nt][1] = n0 == -INFINITY ? 0.f : exp2f(s[nt][1] - n0);
+            s[nt][2] = n1 == -INFINITY ? 0.f : exp2f(s[nt][2] - n1); s[nt][3] = n1 == -INFINITY ? 0.f : exp2f(s[nt][3] - n1);
+            sum0 += s[nt][0] + s[nt][1]; sum1 += s[nt][2] + s[nt][3];
+        }
+        l0 = l0 * c0 + sum0; l1 = l1 * c1 + sum1;
+#pragma unroll
+        for (int i = 0; i < D_PAD / 8; ++i) { o[i][0] *= c0; o[i][1] *= c0; o[i][2] *= c1; o[i][3] *= c1; }
+#pragma unroll
+        for (int kk = 0; kk < 4; ++kk) {                            // 16 keys at a time
+            uint32_t p[4] = {pack_bf16(s[2 * kk][0], s[2 * kk][1]), pack_bf16(s[2 * kk][2], s[2 * kk][3]),
+                             pack_bf16(s[2 * kk + 1][0], s[2 * kk + 1][1]), pack_bf16(s[2 * kk + 1][2], s[2 * kk + 1][3])};
+#pragma unroll
+            for (int dt = 0; dt < D_PAD / 16; ++dt) {
+                if (dt < ksteps) {
+                    uint32_t vb[4];
+                    ldmatrix_x4_trans(vb, smem_u32(vt + swz<D_PAD>(kk * 16 + (lane & 7) + (((lane >> 3) & 1) << 3), dt * 2 + (lane >> 4)) * 8));
+                    mma_bf16(o[2 * dt], p, vb[0], vb[1]);
+                    mma_bf16(o[2 * dt + 1], p, vb[2], vb[3]);
+                }
+            }
+        }
+    }
+    cp_async_wait<0>();
+    l0 += __shfl_xor_sync(0xffffffffu, l0, 1); l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
+    l1 += __shfl_xor_sync(0xffffffffu, l1, 1); l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+    const float i0 = l0 > 0.f ? 1.f / l0 : 0.f, i1 = l1 > 0.f ? 1.f / l1 : 0.f;
+    const int r0 = warp * 16 + (lane >> 2), cq = (lane & 3) * 2;
+#pragma unroll
+    for (int i = 0; i < D_PAD / 8; ++i) {
+        if (i * 8 < head_dim) {
+            if (r0 < qn) *(uint32_t*)(out + ((size_t)(t0 + r0) * heads + h) * head_dim + i * 8 + cq) = pack_bf16(o[i][0] * i0, o[i][1] * i0);
+            if (r0 + 8 < qn) *(uint32_t*)(out + ((size_t)(t0 + r0 + 8) * heads + h) * head_dim + i * 8 + cq) = pack_bf16(o[i][2] * i1, o[i][3] * i1);
+        }
+    }
+}
+
+template <int D_PAD>
+static int launch_prefill(bf16* out, const bf16* q, const bf16* kv, const int32_t* block_table, int table_stride,
+                          const int32_t* row_slot, const int32_t* query_start, const int32_t* kv_len, int row0,
+                          int rows, int q_tiles, int heads, int kv_heads, int head_dim, int pages, int page_size,
+                          float scale, int window, cudaStream_t s) {
+    auto kernel = prefill_kernel<D_PAD>;
+    const size_t smem = (size_t)(64 + 4 * TILE_N) * D_PAD * sizeof(bf16);
+    HB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    kernel<<<dim3(q_tiles, heads), 128, smem, s>>>(out, q, kv, block_table, table_stride, row_slot, query_start,
+                                                   kv_len, row0, rows, heads, kv_heads, head_dim, pages, page_size,
+                                                   scale * 1.4426950408889634f, window);
+    HB_LAUNCH_CHECK("attention_prefill");
+    return 0;
+}
+
+// Rows row0 .. rows - 1 of the batch; q_tiles is an upper bound of sum(ceil(queries / 64)) over them.
+extern "C" int hb_attention_prefill_bf16(void* out, const void* q, const void* kv, const int32_t* block_table,
+                                         int table_stride, const int32_t* row_slot, const int32_t* query_start,
+                                         const int32_t* kv_len, int row0, int rows, int q_tiles, int heads,
+                                         int kv_heads, int head_dim, int pages, int page_size, float scale,
+                                         int window, hb_stream stream) {
+    if (rows <= row0 || q_tiles == 0) return 0;
+    if (head_dim % 16 || head_dim > 256 || head_dim < 16)
+        HB_REFUSE("attention_prefill_bf16: head_dim %d is no multiple of 16 up to 256", head_dim);
+    if (kv_heads < 1 || heads % kv_heads) HB_REFUSE("attention_prefill_bf16: %d heads, %d kv heads", heads, kv_heads);
+    if (heads > 65535) HB_REFUSE("attention_prefill_bf16: %d heads", heads);
+    cudaStream_t s = (cudaStream_t)stream;
+#define HB_ARGS (bf16*)out, (const bf16*)q, (const bf16*)kv, block_table, table_stride, row_slot, query_start, kv_len, \
+    row0, rows, q_tiles, heads, kv_heads, head_dim, pages, page_size, scale, window, s
+    if (head_dim <= 64) return launch_prefill<64>(HB_ARGS);
+    if (head_dim <= 128) return launch_prefill<128>(HB_ARGS);
+    return launch_prefill<256>(HB_ARGS);
+#undef HB_ARGS
+}

@@ -130,7 +130,33 @@ class CudaKernels:
         if out.shape != q.shape or kv.dtype != q.dtype or out.dtype != q.dtype or kv.shape[4] != head_dim:
             raise KernelError("paged_attention: out and q [tokens, heads, head_dim], kv [pages, 2, kv_heads, page_size, "
                               "head_dim], one dtype")
-        self._attention_generic(out, q, kv, block_table, rows, scale, window)
+        fast = q.dtype == torch.bfloat16 and head_dim % 16 == 0 and head_dim <= 256 and self.attention_bf16 == "fast"
+        if not fast:
+            return self._attention_generic(out, q, kv, block_table, rows, scale, window)
+        kv_heads = kv.shape[2]
+        common = (self._i32(block_table, "block_table"), block_table.shape[1], self._i32(rows.row_slot, "row_slot"),
+                  self._i32(rows.query_start, "query_start"), self._i32(rows.kv_len, "kv_len"))
+        sizes = (heads, kv_heads, head_dim, kv.shape[0], kv.shape[3], ctypes.c_float(scale), int(window))
+        if rows.n_decode:
+            splits = self.decode_splits(rows.n_decode, heads, kv_heads, rows.max_kv)
+            floats = rows.n_decode * heads * splits * (head_dim + 2) if splits > 1 else 0
+            scratch = torch.empty(floats, dtype=torch.float32, device=self.device) if floats else None
+            self._call("hb_attention_decode_bf16", self._p(out), self._p(scratch), self._p(q), self._p(kv), *common,
+                       rows.n_decode, *sizes, splits)
+        if rows.n_rows > rows.n_decode:
+            qs = rows.host_query_start
+            tiles = sum((int(qs[b + 1]) - int(qs[b]) + 63) // 64 for b in range(rows.n_decode, rows.n_rows))
+            self._call("hb_attention_prefill_bf16", self._p(out), self._p(q), self._p(kv), *common, rows.n_decode,
+                       rows.n_rows, tiles, *sizes)
+
+    SMS = 148
+
+    def decode_splits(self, rows: int, heads: int, kv_heads: int, max_kv: int) -> int:
+        """Parts the keys of a decode row are cut into: enough CTAs for two per SM, at most one part per 64 keys of
+        the longest row, at most 32. A function of the batch's size and the longest length only
+        (plugins/holon_plugins/kernels/triton_attn/plugin.py:40-96 plans its splits the same way)."""
+        ctas = rows * kv_heads * (-(-(heads // kv_heads) // 16))
+        return max(1, min(-(-2 * self.SMS // ctas), -(-max_kv // 64), 32))
 
     def _attention_generic(self, out, q, kv, block_table, rows, scale, window) -> None:
         t, heads, head_dim = q.shape
