@@ -1,0 +1,250 @@
+"""Measures decode and prefill throughput of holon_b200 at Qwen3-8B sizes with random weights on one B200.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
+
+A "step" is one decode step of the whole batch. The default run: the layer sizes of Qwen3-8B (36 layers, hidden
+4096, 32 query heads, 8 KV heads, head size 128, intermediate 12288, vocabulary 151936), bfloat16, batch 8, each
+request ending at a context of 8,192 tokens. It prints ONE JSON line:
+
+  value            decoded tokens per second, timed on the device with CUDA events around exactly K steps
+  e2e              the same K steps through the public entry point (`Engine.add` / `Engine.step`), by wall clock, host
+                   token ids in and out, with the bytes copied each way per step
+  prefill          one prompt of 2,048 tokens: tokens per second, milliseconds, flops / time / bf16 peak
+  roofline         the decode step's bytes (every weight once, the live requests' cache) / its time against the
+                   measured copy bandwidth
+  points           decode tokens per second at batch 1 and 64
+  clocks           SM clocks sampled with nvidia-smi during the timed steps
+
+Every decode step reads 15 GB of weights and the requests' cache, far more than the 126 MB L2, so consecutive steps
+cannot reuse cached data ("l2": "inputs larger than L2"). Peaks come from MEASURED_PEAKS.json when the driver wrote
+it, else from an earlier measurement on this pool (6.65 TB/s copy, 1.59 PFLOP/s bf16).
+The method is the reference's own: decode throughput from first to last generated token of a batch of equal
+prompts, prefill as prompt tokens over time to first token (bench/holon_tg.py:51-63, bench/llama_bench.py:90-128).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import pathlib
+import statistics
+import subprocess
+import sys
+import time
+
+ROOT = pathlib.Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+QWEN3_8B = dict(architectures=["Qwen3ForCausalLM"], num_hidden_layers=36, hidden_size=4096, num_attention_heads=32,
+                num_key_value_heads=8, head_dim=128, intermediate_size=12288, vocab_size=151936, rope_theta=1000000.0,
+                rms_norm_eps=1e-6, tie_word_embeddings=False, max_position_embeddings=40960)
+FULL_LAYERS = QWEN3_8B["num_hidden_layers"]
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
+
+
+def peaks() -> tuple[dict, str]:
+    path = ROOT / "MEASURED_PEAKS.json"
+    if path.is_file():
+        try:
+            data = json.loads(path.read_text())
+            flat = {k: float(v) for k, v in data.items() if isinstance(v, (int, float))}
+            if "hbm_gbs" in flat and "bf16_tflops" in flat:
+                return flat, "measured"
+        except (ValueError, OSError):
+            pass
+    return dict(FALLBACK_PEAKS), "fallback"
+
+
+class Clocks:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed steps run."""
+
+    QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self) -> None:
+        self.proc = None
+
+    def start(self) -> None:
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", "0", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
+                                          "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        out, _ = self.proc.communicate()
+        sm, top, reasons = [], [], set()
+        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        for line in out.splitlines():
+            cells = [c.strip() for c in line.split(",")]
+            if len(cells) < 6 or not cells[0].isdigit():
+                continue
+            sm.append(int(cells[0]))
+            top.append(int(cells[1]))
+            reasons.update(n for n, c in zip(names, cells[2:6]) if c.lower().startswith("active"))
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(top) if top else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def model_numbers(cfg: dict, layers: int) -> dict:
+    """Parameter bytes a decode step reads and flops per token, from the configuration."""
+    h, d, hq, hkv, inter, v = (cfg[k] for k in ("hidden_size", "head_dim", "num_attention_heads",
+                                                "num_key_value_heads", "intermediate_size", "vocab_size"))
+    per_layer = (hq + 2 * hkv) * d * h + hq * d * h + 3 * inter * h
+    linear = layers * per_layer + v * h                              # the head reads its table once; the embedding rows are few
+    return {"weight_bytes": 2 * linear, "linear_params": linear, "kv_bytes_per_token": layers * 2 * hkv * d * 2,
+            "attn_flops_per_pair": 4 * hq * d * layers}
+
+
+def prompts_of(vocab: int, batch: int, length: int, seed: int) -> list[list[int]]:
+    import torch
+    g = torch.Generator().manual_seed(seed)
+    return torch.randint(1000, vocab // 2, (batch, length), generator=g).tolist()
+
+
+def decode_run(engine, batch: int, context: int, steps: int, warmup: int, seed: int, clocks: Clocks | None = None) -> dict:
+    """`batch` equal prompts, prefilled (untimed) so that the last timed step ends at `context` tokens; then `warmup`
+    untimed and `steps` timed decode steps through `Engine.step`."""
+    import torch
+    from holon_b200.engine import SamplingParams
+    prompt_len = context - (steps + warmup) - 1
+    vocab = engine.built.model.spec.vocab
+    params = SamplingParams(temperature=0.0, max_tokens=steps + warmup + 1, ignore_eos=True)
+    for p in prompts_of(vocab, batch, prompt_len, seed):
+        engine.add(p, params)
+    while engine.scheduler.waiting:                                  # prefill, in portions under the token budget
+        engine.step()
+    assert len(engine.scheduler.running) == batch
+    for _ in range(warmup):
+        engine.step()
+    kernels = engine.built.ctx.kernels
+    torch.cuda.synchronize()
+    h2d0, d2h0, launches0 = engine.h2d_bytes, engine.d2h_bytes, engine.launches()
+    if clocks:
+        clocks.start()
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0 = time.perf_counter()
+    start.record()
+    produced = 0
+    for _ in range(steps):
+        produced += len(engine.step())
+    end.record()
+    torch.cuda.synchronize()
+    wall = time.perf_counter() - t0
+    device_ms = start.elapsed_time(end)
+    clock = clocks.stop() if clocks else None
+    assert produced == batch * steps, (produced, batch, steps)
+    out = {"device_ms": device_ms, "wall_ms": wall * 1e3, "tokens": produced,
+           "h2d_bytes_per_step": (engine.h2d_bytes - h2d0) // steps, "d2h_bytes_per_step": (engine.d2h_bytes - d2h0) // steps,
+           "launches": engine.launches() - launches0, "mean_context": context - (steps + 1) / 2, "clocks": clock}
+    for rid in list(engine.requests):
+        engine.abort(rid)
+    return out
+
+
+def prefill_run(engine, tokens: int, repeats: int, seed: int) -> float:
+    """Milliseconds (device, best of `repeats`) of one step that computes a whole prompt of `tokens` tokens and samples
+    its first token."""
+    import torch
+    from holon_b200.engine import SamplingParams
+    vocab, best = engine.built.model.spec.vocab, float("inf")
+    for i in range(repeats + 1):                                     # the first one is a warm-up
+        engine.add(prompts_of(vocab, 1, tokens, seed + i)[0], SamplingParams(temperature=0.0, max_tokens=1, ignore_eos=True))
+        torch.cuda.synchronize()
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        deltas = engine.step()
+        end.record()
+        torch.cuda.synchronize()
+        assert len(deltas) == 1 and deltas[0].finish_reason == "length"
+        if i:
+            best = min(best, start.elapsed_time(end))
+    return best
+
+
+def run_ours(args) -> dict:
+    import torch
+    from holon_b200.engine import Engine, EngineConfig
+    from holon_b200.weights import RandomSource
+    cfg = dict(QWEN3_8B, num_hidden_layers=args.layers)
+    context, batch = args.context, args.batch
+    engine = Engine(EngineConfig(model="random weights, seed 2", device="cuda:0", dtype="bfloat16", page_size=64,
+                                 max_seqs=64, max_model_len=context, max_step_tokens=8192, seed=0),
+                    source=RandomSource(cfg, seed=2, device="cuda:0"))
+    numbers = model_numbers(cfg, args.layers)
+    peak, peak_kind = peaks()
+    prefill_tokens = 2048
+    prefill_ms = prefill_run(engine, prefill_tokens, repeats=3, seed=100)
+    prefill_flops = 2 * numbers["linear_params"] * prefill_tokens - 2 * cfg["vocab_size"] * cfg["hidden_size"] * (prefill_tokens - 1) \
+        + numbers["attn_flops_per_pair"] * prefill_tokens * (prefill_tokens + 1) / 2
+    clocks = Clocks()
+    main = decode_run(engine, batch, context, args.steps, args.warmup, seed=7, clocks=clocks)
+    points = {}
+    for b in (1, 64):
+        r = decode_run(engine, b, context, max(8, args.steps // 2), args.warmup, seed=11 + b)
+        points[f"decode_b{b}"] = round(r["tokens"] / r["device_ms"] * 1e3, 1)
+    ms_per_step = main["device_ms"] / args.steps
+    value = main["tokens"] / main["device_ms"] * 1e3
+    step_bytes = numbers["weight_bytes"] + batch * main["mean_context"] * numbers["kv_bytes_per_token"]
+    achieved = step_bytes / (ms_per_step * 1e-3) / 1e9
+    free, total = torch.cuda.mem_get_info()
+    return {
+        "metric": "decode tok/s at batch 8 (Qwen3-8B bf16, context 8192)", "value": round(value, 1), "unit": "tok/s",
+        "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms_per_step, 4),
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+        "data": "synthetic: uniform random token ids, seeded random weights", "impl": "holon_b200",
+        "config": {"model": "Qwen3-8B sizes", "layers": args.layers, "layers_full": FULL_LAYERS,
+                   "hidden": cfg["hidden_size"], "heads": cfg["num_attention_heads"],
+                   "kv_heads": cfg["num_key_value_heads"], "head_dim": cfg["head_dim"],
+                   "intermediate": cfg["intermediate_size"], "vocab": cfg["vocab_size"], "global_batch": batch,
+                   "seq_len": context, "page_size": 64, "parallelism": "single GPU", "l2": "inputs larger than L2",
+                   "cuda_graphs": True, "peaks": peak_kind},
+        "e2e": {"value": round(main["tokens"] / main["wall_ms"] * 1e3, 1), "unit": "tok/s",
+                "h2d_bytes_per_step": main["h2d_bytes_per_step"], "d2h_bytes_per_step": main["d2h_bytes_per_step"]},
+        "gpu_launches": main["launches"],
+        "prefill": {"value": round(prefill_tokens / prefill_ms * 1e3, 1), "tokens": prefill_tokens,
+                    "ms": round(prefill_ms, 3), "frac": round(prefill_flops / (prefill_ms * 1e-3) / (peak["bf16_tflops"] * 1e12), 4)},
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peak["hbm_gbs"], "unit": "GB/s",
+                     "frac": round(achieved / peak["hbm_gbs"], 4)},
+        "points": points, "clocks": main["clocks"],
+        "memory": {"weights_gb": round(engine.built.weight_bytes / 1e9, 2), "cache_gb": round(engine.built.cache.bytes / 1e9, 2),
+                   "device_free_gb": round(free / 1e9, 2)},
+    }
+
+
+def run_reference(args) -> dict:
+    ref = ROOT / "baseline" / "_ref"
+    if not ref.is_dir() or not any(ref.iterdir()):
+        return {"impl": "reference", "unavailable": "mxinO/holon is not installed under baseline/_ref (offline install "
+                                                    "did not succeed; see DESIGN.md)"}
+    return {"impl": "reference", "unavailable": "baseline/_ref holds no runnable engine for this benchmark; see DESIGN.md"}
+
+
+def main() -> int:
+    ap = argparse.ArgumentParser(description=__doc__.split("\n\n")[0])
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=64)
+    ap.add_argument("--warmup", type=int, default=4)
+    ap.add_argument("--impl", default="ours", choices=("ours", "reference"))
+    ap.add_argument("--layers", type=int, default=FULL_LAYERS, help="fewer layers than the model has (both are reported)")
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--context", type=int, default=8192)
+    args = ap.parse_args()
+    if args.gpus != 1:
+        print(f"holon_b200 is a single-GPU engine: --gpus {args.gpus} is not supported")
+        return 2
+    if args.warmup < 3:
+        args.warmup = 3
+    if args.impl == "reference":
+        print(json.dumps(run_reference(args)))
+        return 0
+    import torch
+    with torch.inference_mode():
+        print(json.dumps(run_ours(args)))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -60,7 +60,7 @@ class Engine:
         self._host_tokens = torch.zeros(config.max_step_tokens, dtype=torch.int32)
         if self.device.type == "cuda":
             self._host_tokens = self._host_tokens.pin_memory()
-        self.steps = self.graph_steps = 0
+        self.steps = self.graph_steps = self._graph_launches = 0
         self.h2d_bytes = self.d2h_bytes = 0
 
     # ------------------------------------------------------------------ requests
@@ -156,14 +156,17 @@ class Engine:
             out = torch.empty(bucket, dtype=torch.int32, device=self.device)
             self.sampler.sample(runner.model.forward(step), step.extra, False, out)      # warm-up, not captured
             torch.cuda.current_stream(self.device).synchronize()
-            graph = torch.cuda.CUDAGraph()
+            graph, kernels = torch.cuda.CUDAGraph(), self.built.ctx.kernels
+            before = kernels.launches
             with torch.cuda.graph(graph, pool=self._graph_pool):
                 self.sampler.sample(runner.model.forward(step), step.extra, False, out)
+            captured, kernels.launches = kernels.launches - before, before       # recorded, not run
             self._graph_pool = self._graph_pool or graph.pool()
-            self._graphs[bucket] = (graph, out)
-        graph, out = self._graphs[bucket]
+            self._graphs[bucket] = (graph, out, captured)
+        graph, out, captured = self._graphs[bucket]
         graph.replay()
         self.graph_steps += 1
+        self._graph_launches += captured
         return out
 
     def _commit(self, row: Row, token: int) -> TokenDelta:
@@ -199,6 +202,11 @@ class Engine:
                 if delta.rid in out:
                     out[delta.rid].extend(delta.token_ids)
         return [out[rid] for rid in rids]
+
+    def launches(self) -> int:
+        """Kernels of this package launched so far: the ones enqueued directly plus, for every graph replay, the
+        ones its capture recorded."""
+        return getattr(self.built.ctx.kernels, "launches", 0) + self._graph_launches
 
     def stats(self) -> dict[str, int]:
         s = self.scheduler
