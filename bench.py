@@ -176,7 +176,12 @@ def run_ours(args) -> dict:
     numbers = model_numbers(cfg, args.layers)
     peak, peak_kind = peaks()
     prefill_tokens = 2048
+    if args.only == "decode":
+        main = decode_run(engine, batch, context, args.steps, args.warmup, seed=7)
+        return {"only": "decode", "layers": args.layers, "ms_per_step": round(main["device_ms"] / args.steps, 4)}
     prefill_ms = prefill_run(engine, prefill_tokens, repeats=3, seed=100)
+    if args.only == "prefill":
+        return {"only": "prefill", "layers": args.layers, "ms": round(prefill_ms, 3)}
     prefill_flops = 2 * numbers["linear_params"] * prefill_tokens - 2 * cfg["vocab_size"] * cfg["hidden_size"] * (prefill_tokens - 1) \
         + numbers["attn_flops_per_pair"] * prefill_tokens * (prefill_tokens + 1) / 2
     clocks = Clocks()
@@ -231,6 +236,8 @@ def main() -> int:
     ap.add_argument("--layers", type=int, default=FULL_LAYERS, help="fewer layers than the model has (both are reported)")
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--context", type=int, default=8192)
+    ap.add_argument("--only", default="all", choices=("all", "decode", "prefill"),
+                    help="run one part only (for profiling a small case); the JSON line then lacks the other parts")
     args = ap.parse_args()
     if args.gpus != 1:
         print(f"holon_b200 is a single-GPU engine: --gpus {args.gpus} is not supported")

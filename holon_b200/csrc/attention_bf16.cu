@@ -51,27 +51,41 @@ struct KvView {
     const bf16* kv;                // [pages, 2, kv_heads, page_size, head_dim]
     const int32_t* table;          // this row's block-table row
     int pages, page_size, kv_heads, head_dim, hk;
+    int page_shift;                // log2(page_size) when it is a power of two, else -1
 };
 
+__host__ __device__ __forceinline__ int log2_exact(int x) {
+    int s = 0;
+    while ((1 << s) < x) ++s;
+    return (1 << s) == x ? s : -1;
+}
+
 // Loads keys [tile * 64, tile * 64 + 64) of one kv head into k_s / v_s; keys outside [lo, hi) become zeros.
+// A thread copies the same 16-byte column of every (THREADS / chunks-per-row)-th key row.
 template <int D_PAD, int THREADS>
 __device__ __forceinline__ void load_kv_tile(bf16* k_s, bf16* v_s, const KvView& c, int tile, int lo, int hi) {
-    const int chunks = c.head_dim >> 3;                        // 16-byte chunks per key row
+    constexpr int CPR = D_PAD / 8;                              // 16-byte chunks per shared-memory row
+    constexpr int STEP = THREADS / CPR;                         // key rows covered per pass
+    const int ch = threadIdx.x % CPR, r0 = threadIdx.x / CPR;
+    if (ch >= (c.head_dim >> 3)) return;                        // columns past head_dim are never read
     const long head_stride = (long)c.page_size * c.head_dim;
-    for (int i = threadIdx.x; i < TILE_N * (D_PAD / 8); i += THREADS) {
-        const int r = i / (D_PAD / 8), ch = i % (D_PAD / 8);
-        if (ch >= chunks) continue;                           // columns past head_dim are never read
+    const long v_shift = (long)c.kv_heads * head_stride;
+    const long head_base = (long)c.hk * head_stride + ch * 8;
+#pragma unroll
+    for (int r = r0; r < TILE_N; r += STEP) {
         const int j = tile * TILE_N + r;
         bool valid = j >= lo && j < hi;
         long off = 0;
         if (valid) {
-            const int page = c.table[j / c.page_size];
+            const int pi = c.page_shift >= 0 ? j >> c.page_shift : j / c.page_size;
+            const int po = c.page_shift >= 0 ? j & (c.page_size - 1) : j - pi * c.page_size;
+            const int page = c.table[pi];
             valid = page >= 0 && page < c.pages;
-            off = (((long)page * 2) * c.kv_heads + c.hk) * head_stride + (long)(j % c.page_size) * c.head_dim + ch * 8;
+            off = (long)page * 2 * v_shift + head_base + (long)po * c.head_dim;
         }
         const int d = swz<D_PAD>(r, ch) * 8;
         cp_async16(smem_u32(k_s + d), c.kv + off, valid);
-        cp_async16(smem_u32(v_s + d), c.kv + off + (valid ? (long)c.kv_heads * head_stride : 0), valid);
+        cp_async16(smem_u32(v_s + d), c.kv + off + (valid ? v_shift : 0), valid);
     }
 }
 
@@ -100,7 +114,8 @@ __global__ void __launch_bounds__(128) decode_kernel(
     const int per = (tile_hi - tile_lo + splits - 1) / splits;
     const int first = tile_lo + split * per, last = min(tile_hi, first + per);
 
-    KvView view{kv, block_table + (size_t)row_slot[b] * table_stride, pages, page_size, kv_heads, head_dim, hk};
+    KvView view{kv, block_table + (size_t)row_slot[b] * table_stride, pages, page_size, kv_heads, head_dim, hk,
+                log2_exact(page_size)};
     const int chunks = head_dim >> 3;
     for (int i = threadIdx.x; i < 16 * (D_PAD / 8); i += 128) {    // the group's queries; rows past g are zeros
         const int r = i / (D_PAD / 8), ch = i % (D_PAD / 8);
@@ -119,6 +134,9 @@ __global__ void __launch_bounds__(128) decode_kernel(
     for (int i = 0; i < D_PAD / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
     float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;      // rows lane/4 and lane/4 + 8
     const int ksteps = head_dim >> 4;
+    constexpr bool Q_IN_REGS = D_PAD <= 128;                        // larger heads keep the registers for the output
+    uint32_t qf[Q_IN_REGS ? D_PAD / 16 : 1][4];
+    bool q_loaded = false;
 
     for (int tile = first; tile < last; ++tile) {
         const int stage = (tile - first) % STAGES;
@@ -129,6 +147,12 @@ __global__ void __launch_bounds__(128) decode_kernel(
             load_kv_tile<D_PAD, 128>(k_s + s2 * TILE_N * D_PAD, v_s + s2 * TILE_N * D_PAD, view, tile + STAGES - 1, lo, n);
         }
         cp_async_commit();
+        if (Q_IN_REGS && !q_loaded) {
+#pragma unroll
+            for (int ks = 0; ks < D_PAD / 16; ++ks)
+                if (ks < ksteps) ldmatrix_x4(qf[Q_IN_REGS ? ks : 0], smem_u32(q_s + swz<D_PAD>(lane & 15, ks * 2 + (lane >> 4)) * 8));
+            q_loaded = true;
+        }
         const bf16* kt = k_s + stage * TILE_N * D_PAD;
         const bf16* vt = v_s + stage * TILE_N * D_PAD;
         const int key0 = tile * TILE_N + warp * 16;                 // this warp's 16 keys
@@ -138,41 +162,48 @@ __global__ void __launch_bounds__(128) decode_kernel(
         for (int ks = 0; ks < D_PAD / 16; ++ks) {
             if (ks < ksteps) {
                 uint32_t a[4], kb[4];
-                ldmatrix_x4(a, smem_u32(q_s + swz<D_PAD>(lane & 15, ks * 2 + (lane >> 4)) * 8));
+                if (!Q_IN_REGS) ldmatrix_x4(a, smem_u32(q_s + swz<D_PAD>(lane & 15, ks * 2 + (lane >> 4)) * 8));
                 ldmatrix_x4(kb, smem_u32(kt + swz<D_PAD>(warp * 16 + (lane & 7) + ((lane >> 4) << 3), ks * 2 + ((lane >> 3) & 1)) * 8));
-                mma_bf16(s[0], a, kb[0], kb[1]);
-                mma_bf16(s[1], a, kb[2], kb[3]);
+                mma_bf16(s[0], Q_IN_REGS ? qf[Q_IN_REGS ? ks : 0] : a, kb[0], kb[1]);
+                mma_bf16(s[1], Q_IN_REGS ? qf[Q_IN_REGS ? ks : 0] : a, kb[2], kb[3]);
             }
         }
+        const bool edge = key0 < lo || key0 + 16 > n;               // only a row's first and last keys need the mask
         float mx0 = -INFINITY, mx1 = -INFINITY;
 #pragma unroll
         for (int nt = 0; nt < 2; ++nt)
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
-                const int j = key0 + nt * 8 + (lane & 3) * 2 + (e & 1);
-                const float v = (j >= lo && j < n) ? s[nt][e] * scale_log2 : -INFINITY;
+                float v = s[nt][e] * scale_log2;
+                if (edge) {
+                    const int j = key0 + nt * 8 + (lane & 3) * 2 + (e & 1);
+                    if (j < lo || j >= n) v = -INFINITY;
+                }
                 s[nt][e] = v;
                 if (e < 2) mx0 = fmaxf(mx0, v); else mx1 = fmaxf(mx1, v);
             }
         mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1)); mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
         mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1)); mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
         const float n0 = fmaxf(m0, mx0), n1 = fmaxf(m1, mx1);
-        const float c0 = n0 == -INFINITY ? 1.f : exp2f(m0 - n0), c1 = n1 == -INFINITY ? 1.f : exp2f(m1 - n1);
+        const float b0 = n0 == -INFINITY ? 0.f : n0, b1 = n1 == -INFINITY ? 0.f : n1;    // a row with nothing yet: 2^(-inf - 0) = 0
+        const float c0 = exp2f(m0 - b0), c1 = exp2f(m1 - b1);
         m0 = n0; m1 = n1;
         float sum0 = 0.f, sum1 = 0.f;
 #pragma unroll
         for (int nt = 0; nt < 2; ++nt) {
-            s[nt][0] = n0 == -INFINITY ? 0.f : exp2f(s[nt][0] - n0); s[nt][1] = n0 == -INFINITY ? 0.f : exp2f(s[nt][1] - n0);
-            s[nt][2] = n1 == -INFINITY ? 0.f : exp2f(s[nt][2] - n1); s[nt][3] = n1 == -INFINITY ? 0.f : exp2f(s[nt][3] - n1);
+            s[nt][0] = exp2f(s[nt][0] - b0); s[nt][1] = exp2f(s[nt][1] - b0);
+            s[nt][2] = exp2f(s[nt][2] - b1); s[nt][3] = exp2f(s[nt][3] - b1);
             sum0 += s[nt][0] + s[nt][1]; sum1 += s[nt][2] + s[nt][3];
         }
         l0 = l0 * c0 + sum0; l1 = l1 * c1 + sum1;                   // per-lane partial sums; quads are joined at the end
         uint32_t p[4] = {pack_bf16(s[0][0], s[0][1]), pack_bf16(s[0][2], s[0][3]), pack_bf16(s[1][0], s[1][1]), pack_bf16(s[1][2], s[1][3])};
+        if (__any_sync(0xffffffffu, c0 != 1.f || c1 != 1.f)) {      // the running maximum moved: rescale what is summed
+#pragma unroll
+            for (int i = 0; i < D_PAD / 8; ++i) { o[i][0] *= c0; o[i][1] *= c0; o[i][2] *= c1; o[i][3] *= c1; }
+        }
 #pragma unroll
         for (int dt = 0; dt < D_PAD / 16; ++dt) {
             if (dt < ksteps) {
-                o[2 * dt][0] *= c0; o[2 * dt][1] *= c0; o[2 * dt][2] *= c1; o[2 * dt][3] *= c1;
-                o[2 * dt + 1][0] *= c0; o[2 * dt + 1][1] *= c0; o[2 * dt + 1][2] *= c1; o[2 * dt + 1][3] *= c1;
                 uint32_t vb[4];
                 ldmatrix_x4_trans(vb, smem_u32(vt + swz<D_PAD>(warp * 16 + (lane & 7) + (((lane >> 3) & 1) << 3), dt * 2 + (lane >> 4)) * 8));
                 mma_bf16(o[2 * dt], p, vb[0], vb[1]);
@@ -335,7 +366,8 @@ __global__ void __launch_bounds__(128) prefill_kernel(
     const int lo = window > 0 ? max(0, p0 - window + 1) : 0;
     const int tile_lo = lo / TILE_N, tile_hi = (hi + TILE_N - 1) / TILE_N;
 
-    KvView view{kv, block_table + (size_t)row_slot[b] * table_stride, pages, page_size, kv_heads, head_dim, hk};
+    KvView view{kv, block_table + (size_t)row_slot[b] * table_stride, pages, page_size, kv_heads, head_dim, hk,
+                log2_exact(page_size)};
     const int chunks = head_dim >> 3;
     for (int i = threadIdx.x; i < 64 * (D_PAD / 8); i += 128) {
         const int r = i / (D_PAD / 8), ch = i % (D_PAD / 8);
