@@ -220,11 +220,14 @@ def run_ours(args) -> dict:
 
 
 def run_reference(args) -> dict:
+    """The reference arm. mxinO/holon cannot be installed offline here (its build backend, hatchling, is neither
+    installed nor in the wheelhouse), so there is nothing under baseline/_ref to run."""
     ref = ROOT / "baseline" / "_ref"
-    if not ref.is_dir() or not any(ref.iterdir()):
-        return {"impl": "reference", "unavailable": "mxinO/holon is not installed under baseline/_ref (offline install "
-                                                    "did not succeed; see DESIGN.md)"}
-    return {"impl": "reference", "unavailable": "baseline/_ref holds no runnable engine for this benchmark; see DESIGN.md"}
+    if not (ref / "holon").is_dir():
+        return {"impl": "reference", "unavailable": "mxinO/holon is not installed under baseline/_ref: the offline "
+                                                    "pip install fails for want of its build backend (hatchling)"}
+    return {"impl": "reference", "unavailable": "baseline/_ref exists but this benchmark has no driver for it; the "
+                                                "offline install was not possible when bench.py was written"}
 
 
 def main() -> int:

@@ -1,0 +1,103 @@
+"""Generation through the public entry point on the GPU (`Engine.generate`, host token ids in and out) against the
+plain implementation: greedy and seeded temperature sampling, with prompt portions beside decoding requests, with
+CUDA graphs on and off, and in a pool so small that requests are preempted and computed again."""
+from __future__ import annotations
+
+import pytest
+import torch
+
+import plain_qwen3 as plain
+from helpers import make_folder, random_prompt
+from holon_b200.engine import Engine, EngineConfig, SamplingParams
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module", params=["a", "b"])
+def model(request, tmp_path_factory):
+    folder = make_folder(tmp_path_factory.mktemp("models"), request.param)
+    config, weights = plain.read_folder(folder)
+    prompts = [random_prompt(config["vocab_size"], n, 60 + n) for n in (5, 17, 31, 1, 40, 77)]
+    return folder, config, weights, prompts
+
+
+def engine_of(folder, dtype, **kw):
+    args = dict(model=str(folder), dtype=dtype, page_size=16, max_seqs=4, max_model_len=128, max_step_tokens=48,
+                chunk_with_decode=8, state_memory=4 << 20, seed=3)
+    args.update(kw)
+    return Engine(EngineConfig(**args))
+
+
+def check_teacher_forced(config, weights, prompt, tokens, params, seed, exact):
+    """Every generated token against the plain implementation's logits at its place. float32: the very token.
+    bfloat16: greedy tokens must be within a small margin of the best logit (a near-tie may flip)."""
+    ids = list(prompt)
+    for token in tokens:
+        logits = plain.forward(config, weights, ids)[-1]
+        if exact:
+            want = plain.sample(logits, params.temperature, seed, len(ids), params.top_k, params.top_p, params.min_p)
+            assert token == want, (len(ids), token, want)
+        else:
+            assert float(logits[token]) >= float(logits.max()) - 0.06
+        ids.append(token)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("graphs", [True, False])
+def test_greedy_generation(model, dtype, graphs):
+    folder, config, weights, prompts = model
+    engine = engine_of(folder, dtype, cuda_graphs=graphs)
+    params = SamplingParams(temperature=0.0, max_tokens=12)
+    got = engine.generate(prompts, params)
+    assert [len(g) for g in got] == [12] * len(prompts)
+    for prompt, tokens in zip(prompts, got):
+        check_teacher_forced(config, weights, prompt, tokens, params, 0, exact=dtype == "float32")
+    stats = engine.stats()
+    assert stats["mixed_steps"] > 0 and (stats["graph_steps"] > 0) == graphs
+    engine.built.cache.check()
+    assert not engine.built.cache.live
+    if dtype == "float32":
+        again = engine_of(folder, dtype, cuda_graphs=not graphs, chunk_with_decode=0, max_step_tokens=128, page_size=4)
+        assert again.generate(prompts, params) == got            # other batching, other pages: the same tokens
+
+
+def test_sampled_generation_is_seeded_and_survives_preemption(model):
+    folder, config, weights, prompts = model
+    params = [SamplingParams(temperature=0.8, max_tokens=10, seed=100 + i, top_k=(0, 20)[i % 2], top_p=(1.0, 0.9)[i // 3],
+                             min_p=(0.0, 0.01)[i % 3 == 0]) for i in range(len(prompts))]
+    roomy = engine_of(folder, "float32")
+    got = roomy.generate(prompts, params)
+    for prompt, tokens, p in zip(prompts, got, params):
+        check_teacher_forced(config, weights, prompt, tokens, p, p.seed, exact=True)
+    pages = -(-96 // 16) + 1                                         # one longest request and one page more
+    tight = Engine(EngineConfig(model=str(folder), dtype="float32", page_size=16, max_seqs=4, max_model_len=96,
+                                max_step_tokens=48, chunk_with_decode=8, seed=3,
+                                state_memory=page_bytes(config, 16, 4) * (pages + 1)))
+    assert tight.generate(prompts, params) == got
+    assert tight.stats()["preemptions"] > 0
+    tight.built.cache.check()
+
+
+def page_bytes(config, page_size, itemsize):
+    return config["num_hidden_layers"] * 2 * config["num_key_value_heads"] * page_size * config["head_dim"] * itemsize
+
+
+def test_limits_and_errors(model):
+    folder, config, _, _ = model
+    engine = engine_of(folder, "float32", max_model_len=32)
+    with pytest.raises(ValueError, match="empty"):
+        engine.add([])
+    with pytest.raises(ValueError, match="max_model_len"):
+        engine.add(list(range(32)))
+    with pytest.raises(ValueError, match="vocabulary"):
+        engine.add([config["vocab_size"]])
+    with pytest.raises(NotImplementedError):
+        engine.add([1], SamplingParams(repetition_penalty=1.1))
+    out = engine.generate([[1, 2, 3]], SamplingParams(temperature=0.0))          # no max_tokens: stops at max_model_len
+    assert len(out[0]) == 32 - 3
+    rid = engine.add([4, 5, 6], SamplingParams(temperature=0.0, max_tokens=50))
+    engine.step()
+    assert engine.abort(rid).finish_reason == "abort" and not engine.has_work() and not engine.built.cache.live
+    stop = out[0][2]
+    cut = engine.generate([[1, 2, 3]], SamplingParams(temperature=0.0, stop_token_ids=(stop,)))
+    assert cut[0] == out[0][:out[0].index(stop) + 1]
