@@ -40,11 +40,32 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
     return *(uint32_t*)&v;
 }
+__device__ __forceinline__ float ex2(float x) {   // 2^x; -inf gives 0
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
+    return y;
+}
 
-// Shared-memory tiles hold rows of D_PAD bf16 = D_PAD/8 chunks of 16 bytes; the chunk index is XOR-ed with the row
-// within each group of 8 chunks so that ldmatrix's 8 rows fall into 8 different bank groups.
-template <int D_PAD> __device__ __forceinline__ int swz(int row, int chunk) {
-    return row * (D_PAD / 8) + ((chunk & ~7) | ((chunk ^ row) & 7));
+// Shared-memory tiles hold rows of D_PAD bf16 = D_PAD/8 chunks of 16 bytes; the chunk index is XOR-ed with the low
+// three bits of the row so that ldmatrix's 8 rows fall into 8 different bank groups. Byte offset of (row, chunk):
+template <int D_PAD> __device__ __forceinline__ uint32_t tile_off(int row, int chunk) {
+    return (uint32_t)(row * (D_PAD * 2) + ((chunk ^ (row & 7)) << 4));
+}
+
+// Per-lane parts of the ldmatrix addresses, worked out once. A fragment of k-step (or d-step) `step` in a block of 16
+// rows that starts at a multiple of 8 lies at  base + rows * (D_PAD * 2) + lane_row + ((step * 32) ^ lane_xor).
+struct FragLanes {
+    uint32_t a_row, a_xor;         // 16 x 16 A operand (queries): rows lane & 15, k-half lane >> 4
+    uint32_t b_row, b_xor;         // two 8-wide B operands from [n][k] memory (keys): rows (lane & 7) + 8 (lane >> 4)
+    uint32_t t_row, t_xor;         // two 8-wide B operands from [k][n] memory through .trans (values)
+};
+template <int D_PAD> __device__ __forceinline__ FragLanes frag_lanes(int lane) {
+    const uint32_t x = lane & 7, rb = D_PAD * 2;
+    FragLanes f;
+    f.a_row = (lane & 15) * rb;                          f.a_xor = ((uint32_t)(lane >> 4) ^ x) << 4;
+    f.b_row = ((lane & 7) + ((lane >> 4) << 3)) * rb;    f.b_xor = ((uint32_t)((lane >> 3) & 1) ^ x) << 4;
+    f.t_row = ((lane & 7) + (((lane >> 3) & 1) << 3)) * rb;  f.t_xor = ((uint32_t)(lane >> 4) ^ x) << 4;
+    return f;
 }
 
 struct KvView {
@@ -54,16 +75,16 @@ struct KvView {
     int page_shift;                // log2(page_size) when it is a power of two, else -1
 };
 
-__host__ __device__ __forceinline__ int log2_exact(int x) {
+static int log2_exact(int x) {
     int s = 0;
     while ((1 << s) < x) ++s;
     return (1 << s) == x ? s : -1;
 }
 
-// Loads keys [tile * 64, tile * 64 + 64) of one kv head into k_s / v_s; keys outside [lo, hi) become zeros.
-// A thread copies the same 16-byte column of every (THREADS / chunks-per-row)-th key row.
+// Loads keys [tile * 64, tile * 64 + 64) of one kv head into the tiles at shared addresses k_s / v_s; keys outside
+// [lo, hi) become zeros. A thread copies the same 16-byte column of every (THREADS / chunks-per-row)-th key row.
 template <int D_PAD, int THREADS>
-__device__ __forceinline__ void load_kv_tile(bf16* k_s, bf16* v_s, const KvView& c, int tile, int lo, int hi) {
+__device__ __forceinline__ void load_kv_tile(uint32_t k_s, uint32_t v_s, const KvView& c, int tile, int lo, int hi) {
     constexpr int CPR = D_PAD / 8;                              // 16-byte chunks per shared-memory row
     constexpr int STEP = THREADS / CPR;                         // key rows covered per pass
     const int ch = threadIdx.x % CPR, r0 = threadIdx.x / CPR;
@@ -83,10 +104,50 @@ __device__ __forceinline__ void load_kv_tile(bf16* k_s, bf16* v_s, const KvView&
             valid = page >= 0 && page < c.pages;
             off = (long)page * 2 * v_shift + head_base + (long)po * c.head_dim;
         }
-        const int d = swz<D_PAD>(r, ch) * 8;
-        cp_async16(smem_u32(k_s + d), c.kv + off, valid);
-        cp_async16(smem_u32(v_s + d), c.kv + off + (valid ? v_shift : 0), valid);
+        const uint32_t d = tile_off<D_PAD>(r, ch);
+        cp_async16(k_s + d, c.kv + off, valid);
+        cp_async16(v_s + d, c.kv + off + (valid ? v_shift : 0), valid);
     }
+}
+
+// Loads `rows` query rows of one head (row stride heads * head_dim elements) into a tile; the rest become zeros.
+template <int D_PAD, int ROWS, int THREADS>
+__device__ __forceinline__ void load_q_tile(uint32_t q_s, const bf16* q, long row_stride, int rows, int head_dim) {
+    for (int i = threadIdx.x; i < ROWS * (D_PAD / 8); i += THREADS) {
+        const int r = i / (D_PAD / 8), ch = i % (D_PAD / 8);
+        const bool valid = r < rows && ch < (head_dim >> 3);
+        cp_async16(q_s + tile_off<D_PAD>(r, ch), q + (valid ? (long)r * row_stride + ch * 8 : 0), valid);
+    }
+}
+
+// One online-softmax update of a lane's two rows over NT 8-key blocks of raw scores `s` (masked ones are -inf):
+// turns s into weights 2^((s - max) * scale), updates the running maxima and sums, returns the factors by which what
+// was summed before must be scaled.
+template <int NT>
+__device__ __forceinline__ void softmax_step(float (&s)[NT][4], float& m0, float& m1, float& l0, float& l1,
+                                             float scale_log2, float& c0, float& c1) {
+    float mx0 = -INFINITY, mx1 = -INFINITY;
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) {
+        mx0 = fmaxf(mx0, fmaxf(s[nt][0], s[nt][1]));
+        mx1 = fmaxf(mx1, fmaxf(s[nt][2], s[nt][3]));
+    }
+    mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1)); mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+    mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1)); mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+    const float n0 = fmaxf(m0, mx0), n1 = fmaxf(m1, mx1);
+    const float nb0 = n0 == -INFINITY ? 0.f : -n0 * scale_log2;    // a row with nothing yet: 2^(-inf) = 0 below
+    const float nb1 = n1 == -INFINITY ? 0.f : -n1 * scale_log2;
+    c0 = ex2(fmaf(m0, scale_log2, nb0));
+    c1 = ex2(fmaf(m1, scale_log2, nb1));
+    m0 = n0; m1 = n1;
+    float sum0 = 0.f, sum1 = 0.f;
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) {
+        s[nt][0] = ex2(fmaf(s[nt][0], scale_log2, nb0)); s[nt][1] = ex2(fmaf(s[nt][1], scale_log2, nb0));
+        s[nt][2] = ex2(fmaf(s[nt][2], scale_log2, nb1)); s[nt][3] = ex2(fmaf(s[nt][3], scale_log2, nb1));
+        sum0 += s[nt][0] + s[nt][1]; sum1 += s[nt][2] + s[nt][3];
+    }
+    l0 = l0 * c0 + sum0; l1 = l1 * c1 + sum1;                       // per-lane partial sums; quads are joined at the end
 }
 
 // ================================================================ decode
@@ -97,11 +158,12 @@ __global__ void __launch_bounds__(128) decode_kernel(
         const bf16* __restrict__ kv, const int32_t* __restrict__ block_table, int table_stride,
         const int32_t* __restrict__ row_slot, const int32_t* __restrict__ query_start,
         const int32_t* __restrict__ kv_len, int heads, int kv_heads, int head_dim, int pages, int page_size,
-        float scale_log2, int window, int splits) {
+        int page_shift, float scale_log2, int window, int splits) {
     extern __shared__ __align__(128) unsigned char smem_raw[];
-    bf16* q_s = (bf16*)smem_raw;                                   // [16][D_PAD]
-    bf16* k_s = q_s + 16 * D_PAD;                                  // [STAGES][64][D_PAD]
-    bf16* v_s = k_s + STAGES * TILE_N * D_PAD;                     // [STAGES][64][D_PAD]
+    constexpr uint32_t TILE_BYTES = TILE_N * D_PAD * 2;
+    const uint32_t q_s = smem_u32(smem_raw);                       // [16][D_PAD]
+    const uint32_t k_s = q_s + 16 * D_PAD * 2;                     // [STAGES][64][D_PAD]
+    const uint32_t v_s = k_s + STAGES * TILE_BYTES;                // [STAGES][64][D_PAD]
     const int b = blockIdx.x, split = blockIdx.z;
     const int group = heads / kv_heads, m_tiles = (group + 15) / 16;
     const int hk = blockIdx.y / m_tiles, mt = blockIdx.y % m_tiles;
@@ -114,18 +176,11 @@ __global__ void __launch_bounds__(128) decode_kernel(
     const int per = (tile_hi - tile_lo + splits - 1) / splits;
     const int first = tile_lo + split * per, last = min(tile_hi, first + per);
 
-    KvView view{kv, block_table + (size_t)row_slot[b] * table_stride, pages, page_size, kv_heads, head_dim, hk,
-                log2_exact(page_size)};
-    const int chunks = head_dim >> 3;
-    for (int i = threadIdx.x; i < 16 * (D_PAD / 8); i += 128) {    // the group's queries; rows past g are zeros
-        const int r = i / (D_PAD / 8), ch = i % (D_PAD / 8);
-        const bool valid = r < g && ch < chunks;
-        const bf16* src = q + ((size_t)t * heads + (size_t)hk * group + g0 + (valid ? r : 0)) * head_dim + (valid ? ch * 8 : 0);
-        cp_async16(smem_u32(q_s + swz<D_PAD>(r, ch) * 8), src, valid);
-    }
+    KvView view{kv, block_table + (size_t)row_slot[b] * table_stride, pages, page_size, kv_heads, head_dim, hk, page_shift};
+    load_q_tile<D_PAD, 16, 128>(q_s, q + ((size_t)t * heads + (size_t)hk * group + g0) * head_dim, head_dim, g, head_dim);
 #pragma unroll
     for (int s = 0; s < STAGES - 1; ++s) {
-        if (first + s < last) load_kv_tile<D_PAD, 128>(k_s + s * TILE_N * D_PAD, v_s + s * TILE_N * D_PAD, view, first + s, lo, n);
+        if (first + s < last) load_kv_tile<D_PAD, 128>(k_s + s * TILE_BYTES, v_s + s * TILE_BYTES, view, first + s, lo, n);
         cp_async_commit();
     }
 
@@ -134,9 +189,11 @@ __global__ void __launch_bounds__(128) decode_kernel(
     for (int i = 0; i < D_PAD / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
     float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;      // rows lane/4 and lane/4 + 8
     const int ksteps = head_dim >> 4;
+    const FragLanes f = frag_lanes<D_PAD>(lane);
     constexpr bool Q_IN_REGS = D_PAD <= 128;                        // larger heads keep the registers for the output
     uint32_t qf[Q_IN_REGS ? D_PAD / 16 : 1][4];
     bool q_loaded = false;
+    const uint32_t warp_rows = warp * 16 * (D_PAD * 2);             // this warp's 16 keys inside a tile
 
     for (int tile = first; tile < last; ++tile) {
         const int stage = (tile - first) % STAGES;
@@ -144,58 +201,41 @@ __global__ void __launch_bounds__(128) decode_kernel(
         __syncthreads();
         if (tile + STAGES - 1 < last) {
             const int s2 = (tile - first + STAGES - 1) % STAGES;
-            load_kv_tile<D_PAD, 128>(k_s + s2 * TILE_N * D_PAD, v_s + s2 * TILE_N * D_PAD, view, tile + STAGES - 1, lo, n);
+            load_kv_tile<D_PAD, 128>(k_s + s2 * TILE_BYTES, v_s + s2 * TILE_BYTES, view, tile + STAGES - 1, lo, n);
         }
         cp_async_commit();
         if (Q_IN_REGS && !q_loaded) {
 #pragma unroll
             for (int ks = 0; ks < D_PAD / 16; ++ks)
-                if (ks < ksteps) ldmatrix_x4(qf[Q_IN_REGS ? ks : 0], smem_u32(q_s + swz<D_PAD>(lane & 15, ks * 2 + (lane >> 4)) * 8));
+                if (ks < ksteps) ldmatrix_x4(qf[Q_IN_REGS ? ks : 0], q_s + f.a_row + ((ks * 32) ^ f.a_xor));
             q_loaded = true;
         }
-        const bf16* kt = k_s + stage * TILE_N * D_PAD;
-        const bf16* vt = v_s + stage * TILE_N * D_PAD;
         const int key0 = tile * TILE_N + warp * 16;                 // this warp's 16 keys
         if (key0 >= n || key0 + 16 <= lo) continue;                 // (uniform per warp; the barrier is above)
+        const uint32_t kt = k_s + stage * TILE_BYTES + warp_rows + f.b_row;
+        const uint32_t vt = v_s + stage * TILE_BYTES + warp_rows + f.t_row;
         float s[2][4] = {};
 #pragma unroll
         for (int ks = 0; ks < D_PAD / 16; ++ks) {
             if (ks < ksteps) {
                 uint32_t a[4], kb[4];
-                if (!Q_IN_REGS) ldmatrix_x4(a, smem_u32(q_s + swz<D_PAD>(lane & 15, ks * 2 + (lane >> 4)) * 8));
-                ldmatrix_x4(kb, smem_u32(kt + swz<D_PAD>(warp * 16 + (lane & 7) + ((lane >> 4) << 3), ks * 2 + ((lane >> 3) & 1)) * 8));
+                if (!Q_IN_REGS) ldmatrix_x4(a, q_s + f.a_row + ((ks * 32) ^ f.a_xor));
+                ldmatrix_x4(kb, kt + ((ks * 32) ^ f.b_xor));
                 mma_bf16(s[0], Q_IN_REGS ? qf[Q_IN_REGS ? ks : 0] : a, kb[0], kb[1]);
                 mma_bf16(s[1], Q_IN_REGS ? qf[Q_IN_REGS ? ks : 0] : a, kb[2], kb[3]);
             }
         }
-        const bool edge = key0 < lo || key0 + 16 > n;               // only a row's first and last keys need the mask
-        float mx0 = -INFINITY, mx1 = -INFINITY;
+        if (key0 < lo || key0 + 16 > n) {                           // only a row's first and last keys need the mask
 #pragma unroll
-        for (int nt = 0; nt < 2; ++nt)
+            for (int nt = 0; nt < 2; ++nt)
 #pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                float v = s[nt][e] * scale_log2;
-                if (edge) {
+                for (int e = 0; e < 4; ++e) {
                     const int j = key0 + nt * 8 + (lane & 3) * 2 + (e & 1);
-                    if (j < lo || j >= n) v = -INFINITY;
+                    if (j < lo || j >= n) s[nt][e] = -INFINITY;
                 }
-                s[nt][e] = v;
-                if (e < 2) mx0 = fmaxf(mx0, v); else mx1 = fmaxf(mx1, v);
-            }
-        mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1)); mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
-        mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1)); mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
-        const float n0 = fmaxf(m0, mx0), n1 = fmaxf(m1, mx1);
-        const float b0 = n0 == -INFINITY ? 0.f : n0, b1 = n1 == -INFINITY ? 0.f : n1;    // a row with nothing yet: 2^(-inf - 0) = 0
-        const float c0 = exp2f(m0 - b0), c1 = exp2f(m1 - b1);
-        m0 = n0; m1 = n1;
-        float sum0 = 0.f, sum1 = 0.f;
-#pragma unroll
-        for (int nt = 0; nt < 2; ++nt) {
-            s[nt][0] = exp2f(s[nt][0] - b0); s[nt][1] = exp2f(s[nt][1] - b0);
-            s[nt][2] = exp2f(s[nt][2] - b1); s[nt][3] = exp2f(s[nt][3] - b1);
-            sum0 += s[nt][0] + s[nt][1]; sum1 += s[nt][2] + s[nt][3];
         }
-        l0 = l0 * c0 + sum0; l1 = l1 * c1 + sum1;                   // per-lane partial sums; quads are joined at the end
+        float c0, c1;
+        softmax_step<2>(s, m0, m1, l0, l1, scale_log2, c0, c1);
         uint32_t p[4] = {pack_bf16(s[0][0], s[0][1]), pack_bf16(s[0][2], s[0][3]), pack_bf16(s[1][0], s[1][1]), pack_bf16(s[1][2], s[1][3])};
         if (__any_sync(0xffffffffu, c0 != 1.f || c1 != 1.f)) {      // the running maximum moved: rescale what is summed
 #pragma unroll
@@ -205,7 +245,7 @@ __global__ void __launch_bounds__(128) decode_kernel(
         for (int dt = 0; dt < D_PAD / 16; ++dt) {
             if (dt < ksteps) {
                 uint32_t vb[4];
-                ldmatrix_x4_trans(vb, smem_u32(vt + swz<D_PAD>(warp * 16 + (lane & 7) + (((lane >> 3) & 1) << 3), dt * 2 + (lane >> 4)) * 8));
+                ldmatrix_x4_trans(vb, vt + ((dt * 32) ^ f.t_xor));
                 mma_bf16(o[2 * dt], p, vb[0], vb[1]);
                 mma_bf16(o[2 * dt + 1], p, vb[2], vb[3]);
             }
@@ -217,7 +257,7 @@ __global__ void __launch_bounds__(128) decode_kernel(
     __syncthreads();                                                // every warp is done with the tiles: reuse them
 
     // ---- merge the four warps: [warp][row][D_PAD] floats and [warp][row][2] (max, sum) in the tile memory
-    float* wo = (float*)k_s;
+    float* wo = (float*)(smem_raw + 16 * D_PAD * 2);
     float* wml = wo + 4 * 16 * D_PAD;
     const int r0 = lane >> 2, cq = (lane & 3) * 2;
 #pragma unroll
@@ -241,9 +281,9 @@ __global__ void __launch_bounds__(128) decode_kernel(
 #pragma unroll
         for (int w = 0; w < 4; ++w) {
             const float mw = wml[(w * 16 + r) * 2];
-            const float f = mw == -INFINITY ? 0.f : exp2f(mw - mm);
-            acc += f * wo[(w * 16 + r) * D_PAD + d];
-            l += f * wml[(w * 16 + r) * 2 + 1];
+            const float fw = mw == -INFINITY ? 0.f : ex2((mw - mm) * scale_log2);
+            acc += fw * wo[(w * 16 + r) * D_PAD + d];
+            l += fw * wml[(w * 16 + r) * 2 + 1];
         }
         const int h = hk * group + g0 + r;
         if (splits == 1) {
@@ -251,7 +291,7 @@ __global__ void __launch_bounds__(128) decode_kernel(
         } else {
             const size_t slot = ((size_t)b * heads + h) * splits + split;
             part_o[slot * head_dim + d] = acc;
-            if (d == 0) { part_ml[slot * 2] = mm; part_ml[slot * 2 + 1] = l; }
+            if (d == 0) { part_ml[slot * 2] = mm * scale_log2; part_ml[slot * 2 + 1] = l; }   // the maximum in log2 units
         }
     }
 }
@@ -269,9 +309,9 @@ __global__ void decode_merge_kernel(bf16* __restrict__ out, const float* __restr
         float acc = 0.f, l = 0.f;
         for (int s = 0; s < splits; ++s) {
             const float ms = part_ml[(base + s) * 2];
-            const float f = ms == -INFINITY ? 0.f : exp2f(ms - mm);
-            acc += f * part_o[(base + s) * head_dim + d];
-            l += f * part_ml[(base + s) * 2 + 1];
+            const float fs = ms == -INFINITY ? 0.f : ex2(ms - mm);
+            acc += fs * part_o[(base + s) * head_dim + d];
+            l += fs * part_ml[(base + s) * 2 + 1];
         }
         out[((size_t)t * heads + h) * head_dim + d] = __float2bfloat16_rn(l > 0.f ? acc / l : 0.f);
     }
@@ -294,7 +334,7 @@ static int launch_decode(bf16* out, float* part_o, float* part_ml, const bf16* q
     const int group = heads / kv_heads, m_tiles = (group + 15) / 16;
     dim3 grid(rows, kv_heads * m_tiles, splits);
     kernel<<<grid, 128, smem, s>>>(out, part_o, part_ml, q, kv, block_table, table_stride, row_slot, query_start,
-                                   kv_len, heads, kv_heads, head_dim, pages, page_size,
+                                   kv_len, heads, kv_heads, head_dim, pages, page_size, log2_exact(page_size),
                                    scale * 1.4426950408889634f, window, splits);
     HB_LAUNCH_CHECK("attention_decode");
     if (splits > 1) {
@@ -319,6 +359,7 @@ extern "C" int hb_attention_decode_bf16(void* out, float* scratch, const void* q
     if (kv_heads < 1 || heads % kv_heads) HB_REFUSE("attention_decode_bf16: %d heads, %d kv heads", heads, kv_heads);
     if (splits < 1 || splits > 64) HB_REFUSE("attention_decode_bf16: %d splits (1 to 64)", splits);
     if (splits > 1 && !scratch) HB_REFUSE("attention_decode_bf16: more than one split needs scratch memory");
+    if (!(scale > 0.f)) HB_REFUSE("attention_decode_bf16: the score scale must be positive");
     if (rows > 65535 * 32) HB_REFUSE("attention_decode_bf16: %d rows", rows);
     float* part_o = scratch;
     float* part_ml = scratch ? scratch + (size_t)rows * heads * splits * head_dim : nullptr;
@@ -332,23 +373,26 @@ extern "C" int hb_attention_decode_bf16(void* out, float* scratch, const void* q
 }
 
 // ================================================================ prefill
-// grid (query tiles, heads), 128 threads; a CTA finds its (row, first query) by walking the rows' tile counts.
+// grid (query tiles, heads), 128 threads; a CTA finds its (row, first query) by walking the rows' tile counts, the
+// last tile first: under a causal mask the late queries of a row have the most keys, and they should start early.
 template <int D_PAD>
-__global__ void __launch_bounds__(128) prefill_kernel(
+__global__ void __launch_bounds__(128, (D_PAD <= 128 ? 3 : 1)) prefill_kernel(
         bf16* __restrict__ out, const bf16* __restrict__ q, const bf16* __restrict__ kv,
         const int32_t* __restrict__ block_table, int table_stride, const int32_t* __restrict__ row_slot,
         const int32_t* __restrict__ query_start, const int32_t* __restrict__ kv_len, int row0, int rows, int heads,
-        int kv_heads, int head_dim, int pages, int page_size, float scale_log2, int window) {
+        int kv_heads, int head_dim, int pages, int page_size, int page_shift, float scale_log2, int window) {
     extern __shared__ __align__(128) unsigned char smem_raw[];
-    bf16* q_s = (bf16*)smem_raw;                                   // [64][D_PAD]
-    bf16* k_s = q_s + 64 * D_PAD;                                  // [2][64][D_PAD]
-    bf16* v_s = k_s + 2 * TILE_N * D_PAD;
+    constexpr uint32_t TILE_BYTES = TILE_N * D_PAD * 2;
+    constexpr bool Q_IN_REGS = D_PAD <= 128;       // the queries then pass through the second stage's key tile
+    const uint32_t k_s = smem_u32(smem_raw);                        // [2][64][D_PAD]
+    const uint32_t v_s = k_s + 2 * TILE_BYTES;                      // [2][64][D_PAD]
+    const uint32_t q_s = Q_IN_REGS ? k_s + TILE_BYTES : v_s + 2 * TILE_BYTES;
     __shared__ int s_row, s_q0;
     if (threadIdx.x == 0) {
-        int left = blockIdx.x, found = -1, q0 = 0;
-        for (int b = row0; b < rows; ++b) {
+        int left = (int)(gridDim.x - 1 - blockIdx.x), found = -1, q0 = 0;
+        for (int b = rows - 1; b >= row0; --b) {
             const int tiles = (query_start[b + 1] - query_start[b] + 63) >> 6;
-            if (left < tiles) { found = b; q0 = left * 64; break; }
+            if (left < tiles) { found = b; q0 = (tiles - 1 - left) * 64; break; }
             left -= tiles;
         }
         s_row = found; s_q0 = q0;
@@ -366,23 +410,29 @@ __global__ void __launch_bounds__(128) prefill_kernel(
     const int lo = window > 0 ? max(0, p0 - window + 1) : 0;
     const int tile_lo = lo / TILE_N, tile_hi = (hi + TILE_N - 1) / TILE_N;
 
-    KvView view{kv, block_table + (size_t)row_slot[b] * table_stride, pages, page_size, kv_heads, head_dim, hk,
-                log2_exact(page_size)};
-    const int chunks = head_dim >> 3;
-    for (int i = threadIdx.x; i < 64 * (D_PAD / 8); i += 128) {
-        const int r = i / (D_PAD / 8), ch = i % (D_PAD / 8);
-        const bool valid = r < qn && ch < chunks;
-        const bf16* src = q + ((size_t)(t0 + (valid ? r : 0)) * heads + h) * head_dim + (valid ? ch * 8 : 0);
-        cp_async16(smem_u32(q_s + swz<D_PAD>(r, ch) * 8), src, valid);
-    }
+    KvView view{kv, block_table + (size_t)row_slot[b] * table_stride, pages, page_size, kv_heads, head_dim, hk, page_shift};
+    const int ksteps = head_dim >> 4;
+    const FragLanes f = frag_lanes<D_PAD>(lane);
+    const uint32_t warp_rows = warp * 16 * (D_PAD * 2);
+    uint32_t qf[Q_IN_REGS ? D_PAD / 16 : 1][4];
+
+    load_q_tile<D_PAD, 64, 128>(q_s, q + ((size_t)t0 * heads + h) * head_dim, (long)heads * head_dim, qn, head_dim);
+    cp_async_commit();
     if (tile_lo < tile_hi) load_kv_tile<D_PAD, 128>(k_s, v_s, view, tile_lo, lo, hi);
     cp_async_commit();
+    if (Q_IN_REGS) {
+        cp_async_wait<1>();                                         // the queries have landed (the first keys may not)
+        __syncthreads();
+#pragma unroll
+        for (int ks = 0; ks < D_PAD / 16; ++ks)
+            if (ks < ksteps) ldmatrix_x4(qf[Q_IN_REGS ? ks : 0], q_s + warp_rows + f.a_row + ((ks * 32) ^ f.a_xor));
+        __syncthreads();                                            // before the second stage is filled with keys
+    }
 
     float o[D_PAD / 8][4];
 #pragma unroll
     for (int i = 0; i < D_PAD / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
     float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
-    const int ksteps = head_dim >> 4;
     const int pos0 = p0 + warp * 16 + (lane >> 2), pos1 = pos0 + 8;  // this lane's two query positions
 
     for (int tile = tile_lo; tile < tile_hi; ++tile) {
@@ -390,13 +440,13 @@ __global__ void __launch_bounds__(128) prefill_kernel(
         cp_async_wait<0>();
         __syncthreads();
         if (tile + 1 < tile_hi)
-            load_kv_tile<D_PAD, 128>(k_s + (stage ^ 1) * TILE_N * D_PAD, v_s + (stage ^ 1) * TILE_N * D_PAD, view, tile + 1, lo, hi);
+            load_kv_tile<D_PAD, 128>(k_s + (stage ^ 1) * TILE_BYTES, v_s + (stage ^ 1) * TILE_BYTES, view, tile + 1, lo, hi);
         cp_async_commit();
-        const bf16* kt = k_s + stage * TILE_N * D_PAD;
-        const bf16* vt = v_s + stage * TILE_N * D_PAD;
         const int key0 = tile * TILE_N;
         if (warp * 16 >= qn) continue;                              // a warp without queries
         if (key0 > p0 + warp * 16 + 15) continue;                   // every key of the tile is in this warp's future
+        const uint32_t kt = k_s + stage * TILE_BYTES + f.b_row;
+        const uint32_t vt = v_s + stage * TILE_BYTES + f.t_row;
         float s[8][4];
 #pragma unroll
         for (int nt = 0; nt < 8; ++nt) s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.f;
@@ -404,47 +454,32 @@ __global__ void __launch_bounds__(128) prefill_kernel(
         for (int ks = 0; ks < D_PAD / 16; ++ks) {
             if (ks < ksteps) {
                 uint32_t a[4];
-                ldmatrix_x4(a, smem_u32(q_s + swz<D_PAD>(warp * 16 + (lane & 15), ks * 2 + (lane >> 4)) * 8));
+                if (!Q_IN_REGS) ldmatrix_x4(a, q_s + warp_rows + f.a_row + ((ks * 32) ^ f.a_xor));
 #pragma unroll
                 for (int np = 0; np < 4; ++np) {
                     uint32_t kb[4];
-                    ldmatrix_x4(kb, smem_u32(kt + swz<D_PAD>(np * 16 + (lane & 7) + ((lane >> 4) << 3), ks * 2 + ((lane >> 3) & 1)) * 8));
-                    mma_bf16(s[2 * np], a, kb[0], kb[1]);
-                    mma_bf16(s[2 * np + 1], a, kb[2], kb[3]);
+                    ldmatrix_x4(kb, kt + np * 16 * (D_PAD * 2) + ((ks * 32) ^ f.b_xor));
+                    mma_bf16(s[2 * np], Q_IN_REGS ? qf[Q_IN_REGS ? ks : 0] : a, kb[0], kb[1]);
+                    mma_bf16(s[2 * np + 1], Q_IN_REGS ? qf[Q_IN_REGS ? ks : 0] : a, kb[2], kb[3]);
                 }
             }
         }
-        const bool edge = key0 + TILE_N - 1 > p0 + warp * 16 || key0 < lo + 0 || window > 0 || key0 + TILE_N > hi;
-        float mx0 = -INFINITY, mx1 = -INFINITY;
+        if (key0 + TILE_N - 1 > p0 + warp * 16 || window > 0 || key0 + TILE_N > hi) {     // the diagonal, a window, the end
 #pragma unroll
-        for (int nt = 0; nt < 8; ++nt)
+            for (int nt = 0; nt < 8; ++nt)
 #pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                float v = s[nt][e] * scale_log2;
-                if (edge) {
+                for (int e = 0; e < 4; ++e) {
                     const int j = key0 + nt * 8 + (lane & 3) * 2 + (e & 1);
                     const int pos = e < 2 ? pos0 : pos1;
-                    const bool seen = j <= pos && j < hi && (window <= 0 || pos - j < window);
-                    if (!seen) v = -INFINITY;
+                    if (!(j <= pos && j < hi && (window <= 0 || pos - j < window))) s[nt][e] = -INFINITY;
                 }
-                s[nt][e] = v;
-                if (e < 2) mx0 = fmaxf(mx0, v); else mx1 = fmaxf(mx1, v);
-            }
-        mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1)); mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
-        mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1)); mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
-        const float n0 = fmaxf(m0, mx0), n1 = fmaxf(m1, mx1);
-        const float c0 = n0 == -INFINITY ? 1.f : exp2f(m0 - n0), c1 = n1 == -INFINITY ? 1.f : exp2f(m1 - n1);
-        m0 = n0; m1 = n1;
-        float sum0 = 0.f, sum1 = 0.f;
-#pragma unroll
-        for (int nt = 0; nt < 8; ++nt) {
-            s[nt][0] = n0 == -INFINITY ? 0.f : exp2f(s[nt][0] - n0); s[nt][1] = n0 == -INFINITY ? 0.f : exp2f(s[nt][1] - n0);
-            s[nt][2] = n1 == -INFINITY ? 0.f : exp2f(s[nt][2] - n1); s[nt][3] = n1 == -INFINITY ? 0.f : exp2f(s[nt][3] - n1);
-            sum0 += s[nt][0] + s[nt][1]; sum1 += s[nt][2] + s[nt][3];
         }
-        l0 = l0 * c0 + sum0; l1 = l1 * c1 + sum1;
+        float c0, c1;
+        softmax_step<8>(s, m0, m1, l0, l1, scale_log2, c0, c1);
+        if (__any_sync(0xffffffffu, c0 != 1.f || c1 != 1.f)) {
 #pragma unroll
-        for (int i = 0; i < D_PAD / 8; ++i) { o[i][0] *= c0; o[i][1] *= c0; o[i][2] *= c1; o[i][3] *= c1; }
+            for (int i = 0; i < D_PAD / 8; ++i) { o[i][0] *= c0; o[i][1] *= c0; o[i][2] *= c1; o[i][3] *= c1; }
+        }
 #pragma unroll
         for (int kk = 0; kk < 4; ++kk) {                            // 16 keys at a time
             uint32_t p[4] = {pack_bf16(s[2 * kk][0], s[2 * kk][1]), pack_bf16(s[2 * kk][2], s[2 * kk][3]),
@@ -453,7 +488,7 @@ __global__ void __launch_bounds__(128) prefill_kernel(
             for (int dt = 0; dt < D_PAD / 16; ++dt) {
                 if (dt < ksteps) {
                     uint32_t vb[4];
-                    ldmatrix_x4_trans(vb, smem_u32(vt + swz<D_PAD>(kk * 16 + (lane & 7) + (((lane >> 3) & 1) << 3), dt * 2 + (lane >> 4)) * 8));
+                    ldmatrix_x4_trans(vb, vt + kk * 16 * (D_PAD * 2) + ((dt * 32) ^ f.t_xor));
                     mma_bf16(o[2 * dt], p, vb[0], vb[1]);
                     mma_bf16(o[2 * dt + 1], p, vb[2], vb[3]);
                 }
@@ -480,16 +515,16 @@ static int launch_prefill(bf16* out, const bf16* q, const bf16* kv, const int32_
                           int rows, int q_tiles, int heads, int kv_heads, int head_dim, int pages, int page_size,
                           float scale, int window, cudaStream_t s) {
     auto kernel = prefill_kernel<D_PAD>;
-    const size_t smem = (size_t)(64 + 4 * TILE_N) * D_PAD * sizeof(bf16);
+    const size_t smem = (size_t)(4 * TILE_N + (D_PAD <= 128 ? 0 : 64)) * D_PAD * sizeof(bf16);
     HB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     kernel<<<dim3(q_tiles, heads), 128, smem, s>>>(out, q, kv, block_table, table_stride, row_slot, query_start,
                                                    kv_len, row0, rows, heads, kv_heads, head_dim, pages, page_size,
-                                                   scale * 1.4426950408889634f, window);
+                                                   log2_exact(page_size), scale * 1.4426950408889634f, window);
     HB_LAUNCH_CHECK("attention_prefill");
     return 0;
 }
 
-// Rows row0 .. rows - 1 of the batch; q_tiles is an upper bound of sum(ceil(queries / 64)) over them.
+// Rows row0 .. rows - 1 of the batch; q_tiles is the sum of ceil(queries / 64) over them.
 extern "C" int hb_attention_prefill_bf16(void* out, const void* q, const void* kv, const int32_t* block_table,
                                          int table_stride, const int32_t* row_slot, const int32_t* query_start,
                                          const int32_t* kv_len, int row0, int rows, int q_tiles, int heads,
@@ -500,6 +535,7 @@ extern "C" int hb_attention_prefill_bf16(void* out, const void* q, const void* k
         HB_REFUSE("attention_prefill_bf16: head_dim %d is no multiple of 16 up to 256", head_dim);
     if (kv_heads < 1 || heads % kv_heads) HB_REFUSE("attention_prefill_bf16: %d heads, %d kv heads", heads, kv_heads);
     if (heads > 65535) HB_REFUSE("attention_prefill_bf16: %d heads", heads);
+    if (!(scale > 0.f)) HB_REFUSE("attention_prefill_bf16: the score scale must be positive");
     cudaStream_t s = (cudaStream_t)stream;
 #define HB_ARGS (bf16*)out, (const bf16*)q, (const bf16*)kv, block_table, table_stride, row_slot, query_start, kv_len, \
     row0, rows, q_tiles, heads, kv_heads, head_dim, pages, page_size, scale, window, s
