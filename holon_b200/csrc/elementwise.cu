@@ -40,11 +40,30 @@ extern "C" int hb_embed(float* out, const void* table, int table_dtype, const in
 
 // ---------------------------------------------------------------- (add +) RMSNorm
 // One block per output row. The row is kept in shared memory as 32-bit between the two passes.
-template <typename TH, typename TD, typename TW>
+// VEC: dim is a multiple of 4 and every pointer is 16-byte aligned per row, so a thread moves 4 values at a time.
+template <typename T> struct Vec4;
+template <> struct Vec4<float> {
+    static __device__ __forceinline__ void load(const float* p, float (&v)[4]) { const float4 x = *(const float4*)p; v[0] = x.x; v[1] = x.y; v[2] = x.z; v[3] = x.w; }
+    static __device__ __forceinline__ void store(float* p, const float (&v)[4]) { *(float4*)p = make_float4(v[0], v[1], v[2], v[3]); }
+};
+template <> struct Vec4<bf16> {
+    static __device__ __forceinline__ void load(const bf16* p, float (&v)[4]) {
+        const uint2 x = *(const uint2*)p;
+        const float2 a = __bfloat1622float2(*(const __nv_bfloat162*)&x.x), b = __bfloat1622float2(*(const __nv_bfloat162*)&x.y);
+        v[0] = a.x; v[1] = a.y; v[2] = b.x; v[3] = b.y;
+    }
+    static __device__ __forceinline__ void store(bf16* p, const float (&v)[4]) {
+        __nv_bfloat162 a = __floats2bfloat162_rn(v[0], v[1]), b = __floats2bfloat162_rn(v[2], v[3]);
+        uint2 x; x.x = *(uint32_t*)&a; x.y = *(uint32_t*)&b;
+        *(uint2*)p = x;
+    }
+};
+
+template <typename TH, typename TD, typename TW, bool VEC>
 __global__ void add_rmsnorm_kernel(TD* __restrict__ out, TH* h, const TD* __restrict__ delta,
                                    const TW* __restrict__ weight, float eps, float offset,
                                    const int32_t* __restrict__ index, int dim) {
-    extern __shared__ float row[];
+    extern __shared__ __align__(16) float row[];
     __shared__ float scratch[33];
     const int r = blockIdx.x;
     const size_t t = index ? (size_t)index[r] : (size_t)r;
@@ -52,28 +71,56 @@ __global__ void add_rmsnorm_kernel(TD* __restrict__ out, TH* h, const TD* __rest
     const TD* dr = delta ? delta + t * dim : nullptr;
     const bool write_back = delta != nullptr && index == nullptr;
     float ss = 0.f;
-    for (int i = threadIdx.x; i < dim; i += blockDim.x) {
-        float v = to_f32(hr[i]);
-        if (dr) v += to_f32(dr[i]);
-        if (write_back) hr[i] = from_f32<TH>(v);
-        row[i] = v;
-        ss += v * v;
+    if (VEC) {
+        for (int i = threadIdx.x * 4; i < dim; i += blockDim.x * 4) {
+            float v[4], d[4];
+            Vec4<TH>::load(hr + i, v);
+            if (dr) {
+                Vec4<TD>::load(dr + i, d);
+#pragma unroll
+                for (int k = 0; k < 4; ++k) v[k] += d[k];
+            }
+            if (write_back) Vec4<TH>::store(hr + i, v);
+            *(float4*)(row + i) = make_float4(v[0], v[1], v[2], v[3]);
+            ss += v[0] * v[0] + v[1] * v[1] + v[2] * v[2] + v[3] * v[3];
+        }
+    } else {
+        for (int i = threadIdx.x; i < dim; i += blockDim.x) {
+            float v = to_f32(hr[i]);
+            if (dr) v += to_f32(dr[i]);
+            if (write_back) hr[i] = from_f32<TH>(v);
+            row[i] = v;
+            ss += v * v;
+        }
     }
     const float total = block_sum(ss, scratch);
     const float rstd = rsqrtf(total / (float)dim + eps);
     TD* o = out + (size_t)r * dim;
-    for (int i = threadIdx.x; i < dim; i += blockDim.x)
-        o[i] = from_f32<TD>(row[i] * rstd * (to_f32(weight[i]) + offset));
+    if (VEC) {
+        for (int i = threadIdx.x * 4; i < dim; i += blockDim.x * 4) {
+            float w[4], v[4];
+            Vec4<TW>::load(weight + i, w);
+            const float4 x = *(const float4*)(row + i);
+            v[0] = x.x * rstd * (w[0] + offset); v[1] = x.y * rstd * (w[1] + offset);
+            v[2] = x.z * rstd * (w[2] + offset); v[3] = x.w * rstd * (w[3] + offset);
+            Vec4<TD>::store(o + i, v);
+        }
+    } else {
+        for (int i = threadIdx.x; i < dim; i += blockDim.x)
+            o[i] = from_f32<TD>(row[i] * rstd * (to_f32(weight[i]) + offset));
+    }
 }
 
 template <typename TH, typename TD, typename TW>
 static int launch_add_rmsnorm(void* out, void* h, const void* delta, const void* weight, float eps, float offset,
                               const int32_t* index, int rows, int dim, cudaStream_t s) {
     const size_t smem = (size_t)dim * sizeof(float);
-    auto kernel = add_rmsnorm_kernel<TH, TD, TW>;
     if (smem > 200 * 1024) HB_REFUSE("rmsnorm: a row of %d values does not fit shared memory (limit 51200)", dim);
+    const bool vec = dim % 4 == 0 && (((uintptr_t)out | (uintptr_t)h | (uintptr_t)delta | (uintptr_t)weight) % 16 == 0);
+    auto kernel = vec ? add_rmsnorm_kernel<TH, TD, TW, true> : add_rmsnorm_kernel<TH, TD, TW, false>;
     if (smem > 48 * 1024) HB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    const int threads = dim >= 2048 ? 512 : (dim >= 512 ? 256 : 128);
+    const int per = vec ? 4 : 1;
+    const int threads = dim >= 4096 * per ? 1024 : (dim >= 1024 * per ? 512 : (dim >= 256 * per ? 256 : 128));
     kernel<<<rows, threads, smem, s>>>((TD*)out, (TH*)h, (const TD*)delta, (const TW*)weight, eps, offset, index, dim);
     HB_LAUNCH_CHECK("add_rmsnorm");
     return 0;
@@ -106,11 +153,36 @@ __global__ void silu_mul_kernel(T* __restrict__ out, const T* __restrict__ gate_
     }
 }
 
+// bfloat16 with inter a multiple of 8: a thread takes 8 gates and 8 ups as two 16-byte loads.
+__global__ void silu_mul_bf16x8_kernel(bf16* __restrict__ out, const bf16* __restrict__ gate_up, int inter, size_t groups) {
+    const int per_row = inter >> 3;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < groups; i += (size_t)gridDim.x * blockDim.x) {
+        const size_t t = i / per_row, c = (i % per_row) << 3;
+        const uint4 g4 = *(const uint4*)(gate_up + t * 2 * inter + c), u4 = *(const uint4*)(gate_up + t * 2 * inter + inter + c);
+        const uint32_t gw[4] = {g4.x, g4.y, g4.z, g4.w}, uw[4] = {u4.x, u4.y, u4.z, u4.w};
+        uint32_t ow[4];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const float2 g = __bfloat1622float2(*(const __nv_bfloat162*)&gw[k]), u = __bfloat1622float2(*(const __nv_bfloat162*)&uw[k]);
+            __nv_bfloat162 r = __floats2bfloat162_rn(g.x / (1.f + expf(-g.x)) * u.x, g.y / (1.f + expf(-g.y)) * u.y);
+            ow[k] = *(uint32_t*)&r;
+        }
+        *(uint4*)(out + t * inter + c) = make_uint4(ow[0], ow[1], ow[2], ow[3]);
+    }
+}
+
 extern "C" int hb_silu_mul(void* out, const void* gate_up, int dtype, int tokens, int inter, hb_stream stream) {
     const size_t total = (size_t)tokens * inter;
     if (total == 0) return 0;
     cudaStream_t s = (cudaStream_t)stream;
     const int threads = 256;
+    if (dtype == HB_BF16 && inter % 8 == 0 && (((uintptr_t)out | (uintptr_t)gate_up) % 16 == 0)) {
+        const size_t groups = total / 8;
+        const int blocks = (int)((groups + threads - 1) / threads < 148 * 32 ? (groups + threads - 1) / threads : 148 * 32);
+        silu_mul_bf16x8_kernel<<<blocks, threads, 0, s>>>((bf16*)out, (const bf16*)gate_up, inter, groups);
+        HB_LAUNCH_CHECK("silu_mul");
+        return 0;
+    }
     const int blocks = (int)((total + threads - 1) / threads < 148 * 16 ? (total + threads - 1) / threads : 148 * 16);
     if (dtype == HB_F32) silu_mul_kernel<float><<<blocks, threads, 0, s>>>((float*)out, (const float*)gate_up, inter, total);
     else if (dtype == HB_BF16) silu_mul_kernel<bf16><<<blocks, threads, 0, s>>>((bf16*)out, (const bf16*)gate_up, inter, total);

@@ -2,7 +2,18 @@
 // One warp per (token, head): query heads first, then key heads, then value heads (a plain copy).
 #include "common.cuh"
 
-template <typename T, typename TW>
+template <typename T> struct Pair;
+template <> struct Pair<float> {
+    static __device__ __forceinline__ float2 load(const float* p) { return *(const float2*)p; }
+    static __device__ __forceinline__ void store(float* p, float a, float b) { *(float2*)p = make_float2(a, b); }
+};
+template <> struct Pair<bf16> {
+    static __device__ __forceinline__ float2 load(const bf16* p) { return __bfloat1622float2(*(const __nv_bfloat162*)p); }
+    static __device__ __forceinline__ void store(bf16* p, float a, float b) { *(__nv_bfloat162*)p = __floats2bfloat162_rn(a, b); }
+};
+
+// VEC: head_dim and rotary_dim are multiples of 4, so a lane moves two neighbouring values at a time.
+template <typename T, typename TW, bool VEC>
 __global__ void qk_norm_rope_kv_write_kernel(T* __restrict__ q_out, const T* __restrict__ qkv,
                                              const int32_t* __restrict__ positions, const float* __restrict__ table,
                                              int rotary_dim, int max_positions, const TW* __restrict__ q_weight,
@@ -37,6 +48,43 @@ __global__ void qk_norm_rope_kv_write_kernel(T* __restrict__ q_out, const T* __r
         weight = is_v ? nullptr : k_weight;
         rotate = !is_v;
     }
+    const int half = rotary_dim >> 1;
+    if (VEC) {
+        if (!rotate) {                               // values: copied as they are
+            for (int d = lane * 2; d < head_dim; d += 64) {
+                const float2 v = Pair<T>::load(src + d);        // (to 32-bit and back is exact)
+                Pair<T>::store(dst + d, v.x, v.y);
+            }
+            return;
+        }
+        float ss = 0.f;
+        for (int d = lane * 2; d < head_dim; d += 64) {
+            const float2 v = Pair<T>::load(src + d);
+            y[d] = v.x; y[d + 1] = v.y;
+            ss += v.x * v.x + v.y * v.y;
+        }
+        if (weight) {
+            ss = warp_sum(ss);
+            const float rstd = rsqrtf(ss / (float)head_dim + eps);
+            for (int d = lane * 2; d < head_dim; d += 64) {
+                const float2 w = Pair<TW>::load(weight + d);
+                y[d] = rounded<T>(y[d] * rstd * (w.x + offset));
+                y[d + 1] = rounded<T>(y[d + 1] * rstd * (w.y + offset));
+            }
+        }
+        __syncwarp();
+        int pos = positions[t];
+        pos = pos < 0 ? 0 : (pos >= max_positions ? max_positions - 1 : pos);
+        const float* cs = table + (size_t)pos * rotary_dim;
+        for (int i = lane * 2; i < half; i += 64) {
+            const float2 c = *(const float2*)(cs + i), sn = *(const float2*)(cs + half + i);
+            const float a0 = y[i], a1 = y[i + 1], b0 = y[i + half], b1 = y[i + half + 1];
+            Pair<T>::store(dst + i, a0 * c.x - b0 * sn.x, a1 * c.y - b1 * sn.y);
+            Pair<T>::store(dst + i + half, b0 * c.x + a0 * sn.x, b1 * c.y + a1 * sn.y);
+        }
+        for (int d = rotary_dim + lane * 2; d < head_dim; d += 64) Pair<T>::store(dst + d, y[d], y[d + 1]);
+        return;
+    }
     if (!rotate) {                                   // values: copied as they are
         for (int d = lane; d < head_dim; d += 32) dst[d] = src[d];
         return;
@@ -53,7 +101,6 @@ __global__ void qk_norm_rope_kv_write_kernel(T* __restrict__ q_out, const T* __r
         for (int d = lane; d < head_dim; d += 32) y[d] = rounded<T>(y[d] * rstd * (to_f32(weight[d]) + offset));
     }
     __syncwarp();
-    const int half = rotary_dim >> 1;
     int pos = positions[t];
     pos = pos < 0 ? 0 : (pos >= max_positions ? max_positions - 1 : pos);
     const float* cs = table + (size_t)pos * rotary_dim;
@@ -74,7 +121,10 @@ static int launch(void* q_out, const void* qkv, const int32_t* positions, const 
     const int items = heads + (kv ? 2 * kv_heads : 0);
     dim3 grid(tokens, (items + warps - 1) / warps);
     const size_t smem = (size_t)warps * head_dim * sizeof(float);
-    qk_norm_rope_kv_write_kernel<T, TW><<<grid, warps * 32, smem, s>>>(
+    const bool vec = head_dim % 4 == 0 && rotary_dim % 4 == 0 &&
+                     (((uintptr_t)q_out | (uintptr_t)qkv | (uintptr_t)table | (uintptr_t)qw | (uintptr_t)kw | (uintptr_t)kv) % 8 == 0);
+    auto kernel = vec ? qk_norm_rope_kv_write_kernel<T, TW, true> : qk_norm_rope_kv_write_kernel<T, TW, false>;
+    kernel<<<grid, warps * 32, smem, s>>>(
         (T*)q_out, (const T*)qkv, positions, table, rotary_dim, max_positions, (const TW*)qw, (const TW*)kw, eps,
         offset, (T*)kv, write_index, pages, page_size, heads, kv_heads, head_dim);
     HB_LAUNCH_CHECK("qk_norm_rope_kv_write");
