@@ -72,6 +72,12 @@ int hb_attention_prefill_bf16(void* out, const void* q, const void* kv, const in
 // out[m, n] = sum_k x[m, k] * w[n, k], all float32, sums in a fixed order that does not depend on m's neighbours.
 int hb_gemm_f32(float* out, const float* x, const float* w, int m, int n, int k, hb_stream stream);
 
+// bfloat16 product for at most 16 rows of x, bound by reading w once. mode 0: out [m, n] (bfloat16, or float32 when
+// out_f32) = x [m, k] · w [n, k]ᵀ. mode 1: w is [2 inter, k], gate rows first; out [m, inter] = silu(x · gateᵀ) ·
+// (x · upᵀ). k a multiple of 8; pointers 16-byte aligned.
+int hb_gemm_bf16_skinny(void* out, int out_f32, const void* x, const void* w, int m, int n, int k, int mode, int inter,
+                        hb_stream stream);
+
 // One token per logits row: arg max where temperature is 0, else a draw from softmax(logits / temperature) after the
 // filters (when `filtered`), by inverse CDF in vocabulary order with the uniform of (seed, position).
 int hb_sample(int32_t* tokens, const float* logits, const float* temperature, const int32_t* top_k,

@@ -182,10 +182,30 @@ class CudaKernels:
             if out.dtype != torch.float32:
                 raise KernelError("linear: a float32 product writes float32")
             self._call("hb_gemm_f32", self._p(out), self._p(x), self._p(weight), m, n, k)
+        elif m <= self.SKINNY_ROWS and k % 8 == 0:       # decode steps: bound by reading the weight once
+            self._call("hb_gemm_bf16_skinny", self._p(out), int(out.dtype == torch.float32), self._p(x),
+                       self._p(weight), m, n, k, 0, 0)
         elif out.dtype == torch.float32:                 # the head: bfloat16 operands, 32-bit logits
             torch.mm(x, weight.t(), out_dtype=torch.float32, out=out)
         else:
             torch.mm(x, weight.t(), out=out)
+
+    SKINNY_ROWS = 16
+
+    def swiglu_gate_up(self, out, x, weight) -> None:
+        """out [tokens, inter] = silu(x · gateᵀ) · (x · upᵀ) with gate's rows first in `weight` [2 inter, k]: for a
+        few tokens one kernel with the activation in its epilogue, else the product and the activation kernel."""
+        self._check(out, x, weight)
+        m, k = x.shape
+        inter = out.shape[1]
+        if weight.shape != (2 * inter, k) or out.shape[0] != m or not (out.dtype == x.dtype == weight.dtype):
+            raise KernelError("swiglu_gate_up: x [tokens, k], weight [2 inter, k], out [tokens, inter], one dtype")
+        if x.dtype == torch.bfloat16 and m <= self.SKINNY_ROWS and k % 8 == 0:
+            self._call("hb_gemm_bf16_skinny", self._p(out), 0, self._p(x), self._p(weight), m, 2 * inter, k, 1, inter)
+            return
+        gate_up = torch.empty(m, 2 * inter, dtype=x.dtype, device=self.device)
+        self.linear(gate_up, x, weight)
+        self.silu_mul(out, gate_up)
 
     def sample(self, tokens, logits, temperature, top_k, top_p, min_p, seed_lo, seed_hi, position, filtered) -> None:
         self._check(tokens, logits, temperature, top_k, top_p, min_p, seed_lo, seed_hi, position)

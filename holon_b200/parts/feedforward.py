@@ -21,7 +21,6 @@ class SwiGLU(Part):
             yield name.replace(prefix + "gate_up.", prefix, 1), p, rows
 
     def forward(self, x: torch.Tensor, step) -> torch.Tensor:
-        gu = self.gate_up.forward(x)
         act = self.ctx.empty(x.shape[0], self.inter)
-        self.ctx.kernels.silu_mul(act, gu)
+        self.ctx.kernels.swiglu_gate_up(act, x, self.gate_up.weight.tensor)
         return self.down.forward(act)

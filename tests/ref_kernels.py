@@ -92,6 +92,11 @@ class RefKernels:
         gate, up = gate_up.float().chunk(2, dim=-1)
         out.copy_((torch.nn.functional.silu(gate) * up).to(out.dtype))
 
+    def swiglu_gate_up(self, out, x, weight):
+        gate_up = torch.empty(x.shape[0], weight.shape[0], dtype=x.dtype)
+        self.linear(gate_up, x, weight)
+        self.silu_mul(out, gate_up)
+
     def linear(self, out, x, weight):
         out.copy_((x.float() @ weight.float().T).to(out.dtype))
 

@@ -101,6 +101,30 @@ def test_linear_bf16(K, m, n, k):
     assert (logits.cpu() - want).abs().max().item() <= 1e-3 * want.abs().max().item()
 
 
+@pytest.mark.parametrize("m", [1, 3, 8, 9, 16, 17])
+@pytest.mark.parametrize("n,k", [(389, 96), (4096, 4096), (1000, 12288), (160, 104), (9500, 256)])
+def test_linear_bf16_few_rows(K, m, n, k):
+    """Decode-sized products take the weight-streaming kernel (up to 16 rows), others the library's."""
+    x, w = rand(m, k, dtype=torch.bfloat16, seed=1), rand(n, k, dtype=torch.bfloat16, seed=2, scale=0.05)
+    want = x.float() @ w.float().T
+    for out_dtype in (torch.bfloat16, torch.float32):
+        out = torch.full((m, n), float("nan"), dtype=out_dtype, device=DEV)
+        K.linear(out, x.to(DEV), w.to(DEV))
+        tol = (1.6e-2 if out_dtype == torch.bfloat16 else 2e-3) * max(1.0, want.abs().max().item())
+        assert (out.float().cpu() - want).abs().max().item() <= tol
+
+
+@pytest.mark.parametrize("m", [1, 8, 13, 16, 40])
+@pytest.mark.parametrize("inter,k", [(176, 96), (12288, 4096), (1000, 328)])
+def test_swiglu_gate_up(K, m, inter, k):
+    x, w = rand(m, k, dtype=torch.bfloat16, seed=3), rand(2 * inter, k, dtype=torch.bfloat16, seed=4, scale=0.1)
+    gate_up = x.float() @ w.float().T
+    want = torch.nn.functional.silu(gate_up[:, :inter]) * gate_up[:, inter:]
+    out = torch.full((m, inter), float("nan"), dtype=torch.bfloat16, device=DEV)
+    K.swiglu_gate_up(out, x.to(DEV), w.to(DEV))
+    assert (out.float().cpu() - want).abs().max().item() <= 2e-2 * max(1.0, want.abs().max().item())
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("heads,kv_heads,head_dim,rotary,page", [(6, 3, 80, 80, 8), (5, 1, 32, 16, 5), (8, 8, 128, 128, 64)])
 def test_qk_norm_rope_kv_write(K, dtype, heads, kv_heads, head_dim, rotary, page):
