@@ -11,7 +11,6 @@
 #include "common.cuh"
 
 #define SK_WARPS 8
-#define SK_UNROLL 4
 
 __device__ __forceinline__ uint4 ld_stream16(const void* p, bool valid) {
     uint4 v = make_uint4(0u, 0u, 0u, 0u);
@@ -30,7 +29,7 @@ __device__ __forceinline__ void mma16816(float (&c)[4], uint32_t a0, uint32_t a1
 }
 
 // MT tiles of 16 weight rows per CTA, NT tiles of 8 rows of x.
-template <int MT, int NT>
+template <int MT, int NT, int SK_UNROLL>
 __global__ void __launch_bounds__(SK_WARPS * 32) gemm_skinny_kernel(void* __restrict__ out, int out_f32,
                                                                     const bf16* __restrict__ x, const bf16* __restrict__ w,
                                                                     int m, int n, int k, int mode, int inter) {
@@ -141,16 +140,16 @@ extern "C" int hb_gemm_bf16_skinny(void* out, int out_f32, const void* x, const 
     if (mode == 1) {
         if (inter < 1) HB_REFUSE("gemm_bf16_skinny: inter = %d", inter);
         const int grid = (inter + 15) / 16;
-        if (nt == 1) gemm_skinny_kernel<2, 1><<<grid, SK_WARPS * 32, 0, s>>>(out, out_f32, (const bf16*)x, (const bf16*)w, m, n, k, 1, inter);
-        else gemm_skinny_kernel<2, 2><<<grid, SK_WARPS * 32, 0, s>>>(out, out_f32, (const bf16*)x, (const bf16*)w, m, n, k, 1, inter);
+        if (nt == 1) gemm_skinny_kernel<2, 1, 4><<<grid, SK_WARPS * 32, 0, s>>>(out, out_f32, (const bf16*)x, (const bf16*)w, m, n, k, 1, inter);
+        else gemm_skinny_kernel<2, 2, 4><<<grid, SK_WARPS * 32, 0, s>>>(out, out_f32, (const bf16*)x, (const bf16*)w, m, n, k, 1, inter);
     } else {
         if (n < 1) HB_REFUSE("gemm_bf16_skinny: n = %d", n);
         const bool wide = n >= 32 * 2 * 148;             // enough rows to give every SM two CTAs of 32 rows
         const int grid = wide ? (n + 31) / 32 : (n + 15) / 16;
-        if (wide && nt == 1) gemm_skinny_kernel<2, 1><<<grid, SK_WARPS * 32, 0, s>>>(out, out_f32, (const bf16*)x, (const bf16*)w, m, n, k, 0, 0);
-        else if (wide) gemm_skinny_kernel<2, 2><<<grid, SK_WARPS * 32, 0, s>>>(out, out_f32, (const bf16*)x, (const bf16*)w, m, n, k, 0, 0);
-        else if (nt == 1) gemm_skinny_kernel<1, 1><<<grid, SK_WARPS * 32, 0, s>>>(out, out_f32, (const bf16*)x, (const bf16*)w, m, n, k, 0, 0);
-        else gemm_skinny_kernel<1, 2><<<grid, SK_WARPS * 32, 0, s>>>(out, out_f32, (const bf16*)x, (const bf16*)w, m, n, k, 0, 0);
+        if (wide && nt == 1) gemm_skinny_kernel<2, 1, 4><<<grid, SK_WARPS * 32, 0, s>>>(out, out_f32, (const bf16*)x, (const bf16*)w, m, n, k, 0, 0);
+        else if (wide) gemm_skinny_kernel<2, 2, 4><<<grid, SK_WARPS * 32, 0, s>>>(out, out_f32, (const bf16*)x, (const bf16*)w, m, n, k, 0, 0);
+        else if (nt == 1) gemm_skinny_kernel<1, 1, 8><<<grid, SK_WARPS * 32, 0, s>>>(out, out_f32, (const bf16*)x, (const bf16*)w, m, n, k, 0, 0);
+        else gemm_skinny_kernel<1, 2, 8><<<grid, SK_WARPS * 32, 0, s>>>(out, out_f32, (const bf16*)x, (const bf16*)w, m, n, k, 0, 0);
     }
     HB_LAUNCH_CHECK("gemm_bf16_skinny");
     return 0;

@@ -23,10 +23,10 @@ __global__ void qk_norm_rope_kv_write_kernel(T* __restrict__ q_out, const T* __r
     extern __shared__ float smem[];
     const int warps = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int t = blockIdx.x;
-    const int item = blockIdx.y * warps + warp;
     const int items = heads + (kv ? 2 * kv_heads : 0);
-    if (item >= items) return;
     float* y = smem + (size_t)warp * head_dim;
+    for (int item = blockIdx.y * warps + warp; item < items; item += gridDim.y * warps) {
+    __syncwarp();                                    // the buffer y is reused from one head to the next
     const int width = (heads + 2 * kv_heads) * head_dim;
     const T* src = qkv + (size_t)t * width + (size_t)item * head_dim;       // q heads, k heads, v heads in a row
 
@@ -39,9 +39,9 @@ __global__ void qk_norm_rope_kv_write_kernel(T* __restrict__ q_out, const T* __r
         rotate = true;
     } else {
         const int w = write_index[t];
-        if (w < 0) return;
+        if (w < 0) continue;
         const int page = w / page_size, off = w % page_size;
-        if (page >= pages) return;
+        if (page >= pages) continue;
         const int is_v = item >= heads + kv_heads;
         const int head = item - heads - (is_v ? kv_heads : 0);
         dst = kv + ((((size_t)page * 2 + is_v) * kv_heads + head) * page_size + off) * head_dim;
@@ -55,7 +55,7 @@ __global__ void qk_norm_rope_kv_write_kernel(T* __restrict__ q_out, const T* __r
                 const float2 v = Pair<T>::load(src + d);        // (to 32-bit and back is exact)
                 Pair<T>::store(dst + d, v.x, v.y);
             }
-            return;
+            continue;
         }
         float ss = 0.f;
         for (int d = lane * 2; d < head_dim; d += 64) {
@@ -83,11 +83,11 @@ __global__ void qk_norm_rope_kv_write_kernel(T* __restrict__ q_out, const T* __r
             Pair<T>::store(dst + i + half, b0 * c.x + a0 * sn.x, b1 * c.y + a1 * sn.y);
         }
         for (int d = rotary_dim + lane * 2; d < head_dim; d += 64) Pair<T>::store(dst + d, y[d], y[d + 1]);
-        return;
+        continue;
     }
     if (!rotate) {                                   // values: copied as they are
         for (int d = lane; d < head_dim; d += 32) dst[d] = src[d];
-        return;
+        continue;
     }
     float ss = 0.f;
     for (int d = lane; d < head_dim; d += 32) {
@@ -110,6 +110,7 @@ __global__ void qk_norm_rope_kv_write_kernel(T* __restrict__ q_out, const T* __r
         dst[i + half] = from_f32<T>(b * c + a * s);
     }
     for (int d = rotary_dim + lane; d < head_dim; d += 32) dst[d] = from_f32<T>(y[d]);
+    }
 }
 
 template <typename T, typename TW>
@@ -117,9 +118,11 @@ static int launch(void* q_out, const void* qkv, const int32_t* positions, const 
                   int max_positions, const void* qw, const void* kw, float eps, float offset, void* kv,
                   const int32_t* write_index, int pages, int page_size, int tokens, int heads, int kv_heads,
                   int head_dim, cudaStream_t s) {
-    const int warps = 4;
     const int items = heads + (kv ? 2 * kv_heads : 0);
-    dim3 grid(tokens, (items + warps - 1) / warps);
+    // Few tokens (decode): many small blocks, one head per warp. Many tokens: one block per token whose 8 warps walk
+    // the heads, so that the launch is not made of tens of thousands of tiny blocks.
+    const int warps = tokens >= 256 ? 8 : 4;
+    dim3 grid(tokens, tokens >= 256 ? 1 : (items + warps - 1) / warps);
     const size_t smem = (size_t)warps * head_dim * sizeof(float);
     const bool vec = head_dim % 4 == 0 && rotary_dim % 4 == 0 &&
                      (((uintptr_t)q_out | (uintptr_t)qkv | (uintptr_t)table | (uintptr_t)qw | (uintptr_t)kw | (uintptr_t)kv) % 8 == 0);
