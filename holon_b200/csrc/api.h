@@ -78,6 +78,13 @@ int hb_gemm_f32(float* out, const float* x, const float* w, int m, int n, int k,
 int hb_gemm_bf16_skinny(void* out, int out_f32, const void* x, const void* w, int m, int n, int k, int mode, int inter,
                         hb_stream stream);
 
+// bfloat16 product on tcgen05 tensor cores with TMA loads and the accumulator in tensor memory (128 x 256 tiles).
+// Same arguments and modes as hb_gemm_bf16_skinny, any m. hb_gemm_tcgen05_status synchronises the device and
+// returns (and clears) a status word that is non-zero if a bounded wait inside the kernel ever gave up.
+int hb_gemm_bf16_tcgen05(void* out, int out_f32, const void* x, const void* w, int m, int n, int k, int mode, int inter,
+                         hb_stream stream);
+int hb_gemm_tcgen05_status(unsigned int* status);
+
 // One token per logits row: arg max where temperature is 0, else a draw from softmax(logits / temperature) after the
 // filters (when `filtered`), by inverse CDF in vocabulary order with the uniform of (seed, position).
 int hb_sample(int32_t* tokens, const float* logits, const float* temperature, const int32_t* top_k,

@@ -1,0 +1,243 @@
+// bfloat16 GEMM on Blackwell's fifth-generation tensor cores: out[m, n] = sum_k x[m, k] * w[n, k].
+//
+// One CTA computes a 128 x 256 tile of the output. Operands come in by TMA (cp.async.bulk.tensor, no multicast) as
+// 64-wide k blocks into a ring of shared-memory stages in the 128-byte swizzled K-major layout; a single thread
+// issues tcgen05.mma (kind::f16, M 128, N 256, K 16, four per stage) with the accumulator in tensor memory; four
+// epilogue warps read it back with tcgen05.ld, 32 columns at a time, and write bfloat16 (or float32) rows.
+// Warp roles: warp 0 producer (TMA), warp 1 MMA issue and TMEM allocation, warps 2-5 epilogue (warp w reads the
+// TMEM lanes 32 (w mod 4) ..., which are the tile's rows).
+// mode 1 is SwiGLU's first half: w is [2 inter, k] with gate rows first; the tile's first 128 accumulator columns
+// come from gate rows n0.., the other 128 from up rows inter + n0.., and the epilogue writes silu(gate) * up.
+//
+// Every wait on an mbarrier is bounded: after HB_SPIN_LIMIT failed polls a thread records the place in the status
+// word (hb_gemm_tcgen05_status reads and clears it), stops waiting, and the CTA still frees its tensor memory.
+#include <cuda.h>
+
+#include "common.cuh"
+
+#define TC_BM 128
+#define TC_BN 256
+#define TC_BK 64
+#define TC_STAGES 4
+#define TC_A_BYTES (TC_BM * TC_BK * 2)
+#define TC_B_BYTES (TC_BN * TC_BK * 2)
+#define TC_STAGE_BYTES (TC_A_BYTES + TC_B_BYTES)
+#define TC_SMEM (TC_STAGES * TC_STAGE_BYTES + 1024 + 256)
+#define HB_SPIN_LIMIT (1u << 22)
+
+__device__ unsigned int g_tc_status = 0;             // 0 fine; else (place << 28) | block of the first wait that gave up
+
+__device__ __forceinline__ uint32_t smem_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(bar), "r"(bytes) : "memory");
+}
+// Waits until the phase of the given parity has completed; false if it gave up.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, unsigned place) {
+    for (unsigned spin = 0; spin < HB_SPIN_LIMIT; ++spin) {
+        uint32_t done;
+        asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.b32 %0, 1, 0, p;\n\t}\n"
+                     : "=r"(done) : "r"(bar), "r"(parity) : "memory");
+        if (done) return true;
+    }
+    atomicCAS(&g_tc_status, 0u, (place << 28) | (blockIdx.y * gridDim.x + blockIdx.x + 1));
+    return false;
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];\n"
+                 ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y) : "memory");
+}
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tc_mma(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                 "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}\n"
+                 ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+                 "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+                 "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                   "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+                   "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+                   "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+                 : "r"(taddr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+}
+
+// A K-major operand tile in the 128-byte swizzled layout: rows of 128 bytes, groups of 8 rows 1024 bytes apart.
+__device__ __forceinline__ uint64_t tc_smem_desc(uint32_t addr) {
+    return (uint64_t)((addr & 0x3FFFFu) >> 4) | (1ull << 16) | (64ull << 32) | (1ull << 46) | (2ull << 61);
+}
+
+__global__ void __launch_bounds__(192, 1) gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x,
+                                                              const __grid_constant__ CUtensorMap map_w, void* __restrict__ out,
+                                                              int out_f32, int m, int n, int k, int mode, int inter) {
+    extern __shared__ unsigned char smem_raw[];
+    const uint32_t base = (smem_addr(smem_raw) + 1023u) & ~1023u;     // the swizzle pattern needs 1024-byte alignment
+    const uint32_t bars = base + TC_STAGES * TC_STAGE_BYTES;           // full[S], empty[S], accumulator ready, TMEM slot
+    const uint32_t full0 = bars, empty0 = bars + 8 * TC_STAGES, ready = bars + 16 * TC_STAGES, slot = ready + 8;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int m0 = blockIdx.x * TC_BM, n0 = blockIdx.y * TC_BN;
+    const int kblocks = (k + TC_BK - 1) / TC_BK;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < TC_STAGES; ++s) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, 1); }
+        mbar_init(ready, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(slot), "r"(TC_BN) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    uint32_t tmem;
+    asm volatile("ld.shared.b32 %0, [%1];\n" : "=r"(tmem) : "r"(slot));
+
+    if (warp == 0) {
+        if (lane == 0) {
+            for (int kb = 0; kb < kblocks; ++kb) {
+                const int s = kb % TC_STAGES;
+                if (!mbar_wait(empty0 + 8 * s, ((kb / TC_STAGES) & 1) ^ 1, 1)) break;
+                const uint32_t a = base + s * TC_STAGE_BYTES, b = a + TC_A_BYTES;
+                mbar_expect_tx(full0 + 8 * s, TC_STAGE_BYTES);
+                tma_load_2d(a, &map_x, full0 + 8 * s, kb * TC_BK, m0);
+                if (mode == 1) {                                   // 128 gate rows and the 128 up rows of the same columns
+                    tma_load_2d(b, &map_w, full0 + 8 * s, kb * TC_BK, blockIdx.y * 128);
+                    tma_load_2d(b + TC_B_BYTES / 2, &map_w, full0 + 8 * s, kb * TC_BK, inter + blockIdx.y * 128);
+                } else {
+                    tma_load_2d(b, &map_w, full0 + 8 * s, kb * TC_BK, n0);
+                    tma_load_2d(b + TC_B_BYTES / 2, &map_w, full0 + 8 * s, kb * TC_BK, n0 + 128);
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            // kind::f16: D float32 (bit 4), A and B bfloat16 (bits 7, 10), both K-major, N / 8 at bit 17, M / 16 at bit 24
+            const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(TC_BN >> 3) << 17) | ((uint32_t)(TC_BM >> 4) << 24);
+            bool ok = true;
+            for (int kb = 0; kb < kblocks && ok; ++kb) {
+                const int s = kb % TC_STAGES;
+                ok = mbar_wait(full0 + 8 * s, (kb / TC_STAGES) & 1, 2);
+                if (!ok) break;
+                tc_fence_after();
+                const uint32_t a = base + s * TC_STAGE_BYTES, b = a + TC_A_BYTES;
+                const uint64_t da = tc_smem_desc(a), db = tc_smem_desc(b);
+#pragma unroll
+                for (int kk = 0; kk < TC_BK / 16; ++kk)              // 16 k values = 32 bytes further along each row
+                    tc_mma(tmem, da + (uint64_t)(kk * 2), db + (uint64_t)(kk * 2), idesc, (kb | kk) != 0);
+                tc_commit(empty0 + 8 * s);                            // the stage is free once these have read it
+            }
+            tc_commit(ready);                                         // arrives when every MMA above has finished
+        }
+    } else {
+        const int q = warp & 3;                                       // this warp's quarter of the TMEM lanes = tile rows
+        const int row = m0 + q * 32 + lane;
+        const bool ok = mbar_wait(ready, 0, 3);
+        tc_fence_after();
+        if (ok) {
+            const int width = mode == 1 ? inter : n;
+            const int col0 = mode == 1 ? blockIdx.y * 128 : n0;
+            const int chunks = mode == 1 ? 4 : 8;
+            for (int c = 0; c < chunks; ++c) {
+                uint32_t r[32];
+                tc_ld32(tmem + ((uint32_t)(q * 32) << 16) + c * 32, r);
+                float v[32];
+#pragma unroll
+                for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+                if (mode == 1) {
+                    uint32_t u[32];
+                    tc_ld32(tmem + ((uint32_t)(q * 32) << 16) + 128 + c * 32, u);
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) v[i] = v[i] / (1.f + __expf(-v[i])) * __uint_as_float(u[i]);
+                }
+                const int col = col0 + c * 32;
+                if (row < m && col < width) {
+                    if (out_f32) {
+                        float* o = (float*)out + (size_t)row * width + col;
+                        if (col + 32 <= width && (width & 3) == 0) {
+#pragma unroll
+                            for (int i = 0; i < 32; i += 4) *(float4*)(o + i) = make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
+                        } else {
+                            for (int i = 0; i < 32 && col + i < width; ++i) o[i] = v[i];
+                        }
+                    } else {
+                        bf16* o = (bf16*)out + (size_t)row * width + col;
+                        if (col + 32 <= width && (width & 7) == 0) {
+#pragma unroll
+                            for (int i = 0; i < 32; i += 8) {
+                                uint4 p;
+                                __nv_bfloat162 a0 = __floats2bfloat162_rn(v[i], v[i + 1]), a1 = __floats2bfloat162_rn(v[i + 2], v[i + 3]);
+                                __nv_bfloat162 a2 = __floats2bfloat162_rn(v[i + 4], v[i + 5]), a3 = __floats2bfloat162_rn(v[i + 6], v[i + 7]);
+                                p.x = *(uint32_t*)&a0; p.y = *(uint32_t*)&a1; p.z = *(uint32_t*)&a2; p.w = *(uint32_t*)&a3;
+                                *(uint4*)(o + i) = p;
+                            }
+                        } else {
+                            for (int i = 0; i < 32 && col + i < width; ++i) o[i] = __float2bfloat16_rn(v[i]);
+                        }
+                    }
+                }
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem), "r"(TC_BN) : "memory");
+    }
+}
+
+// ---------------------------------------------------------------- host side
+static int encode_map(CUtensorMap* map, const void* ptr, int rows, int k, int box_rows) {
+    const cuuint64_t dims[2] = {(cuuint64_t)k, (cuuint64_t)rows};
+    const cuuint64_t strides[1] = {(cuuint64_t)k * 2};
+    const cuuint32_t box[2] = {TC_BK, (cuuint32_t)box_rows};
+    const cuuint32_t elem[2] = {1, 1};
+    const CUresult r = cuTensorMapEncodeTiled(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box,
+                                              elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                                              CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) HB_REFUSE("gemm_tcgen05: cuTensorMapEncodeTiled failed with %d (rows %d, k %d)", (int)r, rows, k);
+    return 0;
+}
+
+// Reads and clears the status word: 0, or (place << 28) | (block + 1) of the first wait that gave up
+// (place 1 producer, 2 MMA, 3 epilogue). Synchronises the device.
+extern "C" int hb_gemm_tcgen05_status(unsigned int* status) {
+    HB_CUDA(cudaDeviceSynchronize());
+    HB_CUDA(cudaMemcpyFromSymbol(status, g_tc_status, sizeof(unsigned int)));
+    const unsigned int zero = 0;
+    HB_CUDA(cudaMemcpyToSymbol(g_tc_status, &zero, sizeof(unsigned int)));
+    return 0;
+}
+
+// mode 0: out [m, n] (bfloat16, or float32 when out_f32) = x [m, k] · w [n, k]ᵀ.
+// mode 1: w is [2 inter, k], gate rows first; out [m, inter] = silu(x · gateᵀ) · (x · upᵀ).
+// k a multiple of 8 (a row's bytes a multiple of 16); x, w 16-byte aligned.
+extern "C" int hb_gemm_bf16_tcgen05(void* out, int out_f32, const void* x, const void* w, int m, int n, int k, int mode,
+                                    int inter, hb_stream stream) {
+    if (m == 0 || n == 0) return 0;
+    if (k < 8 || k % 8) HB_REFUSE("gemm_tcgen05: k = %d is no multiple of 8", k);
+    if ((((uintptr_t)x | (uintptr_t)w | (uintptr_t)out) % 16) != 0) HB_REFUSE("gemm_tcgen05: pointers must be 16-byte aligned");
+    if (mode != 0 && mode != 1) HB_REFUSE("gemm_tcgen05: mode %d", mode);
+    if (mode == 1 && (inter < 1 || n != 2 * inter)) HB_REFUSE("gemm_tcgen05: mode 1 needs n = 2 inter (n %d, inter %d)", n, inter);
+    CUtensorMap map_x, map_w;
+    int rc = encode_map(&map_x, x, m, k, TC_BM);
+    if (rc) return rc;
+    rc = encode_map(&map_w, w, n, k, 128);
+    if (rc) return rc;
+    HB_CUDA(cudaFuncSetAttribute(gemm_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, TC_SMEM));
+    const int cols = mode == 1 ? inter : n;
+    dim3 grid((m + TC_BM - 1) / TC_BM, mode == 1 ? (cols + 127) / 128 : (cols + TC_BN - 1) / TC_BN);
+    gemm_tcgen05_kernel<<<grid, 192, TC_SMEM, (cudaStream_t)stream>>>(map_x, map_w, out, out_f32, m, n, k, mode, inter);
+    HB_LAUNCH_CHECK("gemm_tcgen05");
+    return 0;
+}

@@ -192,6 +192,25 @@ class CudaKernels:
 
     SKINNY_ROWS = 16
 
+    def linear_tcgen05(self, out, x, weight, swiglu: bool = False) -> None:
+        """The product (or, with `swiglu`, SwiGLU's silu(gate) · up) on the hand-written tcgen05 / TMA / TMEM kernel."""
+        self._check(out, x, weight)
+        m, k = x.shape
+        n = weight.shape[0]
+        inter = n // 2 if swiglu else 0
+        if weight.shape != (n, k) or out.shape != (m, inter if swiglu else n) or x.dtype != torch.bfloat16 \
+                or weight.dtype != torch.bfloat16 or out.dtype not in (torch.bfloat16, torch.float32):
+            raise KernelError("linear_tcgen05: bfloat16 x [m, k] and w [n, k]; out [m, n] (or [m, n / 2]) bfloat16 or float32")
+        self._call("hb_gemm_bf16_tcgen05", self._p(out), int(out.dtype == torch.float32), self._p(x), self._p(weight),
+                   m, n, k, int(swiglu), inter)
+
+    def tcgen05_status(self) -> int:
+        """0, or which bounded wait inside the tcgen05 kernel gave up (synchronises the device)."""
+        status = ctypes.c_uint(0)
+        if self.lib.hb_gemm_tcgen05_status(ctypes.byref(status)):
+            raise KernelError(self.lib.hb_last_error().decode())
+        return status.value
+
     def swiglu_gate_up(self, out, x, weight) -> None:
         """out [tokens, inter] = silu(x · gateᵀ) · (x · upᵀ) with gate's rows first in `weight` [2 inter, k]: for a
         few tokens one kernel with the activation in its epilogue, else the product and the activation kernel."""

@@ -114,6 +114,31 @@ def test_linear_bf16_few_rows(K, m, n, k):
         assert (out.float().cpu() - want).abs().max().item() <= tol
 
 
+@pytest.mark.parametrize("m,n,k", [(128, 256, 64), (128, 256, 256), (5, 40, 72), (300, 389, 96), (2048, 1024, 512),
+                                   (130, 6144, 4096), (257, 4096, 12288)])
+def test_linear_tcgen05(K, m, n, k):
+    """The tcgen05 / TMA / TMEM product: whole tiles, ragged edges in every dimension, long k."""
+    x, w = rand(m, k, dtype=torch.bfloat16, seed=1), rand(n, k, dtype=torch.bfloat16, seed=2, scale=0.05)
+    want = x.float() @ w.float().T
+    for out_dtype in (torch.bfloat16, torch.float32):
+        out = torch.full((m, n), float("nan"), dtype=out_dtype, device=DEV)
+        K.linear_tcgen05(out, x.to(DEV), w.to(DEV))
+        assert K.tcgen05_status() == 0
+        tol = (1.6e-2 if out_dtype == torch.bfloat16 else 2e-3) * max(1.0, want.abs().max().item())
+        assert (out.float().cpu() - want).abs().max().item() <= tol
+
+
+@pytest.mark.parametrize("m,inter,k", [(128, 128, 64), (70, 176, 96), (512, 1000, 328), (300, 12288, 4096)])
+def test_swiglu_tcgen05(K, m, inter, k):
+    x, w = rand(m, k, dtype=torch.bfloat16, seed=3), rand(2 * inter, k, dtype=torch.bfloat16, seed=4, scale=0.1)
+    gate_up = x.float() @ w.float().T
+    want = torch.nn.functional.silu(gate_up[:, :inter]) * gate_up[:, inter:]
+    out = torch.full((m, inter), float("nan"), dtype=torch.bfloat16, device=DEV)
+    K.linear_tcgen05(out, x.to(DEV), w.to(DEV), swiglu=True)
+    assert K.tcgen05_status() == 0
+    assert (out.float().cpu() - want).abs().max().item() <= 2e-2 * max(1.0, want.abs().max().item())
+
+
 @pytest.mark.parametrize("m", [1, 8, 13, 16, 40])
 @pytest.mark.parametrize("inter,k", [(176, 96), (12288, 4096), (1000, 328)])
 def test_swiglu_gate_up(K, m, inter, k):
