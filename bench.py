@@ -205,7 +205,7 @@ def run_ours(args) -> dict:
                    "kv_heads": cfg["num_key_value_heads"], "head_dim": cfg["head_dim"],
                    "intermediate": cfg["intermediate_size"], "vocab": cfg["vocab_size"], "global_batch": batch,
                    "seq_len": context, "page_size": 64, "parallelism": "single GPU", "l2": "inputs larger than L2",
-                   "cuda_graphs": True, "peaks": peak_kind},
+                   "cuda_graphs": True, "peaks": peak_kind, "gemm": engine.built.ctx.kernels.gemm},
         "e2e": {"value": round(main["tokens"] / main["wall_ms"] * 1e3, 1), "unit": "tok/s",
                 "h2d_bytes_per_step": main["h2d_bytes_per_step"], "d2h_bytes_per_step": main["d2h_bytes_per_step"]},
         "gpu_launches": main["launches"],

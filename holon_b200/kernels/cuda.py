@@ -9,6 +9,7 @@ the library's own true 32-bit kernel.
 from __future__ import annotations
 
 import ctypes
+import os
 
 import torch
 
@@ -41,6 +42,11 @@ class CudaKernels:
         self._fn = {}
         self.launches = 0
         self._splits: dict = {}
+        # Which kernel multiplies bfloat16 matrices of more than SKINNY_ROWS rows: "cublas" (through torch, the
+        # default, as the reference uses a library there) or "tcgen05" (csrc/gemm_tcgen05.cu, SwiGLU fused).
+        self.gemm = os.environ.get("HOLON_B200_GEMM", "cublas")
+        if self.gemm not in ("cublas", "tcgen05"):
+            raise KernelError(f"HOLON_B200_GEMM must be cublas or tcgen05, not {self.gemm!r}")
         self.attention_bf16 = "fast"          # "generic" forces the CUDA-core kernel for bfloat16 too (tests)
 
     # ------------------------------------------------------------------ plumbing
@@ -185,6 +191,8 @@ class CudaKernels:
         elif m <= self.SKINNY_ROWS and k % 8 == 0:       # decode steps: bound by reading the weight once
             self._call("hb_gemm_bf16_skinny", self._p(out), int(out.dtype == torch.float32), self._p(x),
                        self._p(weight), m, n, k, 0, 0)
+        elif self.gemm == "tcgen05" and k % 8 == 0:      # the hand-written tensor-memory kernel in place of the library
+            self.linear_tcgen05(out, x, weight)
         elif out.dtype == torch.float32:                 # the head: bfloat16 operands, 32-bit logits
             torch.mm(x, weight.t(), out_dtype=torch.float32, out=out)
         else:
@@ -221,6 +229,9 @@ class CudaKernels:
             raise KernelError("swiglu_gate_up: x [tokens, k], weight [2 inter, k], out [tokens, inter], one dtype")
         if x.dtype == torch.bfloat16 and m <= self.SKINNY_ROWS and k % 8 == 0:
             self._call("hb_gemm_bf16_skinny", self._p(out), 0, self._p(x), self._p(weight), m, 2 * inter, k, 1, inter)
+            return
+        if x.dtype == torch.bfloat16 and self.gemm == "tcgen05" and k % 8 == 0:
+            self.linear_tcgen05(out, x, weight, swiglu=True)
             return
         gate_up = torch.empty(m, 2 * inter, dtype=x.dtype, device=self.device)
         self.linear(gate_up, x, weight)

@@ -101,3 +101,21 @@ def test_limits_and_errors(model):
     stop = out[0][2]
     cut = engine.generate([[1, 2, 3]], SamplingParams(temperature=0.0, stop_token_ids=(stop,)))
     assert cut[0] == out[0][:out[0].index(stop) + 1]
+
+
+def test_generation_with_the_tcgen05_gemm(model):
+    """The same greedy generation with every bfloat16 product of more than 16 rows on the hand-written tcgen05 kernel
+    (SwiGLU fused into the gate/up product) instead of the library's."""
+    folder, config, weights, prompts = model
+    params = SamplingParams(temperature=0.0, max_tokens=6)
+    engine = engine_of(folder, "bfloat16", max_step_tokens=128, chunk_with_decode=64)
+    kernels = engine.built.ctx.kernels
+    before = kernels.gemm
+    kernels.gemm = "tcgen05"
+    try:
+        got = engine.generate(prompts, params)
+        assert kernels.tcgen05_status() == 0
+    finally:
+        kernels.gemm = before
+    for prompt, tokens in zip(prompts, got):
+        check_teacher_forced(config, weights, prompt, tokens, params, 0, exact=False)
