@@ -1,0 +1,72 @@
+"""The engine at Qwen3-8B's layer sizes (hidden 4096, 32 query and 8 KV heads of 128, intermediate 12288, vocabulary
+151,936, rotation base 1e6), cut to two layers so that the plain implementation can follow on the CPU: a prompt in
+one step, the rest in portions and token by token, in true 32-bit and in bfloat16. The tiny configurations cannot show
+a fault that needs a long reduction, a wide head or the production tile shapes; this one can."""
+from __future__ import annotations
+
+import pytest
+import torch
+
+import plain_qwen3 as plain
+from helpers import random_prompt
+from holon_b200.engine import StepEntry, build
+from holon_b200.weights import RandomSource
+
+pytestmark = pytest.mark.gpu
+
+CONFIG = dict(architectures=["Qwen3ForCausalLM"], num_hidden_layers=2, hidden_size=4096, num_attention_heads=32,
+              num_key_value_heads=8, head_dim=128, intermediate_size=12288, vocab_size=151936, rope_theta=1000000.0,
+              rms_norm_eps=1e-6, tie_word_embeddings=False)
+
+
+class Held:
+    """A weight source that draws the random tensors once and hands the same ones to the engine and to the plain code."""
+
+    def __init__(self, config, seed):
+        self._config = config
+        self.kept = {name: t for name, t in RandomSource(config, seed).tensors()}
+
+    def config(self):
+        return self._config
+
+    def eos_token_ids(self):
+        return ()
+
+    def tensors(self):
+        return iter(self.kept.items())
+
+
+@pytest.fixture(scope="module")
+def case():
+    source = Held(CONFIG, seed=2)
+    ids = random_prompt(CONFIG["vocab_size"], 150, 9)
+    weights = {k: v.float() for k, v in source.kept.items()}
+    exact = plain.forward(CONFIG, weights, ids)
+    with plain.rounding(torch.bfloat16):
+        rounded = plain.forward(CONFIG, weights, ids)
+    del weights
+    return source, ids, exact, rounded
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_prompt_portions_and_decoding_at_real_sizes(case, dtype):
+    source, ids, exact, rounded = case
+    b = build(source, dtype=dtype, device="cuda:0", page_size=64, max_seqs=4, max_model_len=256, max_step_tokens=256,
+              pages=8)
+    slot, at, rows = b.cache.admit(), 0, []
+    for n in [97, 17, 2, 20] + [1] * 14:                      # a long portion, ragged ones, then token by token
+        assert b.cache.reserve(slot, at + n)
+        rows.append(b.runner.step([StepEntry(slot, ids[at:at + n], at, range(n))]).float().cpu())
+        at += n
+    assert at == len(ids)
+    got = torch.cat(rows)
+    diff = (got - exact).abs()
+    if dtype == "float32":
+        assert diff.max() <= 1e-4, float(diff.max())
+        assert torch.equal(got.argmax(-1), exact.argmax(-1))
+    else:
+        floor = (rounded - exact).abs()
+        assert diff.max() <= 2.0 * floor.max(), (float(diff.max()), float(floor.max()))
+        assert diff.mean() <= 1.5 * floor.mean(), (float(diff.mean()), float(floor.mean()))
+    b.cache.release(slot)
+    b.cache.check()
