@@ -1,0 +1,320 @@
+// bfloat16 paged prefill attention on tcgen05 tensor cores, head size 128, pages of a multiple of 64 tokens.
+//
+// A CTA owns 128 queries of one head and walks that row's 64-key tiles up to its diagonal:
+//   S = Q K^T    tcgen05.mma 128 x 64 x 16, eight per tile, Q and K in shared memory (TMA, 128-byte swizzle), S in one
+//                of two 64-column tensor-memory buffers;
+//   softmax      four warps, one query row per thread: tcgen05.ld of the row, mask, running maximum, 2^x, row sum, all
+//                without a shuffle; the weights P go to shared memory as bfloat16 in the K-major swizzled layout;
+//   O += P V     tcgen05.mma 128 x 128 x 16, four per tile, V read as an MN-major operand (values are stored
+//                [key][d]), O in 128 tensor-memory columns for the whole walk.
+// The running maximum is allowed to lag: O and the row sums are rescaled only when a row's maximum has grown by more
+// than 2^8 since the last rescale (the weights stay below 256, which bfloat16 holds), so the tensor-memory round trip
+// of O is rare. One thread issues all MMAs and keeps S of tile j + 1 in flight while the softmax of tile j runs.
+// Warp 0 loads by TMA (queries once; keys and values of a tile as four 64 x 64 boxes from the paged cache, found
+// through the block table), warp 1 issues MMAs and owns the tensor memory, warps 2-5 are the softmax and the epilogue.
+// Keys past a row's length are masked; they are read (a page is loaded whole), which is safe because cache pools start
+// as zeros and only ever hold finite values. Every mbarrier wait is bounded (tcgen05.cuh).
+#include "tcgen05.cuh"
+
+#define AT_D 128
+#define AT_BM 128
+#define AT_BN 64
+#define AT_STAGES 3
+#define AT_Q_BYTES (AT_BM * AT_D * 2)             // 32 KB: two [128 x 64] swizzled blocks
+#define AT_KV_BYTES (AT_BN * AT_D * 2)            // 16 KB: two [64 x 64] swizzled blocks
+#define AT_P_BYTES (AT_BM * AT_BN * 2)            // 16 KB: one [128 x 64] swizzled block
+#define AT_SMEM (AT_Q_BYTES + AT_STAGES * 2 * AT_KV_BYTES + 2 * AT_P_BYTES + 1024 + 256)
+#define AT_TMEM_COLS 256                          // S0 [0, 64), S1 [64, 128), O [128, 256)
+#define AT_RESCALE 8.0f
+
+__device__ __forceinline__ float at_ex2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
+    return y;
+}
+__device__ __forceinline__ void tc_mma_f16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                 "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}\n"
+                 ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate) : "memory");
+}
+
+__global__ void __launch_bounds__(192, 1) prefill_tcgen05_kernel(
+        const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_kv, bf16* __restrict__ out,
+        const int32_t* __restrict__ block_table, int table_stride, const int32_t* __restrict__ row_slot,
+        const int32_t* __restrict__ query_start, const int32_t* __restrict__ kv_len, int row0, int rows, int heads,
+        int kv_heads, int pages, int page_size, float scale_log2, int window) {
+    extern __shared__ unsigned char smem_raw[];
+    const uint32_t base = (smem_addr(smem_raw) + 1023u) & ~1023u;
+    const uint32_t q_s = base, kv_s = q_s + AT_Q_BYTES, p_s = kv_s + AT_STAGES * 2 * AT_KV_BYTES;
+    const uint32_t bars = p_s + 2 * AT_P_BYTES;
+    const uint32_t q_full = bars, kv_full0 = bars + 8, kv_empty0 = kv_full0 + 8 * AT_STAGES;
+    const uint32_t s_full0 = kv_empty0 + 8 * AT_STAGES, s_empty0 = s_full0 + 16, p_full0 = s_empty0 + 16;
+    const uint32_t p_empty0 = p_full0 + 16, o_full = p_empty0 + 16, slot = o_full + 8;
+    __shared__ int s_row, s_q0;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+    if (threadIdx.x == 0) {
+        int left = (int)(gridDim.x - 1 - blockIdx.x), found = -1, q0 = 0;      // late query tiles (most keys) first
+        for (int b = rows - 1; b >= row0; --b) {
+            const int tiles = (query_start[b + 1] - query_start[b] + AT_BM - 1) / AT_BM;
+            if (left < tiles) { found = b; q0 = (tiles - 1 - left) * AT_BM; break; }
+            left -= tiles;
+        }
+        s_row = found; s_q0 = q0;
+        mbar_init(q_full, 1);
+        for (int s = 0; s < AT_STAGES; ++s) { mbar_init(kv_full0 + 8 * s, 1); mbar_init(kv_empty0 + 8 * s, 1); }
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(s_full0 + 8 * i, 1); mbar_init(s_empty0 + 8 * i, 4);
+            mbar_init(p_full0 + 8 * i, 4); mbar_init(p_empty0 + 8 * i, 1);
+        }
+        mbar_init(o_full, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(slot), "r"(AT_TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    uint32_t tmem;
+    asm volatile("ld.shared.b32 %0, [%1];\n" : "=r"(tmem) : "r"(slot));
+
+    const int b = s_row;
+    const int h = blockIdx.y, hk = h / (heads / kv_heads);
+    int tile_lo = 0, tile_hi = 0, t0 = 0, qn = 0, p0 = 0, hi = 0;
+    if (b >= 0) {
+        const int nq = query_start[b + 1] - query_start[b], n = kv_len[b];
+        t0 = query_start[b] + s_q0;
+        qn = min(AT_BM, nq - s_q0);
+        p0 = n - nq + s_q0;                                          // position of the tile's first query
+        hi = min(n, p0 + qn);                                        // keys below hi are visible to someone here
+        const int lo = window > 0 ? max(0, p0 - window + 1) : 0;
+        tile_lo = lo / AT_BN;
+        tile_hi = (hi + AT_BN - 1) / AT_BN;
+    }
+    const int tiles = tile_hi - tile_lo;
+
+    if (b >= 0 && warp == 0) {
+        if (lane == 0) {
+            mbar_expect_tx(q_full, AT_Q_BYTES);
+            tma_load_2d(q_s, &map_q, q_full, h * AT_D, t0);
+            tma_load_2d(q_s + AT_Q_BYTES / 2, &map_q, q_full, h * AT_D + 64, t0);
+            const int32_t* table = block_table + (size_t)row_slot[b] * table_stride;
+            for (int j = 0; j < tiles; ++j) {
+                const int s = j % AT_STAGES;
+                if (!mbar_wait(kv_empty0 + 8 * s, ((j / AT_STAGES) & 1) ^ 1, 1)) break;
+                const int key0 = (tile_lo + j) * AT_BN;
+                int page = table[key0 / page_size];
+                page = page < 0 || page >= pages ? 0 : page;
+                const int k_row = ((page * 2) * kv_heads + hk) * page_size + key0 % page_size;   // row of the flattened cache
+                const int v_row = k_row + kv_heads * page_size;
+                const uint32_t k_dst = kv_s + s * 2 * AT_KV_BYTES, v_dst = k_dst + AT_KV_BYTES;
+                mbar_expect_tx(kv_full0 + 8 * s, 2 * AT_KV_BYTES);
+                tma_load_2d(k_dst, &map_kv, kv_full0 + 8 * s, 0, k_row);
+                tma_load_2d(k_dst + AT_KV_BYTES / 2, &map_kv, kv_full0 + 8 * s, 64, k_row);
+                tma_load_2d(v_dst, &map_kv, kv_full0 + 8 * s, 0, v_row);
+                tma_load_2d(v_dst + AT_KV_BYTES / 2, &map_kv, kv_full0 + 8 * s, 64, v_row);
+            }
+        }
+    } else if (b >= 0 && warp == 1) {
+        if (lane == 0) {
+            // kind::f16, D float32, A and B bfloat16; N / 8 at bit 17, M / 16 at bit 24; bit 16: B is MN-major
+            const uint32_t idesc_qk = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(AT_BN >> 3) << 17) | ((uint32_t)(AT_BM >> 4) << 24);
+            const uint32_t idesc_pv = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((uint32_t)(AT_D >> 3) << 17) | ((uint32_t)(AT_BM >> 4) << 24);
+            const uint32_t o_t = tmem + 2 * AT_BN;
+            bool ok = mbar_wait(q_full, 0, 2);
+            auto issue_pv = [&](int i) -> bool {                      // O += P_i V_i
+                if (!mbar_wait(p_full0 + 8 * (i & 1), (i >> 1) & 1, 5)) return false;
+                tc_fence_after();
+                const int s = i % AT_STAGES;
+                const uint32_t v_src = kv_s + s * 2 * AT_KV_BYTES + AT_KV_BYTES, p_src = p_s + (i & 1) * AT_P_BYTES;
+#pragma unroll
+                for (int kk = 0; kk < AT_BN / 16; ++kk)               // 16 keys a step: 32 bytes along P's rows, 16 rows down V
+                    tc_mma_f16(o_t, tc_smem_desc(p_src) + (uint64_t)(kk * 2),
+                               tc_smem_desc_mn(v_src + kk * 16 * 128, AT_KV_BYTES / 2), idesc_pv, (i | kk) != 0);
+                tc_commit(kv_empty0 + 8 * s);                         // the stage's keys and values have been read
+                tc_commit(p_empty0 + 8 * (i & 1));                    // and so has P; O holds tile i
+                return true;
+            };
+            for (int j = 0; j < tiles && ok; ++j) {
+                const int s = j % AT_STAGES;
+                ok = mbar_wait(kv_full0 + 8 * s, (j / AT_STAGES) & 1, 3) &&
+                     mbar_wait(s_empty0 + 8 * (j & 1), ((j >> 1) & 1) ^ 1, 4);
+                if (!ok) break;
+                tc_fence_after();
+                const uint32_t k_src = kv_s + s * 2 * AT_KV_BYTES, s_t = tmem + (j & 1) * AT_BN;
+#pragma unroll
+                for (int kk = 0; kk < AT_D / 16; ++kk) {              // d 0..63 in the first block, 64..127 in the second
+                    const uint32_t blk = kk >> 2, within = (kk & 3) * 2;
+                    tc_mma_f16(s_t, tc_smem_desc(q_s + blk * (AT_Q_BYTES / 2)) + within,
+                               tc_smem_desc(k_src + blk * (AT_KV_BYTES / 2)) + within, idesc_qk, kk != 0);
+                }
+                tc_commit(s_full0 + 8 * (j & 1));
+                if (j >= 1) ok = issue_pv(j - 1);
+            }
+            if (ok && tiles > 0) ok = issue_pv(tiles - 1);
+            tc_commit(o_full);
+        }
+    } else if (b >= 0) {
+        const int q = warp & 3;                                       // this warp's quarter of the TMEM lanes = query rows
+        const int r = q * 32 + lane;                                  // this thread's query row within the tile
+        const int pos = p0 + r;                                       // and its position
+        const uint32_t lane_t = tmem + ((uint32_t)(q * 32) << 16);
+        const uint32_t o_t = lane_t + 2 * AT_BN;
+        float m_used = -INFINITY, l = 0.f;                            // in log2 units; the maximum may lag by AT_RESCALE
+        bool ok = true;
+        for (int j = 0; j < tiles && ok; ++j) {
+            const int buf = j & 1;
+            ok = mbar_wait(s_full0 + 8 * buf, (j >> 1) & 1, 6);
+            if (!ok) break;
+            tc_fence_after();
+            uint32_t sr[2][32];
+            tc_ld32(lane_t + buf * AT_BN, sr[0]);
+            tc_ld32(lane_t + buf * AT_BN + 32, sr[1]);
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(s_empty0 + 8 * buf);           // S is in registers: the buffer may take tile j + 2
+            const int key0 = (tile_lo + j) * AT_BN;
+            const bool edge = key0 + AT_BN - 1 > p0 || window > 0 || key0 + AT_BN > hi;
+            float mx = -INFINITY;
+#pragma unroll
+            for (int c = 0; c < 2; ++c)
+#pragma unroll
+                for (int i = 0; i < 32; ++i) {
+                    float v = __uint_as_float(sr[c][i]);
+                    if (edge) {
+                        const int key = key0 + c * 32 + i;
+                        if (!(key <= pos && key < hi && (window <= 0 || pos - key < window))) v = -INFINITY;
+                    }
+                    sr[c][i] = __float_as_uint(v);
+                    mx = fmaxf(mx, v);
+                }
+            const float mt = mx * scale_log2;
+            const bool grow = mt > m_used + AT_RESCALE || (m_used == -INFINITY && mt > -INFINITY);
+            if (__any_sync(0xffffffffu, grow)) {                      // rescale what is summed (whole warp: the TMEM ops are collective)
+                const float m_new = grow ? mt : m_used;
+                const float f = m_used == -INFINITY ? 0.f : at_ex2(m_used - m_new);
+                if (j > 0) {
+                    ok = mbar_wait(p_empty0 + 8 * ((j - 1) & 1), ((j - 1) >> 1) & 1, 7);   // O holds every tile before j
+                    tc_fence_after();
+                    if (ok) {
+#pragma unroll
+                        for (int c = 0; c < AT_D / 32; ++c) {
+                            uint32_t o[32];
+                            tc_ld32(o_t + c * 32, o);
+#pragma unroll
+                            for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * f);
+                            tc_st32(o_t + c * 32, o);
+                        }
+                    }
+                }
+                l *= f;
+                m_used = m_new;
+            }
+            const float off = m_used == -INFINITY ? 0.f : -m_used;
+            float sum = 0.f;
+            uint32_t pk[32];                                          // 64 weights as bfloat16 pairs
+#pragma unroll
+            for (int c = 0; c < 2; ++c)
+#pragma unroll
+                for (int i = 0; i < 32; i += 2) {
+                    const float a = at_ex2(fmaf(__uint_as_float(sr[c][i]), scale_log2, off));
+                    const float d = at_ex2(fmaf(__uint_as_float(sr[c][i + 1]), scale_log2, off));
+                    sum += a + d;
+                    __nv_bfloat162 pr = __floats2bfloat162_rn(a, d);
+                    pk[c * 16 + i / 2] = *(uint32_t*)&pr;
+                }
+            l += sum;
+            ok = ok && mbar_wait(p_empty0 + 8 * buf, ((j >> 1) & 1) ^ 1, 8);   // P's buffer was read by tile j - 2
+            if (!ok) break;
+            const uint32_t p_row = p_s + buf * AT_P_BYTES + r * 128;
+#pragma unroll
+            for (int c = 0; c < 8; ++c)                                // 8 keys = 16 bytes a chunk, swizzled by the row
+                asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};\n" ::"r"(p_row + ((c ^ (r & 7)) << 4)),
+                             "r"(pk[c * 4]), "r"(pk[c * 4 + 1]), "r"(pk[c * 4 + 2]), "r"(pk[c * 4 + 3]) : "memory");
+            fence_async_smem();
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(p_full0 + 8 * buf);
+        }
+        if (ok) ok = mbar_wait(o_full, 0, 9);
+        tc_fence_after();
+        if (ok) {                                                     // (the tensor-memory loads are warp-collective: no lane skips them)
+            const float inv = l > 0.f ? 1.f / l : 0.f;
+            const bool keep = r < qn && tiles > 0 && l > 0.f;
+            bf16* o_row = out + ((size_t)(t0 + (r < qn ? r : 0)) * heads + h) * AT_D;
+#pragma unroll
+            for (int c = 0; c < AT_D / 32; ++c) {
+                uint32_t o[32];
+                tc_ld32(o_t + c * 32, o);
+                if (r < qn) {
+#pragma unroll
+                    for (int i = 0; i < 32; i += 8) {
+                        float v[8];
+#pragma unroll
+                        for (int e = 0; e < 8; ++e) v[e] = keep ? __uint_as_float(o[i + e]) * inv : 0.f;
+                        uint4 w;
+                        __nv_bfloat162 a0 = __floats2bfloat162_rn(v[0], v[1]), a1 = __floats2bfloat162_rn(v[2], v[3]);
+                        __nv_bfloat162 a2 = __floats2bfloat162_rn(v[4], v[5]), a3 = __floats2bfloat162_rn(v[6], v[7]);
+                        w.x = *(uint32_t*)&a0; w.y = *(uint32_t*)&a1; w.z = *(uint32_t*)&a2; w.w = *(uint32_t*)&a3;
+                        *(uint4*)(o_row + c * 32 + i) = w;
+                    }
+                }
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem), "r"(AT_TMEM_COLS) : "memory");
+    }
+}
+
+static int encode_2d(CUtensorMap* map, const void* ptr, uint64_t cols, uint64_t rows, uint32_t box_rows, const char* what) {
+    const cuuint64_t dims[2] = {cols, rows};
+    const cuuint64_t strides[1] = {cols * 2};
+    const cuuint32_t box[2] = {64, box_rows};
+    const cuuint32_t elem[2] = {1, 1};
+    const CUresult r = cuTensorMapEncodeTiled(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box,
+                                              elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                                              CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) HB_REFUSE("attention_prefill_tcgen05: cuTensorMapEncodeTiled failed with %d for %s", (int)r, what);
+    return 0;
+}
+
+extern "C" int hb_attention_tcgen05_status(unsigned int* status) {
+    HB_CUDA(cudaDeviceSynchronize());
+    HB_CUDA(cudaMemcpyFromSymbol(status, g_tc_status, sizeof(unsigned int)));
+    const unsigned int zero = 0;
+    HB_CUDA(cudaMemcpyToSymbol(g_tc_status, &zero, sizeof(unsigned int)));
+    return 0;
+}
+
+// Rows row0 .. rows - 1 of the batch; q_tiles is the sum of ceil(queries / 128) over them; tokens the step's token count.
+extern "C" int hb_attention_prefill_tcgen05(void* out, const void* q, const void* kv, const int32_t* block_table,
+                                            int table_stride, const int32_t* row_slot, const int32_t* query_start,
+                                            const int32_t* kv_len, int row0, int rows, int q_tiles, int tokens, int heads,
+                                            int kv_heads, int head_dim, int pages, int page_size, float scale, int window,
+                                            hb_stream stream) {
+    if (rows <= row0 || q_tiles == 0) return 0;
+    if (head_dim != AT_D) HB_REFUSE("attention_prefill_tcgen05: head_dim %d; this kernel is for %d", head_dim, AT_D);
+    if (page_size % AT_BN) HB_REFUSE("attention_prefill_tcgen05: page size %d is no multiple of %d", page_size, AT_BN);
+    if (kv_heads < 1 || heads % kv_heads || heads > 65535) HB_REFUSE("attention_prefill_tcgen05: %d heads, %d kv heads", heads, kv_heads);
+    if (!(scale > 0.f)) HB_REFUSE("attention_prefill_tcgen05: the score scale must be positive");
+    if ((((uintptr_t)q | (uintptr_t)kv | (uintptr_t)out) % 16) != 0) HB_REFUSE("attention_prefill_tcgen05: pointers must be 16-byte aligned");
+    const uint64_t kv_rows = (uint64_t)pages * 2 * kv_heads * page_size;
+    if (kv_rows > 0x7fffffffull) HB_REFUSE("attention_prefill_tcgen05: the cache has %llu rows, above 2^31", (unsigned long long)kv_rows);
+    CUtensorMap map_q, map_kv;
+    int rc = encode_2d(&map_q, q, (uint64_t)heads * AT_D, (uint64_t)tokens, AT_BM, "q");
+    if (rc) return rc;
+    rc = encode_2d(&map_kv, kv, AT_D, kv_rows, AT_BN, "the cache");
+    if (rc) return rc;
+    HB_CUDA(cudaFuncSetAttribute(prefill_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, AT_SMEM));
+    prefill_tcgen05_kernel<<<dim3(q_tiles, heads), 192, AT_SMEM, (cudaStream_t)stream>>>(
+        map_q, map_kv, (bf16*)out, block_table, table_stride, row_slot, query_start, kv_len, row0, rows, heads, kv_heads,
+        pages, page_size, scale * 1.4426950408889634f, window);
+    HB_LAUNCH_CHECK("attention_prefill_tcgen05");
+    return 0;
+}

@@ -42,6 +42,12 @@ class CudaKernels:
         self._fn = {}
         self.launches = 0
         self._splits: dict = {}
+        # Which kernel attends for rows of several tokens: "mma" (mma.sync, any head size up to 256, any page size) or
+        # "tcgen05" (csrc/attention_tcgen05.cu: head size 128 and pages of a multiple of 64 tokens; other shapes
+        # still take the mma.sync kernel).
+        self.prefill_attention = os.environ.get("HOLON_B200_PREFILL_ATTENTION", "mma")
+        if self.prefill_attention not in ("mma", "tcgen05"):
+            raise KernelError(f"HOLON_B200_PREFILL_ATTENTION must be mma or tcgen05, not {self.prefill_attention!r}")
         # Which kernel multiplies bfloat16 matrices of more than SKINNY_ROWS rows: "cublas" (through torch, the
         # default, as the reference uses a library there) or "tcgen05" (csrc/gemm_tcgen05.cu, SwiGLU fused).
         self.gemm = os.environ.get("HOLON_B200_GEMM", "cublas")
@@ -152,9 +158,13 @@ class CudaKernels:
                        rows.n_decode, *sizes, splits)
         if rows.n_rows > rows.n_decode:
             qs = rows.host_query_start
-            tiles = sum((int(qs[b + 1]) - int(qs[b]) + 63) // 64 for b in range(rows.n_decode, rows.n_rows))
-            self._call("hb_attention_prefill_bf16", self._p(out), self._p(q), self._p(kv), *common, rows.n_decode,
-                       rows.n_rows, tiles, *sizes)
+            counts = [int(qs[b + 1]) - int(qs[b]) for b in range(rows.n_decode, rows.n_rows)]
+            if self.prefill_attention == "tcgen05" and head_dim == 128 and kv.shape[3] % 64 == 0:
+                self._call("hb_attention_prefill_tcgen05", self._p(out), self._p(q), self._p(kv), *common,
+                           rows.n_decode, rows.n_rows, sum((n + 127) // 128 for n in counts), t, *sizes)
+            else:
+                self._call("hb_attention_prefill_bf16", self._p(out), self._p(q), self._p(kv), *common, rows.n_decode,
+                           rows.n_rows, sum((n + 63) // 64 for n in counts), *sizes)
 
     SMS = 148
 
@@ -213,11 +223,14 @@ class CudaKernels:
                    m, n, k, int(swiglu), inter)
 
     def tcgen05_status(self) -> int:
-        """0, or which bounded wait inside the tcgen05 kernel gave up (synchronises the device)."""
-        status = ctypes.c_uint(0)
-        if self.lib.hb_gemm_tcgen05_status(ctypes.byref(status)):
-            raise KernelError(self.lib.hb_last_error().decode())
-        return status.value
+        """0, or which bounded wait inside a tcgen05 kernel (product or attention) gave up (synchronises the device)."""
+        out = 0
+        for name in ("hb_gemm_tcgen05_status", "hb_attention_tcgen05_status"):
+            status = ctypes.c_uint(0)
+            if getattr(self.lib, name)(ctypes.byref(status)):
+                raise KernelError(self.lib.hb_last_error().decode())
+            out = out or status.value
+        return out
 
     def swiglu_gate_up(self, out, x, weight) -> None:
         """out [tokens, inter] = silu(x · gateᵀ) · (x · upᵀ) with gate's rows first in `weight` [2 inter, k]: for a

@@ -235,6 +235,28 @@ def test_paged_attention(K, dtype, geometry, kind, window):
     assert torch.equal(out, again)                                            # run to run identical
 
 
+@pytest.mark.parametrize("heads,kv_heads,page", [(8, 2, 64), (4, 4, 128), (6, 1, 64)])
+@pytest.mark.parametrize("window", [0, 100])
+def test_prefill_attention_tcgen05(K, heads, kv_heads, page, window):
+    """The tcgen05 prefill kernel (head size 128): ragged rows beside decode rows, portions that continue a context,
+    more than one 128-query tile, long contexts that force the lagging maximum to be rescaled."""
+    spec = [(300, 1), (0, 1), (0, 17), (5, 128), (31, 33), (0, 200), (1000, 130), (64, 64), (0, 700)]
+    q, kv, table, rows = paged_case(heads, kv_heads, 128, page, spec, torch.bfloat16, seed=3 + window)
+    q[40:60] *= 4.0                                     # peaked rows: the running maximum moves by more than the lag
+    scale = 1 / math.sqrt(128)
+    want = torch.empty_like(q)
+    REF.paged_attention(want, q, kv, table, rows, scale, window)
+    before = K.prefill_attention
+    K.prefill_attention = "tcgen05"
+    try:
+        out = torch.full_like(q, float("nan"), device=DEV)
+        K.paged_attention(out, q.to(DEV), kv.to(DEV), table.to(DEV), on_device(rows), scale, window)
+        assert K.tcgen05_status() == 0
+    finally:
+        K.prefill_attention = before
+    close(out, want, torch.bfloat16, scale=4)
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("page", [16, 64])
 def test_attention_finds_one_far_key(K, dtype, page):
