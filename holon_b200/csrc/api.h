@@ -70,7 +70,7 @@ int hb_attention_prefill_bf16(void* out, const void* q, const void* kv, const in
                               float scale, int window, hb_stream stream);
 
 // The same rows on tcgen05 tensor cores (scores and output in tensor memory, operands by TMA): head_dim 128, page
-// sizes that are multiples of 64. q_tiles: the sum over the rows of ceil(tokens / 128); tokens: all tokens of the step.
+// sizes that are multiples of 64. q_tiles: the sum over the rows of ceil(tokens / 256); tokens: all tokens of the step.
 // hb_attention_tcgen05_status synchronises the device and returns (and clears) the kernel's bounded-wait status word.
 int hb_attention_prefill_tcgen05(void* out, const void* q, const void* kv, const int32_t* block_table, int table_stride,
                                  const int32_t* row_slot, const int32_t* query_start, const int32_t* kv_len, int row0,

@@ -1,6 +1,6 @@
 // bfloat16 paged prefill attention on tcgen05 tensor cores, head size 128, pages of a multiple of 64 tokens.
 //
-// A CTA owns 128 queries of one head and walks that row's 64-key tiles up to its diagonal:
+// A CTA owns 256 queries of one head, as two groups of 128, and walks that row's 64-key tiles up to its diagonal; per group:
 //   S = Q K^T    tcgen05.mma 128 x 64 x 16, eight per tile, Q and K in shared memory (TMA, 128-byte swizzle), S in one
 //                of two 64-column tensor-memory buffers;
 //   softmax      four warps, one query row per thread: tcgen05.ld of the row, mask, running maximum, 2^x, row sum, all
@@ -17,14 +17,15 @@
 #include "tcgen05.cuh"
 
 #define AT_D 128
-#define AT_BM 128
+#define AT_BM 128                                 // queries per group; a CTA carries two groups
+#define AT_GROUPS 2
 #define AT_BN 64
 #define AT_STAGES 3
-#define AT_Q_BYTES (AT_BM * AT_D * 2)             // 32 KB: two [128 x 64] swizzled blocks
+#define AT_Q_BYTES (AT_BM * AT_D * 2)             // 32 KB a group: two [128 x 64] swizzled blocks
 #define AT_KV_BYTES (AT_BN * AT_D * 2)            // 16 KB: two [64 x 64] swizzled blocks
 #define AT_P_BYTES (AT_BM * AT_BN * 2)            // 16 KB: one [128 x 64] swizzled block
-#define AT_SMEM (AT_Q_BYTES + AT_STAGES * 2 * AT_KV_BYTES + 2 * AT_P_BYTES + 1024 + 256)
-#define AT_TMEM_COLS 256                          // S0 [0, 64), S1 [64, 128), O [128, 256)
+#define AT_SMEM (AT_GROUPS * AT_Q_BYTES + AT_STAGES * 2 * AT_KV_BYTES + AT_GROUPS * 2 * AT_P_BYTES + 1024 + 256)
+#define AT_TMEM_COLS 512                          // per group: S0 [0, 64), S1 [64, 128), O [128, 256)
 #define AT_RESCALE 8.0f
 
 __device__ __forceinline__ float at_ex2(float x) {
@@ -38,36 +39,39 @@ __device__ __forceinline__ void tc_mma_f16(uint32_t tmem_d, uint64_t desc_a, uin
                  ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate) : "memory");
 }
 
-__global__ void __launch_bounds__(192, 1) prefill_tcgen05_kernel(
+// Two groups of 128 queries share the CTA's key and value tiles; each has its own softmax warps (2-5 and 6-9), its own
+// S, P and O, so that one group's softmax runs while the tensor cores work for the other.
+__global__ void __launch_bounds__(320, 1) prefill_tcgen05_kernel(
         const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_kv, bf16* __restrict__ out,
         const int32_t* __restrict__ block_table, int table_stride, const int32_t* __restrict__ row_slot,
         const int32_t* __restrict__ query_start, const int32_t* __restrict__ kv_len, int row0, int rows, int heads,
         int kv_heads, int pages, int page_size, float scale_log2, int window) {
     extern __shared__ unsigned char smem_raw[];
     const uint32_t base = (smem_addr(smem_raw) + 1023u) & ~1023u;
-    const uint32_t q_s = base, kv_s = q_s + AT_Q_BYTES, p_s = kv_s + AT_STAGES * 2 * AT_KV_BYTES;
-    const uint32_t bars = p_s + 2 * AT_P_BYTES;
+    const uint32_t q_s = base, kv_s = q_s + AT_GROUPS * AT_Q_BYTES, p_s = kv_s + AT_STAGES * 2 * AT_KV_BYTES;
+    const uint32_t bars = p_s + AT_GROUPS * 2 * AT_P_BYTES;
     const uint32_t q_full = bars, kv_full0 = bars + 8, kv_empty0 = kv_full0 + 8 * AT_STAGES;
-    const uint32_t s_full0 = kv_empty0 + 8 * AT_STAGES, s_empty0 = s_full0 + 16, p_full0 = s_empty0 + 16;
-    const uint32_t p_empty0 = p_full0 + 16, o_full = p_empty0 + 16, slot = o_full + 8;
+    // per group g and buffer i, at index (g * 2 + i): scores computed / read out, weights written / read by the MMA
+    const uint32_t s_full0 = kv_empty0 + 8 * AT_STAGES, s_empty0 = s_full0 + 32, p_full0 = s_empty0 + 32;
+    const uint32_t p_empty0 = p_full0 + 32, o_full0 = p_empty0 + 32, slot = o_full0 + 16;
     __shared__ int s_row, s_q0;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
     if (threadIdx.x == 0) {
         int left = (int)(gridDim.x - 1 - blockIdx.x), found = -1, q0 = 0;      // late query tiles (most keys) first
         for (int b = rows - 1; b >= row0; --b) {
-            const int tiles = (query_start[b + 1] - query_start[b] + AT_BM - 1) / AT_BM;
-            if (left < tiles) { found = b; q0 = (tiles - 1 - left) * AT_BM; break; }
+            const int tiles = (query_start[b + 1] - query_start[b] + AT_GROUPS * AT_BM - 1) / (AT_GROUPS * AT_BM);
+            if (left < tiles) { found = b; q0 = (tiles - 1 - left) * AT_GROUPS * AT_BM; break; }
             left -= tiles;
         }
         s_row = found; s_q0 = q0;
         mbar_init(q_full, 1);
         for (int s = 0; s < AT_STAGES; ++s) { mbar_init(kv_full0 + 8 * s, 1); mbar_init(kv_empty0 + 8 * s, 1); }
-        for (int i = 0; i < 2; ++i) {
+        for (int i = 0; i < 2 * AT_GROUPS; ++i) {
             mbar_init(s_full0 + 8 * i, 1); mbar_init(s_empty0 + 8 * i, 4);
             mbar_init(p_full0 + 8 * i, 4); mbar_init(p_empty0 + 8 * i, 1);
         }
-        mbar_init(o_full, 1);
+        for (int g = 0; g < AT_GROUPS; ++g) mbar_init(o_full0 + 8 * g, 1);
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
     }
     if (warp == 1) {
@@ -82,24 +86,32 @@ __global__ void __launch_bounds__(192, 1) prefill_tcgen05_kernel(
 
     const int b = s_row;
     const int h = blockIdx.y, hk = h / (heads / kv_heads);
-    int tile_lo = 0, tile_hi = 0, t0 = 0, qn = 0, p0 = 0, hi = 0;
+    int tile_lo = 0, t0 = 0, p0 = 0, n = 0, nq = 0;
+    int g_tiles[AT_GROUPS] = {0, 0}, g_qn[AT_GROUPS] = {0, 0}, g_hi[AT_GROUPS] = {0, 0};
     if (b >= 0) {
-        const int nq = query_start[b + 1] - query_start[b], n = kv_len[b];
+        nq = query_start[b + 1] - query_start[b];
+        n = kv_len[b];
         t0 = query_start[b] + s_q0;
-        qn = min(AT_BM, nq - s_q0);
-        p0 = n - nq + s_q0;                                          // position of the tile's first query
-        hi = min(n, p0 + qn);                                        // keys below hi are visible to someone here
+        p0 = n - nq + s_q0;                                          // position of the CTA's first query
         const int lo = window > 0 ? max(0, p0 - window + 1) : 0;
         tile_lo = lo / AT_BN;
-        tile_hi = (hi + AT_BN - 1) / AT_BN;
+#pragma unroll
+        for (int g = 0; g < AT_GROUPS; ++g) {
+            g_qn[g] = max(0, min(AT_BM, nq - s_q0 - g * AT_BM));     // queries of this group
+            g_hi[g] = g_qn[g] ? min(n, p0 + g * AT_BM + g_qn[g]) : 0;   // keys below this are visible to some of them
+            g_tiles[g] = g_qn[g] ? (g_hi[g] + AT_BN - 1) / AT_BN - tile_lo : 0;
+        }
     }
-    const int tiles = tile_hi - tile_lo;
+    const int tiles = max(g_tiles[0], g_tiles[1]);
 
     if (b >= 0 && warp == 0) {
         if (lane == 0) {
-            mbar_expect_tx(q_full, AT_Q_BYTES);
-            tma_load_2d(q_s, &map_q, q_full, h * AT_D, t0);
-            tma_load_2d(q_s + AT_Q_BYTES / 2, &map_q, q_full, h * AT_D + 64, t0);
+            mbar_expect_tx(q_full, AT_GROUPS * AT_Q_BYTES);
+#pragma unroll
+            for (int g = 0; g < AT_GROUPS; ++g) {                    // (a group without queries loads rows it never uses)
+                tma_load_2d(q_s + g * AT_Q_BYTES, &map_q, q_full, h * AT_D, t0 + g * AT_BM);
+                tma_load_2d(q_s + g * AT_Q_BYTES + AT_Q_BYTES / 2, &map_q, q_full, h * AT_D + 64, t0 + g * AT_BM);
+            }
             const int32_t* table = block_table + (size_t)row_slot[b] * table_stride;
             for (int j = 0; j < tiles; ++j) {
                 const int s = j % AT_STAGES;
@@ -122,61 +134,76 @@ __global__ void __launch_bounds__(192, 1) prefill_tcgen05_kernel(
             // kind::f16, D float32, A and B bfloat16; N / 8 at bit 17, M / 16 at bit 24; bit 16: B is MN-major
             const uint32_t idesc_qk = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(AT_BN >> 3) << 17) | ((uint32_t)(AT_BM >> 4) << 24);
             const uint32_t idesc_pv = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((uint32_t)(AT_D >> 3) << 17) | ((uint32_t)(AT_BM >> 4) << 24);
-            const uint32_t o_t = tmem + 2 * AT_BN;
             bool ok = mbar_wait(q_full, 0, 2);
-            auto issue_pv = [&](int i) -> bool {                      // O += P_i V_i
-                if (!mbar_wait(p_full0 + 8 * (i & 1), (i >> 1) & 1, 5)) return false;
+            auto issue_pv = [&](int g, int i) -> bool {               // O_g += P_g,i V_i
+                const int gb = g * 2 + (i & 1);
+                if (!mbar_wait(p_full0 + 8 * gb, (i >> 1) & 1, 5)) return false;
                 tc_fence_after();
-                const int s = i % AT_STAGES;
-                const uint32_t v_src = kv_s + s * 2 * AT_KV_BYTES + AT_KV_BYTES, p_src = p_s + (i & 1) * AT_P_BYTES;
+                const uint32_t v_src = kv_s + (i % AT_STAGES) * 2 * AT_KV_BYTES + AT_KV_BYTES, p_src = p_s + gb * AT_P_BYTES;
+                const uint32_t o_t = tmem + g * 256 + 2 * AT_BN;
 #pragma unroll
                 for (int kk = 0; kk < AT_BN / 16; ++kk)               // 16 keys a step: 32 bytes along P's rows, 16 rows down V
                     tc_mma_f16(o_t, tc_smem_desc(p_src) + (uint64_t)(kk * 2),
                                tc_smem_desc_mn(v_src + kk * 16 * 128, AT_KV_BYTES / 2), idesc_pv, (i | kk) != 0);
-                tc_commit(kv_empty0 + 8 * s);                         // the stage's keys and values have been read
-                tc_commit(p_empty0 + 8 * (i & 1));                    // and so has P; O holds tile i
+                tc_commit(p_empty0 + 8 * gb);                         // P has been read; O_g holds tile i
                 return true;
             };
-            for (int j = 0; j < tiles && ok; ++j) {
+            for (int j = 0; j <= tiles && ok; ++j) {
                 const int s = j % AT_STAGES;
-                ok = mbar_wait(kv_full0 + 8 * s, (j / AT_STAGES) & 1, 3) &&
-                     mbar_wait(s_empty0 + 8 * (j & 1), ((j >> 1) & 1) ^ 1, 4);
-                if (!ok) break;
-                tc_fence_after();
-                const uint32_t k_src = kv_s + s * 2 * AT_KV_BYTES, s_t = tmem + (j & 1) * AT_BN;
+                if (j < tiles) {
+                    ok = mbar_wait(kv_full0 + 8 * s, (j / AT_STAGES) & 1, 3);
+                    const uint32_t k_src = kv_s + s * 2 * AT_KV_BYTES;
+                    for (int g = 0; g < AT_GROUPS && ok; ++g) {
+                        if (j >= g_tiles[g]) continue;
+                        const int gb = g * 2 + (j & 1);
+                        ok = mbar_wait(s_empty0 + 8 * gb, ((j >> 1) & 1) ^ 1, 4);
+                        if (!ok) break;
+                        tc_fence_after();
+                        const uint32_t s_t = tmem + g * 256 + (j & 1) * AT_BN;
 #pragma unroll
-                for (int kk = 0; kk < AT_D / 16; ++kk) {              // d 0..63 in the first block, 64..127 in the second
-                    const uint32_t blk = kk >> 2, within = (kk & 3) * 2;
-                    tc_mma_f16(s_t, tc_smem_desc(q_s + blk * (AT_Q_BYTES / 2)) + within,
-                               tc_smem_desc(k_src + blk * (AT_KV_BYTES / 2)) + within, idesc_qk, kk != 0);
+                        for (int kk = 0; kk < AT_D / 16; ++kk) {      // d 0..63 in the first block, 64..127 in the second
+                            const uint32_t blk = kk >> 2, within = (kk & 3) * 2;
+                            tc_mma_f16(s_t, tc_smem_desc(q_s + g * AT_Q_BYTES + blk * (AT_Q_BYTES / 2)) + within,
+                                       tc_smem_desc(k_src + blk * (AT_KV_BYTES / 2)) + within, idesc_qk, kk != 0);
+                        }
+                        tc_commit(s_full0 + 8 * gb);
+                    }
                 }
-                tc_commit(s_full0 + 8 * (j & 1));
-                if (j >= 1) ok = issue_pv(j - 1);
+                if (j >= 1 && ok) {
+                    for (int g = 0; g < AT_GROUPS && ok; ++g)
+                        if (j - 1 < g_tiles[g]) {
+                            ok = issue_pv(g, j - 1);
+                            if (j == g_tiles[g]) tc_commit(o_full0 + 8 * g);   // the group's last tile: its output is complete
+                        }
+                    tc_commit(kv_empty0 + 8 * ((j - 1) % AT_STAGES)); // the stage's keys and values have been read
+                }
             }
-            if (ok && tiles > 0) ok = issue_pv(tiles - 1);
-            tc_commit(o_full);
+            for (int g = 0; g < AT_GROUPS; ++g)
+                if (g_tiles[g] == 0 || !ok) tc_commit(o_full0 + 8 * g);        // (nothing was issued for it, or the walk gave up)
         }
     } else if (b >= 0) {
-        const int q = warp & 3;                                       // this warp's quarter of the TMEM lanes = query rows
-        const int r = q * 32 + lane;                                  // this thread's query row within the tile
-        const int pos = p0 + r;                                       // and its position
-        const uint32_t lane_t = tmem + ((uint32_t)(q * 32) << 16);
+        const int g = (warp - 2) >> 2;                                // this warp's group of queries
+        const int q = warp & 3;                                       // and its quarter of the TMEM lanes = query rows
+        const int r = q * 32 + lane;                                  // this thread's query row within the group
+        const int pos = p0 + g * AT_BM + r;                           // and its position
+        const int hi = g_hi[g], qn = g_qn[g], my_tiles = g_tiles[g];
+        const uint32_t lane_t = tmem + g * 256 + ((uint32_t)(q * 32) << 16);
         const uint32_t o_t = lane_t + 2 * AT_BN;
         float m_used = -INFINITY, l = 0.f;                            // in log2 units; the maximum may lag by AT_RESCALE
         bool ok = true;
-        for (int j = 0; j < tiles && ok; ++j) {
-            const int buf = j & 1;
-            ok = mbar_wait(s_full0 + 8 * buf, (j >> 1) & 1, 6);
+        for (int j = 0; j < my_tiles && ok; ++j) {
+            const int gb = g * 2 + (j & 1);
+            ok = mbar_wait(s_full0 + 8 * gb, (j >> 1) & 1, 6);
             if (!ok) break;
             tc_fence_after();
             uint32_t sr[2][32];
-            tc_ld32(lane_t + buf * AT_BN, sr[0]);
-            tc_ld32(lane_t + buf * AT_BN + 32, sr[1]);
+            tc_ld32(lane_t + (j & 1) * AT_BN, sr[0]);
+            tc_ld32(lane_t + (j & 1) * AT_BN + 32, sr[1]);
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(s_empty0 + 8 * buf);           // S is in registers: the buffer may take tile j + 2
+            if (lane == 0) mbar_arrive(s_empty0 + 8 * gb);            // S is in registers: the buffer may take tile j + 2
             const int key0 = (tile_lo + j) * AT_BN;
-            const bool edge = key0 + AT_BN - 1 > p0 || window > 0 || key0 + AT_BN > hi;
+            const bool edge = key0 + AT_BN - 1 > p0 + g * AT_BM || window > 0 || key0 + AT_BN > hi;
             float mx = -INFINITY;
 #pragma unroll
             for (int c = 0; c < 2; ++c)
@@ -196,7 +223,7 @@ __global__ void __launch_bounds__(192, 1) prefill_tcgen05_kernel(
                 const float m_new = grow ? mt : m_used;
                 const float f = m_used == -INFINITY ? 0.f : at_ex2(m_used - m_new);
                 if (j > 0) {
-                    ok = mbar_wait(p_empty0 + 8 * ((j - 1) & 1), ((j - 1) >> 1) & 1, 7);   // O holds every tile before j
+                    ok = mbar_wait(p_empty0 + 8 * (g * 2 + ((j - 1) & 1)), ((j - 1) >> 1) & 1, 7);   // O holds every tile before j
                     tc_fence_after();
                     if (ok) {
 #pragma unroll
@@ -226,9 +253,9 @@ __global__ void __launch_bounds__(192, 1) prefill_tcgen05_kernel(
                     pk[c * 16 + i / 2] = *(uint32_t*)&pr;
                 }
             l += sum;
-            ok = ok && mbar_wait(p_empty0 + 8 * buf, ((j >> 1) & 1) ^ 1, 8);   // P's buffer was read by tile j - 2
+            ok = ok && mbar_wait(p_empty0 + 8 * gb, ((j >> 1) & 1) ^ 1, 8);   // P's buffer was read by tile j - 2
             if (!ok) break;
-            const uint32_t p_row = p_s + buf * AT_P_BYTES + r * 128;
+            const uint32_t p_row = p_s + gb * AT_P_BYTES + r * 128;
 #pragma unroll
             for (int c = 0; c < 8; ++c)                                // 8 keys = 16 bytes a chunk, swizzled by the row
                 asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};\n" ::"r"(p_row + ((c ^ (r & 7)) << 4)),
@@ -236,14 +263,14 @@ __global__ void __launch_bounds__(192, 1) prefill_tcgen05_kernel(
             fence_async_smem();
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(p_full0 + 8 * buf);
+            if (lane == 0) mbar_arrive(p_full0 + 8 * gb);
         }
-        if (ok) ok = mbar_wait(o_full, 0, 9);
+        if (ok) ok = mbar_wait(o_full0 + 8 * g, 0, 9);
         tc_fence_after();
-        if (ok) {                                                     // (the tensor-memory loads are warp-collective: no lane skips them)
+        if (ok && qn > 0) {                                           // (the tensor-memory loads are warp-collective: no lane skips them)
             const float inv = l > 0.f ? 1.f / l : 0.f;
-            const bool keep = r < qn && tiles > 0 && l > 0.f;
-            bf16* o_row = out + ((size_t)(t0 + (r < qn ? r : 0)) * heads + h) * AT_D;
+            const bool keep = r < qn && my_tiles > 0 && l > 0.f;
+            bf16* o_row = out + ((size_t)(t0 + g * AT_BM + (r < qn ? r : 0)) * heads + h) * AT_D;
 #pragma unroll
             for (int c = 0; c < AT_D / 32; ++c) {
                 uint32_t o[32];
@@ -292,7 +319,7 @@ extern "C" int hb_attention_tcgen05_status(unsigned int* status) {
     return 0;
 }
 
-// Rows row0 .. rows - 1 of the batch; q_tiles is the sum of ceil(queries / 128) over them; tokens the step's token count.
+// Rows row0 .. rows - 1 of the batch; q_tiles is the sum of ceil(queries / 256) over them; tokens the step's token count.
 extern "C" int hb_attention_prefill_tcgen05(void* out, const void* q, const void* kv, const int32_t* block_table,
                                             int table_stride, const int32_t* row_slot, const int32_t* query_start,
                                             const int32_t* kv_len, int row0, int rows, int q_tiles, int tokens, int heads,
@@ -312,7 +339,7 @@ extern "C" int hb_attention_prefill_tcgen05(void* out, const void* q, const void
     rc = encode_2d(&map_kv, kv, AT_D, kv_rows, AT_BN, "the cache");
     if (rc) return rc;
     HB_CUDA(cudaFuncSetAttribute(prefill_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, AT_SMEM));
-    prefill_tcgen05_kernel<<<dim3(q_tiles, heads), 192, AT_SMEM, (cudaStream_t)stream>>>(
+    prefill_tcgen05_kernel<<<dim3(q_tiles, heads), 320, AT_SMEM, (cudaStream_t)stream>>>(
         map_q, map_kv, (bf16*)out, block_table, table_stride, row_slot, query_start, kv_len, row0, rows, heads, kv_heads,
         pages, page_size, scale * 1.4426950408889634f, window);
     HB_LAUNCH_CHECK("attention_prefill_tcgen05");

@@ -42,10 +42,10 @@ class CudaKernels:
         self._fn = {}
         self.launches = 0
         self._splits: dict = {}
-        # Which kernel attends for rows of several tokens: "mma" (mma.sync, any head size up to 256, any page size) or
-        # "tcgen05" (csrc/attention_tcgen05.cu: head size 128 and pages of a multiple of 64 tokens; other shapes
-        # still take the mma.sync kernel).
-        self.prefill_attention = os.environ.get("HOLON_B200_PREFILL_ATTENTION", "mma")
+        # Which kernel attends for rows of several tokens: "tcgen05" (csrc/attention_tcgen05.cu, for head size 128 and
+        # pages of a multiple of 64 tokens; every other shape takes the mma.sync kernel) or "mma" (mma.sync always:
+        # any head size up to 256 in steps of 16, any page size).
+        self.prefill_attention = os.environ.get("HOLON_B200_PREFILL_ATTENTION", "tcgen05")
         if self.prefill_attention not in ("mma", "tcgen05"):
             raise KernelError(f"HOLON_B200_PREFILL_ATTENTION must be mma or tcgen05, not {self.prefill_attention!r}")
         # Which kernel multiplies bfloat16 matrices of more than SKINNY_ROWS rows: "cublas" (through torch, the
@@ -161,7 +161,7 @@ class CudaKernels:
             counts = [int(qs[b + 1]) - int(qs[b]) for b in range(rows.n_decode, rows.n_rows)]
             if self.prefill_attention == "tcgen05" and head_dim == 128 and kv.shape[3] % 64 == 0:
                 self._call("hb_attention_prefill_tcgen05", self._p(out), self._p(q), self._p(kv), *common,
-                           rows.n_decode, rows.n_rows, sum((n + 127) // 128 for n in counts), t, *sizes)
+                           rows.n_decode, rows.n_rows, sum((n + 255) // 256 for n in counts), t, *sizes)
             else:
                 self._call("hb_attention_prefill_bf16", self._p(out), self._p(q), self._p(kv), *common, rows.n_decode,
                            rows.n_rows, sum((n + 63) // 64 for n in counts), *sizes)
