@@ -197,26 +197,29 @@ __global__ void __launch_bounds__(320, 1) prefill_tcgen05_kernel(
             if (!ok) break;
             tc_fence_after();
             uint32_t sr[2][32];
-            tc_ld32(lane_t + (j & 1) * AT_BN, sr[0]);
-            tc_ld32(lane_t + (j & 1) * AT_BN + 32, sr[1]);
+            tc_ld32_nowait(lane_t + (j & 1) * AT_BN, sr[0]);
+            tc_ld32_nowait(lane_t + (j & 1) * AT_BN + 32, sr[1]);
+            tc_ld_wait();
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(s_empty0 + 8 * gb);            // S is in registers: the buffer may take tile j + 2
             const int key0 = (tile_lo + j) * AT_BN;
             const bool edge = key0 + AT_BN - 1 > p0 + g * AT_BM || window > 0 || key0 + AT_BN > hi;
-            float mx = -INFINITY;
+            if (edge) {
+#pragma unroll
+                for (int c = 0; c < 2; ++c)
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) {
+                        const int key = key0 + c * 32 + i;
+                        if (!(key <= pos && key < hi && (window <= 0 || pos - key < window))) sr[c][i] = 0xff800000u;   // -inf
+                    }
+            }
+            float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};   // four chains instead of one of 64
 #pragma unroll
             for (int c = 0; c < 2; ++c)
 #pragma unroll
-                for (int i = 0; i < 32; ++i) {
-                    float v = __uint_as_float(sr[c][i]);
-                    if (edge) {
-                        const int key = key0 + c * 32 + i;
-                        if (!(key <= pos && key < hi && (window <= 0 || pos - key < window))) v = -INFINITY;
-                    }
-                    sr[c][i] = __float_as_uint(v);
-                    mx = fmaxf(mx, v);
-                }
+                for (int i = 0; i < 32; ++i) mx4[i & 3] = fmaxf(mx4[i & 3], __uint_as_float(sr[c][i]));
+            const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
             const float mt = mx * scale_log2;
             const bool grow = mt > m_used + AT_RESCALE || (m_used == -INFINITY && mt > -INFINITY);
             if (__any_sync(0xffffffffu, grow)) {                      // rescale what is summed (whole warp: the TMEM ops are collective)
@@ -240,7 +243,7 @@ __global__ void __launch_bounds__(320, 1) prefill_tcgen05_kernel(
                 m_used = m_new;
             }
             const float off = m_used == -INFINITY ? 0.f : -m_used;
-            float sum = 0.f;
+            float sum4[4] = {0.f, 0.f, 0.f, 0.f};
             uint32_t pk[32];                                          // 64 weights as bfloat16 pairs
 #pragma unroll
             for (int c = 0; c < 2; ++c)
@@ -248,11 +251,11 @@ __global__ void __launch_bounds__(320, 1) prefill_tcgen05_kernel(
                 for (int i = 0; i < 32; i += 2) {
                     const float a = at_ex2(fmaf(__uint_as_float(sr[c][i]), scale_log2, off));
                     const float d = at_ex2(fmaf(__uint_as_float(sr[c][i + 1]), scale_log2, off));
-                    sum += a + d;
+                    sum4[(i >> 1) & 3] += a + d;
                     __nv_bfloat162 pr = __floats2bfloat162_rn(a, d);
                     pk[c * 16 + i / 2] = *(uint32_t*)&pr;
                 }
-            l += sum;
+            l += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
             ok = ok && mbar_wait(p_empty0 + 8 * gb, ((j >> 1) & 1) ^ 1, 8);   // P's buffer was read by tile j - 2
             if (!ok) break;
             const uint32_t p_row = p_s + gb * AT_P_BYTES + r * 128;
