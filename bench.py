@@ -61,14 +61,19 @@ class Clocks:
              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
     def __init__(self) -> None:
-        self.proc = None
+        self.proc, self.marked = None, 0.0
 
     def start(self) -> None:
         try:
-            self.proc = subprocess.Popen(["nvidia-smi", "-i", "0", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
-                                          "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", "0", f"--query-gpu=timestamp,{self.QUERY}",
+                                          "--format=csv,noheader,nounits", "-lms", "50"], stdout=subprocess.PIPE,
+                                         stderr=subprocess.DEVNULL, text=True)
         except OSError:
             self.proc = None
+
+    def mark(self) -> None:
+        """Samples taken before this moment (the warm-up) are left out."""
+        self.marked = time.time()
 
     def stop(self) -> dict:
         if self.proc is None:
@@ -79,7 +84,14 @@ class Clocks:
         names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
         for line in out.splitlines():
             cells = [c.strip() for c in line.split(",")]
-            if len(cells) < 6 or not cells[0].isdigit():
+            if len(cells) < 7:
+                continue
+            try:
+                stamp = time.mktime(time.strptime(cells[0].split(".")[0], "%Y/%m/%d %H:%M:%S"))
+            except ValueError:
+                stamp = self.marked
+            cells = cells[1:]
+            if not cells[0].isdigit() or stamp + 1 < self.marked:
                 continue
             sm.append(int(cells[0]))
             top.append(int(cells[1]))
@@ -117,13 +129,14 @@ def decode_run(engine, batch: int, context: int, steps: int, warmup: int, seed: 
     while engine.scheduler.waiting:                                  # prefill, in portions under the token budget
         engine.step()
     assert len(engine.scheduler.running) == batch
+    if clocks:
+        clocks.start()                                              # (nvidia-smi needs a moment before its first sample)
     for _ in range(warmup):
         engine.step()
-    kernels = engine.built.ctx.kernels
     torch.cuda.synchronize()
-    h2d0, d2h0, launches0 = engine.h2d_bytes, engine.d2h_bytes, engine.launches()
     if clocks:
-        clocks.start()
+        clocks.mark()
+    h2d0, d2h0, launches0 = engine.h2d_bytes, engine.d2h_bytes, engine.launches()
     start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     t0 = time.perf_counter()
     start.record()
@@ -233,7 +246,7 @@ def run_reference(args) -> dict:
 def main() -> int:
     ap = argparse.ArgumentParser(description=__doc__.split("\n\n")[0])
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=64)
+    ap.add_argument("--steps", type=int, default=128)
     ap.add_argument("--warmup", type=int, default=4)
     ap.add_argument("--impl", default="ours", choices=("ours", "reference"))
     ap.add_argument("--layers", type=int, default=FULL_LAYERS, help="fewer layers than the model has (both are reported)")

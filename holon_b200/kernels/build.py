@@ -115,6 +115,12 @@ def _compile(nvcc: str, folder: pathlib.Path, name: str, verbose: bool) -> pathl
     if link.returncode:
         raise BuildError(f"linking {name} failed:\n{link.stdout}{link.stderr}")
     os.replace(tmp, folder / name)                      # another process may have built it meanwhile: same bytes
+    for old in folder.glob("libholon_b200_*.so"):       # libraries of earlier sources are never loaded again
+        if old.name != name:
+            try:
+                old.unlink()
+            except OSError:
+                pass
     shutil.rmtree(work, ignore_errors=True)
     _say(verbose, f"built {name} in {time.time() - began:.0f} s")
     return folder / name
