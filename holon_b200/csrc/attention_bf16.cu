@@ -367,7 +367,7 @@ extern "C" int hb_attention_decode_bf16(void* out, float* scratch, const void* q
 #define HB_ARGS (bf16*)out, part_o, part_ml, (const bf16*)q, (const bf16*)kv, block_table, table_stride, row_slot, \
     query_start, kv_len, rows, heads, kv_heads, head_dim, pages, page_size, scale, window, splits, s
     if (head_dim <= 64) return launch_decode<64, 4>(HB_ARGS);
-    if (head_dim <= 128) return launch_decode<128, 3>(HB_ARGS);
+    if (head_dim <= 128) return launch_decode<128, 2>(HB_ARGS);   // two stages: three CTAs fit an SM, which hides latency better than a third stage
     return launch_decode<256, 2>(HB_ARGS);
 #undef HB_ARGS
 }

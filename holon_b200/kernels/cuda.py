@@ -169,14 +169,14 @@ class CudaKernels:
     SMS = 148
 
     def decode_splits(self, rows: int, heads: int, kv_heads: int, max_kv: int) -> int:
-        """Parts the keys of a decode row are cut into. Two CTAs fit an SM; a launch of `ctas * parts` CTAs runs in
-        waves of 2 x SMs, each CTA walking its share of the longest row's 64-key tiles plus a fixed start-up of
+        """Parts the keys of a decode row are cut into. Three CTAs fit an SM; a launch of `ctas * parts` CTAs runs in
+        waves of 3 x SMs, each CTA walking its share of the longest row's 64-key tiles plus a fixed start-up of
         about one tile. The number of parts (1 to 64) with the least waves x (tiles + 1) wins. It is a function of
         the batch's size and the longest length only, as the reference plans its splits
         (plugins/holon_plugins/kernels/triton_attn/plugin.py:40-96)."""
         key = (rows, heads, kv_heads, -(-max_kv // 64))
         if key not in self._splits:
-            ctas, tiles, slots = rows * kv_heads * (-(-(heads // kv_heads) // 16)), key[3], 2 * self.SMS
+            ctas, tiles, slots = rows * kv_heads * (-(-(heads // kv_heads) // 16)), key[3], 3 * self.SMS
             cost = lambda s: -(-ctas * s // slots) * (-(-tiles // s) + 1)          # noqa: E731
             self._splits[key] = min(range(1, max(1, min(64, tiles)) + 1), key=lambda s: (cost(s), s))
         return self._splits[key]
