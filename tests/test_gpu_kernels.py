@@ -211,7 +211,10 @@ def on_device(rows):
                 rows.n_decode, rows.max_q, rows.max_kv, rows.query_start.numpy(), rows.kv_len.numpy())
 
 
-GEOMETRIES = [(32, 8, 128, 64), (16, 4, 256, 16), (6, 1, 48, 4), (8, 2, 64, 16), (4, 4, 16, 7), (14, 2, 112, 32)]
+# (heads, kv heads, head size, page): production's, the widest tensor-core head, odd groups and pages, a group of 20
+# (two 16-row tiles in the decode kernel), and a head of 320 that bfloat16 hands to the CUDA-core kernel
+GEOMETRIES = [(32, 8, 128, 64), (16, 4, 256, 16), (6, 1, 48, 4), (8, 2, 64, 16), (4, 4, 16, 7), (14, 2, 112, 32),
+              (40, 2, 64, 16), (2, 1, 320, 8)]
 PREFILL_ROWS = [(0, 1), (0, 17), (5, 16), (31, 33), (0, 64), (100, 7), (16, 16), (63, 2), (0, 130)]
 DECODE_ROWS = [(0, 1), (15, 1), (16, 1), (99, 1), (999, 1), (2500, 1), (63, 1), (64, 1)]
 

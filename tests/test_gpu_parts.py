@@ -171,7 +171,9 @@ def toy_recipe(c):
     ffn = PartRef.of("ffn", "swiglu", inter=c["inter"])
     block = PartRef.of("block", "prenorm")
     layers = (LayerSpec(block, attention, ffn, norm), LayerSpec(block, PartRef.of("mixer", "running_mean"), ffn, norm))
-    return ModelSpec(hidden=c["hidden"], vocab=c["vocab"], layers=layers, order=(Run(0, 0), Run(1, 1), Run(0, 2)),
+    # layer 0 runs three times: filling entry 0, filling entry 2, and once more reading entry 0 without writing it
+    order = (Run(0, 0), Run(1, 1), Run(0, 2), Run(0, 0, fills=False))
+    return ModelSpec(hidden=c["hidden"], vocab=c["vocab"], layers=layers, order=order,
                      embed=PartRef.of("embed", "table"), norm=norm, head=PartRef.of("head", "linear", tied=True),
                      weight_rules=(WeightRule("{rest}", "{rest}"),))
 
@@ -183,7 +185,7 @@ def test_toy_mixer_with_state_is_registered_built_and_stepped():
         config = {"architectures": ["ToyMeanForCausalLM"], "hidden": 64, "vocab": 97, "inter": 80}
         b = build(RandomSource(config, seed=3, dtype=torch.float32), dtype="float32", device=DEV, page_size=8,
                   max_seqs=3, max_model_len=64, max_step_tokens=64, pages=12)
-        assert [e.decl is None for e in b.model.entries] == [False, True, False]        # layer 0 runs twice, two entries
+        assert [e.decl is None for e in b.model.entries] == [False, True, False]        # layer 0 fills two entries
         assert set(b.cache.slot_states) == {(1, "sum"), (1, "count")}
         ids = [5, 96, 33, 0, 17, 42, 8, 8, 61, 2, 77]
         other = [9, 1, 4]
