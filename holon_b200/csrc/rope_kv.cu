@@ -113,12 +113,126 @@ __global__ void qk_norm_rope_kv_write_kernel(T* __restrict__ q_out, const T* __r
     }
 }
 
+// The production shape, bfloat16 with head_dim = rotary_dim = 128: eight lanes share one (token, head), each holding
+// 8 values of the head's first half and the 8 it pairs with in the second half, so every access is 16 bytes wide,
+// the norm's sum takes three shuffles and nothing goes through shared memory.
+__device__ __forceinline__ void unpack8(const uint4& v, float (&f)[8]) {
+    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const float2 p = __bfloat1622float2(*(const __nv_bfloat162*)&w[i]);
+        f[2 * i] = p.x; f[2 * i + 1] = p.y;
+    }
+}
+__device__ __forceinline__ uint4 pack8(const float (&f)[8]) {
+    uint32_t w[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        __nv_bfloat162 p = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
+        w[i] = *(uint32_t*)&p;
+    }
+    return make_uint4(w[0], w[1], w[2], w[3]);
+}
+template <typename TW> __device__ __forceinline__ void load_w8(const TW* w, float (&f)[8]);
+template <> __device__ __forceinline__ void load_w8<bf16>(const bf16* w, float (&f)[8]) { unpack8(*(const uint4*)w, f); }
+template <> __device__ __forceinline__ void load_w8<float>(const float* w, float (&f)[8]) {
+    const float4 a = *(const float4*)w, b = *(const float4*)(w + 4);
+    f[0] = a.x; f[1] = a.y; f[2] = a.z; f[3] = a.w; f[4] = b.x; f[5] = b.y; f[6] = b.z; f[7] = b.w;
+}
+
+template <typename TW>
+__global__ void __launch_bounds__(256) qk_norm_rope_kv_write_d128_kernel(
+        bf16* __restrict__ q_out, const bf16* __restrict__ qkv, const int32_t* __restrict__ positions,
+        const float* __restrict__ table, int max_positions, const TW* __restrict__ q_weight,
+        const TW* __restrict__ k_weight, float eps, float offset, bf16* __restrict__ kv,
+        const int32_t* __restrict__ write_index, int pages, int page_size, int tokens, int heads, int kv_heads) {
+    constexpr int D = 128, HALF = 64;
+    const int items = heads + (kv ? 2 * kv_heads : 0);
+    const long unit = (long)blockIdx.x * 32 + (threadIdx.x >> 3);   // one (token, head) per eight lanes
+    const int sub = threadIdx.x & 7;
+    const bool live = unit < (long)tokens * items;
+    const int t = live ? (int)(unit / items) : 0, item = live ? (int)(unit % items) : 0;
+    const bf16* src = qkv + (size_t)t * (heads + 2 * kv_heads) * D + (size_t)item * D;
+    bf16* dst = nullptr;
+    const TW* weight = nullptr;
+    bool rotate = false;
+    if (live) {
+        if (item < heads) {
+            dst = q_out + ((size_t)t * heads + item) * D;
+            weight = q_weight;
+            rotate = true;
+        } else {
+            const int w = write_index[t];
+            const int page = w >= 0 ? w / page_size : -1, off = w >= 0 ? w % page_size : 0;
+            if (page >= 0 && page < pages) {
+                const int is_v = item >= heads + kv_heads;
+                const int head = item - heads - (is_v ? kv_heads : 0);
+                dst = kv + ((((size_t)page * 2 + is_v) * kv_heads + head) * page_size + off) * D;
+                weight = is_v ? nullptr : k_weight;
+                rotate = !is_v;
+            }
+        }
+    }
+    uint4 ra = make_uint4(0, 0, 0, 0), rb = ra;
+    if (dst) { ra = *(const uint4*)(src + sub * 8); rb = *(const uint4*)(src + HALF + sub * 8); }
+    if (dst && !rotate) {                             // values: copied as they are
+        *(uint4*)(dst + sub * 8) = ra;
+        *(uint4*)(dst + HALF + sub * 8) = rb;
+    }
+    float a[8], b[8];
+    unpack8(ra, a);
+    unpack8(rb, b);
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) ss += a[i] * a[i] + b[i] * b[i];
+    ss += __shfl_xor_sync(0xffffffffu, ss, 1);        // (every lane takes part: a group without work adds zeros)
+    ss += __shfl_xor_sync(0xffffffffu, ss, 2);
+    ss += __shfl_xor_sync(0xffffffffu, ss, 4);
+    if (!dst || !rotate) return;
+    if (weight) {
+        const float rstd = rsqrtf(ss / (float)D + eps);
+        float wa[8], wb[8];
+        load_w8<TW>(weight + sub * 8, wa);
+        load_w8<TW>(weight + HALF + sub * 8, wb);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            a[i] = rounded<bf16>(a[i] * rstd * (wa[i] + offset));
+            b[i] = rounded<bf16>(b[i] * rstd * (wb[i] + offset));
+        }
+    }
+    int pos = positions[t];
+    pos = pos < 0 ? 0 : (pos >= max_positions ? max_positions - 1 : pos);
+    const float* cs = table + (size_t)pos * D;
+    float c[8], sn[8];
+    load_w8<float>(cs + sub * 8, c);
+    load_w8<float>(cs + HALF + sub * 8, sn);
+    float oa[8], ob[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        oa[i] = a[i] * c[i] - b[i] * sn[i];
+        ob[i] = b[i] * c[i] + a[i] * sn[i];
+    }
+    *(uint4*)(dst + sub * 8) = pack8(oa);
+    *(uint4*)(dst + HALF + sub * 8) = pack8(ob);
+}
+
 template <typename T, typename TW>
 static int launch(void* q_out, const void* qkv, const int32_t* positions, const float* table, int rotary_dim,
                   int max_positions, const void* qw, const void* kw, float eps, float offset, void* kv,
                   const int32_t* write_index, int pages, int page_size, int tokens, int heads, int kv_heads,
                   int head_dim, cudaStream_t s) {
     const int items = heads + (kv ? 2 * kv_heads : 0);
+    if constexpr (sizeof(T) == 2) {
+        const bool aligned = (((uintptr_t)q_out | (uintptr_t)qkv | (uintptr_t)table | (uintptr_t)qw | (uintptr_t)kw | (uintptr_t)kv) % 16) == 0;
+        if (head_dim == 128 && rotary_dim == 128 && aligned && (long)tokens * items < (1l << 31)) {
+            const unsigned blocks = (unsigned)(((long)tokens * items + 31) / 32);
+            qk_norm_rope_kv_write_d128_kernel<TW><<<blocks, 256, 0, s>>>(
+                (bf16*)q_out, (const bf16*)qkv, positions, table, max_positions, (const TW*)qw, (const TW*)kw, eps, offset,
+                (bf16*)kv, write_index, pages, page_size, tokens, heads, kv_heads);
+            HB_LAUNCH_CHECK("qk_norm_rope_kv_write");
+            return 0;
+        }
+    }
     // Few tokens (decode): many small blocks, one head per warp. Many tokens: one block per token whose 8 warps walk
     // the heads, so that the launch is not made of tens of thousands of tiny blocks.
     const int warps = tokens >= 256 ? 8 : 4;
