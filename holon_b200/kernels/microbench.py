@@ -1,0 +1,100 @@
+"""Times single kernels of the kernel table with CUDA events, the L2 flushed between runs.
+
+    python -m holon_b200.kernels.microbench decode_attention [--rows 8 64 1] [--context 8192] [--splits 4 6 13]
+    python -m holon_b200.kernels.microbench gemm [--rows 2048] [--shapes qkv o gate_up down]
+
+Sizes default to Qwen3-8B's (32 query and 8 KV heads of 128, hidden 4096, intermediate 12288). The numbers under
+`profiles/` that are not ncu captures come from here.
+"""
+from __future__ import annotations
+
+import argparse
+import math
+
+import torch
+
+from . import load_kernels
+from ..engine.batch import Rows
+
+SHAPES = {"qkv": (6144, 4096), "o": (4096, 4096), "gate_up": (24576, 4096), "down": (4096, 12288)}
+
+
+def timed(fn, flush, runs: int = 6) -> float:
+    """Microseconds of the fastest of `runs` calls, each after the L2 was overwritten."""
+    best = float("inf")
+    for i in range(runs):
+        if flush is not None:
+            flush.zero_()
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        fn()
+        end.record()
+        torch.cuda.synchronize()
+        if i:
+            best = min(best, start.elapsed_time(end) * 1e3)
+    return best
+
+
+def decode_attention(k, args) -> None:
+    heads, kv_heads, d, page = 32, 8, 128, 64
+    flush = torch.empty(256 << 20, device=k.device, dtype=torch.uint8)
+    for rows in args.rows:
+        per = args.context // page
+        kv = torch.randn(rows * per + 1, 2, kv_heads, page, d, device=k.device, dtype=torch.bfloat16)
+        table = torch.arange(rows * per, device=k.device, dtype=torch.int32).view(rows, per).contiguous()
+        q = torch.randn(rows, heads, d, device=k.device, dtype=torch.bfloat16)
+        out = torch.empty_like(q)
+        ar = torch.arange(rows + 1, device=k.device, dtype=torch.int32)
+        batch = Rows(ar[:rows].contiguous(), ar, torch.full((rows,), args.context, device=k.device, dtype=torch.int32),
+                     rows, rows, rows, 1, args.context)
+        moved = rows * args.context * kv_heads * d * 2 * 2
+        planned = k.decode_splits(rows, heads, kv_heads, args.context)
+        for splits in (args.splits or [planned]):
+            k._splits[(rows, heads, kv_heads, -(-args.context // 64))] = splits
+            t = timed(lambda: k.paged_attention(out, q, kv, table, batch, 1 / math.sqrt(d), 0), flush)
+            print(f"decode attention rows {rows} context {args.context} splits {splits}: {t:7.1f} us  {moved / t / 1e6:5.2f} TB/s"
+                  + ("  (the planner's choice)" if splits == planned else ""))
+        k._splits.clear()
+
+
+def gemm(k, args) -> None:
+    m = args.rows[0]
+    for name in args.shapes:
+        n, kk = SHAPES[name]
+        x = torch.randn(m, kk, device=k.device, dtype=torch.bfloat16)
+        w = torch.randn(n, kk, device=k.device, dtype=torch.bfloat16) * 0.02
+        out = torch.empty(m, n, device=k.device, dtype=torch.bfloat16)
+        flops = 2 * m * n * kk
+        t_lib = timed(lambda: torch.mm(x, w.t(), out=out), None, 20)
+        t_own = timed(lambda: k.linear_tcgen05(out, x, w), None, 20)
+        line = f"{name:8s} rows {m}: cuBLAS {t_lib:7.1f} us ({flops / t_lib / 1e6:5.0f} TFLOP/s)  tcgen05 {t_own:7.1f} us ({flops / t_own / 1e6:5.0f} TFLOP/s)"
+        if name == "gate_up":
+            act = torch.empty(m, n // 2, device=k.device, dtype=torch.bfloat16)
+            t_fused = timed(lambda: k.linear_tcgen05(act, x, w, swiglu=True), None, 20)
+            t_act = timed(lambda: k.silu_mul(act, out), None, 20)
+            line += f"  tcgen05 with SwiGLU {t_fused:7.1f} us; activation kernel alone {t_act:5.1f} us"
+        print(line)
+    print("tcgen05 status", k.tcgen05_status())
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser(description=__doc__.split("\n\n")[0])
+    ap.add_argument("what", choices=("decode_attention", "gemm"))
+    ap.add_argument("--rows", type=int, nargs="*", default=None)
+    ap.add_argument("--context", type=int, default=8192)
+    ap.add_argument("--splits", type=int, nargs="*", default=None)
+    ap.add_argument("--shapes", nargs="*", default=list(SHAPES), choices=list(SHAPES))
+    ap.add_argument("--device", default="cuda:0")
+    args = ap.parse_args()
+    k = load_kernels(args.device)
+    with torch.inference_mode():
+        if args.what == "decode_attention":
+            args.rows = args.rows or [8, 64, 1]
+            decode_attention(k, args)
+        else:
+            args.rows = args.rows or [2048]
+            gemm(k, args)
+
+
+if __name__ == "__main__":
+    main()
