@@ -4,9 +4,9 @@
 //   S = Q K^T    tcgen05.mma 128 x 64 x 16, eight per tile, Q and K in shared memory (TMA, 128-byte swizzle), S in one
 //                of two 64-column tensor-memory buffers;
 //   softmax      four warps, one query row per thread: tcgen05.ld of the row, mask, running maximum, 2^x, row sum, all
-//                without a shuffle; the weights P go to shared memory as bfloat16 in the K-major swizzled layout;
-//   O += P V     tcgen05.mma 128 x 128 x 16, four per tile, V read as an MN-major operand (values are stored
-//                [key][d]), O in 128 tensor-memory columns for the whole walk.
+//                without a shuffle; the weights P go back to tensor memory as bfloat16 pairs, over the S they came from;
+//   O += P V     tcgen05.mma 128 x 128 x 16, four per tile, P read from tensor memory, V from shared memory as an
+//                MN-major operand (values are stored [key][d]), O in 128 tensor-memory columns for the whole walk.
 // The running maximum is allowed to lag: O and the row sums are rescaled only when a row's maximum has grown by more
 // than 2^8 since the last rescale (the weights stay below 256, which bfloat16 holds), so the tensor-memory round trip
 // of O is rare. One thread issues all MMAs and keeps S of tile j + 1 in flight while the softmax of tile j runs.
@@ -24,7 +24,7 @@
 #define AT_Q_BYTES (AT_BM * AT_D * 2)             // 32 KB a group: two [128 x 64] swizzled blocks
 #define AT_KV_BYTES (AT_BN * AT_D * 2)            // 16 KB: two [64 x 64] swizzled blocks
 #define AT_P_BYTES (AT_BM * AT_BN * 2)            // 16 KB: one [128 x 64] swizzled block
-#define AT_SMEM (AT_GROUPS * AT_Q_BYTES + AT_STAGES * 2 * AT_KV_BYTES + AT_GROUPS * 2 * AT_P_BYTES + 1024 + 256)
+#define AT_SMEM (AT_GROUPS * AT_Q_BYTES + AT_STAGES * 2 * AT_KV_BYTES + 1024 + 256)
 #define AT_TMEM_COLS 512                          // per group: S0 [0, 64), S1 [64, 128), O [128, 256)
 #define AT_RESCALE 8.0f
 
@@ -39,6 +39,13 @@ __device__ __forceinline__ void tc_mma_f16(uint32_t tmem_d, uint64_t desc_a, uin
                  ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate) : "memory");
 }
 
+// The same with the A operand in tensor memory (128 lanes x K/2 columns, two bfloat16 per column).
+__device__ __forceinline__ void tc_mma_f16_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                 "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}\n"
+                 ::"r"(tmem_d), "r"(tmem_a), "l"(desc_b), "r"(idesc), "r"(accumulate) : "memory");
+}
+
 // Two groups of 128 queries share the CTA's key and value tiles; each has its own softmax warps (2-5 and 6-9), its own
 // S, P and O, so that one group's softmax runs while the tensor cores work for the other.
 __global__ void __launch_bounds__(320, 1) prefill_tcgen05_kernel(
@@ -48,8 +55,8 @@ __global__ void __launch_bounds__(320, 1) prefill_tcgen05_kernel(
         int kv_heads, int pages, int page_size, float scale_log2, int window) {
     extern __shared__ unsigned char smem_raw[];
     const uint32_t base = (smem_addr(smem_raw) + 1023u) & ~1023u;
-    const uint32_t q_s = base, kv_s = q_s + AT_GROUPS * AT_Q_BYTES, p_s = kv_s + AT_STAGES * 2 * AT_KV_BYTES;
-    const uint32_t bars = p_s + AT_GROUPS * 2 * AT_P_BYTES;
+    const uint32_t q_s = base, kv_s = q_s + AT_GROUPS * AT_Q_BYTES;
+    const uint32_t bars = kv_s + AT_STAGES * 2 * AT_KV_BYTES;
     const uint32_t q_full = bars, kv_full0 = bars + 8, kv_empty0 = kv_full0 + 8 * AT_STAGES;
     // per group g and buffer i, at index (g * 2 + i): scores computed / read out, weights written / read by the MMA
     const uint32_t s_full0 = kv_empty0 + 8 * AT_STAGES, s_empty0 = s_full0 + 32, p_full0 = s_empty0 + 32;
@@ -139,12 +146,13 @@ __global__ void __launch_bounds__(320, 1) prefill_tcgen05_kernel(
                 const int gb = g * 2 + (i & 1);
                 if (!mbar_wait(p_full0 + 8 * gb, (i >> 1) & 1, 5)) return false;
                 tc_fence_after();
-                const uint32_t v_src = kv_s + (i % AT_STAGES) * 2 * AT_KV_BYTES + AT_KV_BYTES, p_src = p_s + gb * AT_P_BYTES;
+                const uint32_t v_src = kv_s + (i % AT_STAGES) * 2 * AT_KV_BYTES + AT_KV_BYTES;
                 const uint32_t o_t = tmem + g * 256 + 2 * AT_BN;
+                const uint32_t p_t = tmem + g * 256 + (i & 1) * AT_BN;   // P lies over the first half of its own S
 #pragma unroll
-                for (int kk = 0; kk < AT_BN / 16; ++kk)               // 16 keys a step: 32 bytes along P's rows, 16 rows down V
-                    tc_mma_f16(o_t, tc_smem_desc(p_src) + (uint64_t)(kk * 2),
-                               tc_smem_desc_mn(v_src + kk * 16 * 128, AT_KV_BYTES / 2), idesc_pv, (i | kk) != 0);
+                for (int kk = 0; kk < AT_BN / 16; ++kk)               // 16 keys a step: 8 columns along P, 16 rows down V
+                    tc_mma_f16_ts(o_t, p_t + kk * 8, tc_smem_desc_mn(v_src + kk * 16 * 128, AT_KV_BYTES / 2), idesc_pv,
+                                  (i | kk) != 0);
                 tc_commit(p_empty0 + 8 * gb);                         // P has been read; O_g holds tile i
                 return true;
             };
@@ -155,11 +163,8 @@ __global__ void __launch_bounds__(320, 1) prefill_tcgen05_kernel(
                     const uint32_t k_src = kv_s + s * 2 * AT_KV_BYTES;
                     for (int g = 0; g < AT_GROUPS && ok; ++g) {
                         if (j >= g_tiles[g]) continue;
-                        const int gb = g * 2 + (j & 1);
-                        ok = mbar_wait(s_empty0 + 8 * gb, ((j >> 1) & 1) ^ 1, 4);
-                        if (!ok) break;
-                        tc_fence_after();
-                        const uint32_t s_t = tmem + g * 256 + (j & 1) * AT_BN;
+                        const int gb = g * 2 + (j & 1);                // (S_j may overwrite S and P of tile j - 2: the MMAs that
+                        const uint32_t s_t = tmem + g * 256 + (j & 1) * AT_BN;   // read them were issued before, and run in order)
 #pragma unroll
                         for (int kk = 0; kk < AT_D / 16; ++kk) {      // d 0..63 in the first block, 64..127 in the second
                             const uint32_t blk = kk >> 2, within = (kk & 3) * 2;
@@ -200,9 +205,6 @@ __global__ void __launch_bounds__(320, 1) prefill_tcgen05_kernel(
             tc_ld32_nowait(lane_t + (j & 1) * AT_BN, sr[0]);
             tc_ld32_nowait(lane_t + (j & 1) * AT_BN + 32, sr[1]);
             tc_ld_wait();
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(s_empty0 + 8 * gb);            // S is in registers: the buffer may take tile j + 2
             const int key0 = (tile_lo + j) * AT_BN;
             const bool edge = key0 + AT_BN - 1 > p0 + g * AT_BM || window > 0 || key0 + AT_BN > hi;
             if (edge) {
@@ -256,14 +258,8 @@ __global__ void __launch_bounds__(320, 1) prefill_tcgen05_kernel(
                     pk[c * 16 + i / 2] = *(uint32_t*)&pr;
                 }
             l += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
-            ok = ok && mbar_wait(p_empty0 + 8 * gb, ((j >> 1) & 1) ^ 1, 8);   // P's buffer was read by tile j - 2
             if (!ok) break;
-            const uint32_t p_row = p_s + gb * AT_P_BYTES + r * 128;
-#pragma unroll
-            for (int c = 0; c < 8; ++c)                                // 8 keys = 16 bytes a chunk, swizzled by the row
-                asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};\n" ::"r"(p_row + ((c ^ (r & 7)) << 4)),
-                             "r"(pk[c * 4]), "r"(pk[c * 4 + 1]), "r"(pk[c * 4 + 2]), "r"(pk[c * 4 + 3]) : "memory");
-            fence_async_smem();
+            tc_st32(lane_t + (j & 1) * AT_BN, pk);                    // P over the S it came from: 32 columns of bfloat16 pairs
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(p_full0 + 8 * gb);
