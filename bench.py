@@ -154,6 +154,7 @@ def decode_run(engine, batch: int, context: int, steps: int, warmup: int, seed: 
            "launches": engine.launches() - launches0, "mean_context": context - (steps + 1) / 2, "clocks": clock}
     for rid in list(engine.requests):
         engine.abort(rid)
+    engine.drain()
     return out
 
 
@@ -168,7 +169,7 @@ def prefill_run(engine, tokens: int, repeats: int, seed: int) -> float:
         torch.cuda.synchronize()
         start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         start.record()
-        deltas = engine.step()
+        deltas = engine.step() + engine.drain()                      # the step, and its token read back
         end.record()
         torch.cuda.synchronize()
         assert len(deltas) == 1 and deltas[0].finish_reason == "length"
@@ -218,7 +219,8 @@ def run_ours(args) -> dict:
                    "kv_heads": cfg["num_key_value_heads"], "head_dim": cfg["head_dim"],
                    "intermediate": cfg["intermediate_size"], "vocab": cfg["vocab_size"], "global_batch": batch,
                    "seq_len": context, "page_size": 64, "parallelism": "single GPU", "l2": "inputs larger than L2",
-                   "cuda_graphs": True, "peaks": peak_kind, "gemm": engine.built.ctx.kernels.gemm},
+                   "cuda_graphs": True, "overlap": engine.config.overlap, "peaks": peak_kind,
+                   "gemm": engine.built.ctx.kernels.gemm},
         "e2e": {"value": round(main["tokens"] / main["wall_ms"] * 1e3, 1), "unit": "tok/s",
                 "h2d_bytes_per_step": main["h2d_bytes_per_step"], "d2h_bytes_per_step": main["d2h_bytes_per_step"]},
         "gpu_launches": main["launches"],

@@ -24,6 +24,7 @@ class EngineConfig:
     chunk_with_decode: int = _setting(0, "prefill tokens a step with decode rows may also carry (0: none)")
     memory_fraction: float = _setting(0.9, "of the memory left after the weights, for the cache and activations")
     state_memory: int | None = _setting(None, "bytes for the cache pools; default: from memory_fraction")
+    overlap: bool = _setting(True, "schedule step N while step N-1 runs (depth 1); off: depth 0")
     cuda_graphs: bool = _setting(True, "replay decode steps from CUDA graphs, per batch-size bucket")
     seed: int | None = _setting(None, "base seed for requests that bring none; default: drawn at start")
 

@@ -94,6 +94,12 @@ int hb_gemm_bf16_tcgen05(void* out, int out_f32, const void* x, const void* w, i
                          hb_stream stream);
 int hb_gemm_tcgen05_status(unsigned int* status);
 
+// The token each request sampled last, kept on the device by slot. feed: for every row r with from_last[r] != 0,
+// token_ids[query_start[r]] = last_tokens[row_slot[r]]. store: last_tokens[slots[i]] = tokens[i] for i < n.
+int hb_feed_tokens(int32_t* token_ids, const int32_t* last_tokens, const int32_t* row_slot, const int32_t* query_start,
+                   const int32_t* from_last, int rows, hb_stream stream);
+int hb_store_tokens(int32_t* last_tokens, const int32_t* slots, const int32_t* tokens, int n, hb_stream stream);
+
 // One token per logits row: arg max where temperature is 0, else a draw from softmax(logits / temperature) after the
 // filters (when `filtered`), by inverse CDF in vocabulary order with the uniform of (seed, position).
 int hb_sample(int32_t* tokens, const float* logits, const float* temperature, const int32_t* top_k,

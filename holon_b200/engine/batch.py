@@ -24,6 +24,7 @@ class StepEntry:
     tokens: Sequence[int]
     start: int
     want: Sequence[int] = ()
+    from_last: bool = False        # its one token is the one this request sampled last, still on the device
 
 
 class Rows:
@@ -55,6 +56,7 @@ class StepContext:
         self.token_ids, self.positions, self.logits_index, self.rows = token_ids, positions, logits_index, rows
         self.groups, self._cache = groups, cache
         self.extra: dict = {}
+        self.from_last = None        # int32 [rows]: 1 where the row's token is fed from the device
 
     def layer_cache(self, run) -> LayerCache:
         c = self._cache

@@ -2,8 +2,8 @@
 
 `Engine(EngineConfig(model=...)).generate(prompts, params)` returns the generated token ids of each prompt;
 `add` / `step` / `has_work` / `abort` / `stats` / `close` drive it by hand. Names and meanings follow the reference
-(core/holon/core/engine.py:332-376, 461-524, 702-709). Every step runs at depth 0: schedule, run, sample, read the
-tokens back, commit.
+(core/holon/core/engine.py:332-376, 461-524, 702-709). With `overlap` (the default) a step stays in flight while
+the host schedules and enqueues the next one; without it every step is read back before the next is scheduled.
 """
 from __future__ import annotations
 
@@ -20,7 +20,7 @@ from ..sampling.params import SEED_MASK
 from ..weights import SafetensorsSource
 from .batch import StepEntry
 from .build import build
-from .scheduler import Request, Row, Scheduler
+from .scheduler import Request, Row, Scheduler, Status
 
 GRAPH_BUCKETS = (1, 2, 4, 8, 16, 24, 32, 48, 64, 96, 128, 192, 256)
 
@@ -33,6 +33,18 @@ class TokenDelta:
     token_ids: list[int]
     index: int                               # how many tokens the request had generated before these
     finish_reason: str | None = None         # "stop" | "length" | "abort" | None
+
+
+@dataclasses.dataclass
+class _Inflight:
+    """A launched step: its rows, the ones that sample, where their tokens will land on the host, and the event that
+    says they have."""
+
+    rows: list
+    sampled: list
+    host: torch.Tensor | None
+    done: object
+    decode_only: bool
 
 
 class Engine:
@@ -57,9 +69,14 @@ class Engine:
         self._graph_pool = None
         self._use_graphs = config.cuda_graphs and self.device.type == "cuda"
         self._buckets = tuple(x for x in GRAPH_BUCKETS if x <= config.max_seqs)
-        self._host_tokens = torch.zeros(config.max_step_tokens, dtype=torch.int32)
+        self._host_tokens = [torch.zeros(config.max_seqs + 1, dtype=torch.int32) for _ in range(2)]
         if self.device.type == "cuda":
-            self._host_tokens = self._host_tokens.pin_memory()
+            self._host_tokens = [t.pin_memory() for t in self._host_tokens]
+        self._flip = 0
+        self._inflight: _Inflight | None = None
+        # the token each request sampled last, by slot, on the device: decode rows of a step that is enqueued before
+        # the step ahead of it has been read back take their input from here
+        self.last_tokens = torch.zeros(config.max_seqs + 1, dtype=torch.int32, device=self.device)
         self.steps = self.graph_steps = self._graph_launches = 0
         self.h2d_bytes = self.d2h_bytes = 0
 
@@ -91,57 +108,117 @@ class Engine:
         request = self.requests.pop(rid, None)
         if request is None:
             return None
-        self.scheduler.finish(request, "abort")
+        self.scheduler.finish(request, "abort", release=request.pending == 0)   # (a row in flight gives the slot back)
         return TokenDelta(rid, [], request.generated, "abort")
 
     def has_work(self) -> bool:
-        return self.scheduler.has_work()
+        return self.scheduler.has_work() or self._inflight is not None
 
     # ------------------------------------------------------------------ one step
     def step(self) -> list[TokenDelta]:
+        """Runs one step and returns what became known. With `overlap`, the step launched here stays in flight and
+        the deltas are those of the step before it: the host schedules and enqueues step N + 1 while step N runs,
+        decode rows reading their input token from the device (core/holon/core/engine.py:492-524)."""
+        deltas: list[TokenDelta] = []
+        prev, self._inflight = self._inflight, None
+        if prev is not None and not self._may_run_ahead(prev):
+            deltas += self._commit(prev)
+            prev = None
         rows = self.scheduler.schedule()
+        if rows is None and prev is not None:
+            deltas += self._commit(prev)
+            prev = None
+            rows = self.scheduler.schedule()
         if rows is None:
-            if self.has_work():
+            if self.scheduler.has_work():
                 raise RuntimeError("the scheduler made no progress with requests pending")
-            return []
-        entries = [StepEntry(r.request.slot, r.request.tokens[r.request.computed:r.request.computed + r.n_tokens],
-                             r.request.computed, (r.n_tokens - 1,) if r.samples else ()) for r in rows]
+            return deltas
+        current = self._launch(rows)
+        if prev is not None:
+            deltas += self._commit(prev)
+        if self.config.overlap:
+            self._inflight = current
+        else:
+            deltas += self._commit(current)
+        return deltas
+
+    def drain(self) -> list[TokenDelta]:
+        """Commits the step in flight, if any."""
+        prev, self._inflight = self._inflight, None
+        return self._commit(prev) if prev is not None else []
+
+    def _may_run_ahead(self, prev: "_Inflight") -> bool:
+        """Whether the next step can be scheduled before `prev` is committed: `prev` was a pure decode step over every
+        running request, nobody waits, nobody is at its limit, and every request's next token has a page without
+        taking one from another request. Then the next step is the same rows again, fed from the device, and no
+        scheduling decision depends on the tokens still in flight (a stop token costs one wasted row)."""
+        s = self.scheduler
+        if not prev.decode_only or s.waiting or len(prev.rows) != len(s.running):
+            return False
+        need = 0
+        for row in prev.rows:
+            r = row.request
+            if r.status is not Status.RUNNING or s.at_limit(r):
+                return False
+            need += r.computed + 1 > self.built.cache.capacity(r.slot)
+        return need == 0 or all(g.pool.available >= need for g in self.built.cache.groups)
+
+    def _launch(self, rows: list[Row]) -> "_Inflight":
+        """Enqueues a step: forward, sampling, the sampled tokens filed by slot on the device and copied to the host."""
+        runner = self.built.runner
+        entries = []
+        for r in rows:
+            q = r.request
+            if q.pending:                                  # its last token is still on the device
+                entries.append(StepEntry(q.slot, (0,), q.computed, (0,) if r.samples else (), from_last=True))
+            else:
+                entries.append(StepEntry(q.slot, q.tokens[q.computed:q.computed + r.n_tokens], q.computed,
+                                         (r.n_tokens - 1,) if r.samples else ()))
         sampled = [r for r in rows if r.samples]
-        tokens = self._run(entries, sampled) if sampled else self._run_quiet(entries)
-        self.steps += 1
+        n = len(sampled)
+        runner.check(entries)
+        decode_only = n == len(entries) and all(len(e.tokens) == 1 for e in entries)
+        host = None
+        if n:
+            arrays = sampling_arrays([(r.request.params, r.request.seed, r.request.computed + r.n_tokens)
+                                      for r in sampled])
+            arrays["sample_slot"] = np.array([r.request.slot for r in sampled], dtype=np.int32)
+            filtered = any(r.request.params.filtered for r in sampled)
+            if self._use_graphs and decode_only and not filtered and n <= (self._buckets[-1] if self._buckets else 0):
+                tokens = self._replay(entries, arrays)
+            else:
+                step = runner.context(entries, extra=arrays)
+                tokens = self._forward(step, filtered, n)
+            host = self._host_tokens[self._flip][:n]
+            self._flip ^= 1
+            host.copy_(tokens[:n], non_blocking=True)
+            self.d2h_bytes += n * 4
+        else:                                              # every row stops short of its prompt's end: the head is skipped
+            step = runner.context(entries)
+            self._feed(step)
+            runner.model.forward(step)
+        self.h2d_bytes += runner.uploader.bytes_last
+        done = None
+        if self.device.type == "cuda":
+            done = torch.cuda.Event()
+            done.record()
+        runner.commit(entries)                             # the cache's books: these tokens are (being) computed
         for r in rows:
             self.scheduler.computed(r)
-        return [self._commit(r, t) for r, t in zip(sampled, tokens)]
+            r.request.pending += int(r.samples)
+        self.steps += 1
+        return _Inflight(rows, sampled, host, done, decode_only)
 
-    def _run_quiet(self, entries) -> list[int]:
-        """A step in which every row stops short of its prompt's end: nothing is sampled, the head is skipped."""
-        runner = self.built.runner
-        runner.check(entries)
-        runner.model.forward(runner.context(entries))
-        runner.commit(entries)
-        self.h2d_bytes += runner.uploader.bytes_last
-        return []
+    def _feed(self, step) -> None:
+        self.built.ctx.kernels.feed_tokens(step.token_ids, self.last_tokens, step.rows, step.from_last)
 
-    def _run(self, entries, sampled: list[Row]) -> list[int]:
-        runner, n = self.built.runner, len(sampled)
-        runner.check(entries)
-        arrays = sampling_arrays([(r.request.params, r.request.seed, r.request.computed + r.n_tokens)
-                                  for r in sampled])
-        filtered = any(r.request.params.filtered for r in sampled)
-        decode_only = len(sampled) == len(entries) and all(len(e.tokens) == 1 for e in entries)
-        if self._use_graphs and decode_only and not filtered and n <= (self._buckets[-1] if self._buckets else 0):
-            tokens = self._replay(entries, arrays)
-        else:
-            step = runner.context(entries, extra=arrays)
-            logits = runner.model.forward(step)
-            tokens = self.sampler.sample(logits, step.extra, filtered)
-        self.h2d_bytes += runner.uploader.bytes_last
-        host = self._host_tokens[:n]
-        host.copy_(tokens[:n], non_blocking=True)
-        torch.cuda.current_stream(self.device).synchronize() if self.device.type == "cuda" else None
-        self.d2h_bytes += n * 4
-        runner.commit(entries)
-        return host.tolist()
+    def _forward(self, step, filtered: bool, n: int, out: torch.Tensor | None = None) -> torch.Tensor:
+        """feed -> model -> sample -> store, all enqueued; returns the device tensor of sampled tokens."""
+        self._feed(step)
+        logits = self.built.runner.model.forward(step)
+        tokens = self.sampler.sample(logits, step.extra, filtered, out)
+        self.built.ctx.kernels.store_tokens(self.last_tokens, step.extra["sample_slot"], tokens, n)
+        return tokens
 
     def _replay(self, entries, arrays) -> torch.Tensor:
         """A decode step through the CUDA graph of its batch-size bucket (core/holon/core/executor.py:316-344):
@@ -149,17 +226,18 @@ class Engine:
         runner, n = self.built.runner, len(entries)
         bucket = next(b for b in self._buckets if b >= n)
         pad = bucket - n
-        padded = {k: np.concatenate([v, np.zeros(pad, dtype=v.dtype)]) for k, v in arrays.items()}
+        fill = {"sample_slot": self.built.cache.padding_slot}
+        padded = {k: np.concatenate([v, np.full(pad, fill.get(k, 0), dtype=v.dtype)]) for k, v in arrays.items()}
         step = runner.context(entries, pad_rows=pad, extra=padded)
         if bucket not in self._graphs:
             step.rows.max_kv = self.config.max_model_len          # the captured launch must serve any length
             out = torch.empty(bucket, dtype=torch.int32, device=self.device)
-            self.sampler.sample(runner.model.forward(step), step.extra, False, out)      # warm-up, not captured
+            self._forward(step, False, bucket, out)                # warm-up, not captured
             torch.cuda.current_stream(self.device).synchronize()
             graph, kernels = torch.cuda.CUDAGraph(), self.built.ctx.kernels
             before = kernels.launches
             with torch.cuda.graph(graph, pool=self._graph_pool):
-                self.sampler.sample(runner.model.forward(step), step.extra, False, out)
+                self._forward(step, False, bucket, out)
             captured, kernels.launches = kernels.launches - before, before       # recorded, not run
             self._graph_pool = self._graph_pool or graph.pool()
             self._graphs[bucket] = (graph, out, captured)
@@ -169,17 +247,30 @@ class Engine:
         self._graph_launches += captured
         return out
 
-    def _commit(self, row: Row, token: int) -> TokenDelta:
-        request = row.request
-        index = request.generated
-        request.tokens.append(int(token))
-        if request.status.name != "RUNNING":
-            self.scheduler.finished_prefill(request)
-        reason = self._finish_reason(request, int(token))
-        if reason:
-            self.scheduler.finish(request, reason)
-            del self.requests[request.rid]
-        return TokenDelta(request.rid, [int(token)], index, reason)
+    def _commit(self, inflight: "_Inflight") -> list[TokenDelta]:
+        """Waits for a launched step and books its tokens: appended, checked for a finish, reported."""
+        if inflight.done is not None:
+            inflight.done.synchronize()
+        tokens = inflight.host.tolist() if inflight.host is not None else []
+        deltas = []
+        for row, token in zip(inflight.sampled, tokens):
+            request = row.request
+            request.pending -= 1
+            if request.status is Status.FINISHED:          # it stopped a step ago; this row was already in flight
+                if request.pending == 0 and request.slot >= 0:
+                    self.built.cache.release(request.slot)
+                    request.slot = -1
+                continue
+            index = request.generated
+            request.tokens.append(int(token))
+            if request.status is not Status.RUNNING:
+                self.scheduler.finished_prefill(request)
+            reason = self._finish_reason(request, int(token))
+            if reason:
+                self.scheduler.finish(request, reason, release=request.pending == 0)
+                self.requests.pop(request.rid, None)
+            deltas.append(TokenDelta(request.rid, [int(token)], index, reason))
+        return deltas
 
     def _finish_reason(self, request: Request, token: int) -> str | None:
         p = request.params
@@ -201,6 +292,8 @@ class Engine:
             for delta in self.step():
                 if delta.rid in out:
                     out[delta.rid].extend(delta.token_ids)
+        if not self.requests:
+            self.drain()                                   # (a last wasted row may still be in flight)
         return [out[rid] for rid in rids]
 
     def launches(self) -> int:
@@ -217,4 +310,5 @@ class Engine:
     def close(self) -> None:
         for rid in list(self.requests):
             self.abort(rid)
+        self.drain()
         self._graphs.clear()

@@ -23,7 +23,7 @@ class Runner:
         self.model, self.cache, self.ctx = model, cache, build_ctx
         self.device, self.max_step_tokens = build_ctx.device, max_step_tokens
         s, t, g = cache.max_seqs + 1, max_step_tokens, len(cache.groups)
-        self.uploader = Uploader(t * (3 + g) + 12 * s + 64, self.device)
+        self.uploader = Uploader(t * (3 + g) + 16 * s + 64, self.device)
         self.vocab = model.spec.vocab
 
     # ------------------------------------------------------------------ host half
@@ -47,20 +47,28 @@ class Runner:
                                 f"(capacity {c.capacity(e.slot)})")
             if any(not 0 <= w < n for w in e.want):
                 raise StepError(f"slot {e.slot}: wanted places {list(e.want)} are outside its {n} tokens")
+            if e.from_last and n != 1:
+                raise StepError(f"slot {e.slot}: only a single token can be fed from the device")
             if any(not 0 <= t < self.vocab for t in e.tokens):
                 raise StepError(f"slot {e.slot}: a token id is outside the vocabulary of {self.vocab}")
             total += n
         if total > self.max_step_tokens:
             raise StepError(f"{total} tokens in one step; max_step_tokens is {self.max_step_tokens}")
 
-    def context(self, entries: Sequence[StepEntry], pad_rows: int = 0, extra=None) -> StepContext:
+    def context(self, entries: Sequence[StepEntry], pad_rows: int | None = None, extra=None) -> StepContext:
         """Lays the batch out (rows of one token first), uploads it in one copy and returns the device-side view.
-        `pad_rows`: rows of one token each for the padding slot, appended to the one-token rows (graph buckets).
+        `pad_rows` (not None: a graph bucket of decode rows): so many rows of one token each for the padding slot
+        follow the entries, and logits are taken at every row, padding included, so that the layout and the work
+        depend on the bucket's size alone.
         `extra`: {name: int32 array} uploaded alongside; the device views land in `StepContext.extra`."""
         c = self.cache
         order = sorted(range(len(entries)), key=lambda i: len(entries[i].tokens) != 1)       # stable
         counts = [len(entries[i].tokens) for i in order]
         n_decode = sum(1 for n in counts if n == 1)
+        bucket = pad_rows is not None
+        pad_rows = pad_rows or 0
+        if bucket and n_decode != len(entries):
+            raise StepError("a graph bucket holds rows of one token only")
         if pad_rows:
             counts[n_decode:n_decode] = [1] * pad_rows
         b = len(counts)
@@ -70,6 +78,7 @@ class Runner:
         token_ids, positions = np.zeros(t, dtype=np.int32), np.zeros(t, dtype=np.int32)
         row_slot, kv_len = np.full(b, c.padding_slot, dtype=np.int32), np.ones(b, dtype=np.int32)
         token_slot = np.full(t, c.padding_slot, dtype=np.int32)
+        from_last = np.zeros(b, dtype=np.int32)
         offset_of = {}
         rows = list(range(n_decode)) + list(range(n_decode + pad_rows, b))
         for r, i in zip(rows, order):
@@ -78,8 +87,12 @@ class Runner:
             positions[a:a + n] = np.arange(e.start, e.start + n)
             token_slot[a:a + n] = e.slot
             row_slot[r], kv_len[r] = e.slot, e.start + n
+            from_last[r] = int(e.from_last)
             offset_of[i] = a
-        logits_index = np.array([offset_of[i] + w for i, e in enumerate(entries) for w in e.want], dtype=np.int32)
+        if bucket:
+            logits_index = np.arange(b, dtype=np.int32)
+        else:
+            logits_index = np.array([offset_of[i] + w for i, e in enumerate(entries) for w in e.want], dtype=np.int32)
         up = self.uploader
         up.begin()
         up.put("token_ids", token_ids)
@@ -88,6 +101,7 @@ class Runner:
         up.put("row_slot", row_slot)
         up.put("kv_len", kv_len)
         up.put("logits_index", logits_index)
+        up.put("from_last", from_last)
         for g in c.groups:
             up.put(f"write_index.{g.index}", g.write_index(token_slot, positions).astype(np.int32))
         for name, array in (extra or {}).items():
@@ -99,6 +113,7 @@ class Runner:
         groups = [GroupStep(g.table_device, dev[f"write_index.{g.index}"], g.page_size) for g in c.groups]
         step = StepContext(dev["token_ids"], dev["positions"], dev["logits_index"], rows_, groups, c)
         step.extra = {name: dev[name] for name in (extra or {})}
+        step.from_last = dev["from_last"]
         return step
 
     # ------------------------------------------------------------------ the step

@@ -37,7 +37,8 @@ class Request:
     params: SamplingParams
     seed: int = 0
     slot: int = -1
-    computed: int = 0                       # tokens whose keys and values the cache holds
+    computed: int = 0                       # tokens whose keys and values the cache holds (or is being given)
+    pending: int = 0                        # tokens sampled by steps in flight, not yet read back
     status: Status = Status.WAITING
     finish_reason: str | None = None
 
@@ -112,8 +113,9 @@ class Scheduler:
         return rows
 
     def at_limit(self, request: Request) -> bool:
-        m = request.params.max_tokens
-        return len(request.tokens) >= self.max_model_len or (m is not None and request.generated >= m)
+        """Counting the tokens still in flight: a request at its limit is not scheduled again; its commit ends it."""
+        m, length = request.params.max_tokens, len(request.tokens) + request.pending
+        return length >= self.max_model_len or (m is not None and length - request.prompt_len >= m)
 
     # ------------------------------------------------------------------ room
     def _fit(self, request: Request, tokens: int | None) -> bool:
@@ -153,9 +155,10 @@ class Scheduler:
         request.status = Status.RUNNING
         self.running.append(request)
 
-    def finish(self, request: Request, reason: str) -> None:
+    def finish(self, request: Request, reason: str, release: bool = True) -> None:
+        """`release=False`: a row of this request is still in flight; whoever commits it gives the slot back."""
         (self.running if request.status is Status.RUNNING else self.waiting).remove(request)
-        if request.slot >= 0:
+        if release and request.slot >= 0:
             self.cache.release(request.slot)
-        request.slot = -1
+            request.slot = -1
         request.status, request.finish_reason = Status.FINISHED, reason

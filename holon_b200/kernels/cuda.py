@@ -250,6 +250,19 @@ class CudaKernels:
         self.linear(gate_up, x, weight)
         self.silu_mul(out, gate_up)
 
+    def feed_tokens(self, token_ids, last_tokens, rows, from_last) -> None:
+        """token_ids[first token of row r] = last_tokens[slot of row r] for the rows whose `from_last` is set."""
+        self._check(token_ids, last_tokens, rows.row_slot, rows.query_start, from_last)
+        self._call("hb_feed_tokens", self._i32(token_ids, "token_ids"), self._i32(last_tokens, "last_tokens"),
+                   self._i32(rows.row_slot, "row_slot"), self._i32(rows.query_start, "query_start"),
+                   self._i32(from_last, "from_last"), rows.n_rows)
+
+    def store_tokens(self, last_tokens, slots, tokens, n) -> None:
+        """last_tokens[slots[i]] = tokens[i] for i < n."""
+        self._check(last_tokens, slots, tokens)
+        self._call("hb_store_tokens", self._i32(last_tokens, "last_tokens"), self._i32(slots, "slots"),
+                   self._i32(tokens, "tokens"), int(n))
+
     def sample(self, tokens, logits, temperature, top_k, top_p, min_p, seed_lo, seed_hi, position, filtered) -> None:
         self._check(tokens, logits, temperature, top_k, top_p, min_p, seed_lo, seed_hi, position)
         r, v = logits.shape

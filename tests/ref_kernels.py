@@ -100,6 +100,14 @@ class RefKernels:
     def linear(self, out, x, weight):
         out.copy_((x.float() @ weight.float().T).to(out.dtype))
 
+    def feed_tokens(self, token_ids, last_tokens, rows, from_last):
+        for r in range(rows.n_rows):
+            if int(from_last[r]):
+                token_ids[int(rows.query_start[r])] = last_tokens[int(rows.row_slot[r])]
+
+    def store_tokens(self, last_tokens, slots, tokens, n):
+        last_tokens[slots[:n].long()] = tokens[:n]
+
     def sample(self, tokens, logits, temperature, top_k, top_p, min_p, seed_lo, seed_hi, position, filtered):
         """temperature 0: arg max. Else softmax(logits / T) filtered by top-k, top-p, min-p, drawn by inverse CDF in
         vocabulary order with the uniform of (seed, position)."""

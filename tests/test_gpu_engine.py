@@ -57,8 +57,9 @@ def test_greedy_generation(model, dtype, graphs):
     engine.built.cache.check()
     assert not engine.built.cache.live
     if dtype == "float32":
-        again = engine_of(folder, dtype, cuda_graphs=not graphs, chunk_with_decode=0, max_step_tokens=128, page_size=4)
-        assert again.generate(prompts, params) == got            # other batching, other pages: the same tokens
+        again = engine_of(folder, dtype, cuda_graphs=not graphs, chunk_with_decode=0, max_step_tokens=128, page_size=4,
+                          overlap=False)
+        assert again.generate(prompts, params) == got            # other batching, other pages, depth 0: the same tokens
 
 
 def test_sampled_generation_is_seeded_and_survives_preemption(model):
@@ -97,7 +98,9 @@ def test_limits_and_errors(model):
     assert len(out[0]) == 32 - 3
     rid = engine.add([4, 5, 6], SamplingParams(temperature=0.0, max_tokens=50))
     engine.step()
-    assert engine.abort(rid).finish_reason == "abort" and not engine.has_work() and not engine.built.cache.live
+    assert engine.abort(rid).finish_reason == "abort"
+    engine.drain()                                                   # (its first step was still in flight)
+    assert not engine.has_work() and not engine.built.cache.live
     stop = out[0][2]
     cut = engine.generate([[1, 2, 3]], SamplingParams(temperature=0.0, stop_token_ids=(stop,)))
     assert cut[0] == out[0][:out[0].index(stop) + 1]
@@ -119,3 +122,20 @@ def test_generation_with_the_tcgen05_gemm(model):
         kernels.gemm = before
     for prompt, tokens in zip(prompts, got):
         check_teacher_forced(config, weights, prompt, tokens, params, 0, exact=False)
+
+
+@pytest.mark.parametrize("overlap", [True, False])
+def test_stop_tokens_while_a_step_is_in_flight(model, overlap):
+    """With a step in flight a stop token is seen one step late: the request ends where it should, the row that was
+    already enqueued for it is dropped, its slot comes back, and the other requests do not notice."""
+    folder, config, weights, prompts = model
+    free = engine_of(folder, "float32", overlap=overlap)
+    base = free.generate(prompts[:3], SamplingParams(temperature=0.0, max_tokens=14))
+    stops = [(b[4],) for b in base]                                 # each request stops at its own fifth token
+    engine = engine_of(folder, "float32", overlap=overlap)
+    params = [SamplingParams(temperature=0.0, max_tokens=14, stop_token_ids=s) for s in stops]
+    got = engine.generate(prompts[:3], params)
+    for g, b, s in zip(got, base, stops):
+        assert g == b[:b.index(s[0]) + 1]
+    engine.built.cache.check()
+    assert not engine.built.cache.live and not engine.has_work()
