@@ -23,7 +23,6 @@
 #define AT_STAGES 3
 #define AT_Q_BYTES (AT_BM * AT_D * 2)             // 32 KB a group: two [128 x 64] swizzled blocks
 #define AT_KV_BYTES (AT_BN * AT_D * 2)            // 16 KB: two [64 x 64] swizzled blocks
-#define AT_P_BYTES (AT_BM * AT_BN * 2)            // 16 KB: one [128 x 64] swizzled block
 #define AT_SMEM (AT_GROUPS * AT_Q_BYTES + AT_STAGES * 2 * AT_KV_BYTES + 1024 + 256)
 #define AT_TMEM_COLS 512                          // per group: S0 [0, 64), S1 [64, 128), O [128, 256)
 #define AT_RESCALE 8.0f
@@ -58,8 +57,8 @@ __global__ void __launch_bounds__(320, 1) prefill_tcgen05_kernel(
     const uint32_t q_s = base, kv_s = q_s + AT_GROUPS * AT_Q_BYTES;
     const uint32_t bars = kv_s + AT_STAGES * 2 * AT_KV_BYTES;
     const uint32_t q_full = bars, kv_full0 = bars + 8, kv_empty0 = kv_full0 + 8 * AT_STAGES;
-    // per group g and buffer i, at index (g * 2 + i): scores computed / read out, weights written / read by the MMA
-    const uint32_t s_full0 = kv_empty0 + 8 * AT_STAGES, s_empty0 = s_full0 + 32, p_full0 = s_empty0 + 32;
+    // per group g and buffer i, at index (g * 2 + i): scores computed; weights written; weights read (O holds the tile)
+    const uint32_t s_full0 = kv_empty0 + 8 * AT_STAGES, p_full0 = s_full0 + 32;
     const uint32_t p_empty0 = p_full0 + 32, o_full0 = p_empty0 + 32, slot = o_full0 + 16;
     __shared__ int s_row, s_q0;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -75,7 +74,7 @@ __global__ void __launch_bounds__(320, 1) prefill_tcgen05_kernel(
         mbar_init(q_full, 1);
         for (int s = 0; s < AT_STAGES; ++s) { mbar_init(kv_full0 + 8 * s, 1); mbar_init(kv_empty0 + 8 * s, 1); }
         for (int i = 0; i < 2 * AT_GROUPS; ++i) {
-            mbar_init(s_full0 + 8 * i, 1); mbar_init(s_empty0 + 8 * i, 4);
+            mbar_init(s_full0 + 8 * i, 1);
             mbar_init(p_full0 + 8 * i, 4); mbar_init(p_empty0 + 8 * i, 1);
         }
         for (int g = 0; g < AT_GROUPS; ++g) mbar_init(o_full0 + 8 * g, 1);
