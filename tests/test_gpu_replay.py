@@ -183,3 +183,22 @@ def test_command_line_program(model, tmp_path):
     assert s0.shape[0] == 2 and s2.shape[0] == 2
     for row, pos in ((s0[0], 0), (s0[1], 19), (s2[0], len(ids) - 1), (s2[1], 4)):
         assert float((row - want["r2"][0][pos]).abs().max()) <= TOLERANCE
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_weights_stored_in_32_bits(tmp_path, dtype):
+    """A folder whose tensors are all stored as float32. The float32 engine uses them as they are. The bfloat16 engine
+    keeps products' weights and the embedding in bfloat16 and the norm weights in 32 bits (its norm and rotation
+    kernels take both), so the yardstick is the plain implementation on weights rounded the same way."""
+    folder = make_folder(tmp_path, "b", dtype=torch.float32)
+    config, weights = plain.read_folder(folder)
+    if dtype == "bfloat16":
+        weights = {k: (v if k.endswith("norm.weight") or k.endswith("layernorm.weight") else v.bfloat16().float())
+                   for k, v in weights.items()}
+    ids = random_prompt(config["vocab_size"], 90, 3)
+    want = {"x": exact_and_rounded(config, weights, ids)}
+    r = Replayer(str(folder), dtype, max_tokens=128)
+    norms = [p.tensor.dtype for name, p in r.built.model.params() if name.endswith("norm.weight")]
+    assert set(norms) == {torch.float32}
+    got = run(r, [([("x", ids[:61])], []), ([("x", ids[61:63])], [])] + [([("x", [t])], []) for t in ids[63:]])
+    compare(got, want, dtype)
