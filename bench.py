@@ -42,14 +42,35 @@ FULL_LAYERS = QWEN3_8B["num_hidden_layers"]
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
 
 
+def _find_number(data, key: str):
+    """The first number stored under `key` anywhere in a nested JSON value (a dict under the key: its "value")."""
+    if isinstance(data, dict):
+        if key in data:
+            v = data[key]
+            if isinstance(v, dict):
+                v = v.get("value", v.get("median", v.get("max")))
+            if isinstance(v, (int, float)) and not isinstance(v, bool):
+                return float(v)
+        for v in data.values():
+            found = _find_number(v, key)
+            if found is not None:
+                return found
+    elif isinstance(data, list):
+        for v in data:
+            found = _find_number(v, key)
+            if found is not None:
+                return found
+    return None
+
+
 def peaks() -> tuple[dict, str]:
     path = ROOT / "MEASURED_PEAKS.json"
     if path.is_file():
         try:
             data = json.loads(path.read_text())
-            flat = {k: float(v) for k, v in data.items() if isinstance(v, (int, float))}
-            if "hbm_gbs" in flat and "bf16_tflops" in flat:
-                return flat, "measured"
+            hbm, flops = _find_number(data, "hbm_gbs"), _find_number(data, "bf16_tflops")
+            if hbm and flops:
+                return {"hbm_gbs": hbm, "bf16_tflops": flops}, "measured"
         except (ValueError, OSError):
             pass
     return dict(FALLBACK_PEAKS), "fallback"
