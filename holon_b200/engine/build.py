@@ -45,7 +45,10 @@ def build(source, *, dtype: str, device, kernels=None, page_size: int, max_seqs:
     weight_bytes = load_weights(model, spec, source.tensors(), tdtype, device)
     if state_memory is None and pages is None:
         free, _ = torch.cuda.mem_get_info(device)
-        widest = max(max(p.shape[0] for _, p in model.params() if p.kind == "matrix"), spec.hidden)
+        # room for the largest step's activations: a few tensors of the widest layer product per token, the 32-bit
+        # stream, and logits for as many rows as can sample in one step
+        widest = max([p.shape[0] for name, p in model.params() if p.kind == "matrix" and not name.startswith("head.")]
+                     + [spec.hidden])
         activations = max_step_tokens * (widest * 3 + spec.hidden * 8) * 4 + min(max_step_tokens, max_seqs) * spec.vocab * 8
         state_memory = int(free * memory_fraction) - activations
     cache = CacheManager(model.entries, page_size, max_seqs, max_model_len, tdtype, device,
