@@ -389,7 +389,7 @@ __global__ void __launch_bounds__(128, (D_PAD <= 128 ? 3 : 1)) prefill_kernel(
     const uint32_t q_s = Q_IN_REGS ? k_s + TILE_BYTES : v_s + 2 * TILE_BYTES;
     __shared__ int s_row, s_q0;
     if (threadIdx.x == 0) {
-        int left = (int)(gridDim.x - 1 - blockIdx.x), found = -1, q0 = 0;
+        int left = (int)blockIdx.y, found = -1, q0 = 0;              // x is handed out first: all heads' late tiles (longest) start first
         for (int b = rows - 1; b >= row0; --b) {
             const int tiles = (query_start[b + 1] - query_start[b] + 63) >> 6;
             if (left < tiles) { found = b; q0 = (tiles - 1 - left) * 64; break; }
@@ -400,7 +400,7 @@ __global__ void __launch_bounds__(128, (D_PAD <= 128 ? 3 : 1)) prefill_kernel(
     __syncthreads();
     const int b = s_row;
     if (b < 0) return;
-    const int h = blockIdx.y, hk = h / (heads / kv_heads);
+    const int h = blockIdx.x, hk = h / (heads / kv_heads);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int t0 = query_start[b] + s_q0, nq = query_start[b + 1] - query_start[b];
     const int qn = min(64, nq - s_q0);                              // queries in this tile
@@ -517,7 +517,8 @@ static int launch_prefill(bf16* out, const bf16* q, const bf16* kv, const int32_
     auto kernel = prefill_kernel<D_PAD>;
     const size_t smem = (size_t)(4 * TILE_N + (D_PAD <= 128 ? 0 : 64)) * D_PAD * sizeof(bf16);
     HB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    kernel<<<dim3(q_tiles, heads), 128, smem, s>>>(out, q, kv, block_table, table_stride, row_slot, query_start,
+    if (q_tiles > 65535) HB_REFUSE("attention_prefill: %d query tiles in one step, above 65535", q_tiles);
+    kernel<<<dim3(heads, q_tiles), 128, smem, s>>>(out, q, kv, block_table, table_stride, row_slot, query_start,
                                                    kv_len, row0, rows, heads, kv_heads, head_dim, pages, page_size,
                                                    log2_exact(page_size), scale * 1.4426950408889634f, window);
     HB_LAUNCH_CHECK("attention_prefill");

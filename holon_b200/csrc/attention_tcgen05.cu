@@ -64,7 +64,8 @@ __global__ void __launch_bounds__(320, 1) prefill_tcgen05_kernel(
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
     if (threadIdx.x == 0) {
-        int left = (int)(gridDim.x - 1 - blockIdx.x), found = -1, q0 = 0;      // late query tiles (most keys) first
+        int left = (int)blockIdx.y, found = -1, q0 = 0;      // blocks are handed out x first: every head's late query
+                                                             // tiles (the longest walks) start before any short one
         for (int b = rows - 1; b >= row0; --b) {
             const int tiles = (query_start[b + 1] - query_start[b] + AT_GROUPS * AT_BM - 1) / (AT_GROUPS * AT_BM);
             if (left < tiles) { found = b; q0 = (tiles - 1 - left) * AT_GROUPS * AT_BM; break; }
@@ -91,7 +92,7 @@ __global__ void __launch_bounds__(320, 1) prefill_tcgen05_kernel(
     asm volatile("ld.shared.b32 %0, [%1];\n" : "=r"(tmem) : "r"(slot));
 
     const int b = s_row;
-    const int h = blockIdx.y, hk = h / (heads / kv_heads);
+    const int h = blockIdx.x, hk = h / (heads / kv_heads);
     int tile_lo = 0, t0 = 0, p0 = 0, n = 0, nq = 0;
     int g_tiles[AT_GROUPS] = {0, 0}, g_qn[AT_GROUPS] = {0, 0}, g_hi[AT_GROUPS] = {0, 0};
     if (b >= 0) {
@@ -326,7 +327,8 @@ extern "C" int hb_attention_prefill_tcgen05(void* out, const void* q, const void
     if (rows <= row0 || q_tiles == 0) return 0;
     if (head_dim != AT_D) HB_REFUSE("attention_prefill_tcgen05: head_dim %d; this kernel is for %d", head_dim, AT_D);
     if (page_size % AT_BN) HB_REFUSE("attention_prefill_tcgen05: page size %d is no multiple of %d", page_size, AT_BN);
-    if (kv_heads < 1 || heads % kv_heads || heads > 65535) HB_REFUSE("attention_prefill_tcgen05: %d heads, %d kv heads", heads, kv_heads);
+    if (kv_heads < 1 || heads % kv_heads) HB_REFUSE("attention_prefill_tcgen05: %d heads, %d kv heads", heads, kv_heads);
+    if (q_tiles > 65535) HB_REFUSE("attention_prefill_tcgen05: %d query tiles in one step, above 65535", q_tiles);
     if (!(scale > 0.f)) HB_REFUSE("attention_prefill_tcgen05: the score scale must be positive");
     if ((((uintptr_t)q | (uintptr_t)kv | (uintptr_t)out) % 16) != 0) HB_REFUSE("attention_prefill_tcgen05: pointers must be 16-byte aligned");
     const uint64_t kv_rows = (uint64_t)pages * 2 * kv_heads * page_size;
@@ -337,7 +339,7 @@ extern "C" int hb_attention_prefill_tcgen05(void* out, const void* q, const void
     rc = encode_2d(&map_kv, kv, AT_D, kv_rows, AT_BN, "the cache");
     if (rc) return rc;
     HB_CUDA(cudaFuncSetAttribute(prefill_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, AT_SMEM));
-    prefill_tcgen05_kernel<<<dim3(q_tiles, heads), 320, AT_SMEM, (cudaStream_t)stream>>>(
+    prefill_tcgen05_kernel<<<dim3(heads, q_tiles), 320, AT_SMEM, (cudaStream_t)stream>>>(
         map_q, map_kv, (bf16*)out, block_table, table_stride, row_slot, query_start, kv_len, row0, rows, heads, kv_heads,
         pages, page_size, scale * 1.4426950408889634f, window);
     HB_LAUNCH_CHECK("attention_prefill_tcgen05");
