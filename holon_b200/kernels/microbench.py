@@ -2,6 +2,7 @@
 
     python -m holon_b200.kernels.microbench decode_attention [--rows 8 64 1] [--context 8192] [--splits 4 6 13]
     python -m holon_b200.kernels.microbench gemm [--rows 2048] [--shapes qkv o gate_up down]
+    python -m holon_b200.kernels.microbench prefill_attention [--rows 2048] [--context 2048]
 
 Sizes default to Qwen3-8B's (32 query and 8 KV heads of 128, hidden 4096, intermediate 12288). The numbers under
 `profiles/` that are not ncu captures come from here.
@@ -57,6 +58,31 @@ def decode_attention(k, args) -> None:
         k._splits.clear()
 
 
+def prefill_attention(k, args) -> None:
+    """One prompt portion of `rows` tokens whose last token is at position `context` - 1, by both prefill kernels;
+    ten launches between the events, so that the host's share (two tensor maps a launch) is hidden."""
+    heads, kv_heads, d, page = 32, 8, 128, 64
+    for t in args.rows:
+        n = max(args.context, t)
+        per = -(-n // page)
+        kv = torch.randn(per + 1, 2, kv_heads, page, d, device=k.device, dtype=torch.bfloat16)
+        table = (torch.arange(per, device=k.device, dtype=torch.int32) + 1).view(1, per).contiguous()
+        q = torch.randn(t, heads, d, device=k.device, dtype=torch.bfloat16)
+        out = torch.empty_like(q)
+        dev = lambda v: torch.tensor(v, device=k.device, dtype=torch.int32)   # noqa: E731
+        batch = Rows(dev([0]), dev([0, t]), dev([n]), 1, t, 0, t, n, [0, t], [n])
+        flops = 4 * heads * d * (t * (n - t) + t * (t + 1) // 2)
+        for name in ("tcgen05", "mma"):
+            k.prefill_attention = name
+
+            def ten():
+                for _ in range(10):
+                    k.paged_attention(out, q, kv, table, batch, 1 / math.sqrt(d), 0)
+            us = timed(ten, None, 4) / 10
+            print(f"prefill attention {name:8s} tokens {t} keys {n}: {us:7.1f} us  {flops / us / 1e6:6.0f} TFLOP/s (causal)")
+    print("tcgen05 status", k.tcgen05_status())
+
+
 def gemm(k, args) -> None:
     m = args.rows[0]
     for name in args.shapes:
@@ -79,7 +105,7 @@ def gemm(k, args) -> None:
 
 def main() -> None:
     ap = argparse.ArgumentParser(description=__doc__.split("\n\n")[0])
-    ap.add_argument("what", choices=("decode_attention", "gemm"))
+    ap.add_argument("what", choices=("decode_attention", "gemm", "prefill_attention"))
     ap.add_argument("--rows", type=int, nargs="*", default=None)
     ap.add_argument("--context", type=int, default=8192)
     ap.add_argument("--splits", type=int, nargs="*", default=None)
@@ -91,6 +117,9 @@ def main() -> None:
         if args.what == "decode_attention":
             args.rows = args.rows or [8, 64, 1]
             decode_attention(k, args)
+        elif args.what == "prefill_attention":
+            args.rows = args.rows or [2048]
+            prefill_attention(k, args)
         else:
             args.rows = args.rows or [2048]
             gemm(k, args)
