@@ -110,6 +110,33 @@ __device__ __forceinline__ void load_kv_tile(uint32_t k_s, uint32_t v_s, const K
     }
 }
 
+// The same when a page holds a whole number of 64-key tiles (a power of two of at least 64): the tile lies in one
+// page, whose number the caller has read already (one table entry a tile instead of one a key row), and a key row's
+// address is the tile's plus a multiple of head_dim.
+template <int D_PAD, int THREADS>
+__device__ __forceinline__ void load_kv_tile_in_page(uint32_t k_s, uint32_t v_s, const KvView& c, int tile, int lo, int hi,
+                                                     int page) {
+    constexpr int CPR = D_PAD / 8;
+    constexpr int STEP = THREADS / CPR;
+    const int ch = threadIdx.x % CPR, r0 = threadIdx.x / CPR;
+    if (ch >= (c.head_dim >> 3)) return;
+    const long head_stride = (long)c.page_size * c.head_dim;
+    const long v_shift = (long)c.kv_heads * head_stride;
+    const int j0 = tile * TILE_N;
+    const bool page_ok = page >= 0 && page < c.pages;
+    const bool whole = j0 >= lo && j0 + TILE_N <= hi;            // no key of the tile is outside the row's range
+    const bf16* base = c.kv + ((long)(page_ok ? page : 0) * 2 * v_shift + (long)c.hk * head_stride + ch * 8 +
+                               (long)(j0 & (c.page_size - 1)) * c.head_dim);
+#pragma unroll
+    for (int r = r0; r < TILE_N; r += STEP) {
+        const bool valid = page_ok && (whole || (j0 + r >= lo && j0 + r < hi));
+        const bf16* src = base + (valid ? (long)r * c.head_dim : 0);
+        const uint32_t d = tile_off<D_PAD>(r, ch);
+        cp_async16(k_s + d, src, valid);
+        cp_async16(v_s + d, src + (valid ? v_shift : 0), valid);
+    }
+}
+
 // Loads `rows` query rows of one head (row stride heads * head_dim elements) into a tile; the rest become zeros.
 template <int D_PAD, int ROWS, int THREADS>
 __device__ __forceinline__ void load_q_tile(uint32_t q_s, const bf16* q, long row_stride, int rows, int head_dim) {
@@ -151,38 +178,34 @@ __device__ __forceinline__ void softmax_step(float (&s)[NT][4], float& m0, float
 }
 
 // ================================================================ decode
-// grid (rows, kv_heads * m_tiles, splits), 128 threads. m_tiles = ceil(group / 16).
+// One walk of the four warps over tiles [first, last) of one (row, kv head, 16-head tile of its group); the result
+// goes to `out` (part_stride 0) or, unnormalised with its maximum and sum, to partial slot part_base + r * part_stride
+// for the tile's r-th head. Ends with a barrier, so that the next walk of the same CTA may overwrite the tiles.
 template <int D_PAD, int STAGES>
-__global__ void __launch_bounds__(128) decode_kernel(
-        bf16* __restrict__ out, float* __restrict__ part_o, float* __restrict__ part_ml, const bf16* __restrict__ q,
-        const bf16* __restrict__ kv, const int32_t* __restrict__ block_table, int table_stride,
-        const int32_t* __restrict__ row_slot, const int32_t* __restrict__ query_start,
-        const int32_t* __restrict__ kv_len, int heads, int kv_heads, int head_dim, int pages, int page_size,
-        int page_shift, float scale_log2, int window, int splits) {
-    extern __shared__ __align__(128) unsigned char smem_raw[];
+__device__ __forceinline__ void decode_walk(
+        unsigned char* smem_raw, bf16* __restrict__ out, float* __restrict__ part_o, float* __restrict__ part_ml,
+        size_t part_base, int part_stride, const bf16* __restrict__ q, const bf16* __restrict__ kv,
+        const int32_t* __restrict__ table, int t, int heads, int kv_heads, int head_dim, int pages, int page_size,
+        int page_shift, float scale_log2, int hk, int group, int g0, int g, int first, int last, int lo, int n) {
     constexpr uint32_t TILE_BYTES = TILE_N * D_PAD * 2;
     const uint32_t q_s = smem_u32(smem_raw);                       // [16][D_PAD]
     const uint32_t k_s = q_s + 16 * D_PAD * 2;                     // [STAGES][64][D_PAD]
     const uint32_t v_s = k_s + STAGES * TILE_BYTES;                // [STAGES][64][D_PAD]
-    const int b = blockIdx.x, split = blockIdx.z;
-    const int group = heads / kv_heads, m_tiles = (group + 15) / 16;
-    const int hk = blockIdx.y / m_tiles, mt = blockIdx.y % m_tiles;
-    const int g0 = mt * 16, g = min(16, group - g0);                // this CTA's query heads: hk * group + g0 + [0, g)
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int t = query_start[b];
-    const int n = kv_len[b];
-    const int lo = window > 0 ? max(0, n - window) : 0;             // the one query sits at position n - 1
-    const int tile_lo = lo / TILE_N, tile_hi = (n + TILE_N - 1) / TILE_N;
-    const int per = (tile_hi - tile_lo + splits - 1) / splits;
-    const int first = tile_lo + split * per, last = min(tile_hi, first + per);
-
-    KvView view{kv, block_table + (size_t)row_slot[b] * table_stride, pages, page_size, kv_heads, head_dim, hk, page_shift};
+    KvView view{kv, table, pages, page_size, kv_heads, head_dim, hk, page_shift};
+    const bool in_page = page_shift >= 6;                           // a 64-key tile lies in one page: one table entry a tile,
+    const int tile_shift = page_shift - 6;                          // read one tile ahead of the load that needs it
     load_q_tile<D_PAD, 16, 128>(q_s, q + ((size_t)t * heads + (size_t)hk * group + g0) * head_dim, head_dim, g, head_dim);
 #pragma unroll
     for (int s = 0; s < STAGES - 1; ++s) {
-        if (first + s < last) load_kv_tile<D_PAD, 128>(k_s + s * TILE_BYTES, v_s + s * TILE_BYTES, view, first + s, lo, n);
+        if (first + s < last) {
+            if (in_page) load_kv_tile_in_page<D_PAD, 128>(k_s + s * TILE_BYTES, v_s + s * TILE_BYTES, view, first + s, lo, n,
+                                                          view.table[(first + s) >> tile_shift]);
+            else load_kv_tile<D_PAD, 128>(k_s + s * TILE_BYTES, v_s + s * TILE_BYTES, view, first + s, lo, n);
+        }
         cp_async_commit();
     }
+    int page_ahead = in_page && first + STAGES - 1 < last ? view.table[(first + STAGES - 1) >> tile_shift] : 0;
 
     float o[D_PAD / 8][4];
 #pragma unroll
@@ -201,9 +224,12 @@ __global__ void __launch_bounds__(128) decode_kernel(
         __syncthreads();
         if (tile + STAGES - 1 < last) {
             const int s2 = (tile - first + STAGES - 1) % STAGES;
-            load_kv_tile<D_PAD, 128>(k_s + s2 * TILE_BYTES, v_s + s2 * TILE_BYTES, view, tile + STAGES - 1, lo, n);
+            if (in_page) load_kv_tile_in_page<D_PAD, 128>(k_s + s2 * TILE_BYTES, v_s + s2 * TILE_BYTES, view, tile + STAGES - 1, lo, n,
+                                                          page_ahead);
+            else load_kv_tile<D_PAD, 128>(k_s + s2 * TILE_BYTES, v_s + s2 * TILE_BYTES, view, tile + STAGES - 1, lo, n);
         }
         cp_async_commit();
+        if (in_page && tile + STAGES < last) page_ahead = view.table[(tile + STAGES) >> tile_shift];
         if (Q_IN_REGS && !q_loaded) {
 #pragma unroll
             for (int ks = 0; ks < D_PAD / 16; ++ks)
@@ -286,35 +312,92 @@ __global__ void __launch_bounds__(128) decode_kernel(
             l += fw * wml[(w * 16 + r) * 2 + 1];
         }
         const int h = hk * group + g0 + r;
-        if (splits == 1) {
+        if (part_stride == 0) {
             out[((size_t)t * heads + h) * head_dim + d] = __float2bfloat16_rn(l > 0.f ? acc / l : 0.f);
         } else {
-            const size_t slot = ((size_t)b * heads + h) * splits + split;
+            const size_t slot = part_base + (size_t)r * part_stride;
             part_o[slot * head_dim + d] = acc;
             if (d == 0) { part_ml[slot * 2] = mm * scale_log2; part_ml[slot * 2 + 1] = l; }   // the maximum in log2 units
         }
     }
+    __syncthreads();
 }
 
-// out[t, h, :] = sum_s w_s o_s / sum_s w_s l_s, w_s = 2^(m_s - max m), splits in ascending order.
+// grid (rows, kv_heads * m_tiles, splits), 128 threads. m_tiles = ceil(group / 16).
+template <int D_PAD, int STAGES>
+__global__ void __launch_bounds__(128) decode_kernel(
+        bf16* __restrict__ out, float* __restrict__ part_o, float* __restrict__ part_ml, const bf16* __restrict__ q,
+        const bf16* __restrict__ kv, const int32_t* __restrict__ block_table, int table_stride,
+        const int32_t* __restrict__ row_slot, const int32_t* __restrict__ query_start,
+        const int32_t* __restrict__ kv_len, int heads, int kv_heads, int head_dim, int pages, int page_size,
+        int page_shift, float scale_log2, int window, int splits) {
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+    const int b = blockIdx.x, split = blockIdx.z;
+    const int group = heads / kv_heads, m_tiles = (group + 15) / 16;
+    const int hk = blockIdx.y / m_tiles, mt = blockIdx.y % m_tiles;
+    const int g0 = mt * 16, g = min(16, group - g0);                // this CTA's query heads: hk * group + g0 + [0, g)
+    const int n = kv_len[b];
+    const int lo = window > 0 ? max(0, n - window) : 0;             // the one query sits at position n - 1
+    const int tile_lo = lo / TILE_N, tile_hi = (n + TILE_N - 1) / TILE_N;
+    const int per = (tile_hi - tile_lo + splits - 1) / splits;
+    const int first = tile_lo + split * per, last = min(tile_hi, first + per);
+    decode_walk<D_PAD, STAGES>(smem_raw, out, part_o, part_ml, ((size_t)b * heads + (size_t)hk * group + g0) * splits + split,
+                               splits > 1 ? splits : 0, q, kv, block_table + (size_t)row_slot[b] * table_stride,
+                               query_start[b], heads, kv_heads, head_dim, pages, page_size, page_shift, scale_log2, hk,
+                               group, g0, g, first, last, lo, n);
+}
+
+// out[0 .. head_dim) = sum_i w_i o_i / sum_i w_i l_i over `count` partial results at slots base + i * stride,
+// w_i = 2^(m_i - max m). 128 threads: the maximum first (every thread a share of the partials), then warp w sums the
+// partials i = w, w + 4, ... with a lane per four values, and the four warps' sums are added in warp order; the
+// order of the sums depends on `count` alone, so equal inputs give equal outputs.
+__device__ __forceinline__ void merge_partials(bf16* __restrict__ out, const float* __restrict__ part_o,
+                                               const float* __restrict__ part_ml, size_t base, size_t stride, int count,
+                                               int head_dim) {
+    __shared__ float red[4];
+    __shared__ float sums[4][257];                                   // per warp: up to 256 values and the sum of weights
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    float mm = -INFINITY;
+    for (int i = threadIdx.x; i < count; i += 128) mm = fmaxf(mm, part_ml[(base + i * stride) * 2]);
+#pragma unroll
+    for (int d = 16; d > 0; d >>= 1) mm = fmaxf(mm, __shfl_xor_sync(0xffffffffu, mm, d));
+    if (lane == 0) red[warp] = mm;
+    __syncthreads();
+    mm = fmaxf(fmaxf(red[0], red[1]), fmaxf(red[2], red[3]));
+    for (int d0 = 0; d0 < head_dim; d0 += 128) {                     // head sizes are multiples of 16: a lane's four values
+        const int d = d0 + lane * 4;                                 // are all inside or all outside
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+        float l = 0.f;
+        for (int i = warp; i < count; i += 4) {
+            const size_t slot = base + i * stride;
+            const float ms = part_ml[slot * 2];
+            const float w = ms == -INFINITY ? 0.f : ex2(ms - mm);
+            l += w * part_ml[slot * 2 + 1];
+            if (d < head_dim) {
+                const float4 o = *(const float4*)(part_o + slot * head_dim + d);
+                acc.x += w * o.x; acc.y += w * o.y; acc.z += w * o.z; acc.w += w * o.w;
+            }
+        }
+        if (d < head_dim) { sums[warp][lane * 4] = acc.x; sums[warp][lane * 4 + 1] = acc.y; sums[warp][lane * 4 + 2] = acc.z; sums[warp][lane * 4 + 3] = acc.w; }
+        if (lane == 0) sums[warp][256] = l;
+        __syncthreads();
+        const int dd = d0 + (int)threadIdx.x;
+        if (dd < head_dim) {
+            const float total = ((sums[0][256] + sums[1][256]) + sums[2][256]) + sums[3][256];
+            const float v = ((sums[0][threadIdx.x] + sums[1][threadIdx.x]) + sums[2][threadIdx.x]) + sums[3][threadIdx.x];
+            out[dd] = __float2bfloat16_rn(total > 0.f ? v / total : 0.f);
+        }
+        __syncthreads();
+    }
+}
+
+// out[t, h, :] from the partial results of (row, head)'s splits, in ascending order.
 __global__ void decode_merge_kernel(bf16* __restrict__ out, const float* __restrict__ part_o,
                                     const float* __restrict__ part_ml, const int32_t* __restrict__ query_start,
                                     int heads, int head_dim, int splits) {
     const int b = blockIdx.x, h = blockIdx.y;
-    const size_t base = ((size_t)b * heads + h) * splits;
-    float mm = -INFINITY;
-    for (int s = 0; s < splits; ++s) mm = fmaxf(mm, part_ml[(base + s) * 2]);
-    const int t = query_start[b];
-    for (int d = threadIdx.x; d < head_dim; d += blockDim.x) {
-        float acc = 0.f, l = 0.f;
-        for (int s = 0; s < splits; ++s) {
-            const float ms = part_ml[(base + s) * 2];
-            const float fs = ms == -INFINITY ? 0.f : ex2(ms - mm);
-            acc += fs * part_o[(base + s) * head_dim + d];
-            l += fs * part_ml[(base + s) * 2 + 1];
-        }
-        out[((size_t)t * heads + h) * head_dim + d] = __float2bfloat16_rn(l > 0.f ? acc / l : 0.f);
-    }
+    merge_partials(out + ((size_t)query_start[b] * heads + h) * head_dim, part_o, part_ml,
+                   ((size_t)b * heads + h) * splits, 1, splits, head_dim);
 }
 
 template <int D_PAD> static size_t decode_smem(int stages) {
@@ -369,6 +452,189 @@ extern "C" int hb_attention_decode_bf16(void* out, float* scratch, const void* q
     if (head_dim <= 64) return launch_decode<64, 4>(HB_ARGS);
     if (head_dim <= 128) return launch_decode<128, 2>(HB_ARGS);   // two stages: three CTAs fit an SM, which hides latency better than a third stage
     return launch_decode<256, 2>(HB_ARGS);
+#undef HB_ARGS
+}
+
+// ================================================================ decode, the keys of all rows shared out evenly
+// The 64-key tiles of every (row, kv head, 16-head tile) are numbered in one line, row by row; CTA c of C takes tiles
+// [c T / C, (c + 1) T / C) of the T there are, in as many walks as that stretch touches (row, head) pairs. Every CTA
+// reads the same number of keys whatever the rows' lengths are, and one wave of CTAs that fills the GPU does all of it.
+// A walk's partial result goes to slot c + p (p the pair's number): along the line either c or p grows from one
+// walk to the next, so the slots of a pair's walks are distinct and follow one another. The merge kernel works the
+// same numbers out again. C is cut to T / 2 when there are fewer tiles than that (a CTA then has at least two).
+#define HB_BALANCED_ROWS 256
+
+struct BalancedPlan {
+    long long tiles;               // T
+    int ctas;                      // C
+    int pairs_per_row;
+};
+
+// Tiles of row b: the ones that hold keys the row's query may see.
+__device__ __forceinline__ int row_tiles(int n, int window, int* tile_lo) {
+    const int lo = window > 0 ? max(0, n - window) : 0;
+    *tile_lo = lo / TILE_N;
+    return (n + TILE_N - 1) / TILE_N - lo / TILE_N;
+}
+
+// prefix[b] = tiles of rows before b, prefix[rows] their total; by warp 0, 32 rows a pass.
+__device__ __forceinline__ void tile_prefix(int* prefix, const int32_t* __restrict__ kv_len, int rows, int window) {
+    if (threadIdx.x < 32) {
+        int carry = 0;
+        for (int b0 = 0; b0 < rows; b0 += 32) {
+            const int b = b0 + (int)threadIdx.x;
+            int unused, v = b < rows ? row_tiles(kv_len[b], window, &unused) : 0;
+#pragma unroll
+            for (int d = 1; d < 32; d <<= 1) {
+                const int up = __shfl_up_sync(0xffffffffu, v, d);
+                if ((int)threadIdx.x >= d) v += up;
+            }
+            if (b < rows) prefix[b + 1] = carry + v;
+            carry += __shfl_sync(0xffffffffu, v, 31);
+        }
+        if (threadIdx.x == 0) prefix[0] = 0;
+    }
+    __syncthreads();
+}
+
+__device__ __forceinline__ BalancedPlan balanced_plan(const int* prefix, int rows, int pairs_per_row, int max_ctas) {
+    BalancedPlan plan;
+    plan.pairs_per_row = pairs_per_row;
+    plan.tiles = (long long)prefix[rows] * pairs_per_row;
+    const long long want = plan.tiles / 2 > 1 ? plan.tiles / 2 : 1;
+    plan.ctas = (int)(want < max_ctas ? want : max_ctas);
+    return plan;
+}
+
+template <int D_PAD, int STAGES>
+__global__ void __launch_bounds__(128, (D_PAD <= 64 ? 4 : D_PAD <= 128 ? 3 : 1)) decode_balanced_kernel(
+        float* __restrict__ part_o, float* __restrict__ part_ml, const bf16* __restrict__ q,
+        const bf16* __restrict__ kv, const int32_t* __restrict__ block_table, int table_stride,
+        const int32_t* __restrict__ row_slot, const int32_t* __restrict__ query_start,
+        const int32_t* __restrict__ kv_len, int rows, int heads, int kv_heads, int head_dim, int pages, int page_size,
+        int page_shift, float scale_log2, int window) {
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+    __shared__ int prefix[HB_BALANCED_ROWS + 1];
+    tile_prefix(prefix, kv_len, rows, window);
+    const int group = heads / kv_heads, m_tiles = (group + 15) / 16, gmax = min(16, group);
+    const BalancedPlan plan = balanced_plan(prefix, rows, kv_heads * m_tiles, (int)gridDim.x);
+    const int c = blockIdx.x;
+    if (c >= plan.ctas) return;
+    long long f = (long long)c * plan.tiles / plan.ctas;
+    const long long end = (long long)(c + 1) * plan.tiles / plan.ctas;
+    int b = 0;
+    while (f < end) {
+        while ((long long)prefix[b + 1] * plan.pairs_per_row <= f) ++b;          // the row this tile belongs to
+        const int tiles_b = prefix[b + 1] - prefix[b];
+        const long long in_row = f - (long long)prefix[b] * plan.pairs_per_row;
+        const int pair = (int)(in_row / tiles_b), tile = (int)(in_row % tiles_b);
+        const int count = (int)min((long long)(tiles_b - tile), end - f);
+        const int hk = pair / m_tiles, mt = pair % m_tiles;
+        const int g0 = mt * 16, g = min(16, group - g0);
+        const int n = kv_len[b];
+        int tile_lo;
+        row_tiles(n, window, &tile_lo);
+        const int lo = window > 0 ? max(0, n - window) : 0;
+        const size_t slot = (size_t)c + (size_t)b * plan.pairs_per_row + pair;
+        decode_walk<D_PAD, STAGES>(smem_raw, nullptr, part_o, part_ml, slot * gmax, 1, q, kv,
+                                   block_table + (size_t)row_slot[b] * table_stride, query_start[b], heads, kv_heads,
+                                   head_dim, pages, page_size, page_shift, scale_log2, hk, group, g0, g,
+                                   tile_lo + tile, tile_lo + tile + count, lo, n);
+        f += count;
+    }
+}
+
+// out[t, h, :] from the partial results of the walks over (row, head)'s pair, in the order of the CTAs that made them.
+__global__ void decode_balanced_merge_kernel(bf16* __restrict__ out, const float* __restrict__ part_o,
+                                             const float* __restrict__ part_ml, const int32_t* __restrict__ query_start,
+                                             const int32_t* __restrict__ kv_len, int rows, int heads, int kv_heads,
+                                             int head_dim, int window, int max_ctas) {
+    __shared__ int sums[2][4];
+    const int b = blockIdx.x, h = blockIdx.y;
+    int before = 0, total = 0, unused;                               // tiles of the rows before b, and of all rows
+    for (int r = threadIdx.x; r < rows; r += blockDim.x) {
+        const int v = row_tiles(kv_len[r], window, &unused);
+        total += v;
+        if (r < b) before += v;
+    }
+#pragma unroll
+    for (int d = 16; d > 0; d >>= 1) {
+        before += __shfl_xor_sync(0xffffffffu, before, d);
+        total += __shfl_xor_sync(0xffffffffu, total, d);
+    }
+    if ((threadIdx.x & 31) == 0) { sums[0][threadIdx.x >> 5] = before; sums[1][threadIdx.x >> 5] = total; }
+    __syncthreads();
+    before = sums[0][0] + sums[0][1] + sums[0][2] + sums[0][3];
+    total = sums[1][0] + sums[1][1] + sums[1][2] + sums[1][3];
+    const int group = heads / kv_heads, m_tiles = (group + 15) / 16, gmax = min(16, group);
+    const int pairs_per_row = kv_heads * m_tiles;
+    const long long tiles = (long long)total * pairs_per_row;
+    const long long want = tiles / 2 > 1 ? tiles / 2 : 1;
+    const int ctas = (int)(want < max_ctas ? want : max_ctas);
+    const int tiles_b = row_tiles(kv_len[b], window, &unused);
+    const int hk = h / group, in_group = h - hk * group;
+    const int pair = hk * m_tiles + in_group / 16, r = in_group % 16;
+    const int t = query_start[b];
+    if (tiles_b == 0) {
+        for (int d = threadIdx.x; d < head_dim; d += blockDim.x) out[((size_t)t * heads + h) * head_dim + d] = __float2bfloat16_rn(0.f);
+        return;
+    }
+    // CTA c owns tiles [c T / C, (c + 1) T / C): tile f belongs to the largest c with c T / C <= f
+    const long long f_lo = (long long)before * pairs_per_row + (long long)pair * tiles_b, f_hi = f_lo + tiles_b - 1;
+    const int c_lo = (int)(((f_lo + 1) * ctas - 1) / tiles), c_hi = (int)(((f_hi + 1) * ctas - 1) / tiles);
+    const size_t p = (size_t)b * pairs_per_row + pair;
+    merge_partials(out + ((size_t)t * heads + h) * head_dim, part_o, part_ml, ((size_t)c_lo + p) * gmax + r, gmax,
+                   c_hi - c_lo + 1, head_dim);
+}
+
+template <int D_PAD, int STAGES>
+static int launch_decode_balanced(bf16* out, float* part_o, float* part_ml, const bf16* q, const bf16* kv,
+                                  const int32_t* block_table, int table_stride, const int32_t* row_slot,
+                                  const int32_t* query_start, const int32_t* kv_len, int rows, int heads, int kv_heads,
+                                  int head_dim, int pages, int page_size, float scale, int window, int ctas,
+                                  cudaStream_t s) {
+    auto kernel = decode_balanced_kernel<D_PAD, STAGES>;
+    const size_t smem = decode_smem<D_PAD>(STAGES);
+    HB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    kernel<<<ctas, 128, smem, s>>>(part_o, part_ml, q, kv, block_table, table_stride, row_slot, query_start, kv_len, rows,
+                                   heads, kv_heads, head_dim, pages, page_size, log2_exact(page_size),
+                                   scale * 1.4426950408889634f, window);
+    HB_LAUNCH_CHECK("attention_decode_balanced");
+    decode_balanced_merge_kernel<<<dim3(rows, heads), 128, 0, s>>>(out, part_o, part_ml, query_start, kv_len, rows, heads,
+                                                                   kv_heads, head_dim, window, ctas);
+    HB_LAUNCH_CHECK("attention_decode_balanced_merge");
+    return 0;
+}
+
+// Floats of scratch for `ctas` CTAs: one partial (head_dim values, a maximum and a sum) per walk and head.
+extern "C" size_t hb_attention_decode_balanced_scratch_floats(int rows, int heads, int kv_heads, int head_dim, int ctas) {
+    const int group = heads / kv_heads, m_tiles = (group + 15) / 16, gmax = group < 16 ? group : 16;
+    return ((size_t)ctas + (size_t)rows * kv_heads * m_tiles) * gmax * (head_dim + 2);
+}
+
+extern "C" int hb_attention_decode_bf16_balanced(void* out, float* scratch, const void* q, const void* kv,
+                                                 const int32_t* block_table, int table_stride, const int32_t* row_slot,
+                                                 const int32_t* query_start, const int32_t* kv_len, int rows, int heads,
+                                                 int kv_heads, int head_dim, int pages, int page_size, float scale,
+                                                 int window, int ctas, hb_stream stream) {
+    if (rows == 0) return 0;
+    if (head_dim % 16 || head_dim > 256 || head_dim < 16)
+        HB_REFUSE("attention_decode_bf16_balanced: head_dim %d is no multiple of 16 up to 256", head_dim);
+    if (kv_heads < 1 || heads % kv_heads) HB_REFUSE("attention_decode_bf16_balanced: %d heads, %d kv heads", heads, kv_heads);
+    if (heads > 65535) HB_REFUSE("attention_decode_bf16_balanced: %d heads", heads);
+    if (rows > HB_BALANCED_ROWS) HB_REFUSE("attention_decode_bf16_balanced: %d rows, at most %d", rows, HB_BALANCED_ROWS);
+    if (ctas < 1 || ctas > 65535) HB_REFUSE("attention_decode_bf16_balanced: %d CTAs (1 to 65535)", ctas);
+    if (!scratch) HB_REFUSE("attention_decode_bf16_balanced: needs scratch memory");
+    if (!(scale > 0.f)) HB_REFUSE("attention_decode_bf16_balanced: the score scale must be positive");
+    const size_t slots = hb_attention_decode_balanced_scratch_floats(rows, heads, kv_heads, head_dim, ctas) / (head_dim + 2);
+    float* part_o = scratch;
+    float* part_ml = scratch + slots * head_dim;
+    cudaStream_t s = (cudaStream_t)stream;
+#define HB_ARGS (bf16*)out, part_o, part_ml, (const bf16*)q, (const bf16*)kv, block_table, table_stride, row_slot, \
+    query_start, kv_len, rows, heads, kv_heads, head_dim, pages, page_size, scale, window, ctas, s
+    if (head_dim <= 64) return launch_decode_balanced<64, 4>(HB_ARGS);
+    if (head_dim <= 128) return launch_decode_balanced<128, 2>(HB_ARGS);
+    return launch_decode_balanced<256, 2>(HB_ARGS);
 #undef HB_ARGS
 }
 

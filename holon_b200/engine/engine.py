@@ -68,7 +68,7 @@ class Engine:
         self._graphs: dict[int, tuple] = {}
         self._graph_pool = None
         self._use_graphs = config.cuda_graphs and self.device.type == "cuda"
-        self._buckets = tuple(x for x in GRAPH_BUCKETS if x <= config.max_seqs)
+        self._buckets = tuple(x for x in GRAPH_BUCKETS if x < config.max_seqs) + (config.max_seqs,)   # the fullest batch too
         self._host_tokens = [torch.zeros(config.max_seqs + 1, dtype=torch.int32) for _ in range(2)]
         if self.device.type == "cuda":
             self._host_tokens = [t.pin_memory() for t in self._host_tokens]
@@ -229,19 +229,27 @@ class Engine:
         fill = {"sample_slot": self.built.cache.padding_slot}
         padded = {k: np.concatenate([v, np.full(pad, fill.get(k, 0), dtype=v.dtype)]) for k, v in arrays.items()}
         step = runner.context(entries, pad_rows=pad, extra=padded)
-        if bucket not in self._graphs:
+        kernels = self.built.ctx.kernels
+        lens = step.rows.host_kv_len
+        mode = kernels.decode_mode(lens[:n] if lens is not None else None) if hasattr(kernels, "decode_mode") else None
+        key = (bucket, mode)                                       # a graph per way of sharing out the keys it was captured with
+        if key not in self._graphs:
             step.rows.max_kv = self.config.max_model_len          # the captured launch must serve any length
             out = torch.empty(bucket, dtype=torch.int32, device=self.device)
-            self._forward(step, False, bucket, out)                # warm-up, not captured
-            torch.cuda.current_stream(self.device).synchronize()
-            graph, kernels = torch.cuda.CUDAGraph(), self.built.ctx.kernels
-            before = kernels.launches
-            with torch.cuda.graph(graph, pool=self._graph_pool):
-                self._forward(step, False, bucket, out)
-            captured, kernels.launches = kernels.launches - before, before       # recorded, not run
+            kernels.decode_pinned = mode
+            try:
+                self._forward(step, False, bucket, out)            # warm-up, not captured
+                torch.cuda.current_stream(self.device).synchronize()
+                graph = torch.cuda.CUDAGraph()
+                before = kernels.launches
+                with torch.cuda.graph(graph, pool=self._graph_pool):
+                    self._forward(step, False, bucket, out)
+                captured, kernels.launches = kernels.launches - before, before   # recorded, not run
+            finally:
+                kernels.decode_pinned = None
             self._graph_pool = self._graph_pool or graph.pool()
-            self._graphs[bucket] = (graph, out, captured)
-        graph, out, captured = self._graphs[bucket]
+            self._graphs[key] = (graph, out, captured)
+        graph, out, captured = self._graphs[key]
         graph.replay()
         self.graph_steps += 1
         self._graph_launches += captured

@@ -54,6 +54,16 @@ class CudaKernels:
         if self.gemm not in ("cublas", "tcgen05"):
             raise KernelError(f"HOLON_B200_GEMM must be cublas or tcgen05, not {self.gemm!r}")
         self.attention_bf16 = "fast"          # "generic" forces the CUDA-core kernel for bfloat16 too (tests)
+        # How the keys of rows that bring one token are shared out when one CTA per (row, kv head) is too few:
+        # "splits" (every row cut into the same number of parts), "balanced" (every CTA of one GPU-filling wave takes
+        # the same number of 64-key tiles, whatever the rows' lengths) or "auto" (balanced for a batch with one row far
+        # longer than the others, where equal cuts leave most CTAs with almost nothing; see decode_mode).
+        self.decode_attention = os.environ.get("HOLON_B200_DECODE_ATTENTION", "auto")
+        if self.decode_attention not in ("auto", "balanced", "splits"):
+            raise KernelError(f"HOLON_B200_DECODE_ATTENTION must be auto, balanced or splits, not {self.decode_attention!r}")
+        self.decode_pinned = None             # set around a CUDA-graph capture: the captured launches keep this mode
+        self.SMS = torch.cuda.get_device_properties(self.device).multi_processor_count
+        self.decode_ctas = None               # tests: a fixed number of CTAs for the balanced kernel
 
     # ------------------------------------------------------------------ plumbing
     def _call(self, name: str, *args) -> None:
@@ -152,10 +162,23 @@ class CudaKernels:
         sizes = (heads, kv_heads, head_dim, kv.shape[0], kv.shape[3], ctypes.c_float(scale), int(window))
         if rows.n_decode:
             splits = self.decode_splits(rows.n_decode, heads, kv_heads, rows.max_kv)
-            floats = rows.n_decode * heads * splits * (head_dim + 2) if splits > 1 else 0
-            scratch = torch.empty(floats, dtype=torch.float32, device=self.device) if floats else None
-            self._call("hb_attention_decode_bf16", self._p(out), self._p(scratch), self._p(q), self._p(kv), *common,
-                       rows.n_decode, *sizes, splits)
+            lens = rows.host_kv_len[:rows.n_decode] if rows.host_kv_len is not None else None
+            mode = self.decode_pinned or self.decode_mode(lens)
+            if splits > 1 and mode == "balanced" and rows.n_decode <= self.BALANCED_ROWS:
+                pairs = rows.n_decode * kv_heads * (-(-(heads // kv_heads) // 16))
+                slots = self.SMS * (1 if head_dim > 128 else 3)       # CTAs of this kernel that one wave holds
+                if pairs <= slots:                                    # a whole number of CTAs per (row, kv head): rows of
+                    slots = pairs * (slots // pairs)                  # equal length are then cut at their own ends only
+                ctas = self.decode_ctas or max(1, min(slots, pairs * (-(-rows.max_kv // 64)) // 2))
+                floats = (ctas + pairs) * min(16, heads // kv_heads) * (head_dim + 2)
+                scratch = torch.empty(floats, dtype=torch.float32, device=self.device)
+                self._call("hb_attention_decode_bf16_balanced", self._p(out), self._p(scratch), self._p(q), self._p(kv),
+                           *common, rows.n_decode, *sizes, ctas)
+            else:
+                floats = rows.n_decode * heads * splits * (head_dim + 2) if splits > 1 else 0
+                scratch = torch.empty(floats, dtype=torch.float32, device=self.device) if floats else None
+                self._call("hb_attention_decode_bf16", self._p(out), self._p(scratch), self._p(q), self._p(kv), *common,
+                           rows.n_decode, *sizes, splits)
         if rows.n_rows > rows.n_decode:
             qs = rows.host_query_start
             counts = [int(qs[b + 1]) - int(qs[b]) for b in range(rows.n_decode, rows.n_rows)]
@@ -166,7 +189,20 @@ class CudaKernels:
                 self._call("hb_attention_prefill_bf16", self._p(out), self._p(q), self._p(kv), *common, rows.n_decode,
                            rows.n_rows, sum((n + 63) // 64 for n in counts), *sizes)
 
-    SMS = 148
+    SMS = 148                                 # replaced by the device's count when the table is made
+    BALANCED_ROWS = 256                       # rows the balanced decode kernel takes (its prefix array)
+
+    def decode_mode(self, kv_lens) -> str:
+        """"balanced" or "splits" for decode rows that hold `kv_lens` tokens (host values; None: unknown). Equal cuts
+        are a little faster while rows are alike (no walk crosses a row's end, one table read less before the first
+        tile); one long row among short ones is where they lose: measured at 32 kv-head-8 rows, one of 8,192 tokens
+        and 31 of 500, 36 µs against 56 µs."""
+        if self.decode_attention != "auto":
+            return self.decode_attention
+        if kv_lens is None or len(kv_lens) < 2:
+            return "splits"
+        longest, total = int(max(kv_lens)), int(sum(int(v) for v in kv_lens))
+        return "balanced" if longest >= 4096 and longest * len(kv_lens) >= 8 * total else "splits"
 
     def decode_splits(self, rows: int, heads: int, kv_heads: int, max_kv: int) -> int:
         """Parts the keys of a decode row are cut into. Three CTAs fit an SM; a launch of `ctas * parts` CTAs runs in

@@ -1,4 +1,4 @@
-"""Times single kernels of the kernel table with CUDA events, the L2 flushed between runs.
+"""Times single kernels of the kernel table with CUDA events, the L2 replaced between runs.
 
     python -m holon_b200.kernels.microbench decode_attention [--rows 8 64 1] [--context 8192] [--splits 4 6 13]
     python -m holon_b200.kernels.microbench gemm [--rows 2048] [--shapes qkv o gate_up down]
@@ -21,11 +21,13 @@ SHAPES = {"qkv": (6144, 4096), "o": (4096, 4096), "gate_up": (24576, 4096), "dow
 
 
 def timed(fn, flush, runs: int = 6) -> float:
-    """Microseconds of the fastest of `runs` calls, each after the L2 was overwritten."""
+    """Microseconds of the fastest of `runs` calls, each after a buffer larger than the L2 was read through it
+    (reading leaves clean lines; lines left dirty by a write would be written back during the timed kernel and
+    take a share of its bandwidth)."""
     best = float("inf")
     for i in range(runs):
         if flush is not None:
-            flush.zero_()
+            flush.view(torch.int32).sum()
         start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         start.record()
         fn()
@@ -38,7 +40,7 @@ def timed(fn, flush, runs: int = 6) -> float:
 
 def decode_attention(k, args) -> None:
     heads, kv_heads, d, page = 32, 8, 128, 64
-    flush = torch.empty(256 << 20, device=k.device, dtype=torch.uint8)
+    flush = torch.zeros(256 << 20, device=k.device, dtype=torch.uint8)
     for rows in args.rows:
         per = args.context // page
         kv = torch.randn(rows * per + 1, 2, kv_heads, page, d, device=k.device, dtype=torch.bfloat16)
@@ -50,11 +52,17 @@ def decode_attention(k, args) -> None:
                      rows, rows, rows, 1, args.context)
         moved = rows * args.context * kv_heads * d * 2 * 2
         planned = k.decode_splits(rows, heads, kv_heads, args.context)
+        call = lambda: k.paged_attention(out, q, kv, table, batch, 1 / math.sqrt(d), 0)   # noqa: E731
+        k.decode_attention = "balanced"
+        t = timed(call, flush)
+        print(f"decode attention rows {rows} context {args.context} balanced: {t:7.1f} us  {moved / t / 1e6:5.2f} TB/s")
+        k.decode_attention = "splits"
         for splits in (args.splits or [planned]):
             k._splits[(rows, heads, kv_heads, -(-args.context // 64))] = splits
-            t = timed(lambda: k.paged_attention(out, q, kv, table, batch, 1 / math.sqrt(d), 0), flush)
+            t = timed(call, flush)
             print(f"decode attention rows {rows} context {args.context} splits {splits}: {t:7.1f} us  {moved / t / 1e6:5.2f} TB/s"
                   + ("  (the planner's choice)" if splits == planned else ""))
+        k.decode_attention = "balanced"
         k._splits.clear()
 
 

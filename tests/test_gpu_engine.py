@@ -139,3 +139,23 @@ def test_stop_tokens_while_a_step_is_in_flight(model, overlap):
         assert g == b[:b.index(s[0]) + 1]
     engine.built.cache.check()
     assert not engine.built.cache.live and not engine.has_work()
+
+
+def test_one_long_request_among_short_ones_takes_the_balanced_decode_graph(tmp_path):
+    """A batch with one row far longer than the rest decodes through a graph captured with the keys shared out evenly;
+    alike rows keep the graph with equal cuts. Both give the tokens of a run without graphs."""
+    folder = make_folder(tmp_path, "a")
+    config, _ = plain.read_folder(folder)
+    prompts = [random_prompt(config["vocab_size"], n, 7 + n) for n in (4200, 30, 12, 55, 9, 21, 40, 3, 17, 26, 33, 8)]
+    params = SamplingParams(temperature=0.0, max_tokens=12)          # the short ones still decode when the long one starts to
+    kw = dict(page_size=64, max_seqs=12, max_model_len=4608, max_step_tokens=1024, chunk_with_decode=64)
+    engine = engine_of(folder, "bfloat16", **kw)
+    got = engine.generate(prompts, params)
+    modes = {mode for _, mode in engine._graphs}
+    assert "balanced" in modes, modes
+    short = engine.generate(prompts[1:], params)
+    assert {mode for _, mode in engine._graphs} == {"balanced", "splits"}
+    plain_run = engine_of(folder, "bfloat16", cuda_graphs=False, **kw)
+    plain_run.built.ctx.kernels.decode_attention = "splits"
+    assert plain_run.generate(prompts, params) == got and got[1:] == short
+    engine.built.cache.check()

@@ -246,6 +246,41 @@ def test_paged_attention(K, dtype, geometry, kind, window):
     assert torch.equal(out, again)                                            # run to run identical
 
 
+@pytest.mark.parametrize("geometry", [(32, 8, 128, 64), (40, 2, 64, 16), (6, 1, 48, 4), (16, 4, 256, 128)])
+@pytest.mark.parametrize("window", [0, 300])
+def test_decode_attention_with_keys_shared_out_evenly(K, geometry, window):
+    """The decode kernel whose CTAs each take an equal stretch of all rows' 64-key tiles: rows of very different
+    lengths, with CTA counts that put a stretch's ends inside rows, at rows' ends and across several short rows, with
+    more CTAs than tiles, and with a group of 20 heads (two 16-head tiles per kv head); against the plain formula and
+    against the kernel that cuts every row into equal parts."""
+    heads, kv_heads, head_dim, page = geometry
+    spec = [(2999, 1), (0, 1), (63, 1), (64, 1), (700, 1), (5, 1), (1300, 1), (127, 1), (128, 1)]
+    q, kv, table, rows = paged_case(heads, kv_heads, head_dim, page, spec, torch.bfloat16, seed=17 + window)
+    scale = 1 / math.sqrt(head_dim)
+    want = torch.empty_like(q)
+    REF.paged_attention(want, q, kv, table, rows, scale, window)
+    args = (q.to(DEV), kv.to(DEV), table.to(DEV), on_device(rows), scale, window)
+    before = K.decode_attention, K.decode_ctas
+    try:
+        K.decode_attention = "splits"
+        cut = torch.full_like(q, float("nan"), device=DEV)
+        K.paged_attention(cut, *args)
+        close(cut, want, torch.bfloat16, scale=4)
+        K.decode_attention = "balanced"
+        for ctas in (None, 1, 2, 7, 50, 443, 5000):
+            K.decode_ctas = ctas
+            out = torch.full_like(q, float("nan"), device=DEV)
+            K.paged_attention(out, *args)
+            close(out, want, torch.bfloat16, scale=4)
+            again = torch.full_like(q, float("nan"), device=DEV)
+            K.paged_attention(again, *args)
+            assert torch.equal(out, again), ctas
+    finally:
+        K.decode_attention, K.decode_ctas = before
+    assert K.decode_mode([8192] + [500] * 31) == "balanced" and K.decode_mode([8192] * 8) == "splits"
+    assert K.decode_mode([300, 20, 5000]) == "splits" and K.decode_mode(None) == "splits"
+
+
 @pytest.mark.parametrize("heads,kv_heads,page", [(8, 2, 64), (4, 4, 128), (6, 1, 64)])
 @pytest.mark.parametrize("window", [0, 100])
 def test_prefill_attention_tcgen05(K, heads, kv_heads, page, window):
