@@ -104,6 +104,13 @@ int hb_gemm_bf16_tcgen05(void* out, int out_f32, const void* x, const void* w, i
                          hb_stream stream);
 int hb_gemm_tcgen05_status(unsigned int* status);
 
+// The same product by pairs of CTAs on neighbouring SMs (tcgen05 cta_group::2: 256 x 256 tiles, each CTA loading half
+// of both operands); same arguments and modes, its own status word.
+int hb_gemm_bf16_tcgen05_pair(void* out, int out_f32, const void* x, const void* w, int m, int n, int k, int mode,
+                              int inter, hb_stream stream);
+int hb_gemm_tcgen05_pair_status(unsigned int* status);
+int hb_gemm_tcgen05_pair_width(int bn);             // tests: fix the tile width (0: chosen per launch)
+
 // The token each request sampled last, kept on the device by slot. feed: for every row r with from_last[r] != 0,
 // token_ids[query_start[r]] = last_tokens[row_slot[r]]. store: last_tokens[slots[i]] = tokens[i] for i < n.
 int hb_feed_tokens(int32_t* token_ids, const int32_t* last_tokens, const int32_t* row_slot, const int32_t* query_start,

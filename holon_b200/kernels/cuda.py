@@ -48,11 +48,14 @@ class CudaKernels:
         self.prefill_attention = os.environ.get("HOLON_B200_PREFILL_ATTENTION", "tcgen05")
         if self.prefill_attention not in ("mma", "tcgen05"):
             raise KernelError(f"HOLON_B200_PREFILL_ATTENTION must be mma or tcgen05, not {self.prefill_attention!r}")
-        # Which kernel multiplies bfloat16 matrices of more than SKINNY_ROWS rows: "cublas" (through torch, the
-        # default, as the reference uses a library there) or "tcgen05" (csrc/gemm_tcgen05.cu, SwiGLU fused).
-        self.gemm = os.environ.get("HOLON_B200_GEMM", "cublas")
-        if self.gemm not in ("cublas", "tcgen05"):
-            raise KernelError(f"HOLON_B200_GEMM must be cublas or tcgen05, not {self.gemm!r}")
+        # Which kernel multiplies bfloat16 matrices of more than SKINNY_ROWS rows: "auto" (the default: the library
+        # through torch, as the reference uses one there, except SwiGLU's gate/up product, which goes to the
+        # hand-written tcgen05 kernel with the activation in its epilogue where that is faster than the library's
+        # product plus an activation kernel), "cublas" (the library always) or "tcgen05" (csrc/gemm_tcgen05*.cu always).
+        self.gemm = os.environ.get("HOLON_B200_GEMM", "auto")
+        if self.gemm not in ("auto", "cublas", "tcgen05"):
+            raise KernelError(f"HOLON_B200_GEMM must be auto, cublas or tcgen05, not {self.gemm!r}")
+        self.gemm_pair = os.environ.get("HOLON_B200_GEMM_PAIR", "1") != "0"   # the tcgen05 product by CTA pairs
         self.attention_bf16 = "fast"          # "generic" forces the CUDA-core kernel for bfloat16 too (tests)
         # How the keys of rows that bring one token are shared out when one CTA per (row, kv head) is too few:
         # "splits" (every row cut into the same number of parts), "balanced" (every CTA of one GPU-filling wave takes
@@ -246,8 +249,9 @@ class CudaKernels:
 
     SKINNY_ROWS = 16
 
-    def linear_tcgen05(self, out, x, weight, swiglu: bool = False) -> None:
-        """The product (or, with `swiglu`, SwiGLU's silu(gate) · up) on the hand-written tcgen05 / TMA / TMEM kernel."""
+    def linear_tcgen05(self, out, x, weight, swiglu: bool = False, pair: bool | None = None) -> None:
+        """The product (or, with `swiglu`, SwiGLU's silu(gate) · up) on the hand-written tcgen05 / TMA / TMEM kernels:
+        `pair` picks the one that puts two CTAs on a 256 x 256 tile (default: self.gemm_pair)."""
         self._check(out, x, weight)
         m, k = x.shape
         n = weight.shape[0]
@@ -255,13 +259,14 @@ class CudaKernels:
         if weight.shape != (n, k) or out.shape != (m, inter if swiglu else n) or x.dtype != torch.bfloat16 \
                 or weight.dtype != torch.bfloat16 or out.dtype not in (torch.bfloat16, torch.float32):
             raise KernelError("linear_tcgen05: bfloat16 x [m, k] and w [n, k]; out [m, n] (or [m, n / 2]) bfloat16 or float32")
-        self._call("hb_gemm_bf16_tcgen05", self._p(out), int(out.dtype == torch.float32), self._p(x), self._p(weight),
-                   m, n, k, int(swiglu), inter)
+        name = "hb_gemm_bf16_tcgen05_pair" if (self.gemm_pair if pair is None else pair) else "hb_gemm_bf16_tcgen05"
+        self._call(name, self._p(out), int(out.dtype == torch.float32), self._p(x), self._p(weight), m, n, k,
+                   int(swiglu), inter)
 
     def tcgen05_status(self) -> int:
         """0, or which bounded wait inside a tcgen05 kernel (product or attention) gave up (synchronises the device)."""
         out = 0
-        for name in ("hb_gemm_tcgen05_status", "hb_attention_tcgen05_status"):
+        for name in ("hb_gemm_tcgen05_status", "hb_gemm_tcgen05_pair_status", "hb_attention_tcgen05_status"):
             status = ctypes.c_uint(0)
             if getattr(self.lib, name)(ctypes.byref(status)):
                 raise KernelError(self.lib.hb_last_error().decode())
@@ -279,9 +284,16 @@ class CudaKernels:
         if x.dtype == torch.bfloat16 and m <= self.SKINNY_ROWS and k % 8 == 0:
             self._call("hb_gemm_bf16_skinny", self._p(out), 0, self._p(x), self._p(weight), m, 2 * inter, k, 1, inter)
             return
-        if x.dtype == torch.bfloat16 and self.gemm == "tcgen05" and k % 8 == 0:
-            self.linear_tcgen05(out, x, weight, swiglu=True)
-            return
+        if x.dtype == torch.bfloat16 and k % 8 == 0 and self.gemm != "cublas":
+            # Measured at 24576 x 4096 against the library's product plus the activation kernel: by CTA pairs 66 us
+            # against 74 at 256 rows, 280 against 317 at 2,048, 555 against 627 at 4,096, but 1,226 against 1,202 at
+            # 8,192; one CTA a tile 59 against 66 at 128 rows; below about 100 rows the library wins (64 against 70).
+            if self.gemm == "tcgen05" or 192 < m <= 6144:
+                self.linear_tcgen05(out, x, weight, swiglu=True)
+                return
+            if 96 < m <= 192:
+                self.linear_tcgen05(out, x, weight, swiglu=True, pair=False)
+                return
         gate_up = torch.empty(m, 2 * inter, dtype=x.dtype, device=self.device)
         self.linear(gate_up, x, weight)
         self.silu_mul(out, gate_up)

@@ -100,13 +100,16 @@ def gemm(k, args) -> None:
         out = torch.empty(m, n, device=k.device, dtype=torch.bfloat16)
         flops = 2 * m * n * kk
         t_lib = timed(lambda: torch.mm(x, w.t(), out=out), None, 20)
-        t_own = timed(lambda: k.linear_tcgen05(out, x, w), None, 20)
-        line = f"{name:8s} rows {m}: cuBLAS {t_lib:7.1f} us ({flops / t_lib / 1e6:5.0f} TFLOP/s)  tcgen05 {t_own:7.1f} us ({flops / t_own / 1e6:5.0f} TFLOP/s)"
+        t_own = timed(lambda: k.linear_tcgen05(out, x, w, pair=False), None, 20)
+        t_pair = timed(lambda: k.linear_tcgen05(out, x, w, pair=True), None, 20)
+        line = (f"{name:8s} rows {m}: cuBLAS {t_lib:7.1f} us ({flops / t_lib / 1e6:5.0f} TFLOP/s)  tcgen05 {t_own:7.1f} us "
+                f"({flops / t_own / 1e6:5.0f})  tcgen05 CTA pairs {t_pair:7.1f} us ({flops / t_pair / 1e6:5.0f})")
         if name == "gate_up":
             act = torch.empty(m, n // 2, device=k.device, dtype=torch.bfloat16)
-            t_fused = timed(lambda: k.linear_tcgen05(act, x, w, swiglu=True), None, 20)
+            t_fused = timed(lambda: k.linear_tcgen05(act, x, w, swiglu=True, pair=False), None, 20)
+            t_fused_pair = timed(lambda: k.linear_tcgen05(act, x, w, swiglu=True, pair=True), None, 20)
             t_act = timed(lambda: k.silu_mul(act, out), None, 20)
-            line += f"  tcgen05 with SwiGLU {t_fused:7.1f} us; activation kernel alone {t_act:5.1f} us"
+            line += (f"  with SwiGLU {t_fused:7.1f} us, by pairs {t_fused_pair:7.1f} us; activation kernel alone {t_act:5.1f} us")
         print(line)
     print("tcgen05 status", k.tcgen05_status())
 

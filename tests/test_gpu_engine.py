@@ -156,6 +156,10 @@ def test_one_long_request_among_short_ones_takes_the_balanced_decode_graph(tmp_p
     short = engine.generate(prompts[1:], params)
     assert {mode for _, mode in engine._graphs} == {"balanced", "splits"}
     plain_run = engine_of(folder, "bfloat16", cuda_graphs=False, **kw)
-    plain_run.built.ctx.kernels.decode_attention = "splits"
-    assert plain_run.generate(prompts, params) == got and got[1:] == short
+    kernels = plain_run.built.ctx.kernels                            # (one kernel table per device: put the setting back)
+    before, kernels.decode_attention = kernels.decode_attention, "splits"
+    try:
+        assert plain_run.generate(prompts, params) == got and got[1:] == short
+    finally:
+        kernels.decode_attention = before
     engine.built.cache.check()

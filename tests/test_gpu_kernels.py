@@ -116,27 +116,56 @@ def test_linear_bf16_few_rows(K, m, n, k):
 
 @pytest.mark.parametrize("m,n,k", [(128, 256, 64), (128, 256, 256), (5, 40, 72), (300, 389, 96), (2048, 1024, 512),
                                    (130, 6144, 4096), (257, 4096, 12288)])
-def test_linear_tcgen05(K, m, n, k):
-    """The tcgen05 / TMA / TMEM product: whole tiles, ragged edges in every dimension, long k."""
+@pytest.mark.parametrize("pair", [False, True])
+def test_linear_tcgen05(K, m, n, k, pair):
+    """The tcgen05 / TMA / TMEM products (one CTA a tile; two CTAs a tile): whole tiles, ragged edges in every
+    dimension, long k."""
     x, w = rand(m, k, dtype=torch.bfloat16, seed=1), rand(n, k, dtype=torch.bfloat16, seed=2, scale=0.05)
     want = x.float() @ w.float().T
     for out_dtype in (torch.bfloat16, torch.float32):
         out = torch.full((m, n), float("nan"), dtype=out_dtype, device=DEV)
-        K.linear_tcgen05(out, x.to(DEV), w.to(DEV))
+        K.linear_tcgen05(out, x.to(DEV), w.to(DEV), pair=pair)
         assert K.tcgen05_status() == 0
         tol = (1.6e-2 if out_dtype == torch.bfloat16 else 2e-3) * max(1.0, want.abs().max().item())
         assert (out.float().cpu() - want).abs().max().item() <= tol
 
 
 @pytest.mark.parametrize("m,inter,k", [(128, 128, 64), (70, 176, 96), (512, 1000, 328), (300, 12288, 4096)])
-def test_swiglu_tcgen05(K, m, inter, k):
+@pytest.mark.parametrize("pair", [False, True])
+def test_swiglu_tcgen05(K, m, inter, k, pair):
     x, w = rand(m, k, dtype=torch.bfloat16, seed=3), rand(2 * inter, k, dtype=torch.bfloat16, seed=4, scale=0.1)
     gate_up = x.float() @ w.float().T
     want = torch.nn.functional.silu(gate_up[:, :inter]) * gate_up[:, inter:]
     out = torch.full((m, inter), float("nan"), dtype=torch.bfloat16, device=DEV)
-    K.linear_tcgen05(out, x.to(DEV), w.to(DEV), swiglu=True)
+    K.linear_tcgen05(out, x.to(DEV), w.to(DEV), swiglu=True, pair=pair)
     assert K.tcgen05_status() == 0
     assert (out.float().cpu() - want).abs().max().item() <= 2e-2 * max(1.0, want.abs().max().item())
+
+
+@pytest.mark.parametrize("bn", [32, 128, 144, 176, 240])
+def test_linear_tcgen05_pair_tile_widths(K, bn):
+    """The CTA-pair product at tile widths other than the one it would choose (the last 32-column piece of a tile partly
+    outside it, w's rows split 72 + 72 or 88 + 88 between the CTAs), and SwiGLU at its narrower widths."""
+    m, n, k = 300, 1000, 328
+    x, w = rand(m, k, dtype=torch.bfloat16, seed=5), rand(n, k, dtype=torch.bfloat16, seed=6, scale=0.05)
+    want = x.float() @ w.float().T
+    try:
+        K.lib.hb_gemm_tcgen05_pair_width(bn)
+        for out_dtype in (torch.bfloat16, torch.float32):
+            out = torch.full((m, n), float("nan"), dtype=out_dtype, device=DEV)
+            K.linear_tcgen05(out, x.to(DEV), w.to(DEV), pair=True)
+            assert K.tcgen05_status() == 0
+            tol = (1.6e-2 if out_dtype == torch.bfloat16 else 2e-3) * max(1.0, want.abs().max().item())
+            assert (out.float().cpu() - want).abs().max().item() <= tol
+        if bn % 64 == 0:
+            inter = n // 2
+            act = torch.nn.functional.silu(want[:, :inter]) * want[:, inter:]
+            out = torch.full((m, inter), float("nan"), dtype=torch.bfloat16, device=DEV)
+            K.linear_tcgen05(out, x.to(DEV), w.to(DEV), swiglu=True, pair=True)
+            assert K.tcgen05_status() == 0
+            assert (out.float().cpu() - act).abs().max().item() <= 2e-2 * max(1.0, act.abs().max().item())
+    finally:
+        K.lib.hb_gemm_tcgen05_pair_width(0)
 
 
 @pytest.mark.parametrize("m", [1, 8, 13, 16, 40])
@@ -275,10 +304,11 @@ def test_decode_attention_with_keys_shared_out_evenly(K, geometry, window):
             again = torch.full_like(q, float("nan"), device=DEV)
             K.paged_attention(again, *args)
             assert torch.equal(out, again), ctas
+        K.decode_attention = "auto"
+        assert K.decode_mode([8192] + [500] * 31) == "balanced" and K.decode_mode([8192] * 8) == "splits"
+        assert K.decode_mode([300, 20, 5000]) == "splits" and K.decode_mode(None) == "splits"
     finally:
         K.decode_attention, K.decode_ctas = before
-    assert K.decode_mode([8192] + [500] * 31) == "balanced" and K.decode_mode([8192] * 8) == "splits"
-    assert K.decode_mode([300, 20, 5000]) == "splits" and K.decode_mode(None) == "splits"
 
 
 @pytest.mark.parametrize("heads,kv_heads,page", [(8, 2, 64), (4, 4, 128), (6, 1, 64)])
