@@ -29,17 +29,21 @@ __device__ __forceinline__ void mma16816(float (&c)[4], uint32_t a0, uint32_t a1
 }
 
 // MT tiles of 16 weight rows per CTA, NT tiles of 8 rows of x.
-template <int MT, int NT, int SK_UNROLL>
-__global__ void __launch_bounds__(SK_WARPS * 32) gemm_skinny_kernel(void* __restrict__ out, int out_f32,
+template <int MT, int NT, int SK_UNROLL, int MIN_CTAS>
+__global__ void __launch_bounds__(SK_WARPS * 32, MIN_CTAS) gemm_skinny_kernel(void* __restrict__ out, int out_f32,
                                                                     const bf16* __restrict__ x, const bf16* __restrict__ w,
                                                                     int m, int n, int k, int mode, int inter) {
     __shared__ float red[SK_WARPS][MT * 16][NT * 8 + 1];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, r = lane >> 2, c = lane & 3;
     int row0[MT];                                        // first weight row of each tile
     int limit[MT];                                       // rows below this exist
+    constexpr int HALF = MT > 1 ? MT / 2 : 1;           // mode 1: the CTA's gate tiles, then as many up tiles
     if (mode == 1) {
-        row0[0] = blockIdx.x * 16; limit[0] = inter;
-        if (MT > 1) { row0[MT - 1] = inter + blockIdx.x * 16; limit[MT - 1] = 2 * inter; }
+#pragma unroll
+        for (int t = 0; t < HALF; ++t) {
+            row0[t] = (blockIdx.x * HALF + t) * 16; limit[t] = inter;
+            if (MT > 1) { row0[HALF + t] = inter + row0[t]; limit[HALF + t] = 2 * inter; }
+        }
     } else {
 #pragma unroll
         for (int t = 0; t < MT; ++t) { row0[t] = (blockIdx.x * MT + t) * 16; limit[t] = n; }
@@ -102,7 +106,7 @@ __global__ void __launch_bounds__(SK_WARPS * 32) gemm_skinny_kernel(void* __rest
             red[warp][a * 16 + r + 8][b * 8 + c * 2 + 1] = acc[a][b][3];
         }
     __syncthreads();
-    const int rows_out = mode == 1 ? 16 : MT * 16;
+    const int rows_out = mode == 1 ? HALF * 16 : MT * 16;
     const int width = mode == 1 ? inter : n;
     for (int i = threadIdx.x; i < rows_out * m; i += SK_WARPS * 32) {
         const int rr = i % rows_out, tok = i / rows_out;
@@ -110,13 +114,12 @@ __global__ void __launch_bounds__(SK_WARPS * 32) gemm_skinny_kernel(void* __rest
 #pragma unroll
         for (int wv = 0; wv < SK_WARPS; ++wv) v += red[wv][rr][tok];
         int col = row0[0] + rr;
+        if (MT > 1 && rr >= 16) col = row0[rr >> 4] + (rr & 15);
         if (mode == 1) {
             float u = 0.f;
 #pragma unroll
-            for (int wv = 0; wv < SK_WARPS; ++wv) u += red[wv][(MT - 1) * 16 + rr][tok];
+            for (int wv = 0; wv < SK_WARPS; ++wv) u += red[wv][HALF * 16 + rr][tok];
             v = v / (1.f + expf(-v)) * u;
-        } else if (MT > 1 && rr >= 16) {
-            col = row0[rr >> 4] + (rr & 15);
         }
         if (col < width) {
             if (out_f32) ((float*)out)[(size_t)tok * width + col] = v;
@@ -136,20 +139,28 @@ extern "C" int hb_gemm_bf16_skinny(void* out, int out_f32, const void* x, const 
     if ((((uintptr_t)out | (uintptr_t)x | (uintptr_t)w) % 16) != 0) HB_REFUSE("gemm_bf16_skinny: pointers must be 16-byte aligned");
     if (mode != 0 && mode != 1) HB_REFUSE("gemm_bf16_skinny: mode %d", mode);
     cudaStream_t s = (cudaStream_t)stream;
+    static int sms = 0;
+    if (sms == 0) {
+        int device = 0;
+        HB_CUDA(cudaGetDevice(&device));
+        HB_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device));
+    }
     const int nt = m <= 8 ? 1 : 2;
     if (mode == 1) {
         if (inter < 1) HB_REFUSE("gemm_bf16_skinny: inter = %d", inter);
         const int grid = (inter + 15) / 16;
-        if (nt == 1) gemm_skinny_kernel<2, 1, 4><<<grid, SK_WARPS * 32, 0, s>>>(out, out_f32, (const bf16*)x, (const bf16*)w, m, n, k, 1, inter);
-        else gemm_skinny_kernel<2, 2, 4><<<grid, SK_WARPS * 32, 0, s>>>(out, out_f32, (const bf16*)x, (const bf16*)w, m, n, k, 1, inter);
+        if (nt == 1) gemm_skinny_kernel<2, 1, 4, 2><<<grid, SK_WARPS * 32, 0, s>>>(out, out_f32, (const bf16*)x, (const bf16*)w, m, n, k, 1, inter);
+        else gemm_skinny_kernel<2, 2, 4, 2><<<grid, SK_WARPS * 32, 0, s>>>(out, out_f32, (const bf16*)x, (const bf16*)w, m, n, k, 1, inter);
     } else {
         if (n < 1) HB_REFUSE("gemm_bf16_skinny: n = %d", n);
-        const bool wide = n >= 32 * 2 * 148;             // enough rows to give every SM two CTAs of 32 rows
+        const bool wide = n >= 32 * 2 * sms;             // enough rows to give every SM two CTAs of 32 rows
         const int grid = wide ? (n + 31) / 32 : (n + 15) / 16;
-        if (wide && nt == 1) gemm_skinny_kernel<2, 1, 4><<<grid, SK_WARPS * 32, 0, s>>>(out, out_f32, (const bf16*)x, (const bf16*)w, m, n, k, 0, 0);
-        else if (wide) gemm_skinny_kernel<2, 2, 4><<<grid, SK_WARPS * 32, 0, s>>>(out, out_f32, (const bf16*)x, (const bf16*)w, m, n, k, 0, 0);
-        else if (nt == 1) gemm_skinny_kernel<1, 1, 8><<<grid, SK_WARPS * 32, 0, s>>>(out, out_f32, (const bf16*)x, (const bf16*)w, m, n, k, 0, 0);
-        else gemm_skinny_kernel<1, 2, 8><<<grid, SK_WARPS * 32, 0, s>>>(out, out_f32, (const bf16*)x, (const bf16*)w, m, n, k, 0, 0);
+        if (wide && nt == 1) gemm_skinny_kernel<2, 1, 4, 2><<<grid, SK_WARPS * 32, 0, s>>>(out, out_f32, (const bf16*)x, (const bf16*)w, m, n, k, 0, 0);
+        else if (wide) gemm_skinny_kernel<2, 2, 4, 2><<<grid, SK_WARPS * 32, 0, s>>>(out, out_f32, (const bf16*)x, (const bf16*)w, m, n, k, 0, 0);
+        else if (nt == 1 && grid > 2 * sms && grid <= 3 * sms)       // one wave of three CTAs per SM instead of one and a bit of two
+            gemm_skinny_kernel<1, 1, 4, 3><<<grid, SK_WARPS * 32, 0, s>>>(out, out_f32, (const bf16*)x, (const bf16*)w, m, n, k, 0, 0);
+        else if (nt == 1) gemm_skinny_kernel<1, 1, 8, 2><<<grid, SK_WARPS * 32, 0, s>>>(out, out_f32, (const bf16*)x, (const bf16*)w, m, n, k, 0, 0);
+        else gemm_skinny_kernel<1, 2, 8, 2><<<grid, SK_WARPS * 32, 0, s>>>(out, out_f32, (const bf16*)x, (const bf16*)w, m, n, k, 0, 0);
     }
     HB_LAUNCH_CHECK("gemm_bf16_skinny");
     return 0;
