@@ -71,6 +71,31 @@ __global__ void add_rmsnorm_kernel(TD* __restrict__ out, TH* h, const TD* __rest
     const TD* dr = delta ? delta + t * dim : nullptr;
     const bool write_back = delta != nullptr && index == nullptr;
     float ss = 0.f;
+    if (VEC && dim <= (int)blockDim.x * 4) {
+        // A thread holds its (at most) four values in registers and reads the weight before the block-wide sum, so
+        // that load's latency passes while the sum is formed; the values and their order are those of the loops below.
+        const int i = threadIdx.x * 4;
+        float v[4] = {0.f, 0.f, 0.f, 0.f}, w[4] = {0.f, 0.f, 0.f, 0.f};
+        if (i < dim) {
+            float d[4];
+            Vec4<TH>::load(hr + i, v);
+            if (dr) {
+                Vec4<TD>::load(dr + i, d);
+#pragma unroll
+                for (int k = 0; k < 4; ++k) v[k] += d[k];
+            }
+            Vec4<TW>::load(weight + i, w);
+            if (write_back) Vec4<TH>::store(hr + i, v);
+            ss = v[0] * v[0] + v[1] * v[1] + v[2] * v[2] + v[3] * v[3];
+        }
+        const float rstd = rsqrtf(block_sum(ss, scratch) / (float)dim + eps);
+        if (i < dim) {
+#pragma unroll
+            for (int k = 0; k < 4; ++k) v[k] = v[k] * rstd * (w[k] + offset);
+            Vec4<TD>::store(out + (size_t)r * dim + i, v);
+        }
+        return;
+    }
     if (VEC) {
         for (int i = threadIdx.x * 4; i < dim; i += blockDim.x * 4) {
             float v[4], d[4];
@@ -120,7 +145,8 @@ static int launch_add_rmsnorm(void* out, void* h, const void* delta, const void*
     auto kernel = vec ? add_rmsnorm_kernel<TH, TD, TW, true> : add_rmsnorm_kernel<TH, TD, TW, false>;
     if (smem > 48 * 1024) HB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     const int per = vec ? 4 : 1;
-    const int threads = dim >= 4096 * per ? 1024 : (dim >= 1024 * per ? 512 : (dim >= 256 * per ? 256 : 128));
+    int threads = dim >= 4096 * per ? 1024 : (dim >= 1024 * per ? 512 : (dim >= 256 * per ? 256 : 128));
+    if (vec && dim <= 4096 && rows <= 256) threads = (dim / 4 + 31) / 32 * 32;   // few rows (latency counts): a row in one pass, four values a thread in registers
     kernel<<<rows, threads, smem, s>>>((TD*)out, (TH*)h, (const TD*)delta, (const TW*)weight, eps, offset, index, dim);
     HB_LAUNCH_CHECK("add_rmsnorm");
     return 0;
