@@ -2,9 +2,9 @@
 
 Every method takes torch tensors on one CUDA device, checks what the kernel assumes (device, dtype, contiguity,
 shapes) and enqueues the kernel on torch's current stream. There is no other path: a size a kernel refuses raises
-`KernelError` with the kernel's own message. bfloat16 matrix products go to cuBLAS through torch, as the
-reference's go through `torch.nn.functional.linear` (std/holon_std/ops/units.py:223-229); float32 products run
-the library's own true 32-bit kernel.
+`KernelError` with the kernel's own message. Plain bfloat16 matrix products of more than 16 rows go to cuBLAS through
+torch, as the reference's go through `torch.nn.functional.linear` (std/holon_std/ops/units.py:223-229); products
+of up to 16 rows, SwiGLU's product with its activation, and float32 products run the library's own kernels.
 """
 from __future__ import annotations
 
@@ -65,7 +65,7 @@ class CudaKernels:
         if self.decode_attention not in ("auto", "balanced", "splits"):
             raise KernelError(f"HOLON_B200_DECODE_ATTENTION must be auto, balanced or splits, not {self.decode_attention!r}")
         self.decode_pinned = None             # set around a CUDA-graph capture: the captured launches keep this mode
-        self.SMS = torch.cuda.get_device_properties(self.device).multi_processor_count
+        self.sms = torch.cuda.get_device_properties(self.device).multi_processor_count
         self.decode_ctas = None               # tests: a fixed number of CTAs for the balanced kernel
 
     # ------------------------------------------------------------------ plumbing
@@ -169,7 +169,7 @@ class CudaKernels:
             mode = self.decode_pinned or self.decode_mode(lens)
             if splits > 1 and mode == "balanced" and rows.n_decode <= self.BALANCED_ROWS:
                 pairs = rows.n_decode * kv_heads * (-(-(heads // kv_heads) // 16))
-                slots = self.SMS * (1 if head_dim > 128 else 3)       # CTAs of this kernel that one wave holds
+                slots = self.sms * (1 if head_dim > 128 else 3)       # CTAs of this kernel that one wave holds
                 if pairs <= slots:                                    # a whole number of CTAs per (row, kv head): rows of
                     slots = pairs * (slots // pairs)                  # equal length are then cut at their own ends only
                 ctas = self.decode_ctas or max(1, min(slots, pairs * (-(-rows.max_kv // 64)) // 2))
@@ -192,7 +192,6 @@ class CudaKernels:
                 self._call("hb_attention_prefill_bf16", self._p(out), self._p(q), self._p(kv), *common, rows.n_decode,
                            rows.n_rows, sum((n + 63) // 64 for n in counts), *sizes)
 
-    SMS = 148                                 # replaced by the device's count when the table is made
     BALANCED_ROWS = 256                       # rows the balanced decode kernel takes (its prefix array)
 
     def decode_mode(self, kv_lens) -> str:
@@ -215,7 +214,7 @@ class CudaKernels:
         (plugins/holon_plugins/kernels/triton_attn/plugin.py:40-96)."""
         key = (rows, heads, kv_heads, -(-max_kv // 64))
         if key not in self._splits:
-            ctas, tiles, slots = rows * kv_heads * (-(-(heads // kv_heads) // 16)), key[3], 3 * self.SMS
+            ctas, tiles, slots = rows * kv_heads * (-(-(heads // kv_heads) // 16)), key[3], 3 * self.sms
             cost = lambda s: -(-ctas * s // slots) * (-(-tiles // s) + 1)          # noqa: E731
             self._splits[key] = min(range(1, max(1, min(64, tiles)) + 1), key=lambda s: (cost(s), s))
         return self._splits[key]
