@@ -252,6 +252,9 @@ def run_ours(args) -> dict:
     for b in (1, 64):
         r = decode_run(engine, b, context, max(8, args.steps // 2), args.warmup, seed=11 + b)
         points[f"decode_b{b}"] = round(r["tokens"] / r["device_ms"] * 1e3, 1)
+    for b in (1, 8, 64):                                             # the same with 2,048-token prompts and 256 decoded tokens
+        r = decode_run(engine, b, 2048 + 256, max(8, args.steps // 2), args.warmup, seed=41 + b)
+        points[f"decode_b{b}_prompt2048"] = round(r["tokens"] / r["device_ms"] * 1e3, 1)
     ms_per_step = main["device_ms"] / args.steps
     value = main["tokens"] / main["device_ms"] * 1e3
     step_bytes = numbers["weight_bytes"] + batch * main["mean_context"] * numbers["kv_bytes_per_token"]
