@@ -33,13 +33,14 @@ class Rows:
     Rows that bring one token come first (`n_decode` of them)."""
 
     __slots__ = ("row_slot", "query_start", "kv_len", "n_rows", "n_tokens", "n_decode", "max_q", "max_kv",
-                 "host_query_start", "host_kv_len")
+                 "host_query_start", "host_kv_len", "plan")
 
     def __init__(self, row_slot, query_start, kv_len, n_rows, n_tokens, n_decode, max_q, max_kv,
                  host_query_start=None, host_kv_len=None) -> None:
         self.row_slot, self.query_start, self.kv_len = row_slot, query_start, kv_len
         self.n_rows, self.n_tokens, self.n_decode, self.max_q, self.max_kv = n_rows, n_tokens, n_decode, max_q, max_kv
         self.host_query_start, self.host_kv_len = host_query_start, host_kv_len
+        self.plan: dict = {}                           # what the kernel table worked out for these rows, for the next layer
 
 
 class GroupStep:

@@ -40,6 +40,8 @@ class CudaKernels:
         self.lib = ctypes.CDLL(str(self.path))
         self.lib.hb_last_error.restype = ctypes.c_char_p
         self._fn = {}
+        self._index = self.device.index if self.device.index is not None else torch.cuda.current_device()
+        self._raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
         self.launches = 0
         self._splits: dict = {}
         # Which kernel attends for rows of several tokens: "tcgen05" (csrc/attention_tcgen05.cu, for head size 128 and
@@ -74,19 +76,25 @@ class CudaKernels:
         if fn is None:
             fn = self._fn[name] = getattr(self.lib, name)
             fn.restype = ctypes.c_int
-        code = fn(*args, ctypes.c_void_p(torch.cuda.current_stream(self.device).cuda_stream))
+        code = fn(*args, ctypes.c_void_p(self._stream()))
         self.launches += 1
         if code:
             raise KernelError(f"{name}: {self.lib.hb_last_error().decode()}")
 
+    def _stream(self) -> int:
+        """The handle of torch's current stream on the device (a few hundred kernels a step ask for it)."""
+        if self._raw_stream is not None:
+            return self._raw_stream(self._index)
+        return torch.cuda.current_stream(self.device).cuda_stream
+
     def _check(self, *tensors: torch.Tensor | None) -> None:
+        index = self._index
         for t in tensors:
-            if t is None:
+            if t is None or (t.is_cuda and t.get_device() == index and t.is_contiguous()):
                 continue
             if t.device != self.device:
                 raise KernelError(f"a tensor lives on {t.device}, the kernels run on {self.device}")
-            if not t.is_contiguous():
-                raise KernelError(f"kernels take contiguous tensors; got strides {t.stride()} for shape {tuple(t.shape)}")
+            raise KernelError(f"kernels take contiguous tensors; got strides {t.stride()} for shape {tuple(t.shape)}")
 
     @staticmethod
     def _p(t: torch.Tensor | None) -> ctypes.c_void_p:
@@ -165,8 +173,7 @@ class CudaKernels:
         sizes = (heads, kv_heads, head_dim, kv.shape[0], kv.shape[3], ctypes.c_float(scale), int(window))
         if rows.n_decode:
             splits = self.decode_splits(rows.n_decode, heads, kv_heads, rows.max_kv)
-            lens = rows.host_kv_len[:rows.n_decode] if rows.host_kv_len is not None else None
-            mode = self.decode_pinned or self.decode_mode(lens)
+            mode = self.decode_pinned or self._decode_mode_of(rows)
             if splits > 1 and mode == "balanced" and rows.n_decode <= self.BALANCED_ROWS:
                 pairs = rows.n_decode * kv_heads * (-(-(heads // kv_heads) // 16))
                 slots = self.sms * (1 if head_dim > 128 else 3)       # CTAs of this kernel that one wave holds
@@ -183,14 +190,29 @@ class CudaKernels:
                 self._call("hb_attention_decode_bf16", self._p(out), self._p(scratch), self._p(q), self._p(kv), *common,
                            rows.n_decode, *sizes, splits)
         if rows.n_rows > rows.n_decode:
-            qs = rows.host_query_start
-            counts = [int(qs[b + 1]) - int(qs[b]) for b in range(rows.n_decode, rows.n_rows)]
             if self.prefill_attention == "tcgen05" and head_dim == 128 and kv.shape[3] % 64 == 0:
                 self._call("hb_attention_prefill_tcgen05", self._p(out), self._p(q), self._p(kv), *common,
-                           rows.n_decode, rows.n_rows, sum((n + 255) // 256 for n in counts), t, *sizes)
+                           rows.n_decode, rows.n_rows, self._query_tiles(rows, 256), t, *sizes)
             else:
                 self._call("hb_attention_prefill_bf16", self._p(out), self._p(q), self._p(kv), *common, rows.n_decode,
-                           rows.n_rows, sum((n + 63) // 64 for n in counts), *sizes)
+                           rows.n_rows, self._query_tiles(rows, 64), *sizes)
+
+    # Every layer of a step asks the same questions about the step's rows: the answers are kept on the rows.
+    def _decode_mode_of(self, rows) -> str:
+        plan = rows.plan
+        if "mode" not in plan:
+            lens = rows.host_kv_len[:rows.n_decode] if rows.host_kv_len is not None else None
+            plan["mode"] = self.decode_mode(lens)
+        return plan["mode"]
+
+    @staticmethod
+    def _query_tiles(rows, size: int) -> int:
+        """Tiles of `size` queries over the rows that bring several tokens."""
+        plan = rows.plan
+        if size not in plan:
+            qs = rows.host_query_start
+            plan[size] = sum((int(qs[b + 1]) - int(qs[b]) + size - 1) // size for b in range(rows.n_decode, rows.n_rows))
+        return plan[size]
 
     BALANCED_ROWS = 256                       # rows the balanced decode kernel takes (its prefix array)
 
