@@ -9,10 +9,11 @@
 //                MN-major operand (values are stored [key][d]), O in 128 tensor-memory columns for the whole walk.
 // The running maximum is allowed to lag: O and the row sums are rescaled only when a row's maximum has grown by more
 // than 2^8 since the last rescale (the weights stay below 256, which bfloat16 holds), so the tensor-memory round trip
-// of O is rare. Each group has one thread that issues its MMAs and keeps S of tile j + 1 in flight while the softmax of
-// tile j runs. Warp 0 loads by TMA (queries once; keys and values of a tile as four 64 x 64 boxes from the paged cache,
-// found through the block table), warps 1 and 10 issue the groups' MMAs (warp 1 owns the tensor memory), warps 2-5 and
-// 6-9 are the groups' softmax and epilogue.
+// of O is rare. One thread issues the score MMAs of both groups, keeping S of tile j + 1 in flight while the
+// softmax of tile j runs, and each group has a thread that issues its P V MMAs. Warp 0 loads by TMA (queries once;
+// keys and values of a tile as four 64 x 64 boxes from the paged cache, found through the block table), warp 1 issues
+// the score MMAs and owns the tensor memory, warps 10 and 11 issue the groups' P V MMAs, warps 2-5 and 6-9 are the
+// groups' softmax and epilogue.
 // Keys past a row's length are masked; they are read (a page is loaded whole), which is safe because cache pools start
 // as zeros and only ever hold finite values. Every mbarrier wait is bounded (tcgen05.cuh).
 #include "tcgen05.cuh"
@@ -27,8 +28,8 @@
 #define AT_SMEM (AT_GROUPS * AT_Q_BYTES + AT_STAGES * 2 * AT_KV_BYTES + 1024 + 256)
 #define AT_TMEM_COLS 512                          // per group: S0 [0, 64), S1 [64, 128), O [128, 256)
 #define AT_RESCALE 8.0f
-#define AT_MMA_WARP1 10                            // the second group's issuing warp; warps 2-9 are the softmax
-#define AT_THREADS 352
+#define AT_MMA_WARP1 10                            // warps 10, 11: the groups' P V issuing warps; warps 2-9 are the softmax
+#define AT_THREADS 384
 
 __device__ __forceinline__ float at_ex2(float x) {
     float y;
@@ -76,7 +77,7 @@ __global__ void __launch_bounds__(AT_THREADS, 1) prefill_tcgen05_kernel(
         }
         s_row = found; s_q0 = q0;
         mbar_init(q_full, 1);
-        for (int s = 0; s < AT_STAGES; ++s) { mbar_init(kv_full0 + 8 * s, 1); mbar_init(kv_empty0 + 8 * s, AT_GROUPS); }
+        for (int s = 0; s < AT_STAGES; ++s) { mbar_init(kv_full0 + 8 * s, 1); mbar_init(kv_empty0 + 8 * s, 1 + AT_GROUPS); }
         for (int i = 0; i < 2 * AT_GROUPS; ++i) {
             mbar_init(s_full0 + 8 * i, 1);
             mbar_init(p_full0 + 8 * i, 4); mbar_init(p_empty0 + 8 * i, 1);
@@ -139,54 +140,64 @@ __global__ void __launch_bounds__(AT_THREADS, 1) prefill_tcgen05_kernel(
                 tma_load_2d(v_dst + AT_KV_BYTES / 2, &map_kv, kv_full0 + 8 * s, 64, v_row);
             }
         }
-    } else if (b >= 0 && (warp == 1 || warp == AT_MMA_WARP1)) {
+    } else if (b >= 0 && (warp == 1 || warp >= AT_MMA_WARP1)) {
         if (lane == 0) {
-            // One issuing thread for each group: a thread issues an MMA every 60 to 90 cycles beside busy softmax warps,
-            // which with both groups' 24 MMAs a tile on one thread was the kernel's bound.
-            const int g = warp == 1 ? 0 : 1;
-            const int my_tiles = g_tiles[g];
+            // Three issuing threads: one for the scores S = Q K^T of both groups, and for each group one for O += P V.
+            // An MMA costs its issuing thread 60 to 200 cycles however small it is (a 128 x 64 x 16 one needs 32 cycles
+            // of the tensor pipe), so a single thread with all 24 MMAs of a tile-step, or even one thread per group,
+            // was the kernel's bound. (Four threads would need 416 threads a CTA, and the softmax warps their registers.)
             // kind::f16, D float32, A and B bfloat16; N / 8 at bit 17, M / 16 at bit 24; bit 16: B is MN-major
             const uint32_t idesc_qk = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(AT_BN >> 3) << 17) | ((uint32_t)(AT_BM >> 4) << 24);
             const uint32_t idesc_pv = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((uint32_t)(AT_D >> 3) << 17) | ((uint32_t)(AT_BM >> 4) << 24);
-            const uint32_t o_t = tmem + g * 256 + 2 * AT_BN;
-            const uint32_t q_src = q_s + g * AT_Q_BYTES;
-            bool ok = mbar_wait(q_full, 0, 2);
-            for (int j = 0; j <= tiles && ok; ++j) {
-                if (j < tiles) {                                      // (a group past its own last tile still paces the stages)
+            if (warp == 1) {
+                bool ok = mbar_wait(q_full, 0, 2);
+                for (int j = 0; j < tiles && ok; ++j) {
                     const int s = j % AT_STAGES;
                     ok = mbar_wait(kv_full0 + 8 * s, (j / AT_STAGES) & 1, 3);
-                    if (ok && j < my_tiles) {
-                        const uint32_t k_src = kv_s + s * 2 * AT_KV_BYTES;
-                        const uint32_t s_t = tmem + g * 256 + (j & 1) * AT_BN;   // (S_j may overwrite S and P of tile j - 2: the MMAs
-#pragma unroll                                                                   // that read them were issued before, by this thread)
-                        for (int kk = 0; kk < AT_D / 16; ++kk) {      // d 0..63 in the first block, 64..127 in the second
-                            const uint32_t blk = kk >> 2, within = (kk & 3) * 2;
-                            tc_mma_f16(s_t, tc_smem_desc(q_src + blk * (AT_Q_BYTES / 2)) + within,
-                                       tc_smem_desc(k_src + blk * (AT_KV_BYTES / 2)) + within, idesc_qk, kk != 0);
-                        }
-                        tc_commit(s_full0 + 8 * (g * 2 + (j & 1)));
-                    }
-                }
-                if (j >= 1 && ok) {
-                    const int i = j - 1;
-                    if (i < my_tiles) {                               // O_g += P_g,i V_i
-                        const int gb = g * 2 + (i & 1);
-                        ok = mbar_wait(p_full0 + 8 * gb, (i >> 1) & 1, 5);
+                    const uint32_t k_src = kv_s + s * 2 * AT_KV_BYTES;
+                    for (int g = 0; g < AT_GROUPS && ok; ++g) {
+                        if (j >= g_tiles[g]) continue;
+                        const int gb = g * 2 + (j & 1);
+                        // S_j overwrites S and P of tile j - 2: wait until P V of that tile has read them
+                        if (j >= 2) ok = mbar_wait(p_empty0 + 8 * gb, ((j - 2) >> 1) & 1, 4);
                         if (!ok) break;
                         tc_fence_after();
-                        const uint32_t v_src = kv_s + (i % AT_STAGES) * 2 * AT_KV_BYTES + AT_KV_BYTES;
-                        const uint32_t p_t = tmem + g * 256 + (i & 1) * AT_BN;   // P lies over the first half of its own S
+                        const uint32_t s_t = tmem + g * 256 + (j & 1) * AT_BN;
+#pragma unroll
+                        for (int kk = 0; kk < AT_D / 16; ++kk) {      // d 0..63 in the first block, 64..127 in the second
+                            const uint32_t blk = kk >> 2, within = (kk & 3) * 2;
+                            tc_mma_f16(s_t, tc_smem_desc(q_s + g * AT_Q_BYTES + blk * (AT_Q_BYTES / 2)) + within,
+                                       tc_smem_desc(k_src + blk * (AT_KV_BYTES / 2)) + within, idesc_qk, kk != 0);
+                        }
+                        tc_commit(s_full0 + 8 * gb);
+                    }
+                    if (ok) tc_commit(kv_empty0 + 8 * s);             // the keys of the stage have been read (all three must arrive)
+                }
+            } else {
+                const int g = warp - AT_MMA_WARP1;
+                const int my_tiles = g_tiles[g];
+                const uint32_t o_t = tmem + g * 256 + 2 * AT_BN;
+                bool ok = true;
+                for (int j = 0; j < tiles && ok; ++j) {               // (a group past its own last tile still paces the stages)
+                    const int s = j % AT_STAGES, gb = g * 2 + (j & 1);
+                    ok = mbar_wait(kv_full0 + 8 * s, (j / AT_STAGES) & 1, 3);
+                    if (ok && j < my_tiles) {                         // O_g += P_g,j V_j
+                        ok = mbar_wait(p_full0 + 8 * gb, (j >> 1) & 1, 5);
+                        if (!ok) break;
+                        tc_fence_after();
+                        const uint32_t v_src = kv_s + s * 2 * AT_KV_BYTES + AT_KV_BYTES;
+                        const uint32_t p_t = tmem + g * 256 + (j & 1) * AT_BN;   // P lies over the first half of its own S
 #pragma unroll
                         for (int kk = 0; kk < AT_BN / 16; ++kk)       // 16 keys a step: 8 columns along P, 16 rows down V
                             tc_mma_f16_ts(o_t, p_t + kk * 8, tc_smem_desc_mn(v_src + kk * 16 * 128, AT_KV_BYTES / 2), idesc_pv,
-                                          (i | kk) != 0);
-                        tc_commit(p_empty0 + 8 * gb);                 // P has been read; O_g holds tile i
-                        if (j == my_tiles) tc_commit(o_full0 + 8 * g);   // the group's last tile: its output is complete
+                                          (j | kk) != 0);
+                        tc_commit(p_empty0 + 8 * gb);                 // P has been read; O_g holds tile j
+                        if (j == my_tiles - 1) tc_commit(o_full0 + 8 * g);   // the group's last tile: its output is complete
                     }
-                    tc_commit(kv_empty0 + 8 * (i % AT_STAGES));       // this group is done with the stage (both must arrive)
+                    if (ok) tc_commit(kv_empty0 + 8 * s);             // the values of the stage have been read
                 }
+                if (my_tiles == 0 || !ok) tc_commit(o_full0 + 8 * g);    // (nothing was issued for it, or the walk gave up)
             }
-            if (my_tiles == 0 || !ok) tc_commit(o_full0 + 8 * g);    // (nothing was issued for it, or the walk gave up)
         }
     } else if (b >= 0 && warp < AT_MMA_WARP1) {
         const int g = (warp - 2) >> 2;                                // this warp's group of queries
