@@ -225,10 +225,46 @@ def prefill_run(engine, tokens: int, repeats: int, seed: int) -> float:
     return best
 
 
+def long_prompt_run(args) -> dict:
+    """Time to the first token of a 30,000-token prompt that arrives while three requests decode (prompt portions of
+    up to 2,048 tokens beside their decode rows): the reference's long-prompt case (docs/dev/release.md:3103)."""
+    import torch
+    from holon_b200.engine import Engine, EngineConfig, SamplingParams
+    from holon_b200.weights import RandomSource
+    cfg = dict(QWEN3_8B, num_hidden_layers=args.layers)
+    engine = Engine(EngineConfig(model="random weights, seed 2", device="cuda:0", dtype="bfloat16", page_size=64,
+                                 max_seqs=8, max_model_len=32768, max_step_tokens=4096, chunk_with_decode=2048, seed=0),
+                    source=RandomSource(cfg, seed=2, device="cuda:0"))
+    vocab, best = engine.built.model.spec.vocab, float("inf")
+    streams = SamplingParams(temperature=0.0, max_tokens=400, ignore_eos=True)
+    for rep in range(3):                                             # the first one is a warm-up
+        for prompt in prompts_of(vocab, 3, 256, 70 + rep):
+            engine.add(prompt, streams)
+        for _ in range(20):
+            engine.step()
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        rid = engine.add(prompts_of(vocab, 1, 30000, 80 + rep)[0], SamplingParams(temperature=0.0, max_tokens=2, ignore_eos=True))
+        first, steps = None, 0
+        while first is None:
+            steps += 1
+            if any(d.rid == rid for d in engine.step()):
+                first = time.perf_counter() - t0
+        if rep:
+            best = min(best, first)
+        for r in list(engine.requests):
+            engine.abort(r)
+        engine.drain()
+    return {"only": "long_prompt", "layers": args.layers, "prompt_tokens": 30000, "streams": 3, "ttft_ms": round(best * 1e3, 1),
+            "prompt_tokens_per_s": round(30000 / best, 1), "steps": steps}
+
+
 def run_ours(args) -> dict:
     import torch
     from holon_b200.engine import Engine, EngineConfig
     from holon_b200.weights import RandomSource
+    if args.only == "long_prompt":
+        return long_prompt_run(args)
     cfg = dict(QWEN3_8B, num_hidden_layers=args.layers)
     context, batch = args.context, args.batch
     engine = Engine(EngineConfig(model="random weights, seed 2", device="cuda:0", dtype="bfloat16", page_size=64,
@@ -306,8 +342,9 @@ def main() -> int:
     ap.add_argument("--layers", type=int, default=FULL_LAYERS, help="fewer layers than the model has (both are reported)")
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--context", type=int, default=8192)
-    ap.add_argument("--only", default="all", choices=("all", "decode", "prefill"),
-                    help="run one part only (for profiling a small case); the JSON line then lacks the other parts")
+    ap.add_argument("--only", default="all", choices=("all", "decode", "prefill", "long_prompt"),
+                    help="run one part only (for profiling a small case); the JSON line then lacks the other parts. "
+                         "long_prompt: time to first token of a 30,000-token prompt behind three decoding requests")
     args = ap.parse_args()
     if args.gpus != 1:
         print(f"holon_b200 is a single-GPU engine: --gpus {args.gpus} is not supported")
