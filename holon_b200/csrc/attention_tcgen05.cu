@@ -42,6 +42,23 @@ __device__ __forceinline__ void tc_mma_f16(uint32_t tmem_d, uint64_t desc_a, uin
                  ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate) : "memory");
 }
 
+// Two float32 in one 64-bit register, for the packed arithmetic of sm_100 (one instruction, two results).
+__device__ __forceinline__ uint64_t pack2(float lo, float hi) {
+    uint64_t r;
+    asm("mov.b64 %0, {%1, %2};\n" : "=l"(r) : "f"(lo), "f"(hi));
+    return r;
+}
+__device__ __forceinline__ void unpack2(uint64_t v, float& lo, float& hi) { asm("mov.b64 {%0, %1}, %2;\n" : "=f"(lo), "=f"(hi) : "l"(v)); }
+__device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
+    uint64_t d;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;\n" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+    return d;
+}
+__device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b) {
+    uint64_t d;
+    asm("add.rn.f32x2 %0, %1, %2;\n" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+}
 // The same with the A operand in tensor memory (128 lanes x K/2 columns, two bfloat16 per column).
 __device__ __forceinline__ void tc_mma_f16_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
     asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
@@ -258,19 +275,26 @@ __global__ void __launch_bounds__(AT_THREADS, 1) prefill_tcgen05_kernel(
                 m_used = m_new;
             }
             const float off = m_used == -INFINITY ? 0.f : -m_used;
-            float sum4[4] = {0.f, 0.f, 0.f, 0.f};
+            const uint64_t scale2 = pack2(scale_log2, scale_log2), off2 = pack2(off, off);
+            uint64_t sum2[4] = {0ull, 0ull, 0ull, 0ull};              // four chains of packed sums
             uint32_t pk[32];                                          // 64 weights as bfloat16 pairs
 #pragma unroll
             for (int c = 0; c < 2; ++c)
 #pragma unroll
                 for (int i = 0; i < 32; i += 2) {
-                    const float a = at_ex2(fmaf(__uint_as_float(sr[c][i]), scale_log2, off));
-                    const float d = at_ex2(fmaf(__uint_as_float(sr[c][i + 1]), scale_log2, off));
-                    sum4[(i >> 1) & 3] += a + d;
+                    float a, d;
+                    unpack2(fma2(pack2(__uint_as_float(sr[c][i]), __uint_as_float(sr[c][i + 1])), scale2, off2), a, d);
+                    a = at_ex2(a);
+                    d = at_ex2(d);
+                    sum2[(i >> 1) & 3] = add2(sum2[(i >> 1) & 3], pack2(a, d));
                     __nv_bfloat162 pr = __floats2bfloat162_rn(a, d);
                     pk[c * 16 + i / 2] = *(uint32_t*)&pr;
                 }
-            l += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
+            {
+                float lo, hi;
+                unpack2(add2(add2(sum2[0], sum2[1]), add2(sum2[2], sum2[3])), lo, hi);
+                l += lo + hi;
+            }
             if (!ok) break;
             tc_st32(lane_t + (j & 1) * AT_BN, pk);                    // P over the S it came from: 32 columns of bfloat16 pairs
             tc_fence_before();
