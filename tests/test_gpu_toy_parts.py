@@ -1,7 +1,8 @@
 """Two more toy parts that are defined here, registered, built into a model and stepped without any change to the
 framework: a feed-forward that routes every token to one of several experts, and a position encoding whose angles
 grow with the logarithm of the position. The model that holds them is compared, whole and in portions, with the
-formulas written out below; it is nobody's architecture."""
+formulas written out below; it is nobody's architecture. A second toy model puts layers with a window beside layers
+without one (two cache groups)."""
 from __future__ import annotations
 
 import pytest
@@ -91,14 +92,14 @@ def rotate(x, table, rotary_dim):
 
 
 def plain_attention(x, mixer):
-    t = x.shape[0]
+    t, heads, kv_heads, d = x.shape[0], mixer.heads, mixer.kv_heads, mixer.head_dim
     w = mixer.qkv.weight.tensor.float().cpu()
-    q, k, v = (x @ w.T).split((HEADS * HEAD_DIM, KV_HEADS * HEAD_DIM, KV_HEADS * HEAD_DIM), dim=-1)
-    q = plain.rms_norm(q.reshape(t, HEADS, HEAD_DIM), mixer.q_norm.weight.tensor.float().cpu(), EPS)
-    k = plain.rms_norm(k.reshape(t, KV_HEADS, HEAD_DIM), mixer.k_norm.weight.tensor.float().cpu(), EPS)
+    q, k, v = (x @ w.T).split((heads * d, kv_heads * d, kv_heads * d), dim=-1)
+    q = plain.rms_norm(q.reshape(t, heads, d), mixer.q_norm.weight.tensor.float().cpu(), EPS)
+    k = plain.rms_norm(k.reshape(t, kv_heads, d), mixer.k_norm.weight.tensor.float().cpu(), EPS)
     table, rd = mixer.position.table.cpu(), mixer.position.rotary_dim
-    o = plain.causal_attention(rotate(q, table, rd), rotate(k, table, rd), v.reshape(t, KV_HEADS, HEAD_DIM))
-    return o.reshape(t, HEADS * HEAD_DIM) @ mixer.o_proj.weight.tensor.float().cpu().T
+    o = plain.causal_attention(rotate(q, table, rd), rotate(k, table, rd), v.reshape(t, kv_heads, d), mixer.window)
+    return o.reshape(t, heads * d) @ mixer.o_proj.weight.tensor.float().cpu().T
 
 
 def plain_ffn(x, ffn):
@@ -123,7 +124,8 @@ def plain_forward(model, ids):
             choices.append(choice)
         h = h + y
     h = plain.rms_norm(h, model.norm.weight.tensor.float().cpu(), EPS)
-    return h @ model.head.weight.tensor.float().cpu().T, choices
+    head = model.head.weight if model.head.weight is not None else model.embed.weight        # a tied head reads the table
+    return h @ head.tensor.float().cpu().T, choices
 
 
 def test_toy_routed_feed_forward_and_toy_position_encoding():
@@ -164,3 +166,58 @@ def test_toy_routed_feed_forward_and_toy_position_encoding():
         unregister_part("ffn", "toy_top_one")
         unregister_part("position", "toy_log")
         unregister_architecture("ToyRoutedForCausalLM")
+
+
+# ---------------------------------------------------------------- layers with a window beside layers without: two cache groups
+
+def window_recipe(c):
+    norm = PartRef.of("norm", "rmsnorm", eps=EPS)
+    rope = PartRef.of("position", "rope", theta=1e4, rotary_dim=c["head_dim"])
+    full = PartRef.of("mixer", "gqa", heads=4, kv_heads=2, head_dim=c["head_dim"], qk_norm=norm, window=0, position=rope)
+    near = PartRef.of("mixer", "gqa", heads=4, kv_heads=2, head_dim=c["head_dim"], qk_norm=norm, window=c["window"], position=rope)
+    ffn = PartRef.of("ffn", "swiglu", inter=c["inter"])
+    block = PartRef.of("block", "prenorm")
+    layers = tuple(LayerSpec(block, mixer, ffn, norm) for mixer in (near, full, near, full))
+    return ModelSpec(hidden=c["hidden"], vocab=c["vocab"], layers=layers, order=tuple(Run(i, i) for i in range(4)),
+                     embed=PartRef.of("embed", "table"), norm=norm, head=PartRef.of("head", "linear", tied=True),
+                     weight_rules=(WeightRule("{rest}", "{rest}"),))
+
+
+@pytest.mark.parametrize("dtype,head_dim,page,window,tol", [("float32", 16, 8, 20, 1e-4), ("bfloat16", 16, 8, 20, 6e-2),
+                                                            ("bfloat16", 128, 64, 150, 6e-2)])
+def test_layers_with_a_window_beside_layers_without(dtype, head_dim, page, window, tol):
+    """Two layers that see only the last `window` keys and two that see all: two cache groups with pools and block
+    tables of their own. Whole, in portions and token by token give the plain formula's logits, and in the window's group
+    a request never holds more pages than its window and the step's portion span: the pages it has passed come back
+    (head size 128 with pages of 64 puts the prompt portions on the tcgen05 kernel)."""
+    register_architecture("ToyWindowForCausalLM", dict, window_recipe)
+    try:
+        config = {"architectures": ["ToyWindowForCausalLM"], "hidden": 64, "vocab": 113, "inter": 96, "head_dim": head_dim,
+                  "window": window}
+        n = 5 * window // 2 + 7
+        b = build(RandomSource(config, seed=13, dtype=torch.float32), dtype=dtype, device=DEV, page_size=page, max_seqs=2,
+                  max_model_len=-(-(n + 8) // page) * page, max_step_tokens=512, pages=-(-n // page) + 3)
+        assert len(b.cache.groups) == 2
+        near = next(g for g in b.cache.groups if g.decl.window)
+        ids = torch.randint(0, 113, (n,), generator=torch.Generator().manual_seed(6)).tolist()
+        want, _ = plain_forward(b.model, ids)
+
+        def run(portions):
+            slot, at, rows, held = b.cache.admit(), 0, [], 0
+            for size in portions:
+                b.cache.reserve(slot, at + size)
+                rows.append(b.runner.step([StepEntry(slot, ids[at:at + size], at, range(size))]))
+                at += size
+                held = max(held, int((near.table[slot] != near.null_page).sum()))
+            b.cache.release(slot)
+            b.cache.check()
+            return torch.cat(rows).float().cpu(), held
+
+        for portions in ([n], [window + 3, 2, n - window - 5 - 9] + [1] * 9, [7] * (n // 7) + [n % 7] * (1 if n % 7 else 0)):
+            got, held = run(portions)
+            diff = float((got - want).abs().max())
+            assert diff < tol, (portions[:4], diff)
+            if len(portions) > 1:
+                assert held <= -(-window // page) + -(-max(portions) // page) + 1      # never the whole sequence's pages
+    finally:
+        unregister_architecture("ToyWindowForCausalLM")
