@@ -369,6 +369,40 @@ def test_attention_finds_one_far_key(K, dtype, page):
                 assert first_row.abs().max() < 1.0, (window, target)
 
 
+@pytest.mark.parametrize("window", [0, 4096])
+def test_attention_over_a_long_context(K, window):
+    """20,000 keys a row at head size 128 and pages of 64 (313 pages a row, shuffled): a decode row, a two-token portion
+    and a 300-token portion at the end of such contexts, through the split and the balanced decode kernels and both
+    prefill kernels, against the plain formula; one far key is made to stand out in the decode row."""
+    heads, kv_heads, head_dim, page, n = 8, 2, 128, 64, 20000
+    spec = [(n - 1, 1), (n - 2, 2), (n - 300, 300)]
+    q, kv, table, rows = paged_case(heads, kv_heads, head_dim, page, spec, torch.bfloat16, seed=23 + window)
+    kv[:, 0].mul_(0.3)
+    target = n - 3000 if window else 1234                             # inside the window, or far back
+    slot = int(rows.row_slot[0])
+    pg, off = int(table[slot, target // page]), target % page
+    for hk in range(kv_heads):
+        group = q[0, hk * 4:(hk + 1) * 4].float()
+        kv[pg, 0, hk, off] = (torch.nn.functional.normalize(group.mean(0), dim=0) * 40).to(torch.bfloat16)
+        kv[pg, 1, hk, off] = 5.0
+    scale = 1 / math.sqrt(head_dim)
+    want = torch.empty_like(q)
+    REF.paged_attention(want, q, kv, table, rows, scale, window)
+    assert (want[0].float() - 5.0).abs().max() < 0.5                  # the plain formula finds the key too
+    args = (q.to(DEV), kv.to(DEV), table.to(DEV), on_device(rows), scale, window)
+    before = K.decode_attention, K.prefill_attention
+    try:
+        for decode in ("splits", "balanced"):
+            for prefill in ("tcgen05", "mma"):
+                K.decode_attention, K.prefill_attention = decode, prefill
+                out = torch.full_like(q, float("nan"), device=DEV)
+                K.paged_attention(out, *args)
+                assert K.tcgen05_status() == 0
+                close(out, want, torch.bfloat16, scale=4)
+    finally:
+        K.decode_attention, K.prefill_attention = before
+
+
 def test_sample_greedy_and_temperature(K):
     v, rows = 1531, 6
     logits = rand(rows, v, seed=3, scale=2.0)
