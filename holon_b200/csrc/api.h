@@ -62,6 +62,13 @@ int hb_attention_decode_bf16(void* out, float* scratch, const void* q, const voi
                              const int32_t* kv_len, int rows, int heads, int kv_heads, int head_dim, int pages,
                              int page_size, float scale, int window, int splits, hb_stream stream);
 
+// The same rows with 2 to 8 splits whose CTAs form a thread-block cluster and merge through distributed shared memory
+// inside the kernel: no scratch, no second kernel.
+int hb_attention_decode_bf16_cluster(void* out, const void* q, const void* kv, const int32_t* block_table,
+                                     int table_stride, const int32_t* row_slot, const int32_t* query_start,
+                                     const int32_t* kv_len, int rows, int heads, int kv_heads, int head_dim, int pages,
+                                     int page_size, float scale, int window, int splits, hb_stream stream);
+
 // The same rows with the keys of all of them shared out evenly over `ctas` CTAs (one wave that fills the GPU): each
 // takes the same number of 64-key tiles, across rows and heads where its stretch crosses them, so rows of any lengths
 // cost what their sum costs. At most 256 rows. `scratch`: hb_attention_decode_balanced_scratch_floats(...) floats.

@@ -314,6 +314,10 @@ __device__ __forceinline__ void decode_walk(
         const int h = hk * group + g0 + r;
         if (part_stride == 0) {
             out[((size_t)t * heads + h) * head_dim + d] = __float2bfloat16_rn(l > 0.f ? acc / l : 0.f);
+        } else if (part_stride < 0) {                               // left in shared memory for the CTA's cluster
+            float* stage = wml + 4 * 16 * 2;                        // [16][D_PAD] sums, then [16][2] (max in log2 units, sum)
+            stage[r * D_PAD + d] = acc;
+            if (d == 0) { stage[16 * D_PAD + r * 2] = mm * scale_log2; stage[16 * D_PAD + r * 2 + 1] = l; }
         } else {
             const size_t slot = part_base + (size_t)r * part_stride;
             part_o[slot * head_dim + d] = acc;
@@ -345,6 +349,64 @@ __global__ void __launch_bounds__(128) decode_kernel(
                                splits > 1 ? splits : 0, q, kv, block_table + (size_t)row_slot[b] * table_stride,
                                query_start[b], heads, kv_heads, head_dim, pages, page_size, page_shift, scale_log2, hk,
                                group, g0, g, first, last, lo, n);
+}
+
+// The same rows with the splits of a (row, kv head) as one thread-block cluster: each CTA leaves its partial result in
+// its shared memory, and after a cluster barrier every CTA combines a share of the outputs from all of them through
+// distributed shared memory, in the order of the splits. No scratch in global memory and no second kernel.
+__device__ __forceinline__ float ld_cluster_f32(uint32_t local_addr, uint32_t rank) {
+    uint32_t remote;
+    float v;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;\n" : "=r"(remote) : "r"(local_addr), "r"(rank));
+    asm volatile("ld.shared::cluster.f32 %0, [%1];\n" : "=f"(v) : "r"(remote) : "memory");
+    return v;
+}
+__device__ __forceinline__ void cluster_barrier() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;\n" ::: "memory");
+}
+
+template <int D_PAD, int STAGES>
+__global__ void __launch_bounds__(128) decode_cluster_kernel(
+        bf16* __restrict__ out, const bf16* __restrict__ q, const bf16* __restrict__ kv,
+        const int32_t* __restrict__ block_table, int table_stride, const int32_t* __restrict__ row_slot,
+        const int32_t* __restrict__ query_start, const int32_t* __restrict__ kv_len, int heads, int kv_heads,
+        int head_dim, int pages, int page_size, int page_shift, float scale_log2, int window, int splits) {
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+    const int b = blockIdx.x, split = blockIdx.z;                   // the cluster is the z direction: split = rank in it
+    const int group = heads / kv_heads, m_tiles = (group + 15) / 16;
+    const int hk = blockIdx.y / m_tiles, mt = blockIdx.y % m_tiles;
+    const int g0 = mt * 16, g = min(16, group - g0);
+    const int n = kv_len[b];
+    const int lo = window > 0 ? max(0, n - window) : 0;
+    const int tile_lo = lo / TILE_N, tile_hi = (n + TILE_N - 1) / TILE_N;
+    const int per = (tile_hi - tile_lo + splits - 1) / splits;
+    const int first = tile_lo + split * per, last = min(tile_hi, first + per);
+    const int t = query_start[b];
+    decode_walk<D_PAD, STAGES>(smem_raw, out, nullptr, nullptr, 0, -1, q, kv, block_table + (size_t)row_slot[b] * table_stride,
+                               t, heads, kv_heads, head_dim, pages, page_size, page_shift, scale_log2, hk, group, g0, g,
+                               first, last, lo, n);
+    __syncwarp();
+    cluster_barrier();                                              // every split's sums are in its shared memory
+    const uint32_t stage = smem_u32(smem_raw) + 16 * D_PAD * 2 + (4 * 16 * D_PAD + 4 * 16 * 2) * 4;
+    const int total = g * head_dim, share = (total + splits - 1) / splits;
+    for (int i = threadIdx.x; i < share; i += 128) {
+        const int e = split * share + i;
+        if (e >= total) break;
+        const int r = e / head_dim, d = e % head_dim;
+        float mm = -INFINITY;
+        for (int s2 = 0; s2 < splits; ++s2) mm = fmaxf(mm, ld_cluster_f32(stage + (16 * D_PAD + r * 2) * 4, s2));
+        float acc = 0.f, l = 0.f;
+        for (int s2 = 0; s2 < splits; ++s2) {                       // in the order of the splits
+            const float ms = ld_cluster_f32(stage + (16 * D_PAD + r * 2) * 4, s2);
+            const float fs = ms == -INFINITY ? 0.f : ex2(ms - mm);
+            acc += fs * ld_cluster_f32(stage + (r * D_PAD + d) * 4, s2);
+            l += fs * ld_cluster_f32(stage + (16 * D_PAD + r * 2 + 1) * 4, s2);
+        }
+        out[((size_t)t * heads + hk * group + g0 + r) * head_dim + d] = __float2bfloat16_rn(l > 0.f ? acc / l : 0.f);
+    }
+    __syncwarp();
+    cluster_barrier();                                              // nobody leaves while its shared memory may be read
 }
 
 // out[0 .. head_dim) = sum_i w_i o_i / sum_i w_i l_i over `count` partial results at slots base + i * stride,
@@ -402,7 +464,7 @@ __global__ void decode_merge_kernel(bf16* __restrict__ out, const float* __restr
 
 template <int D_PAD> static size_t decode_smem(int stages) {
     const size_t tiles = (size_t)(16 + 2 * stages * TILE_N) * D_PAD * sizeof(bf16);
-    const size_t merge = 16 * D_PAD * sizeof(bf16) + (size_t)(4 * 16 * D_PAD + 4 * 16 * 2) * sizeof(float);
+    const size_t merge = 16 * D_PAD * sizeof(bf16) + (size_t)(4 * 16 * D_PAD + 4 * 16 * 2 + 16 * D_PAD + 16 * 2) * sizeof(float);
     return tiles > merge ? tiles : merge;
 }
 
@@ -425,6 +487,53 @@ static int launch_decode(bf16* out, float* part_o, float* part_ml, const bf16* q
         HB_LAUNCH_CHECK("attention_decode_merge");
     }
     return 0;
+}
+
+template <int D_PAD, int STAGES>
+static int launch_decode_cluster(bf16* out, const bf16* q, const bf16* kv, const int32_t* block_table, int table_stride,
+                                 const int32_t* row_slot, const int32_t* query_start, const int32_t* kv_len, int rows,
+                                 int heads, int kv_heads, int head_dim, int pages, int page_size, float scale, int window,
+                                 int splits, cudaStream_t s) {
+    auto kernel = decode_cluster_kernel<D_PAD, STAGES>;
+    const size_t smem = decode_smem<D_PAD>(STAGES);
+    HB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    const int group = heads / kv_heads, m_tiles = (group + 15) / 16;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(rows, kv_heads * m_tiles, splits);
+    cfg.blockDim = dim3(128);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = s;
+    cudaLaunchAttribute attr = {};
+    attr.id = cudaLaunchAttributeClusterDimension;
+    attr.val.clusterDim.x = 1; attr.val.clusterDim.y = 1; attr.val.clusterDim.z = splits;
+    cfg.attrs = &attr;
+    cfg.numAttrs = 1;
+    HB_CUDA(cudaLaunchKernelEx(&cfg, kernel, out, q, kv, block_table, table_stride, row_slot, query_start, kv_len, heads,
+                               kv_heads, head_dim, pages, page_size, log2_exact(page_size), scale * 1.4426950408889634f,
+                               window, splits));
+    return 0;
+}
+
+// The rows of hb_attention_decode_bf16 with 2 to 8 splits that merge inside the kernel (a cluster per row and kv head).
+extern "C" int hb_attention_decode_bf16_cluster(void* out, const void* q, const void* kv, const int32_t* block_table,
+                                                int table_stride, const int32_t* row_slot, const int32_t* query_start,
+                                                const int32_t* kv_len, int rows, int heads, int kv_heads, int head_dim,
+                                                int pages, int page_size, float scale, int window, int splits,
+                                                hb_stream stream) {
+    if (rows == 0) return 0;
+    if (head_dim % 16 || head_dim > 256 || head_dim < 16)
+        HB_REFUSE("attention_decode_bf16_cluster: head_dim %d is no multiple of 16 up to 256", head_dim);
+    if (kv_heads < 1 || heads % kv_heads) HB_REFUSE("attention_decode_bf16_cluster: %d heads, %d kv heads", heads, kv_heads);
+    if (splits < 2 || splits > 8) HB_REFUSE("attention_decode_bf16_cluster: %d splits (2 to 8, a cluster's size)", splits);
+    if (!(scale > 0.f)) HB_REFUSE("attention_decode_bf16_cluster: the score scale must be positive");
+    if (rows > 65535 * 32) HB_REFUSE("attention_decode_bf16_cluster: %d rows", rows);
+    cudaStream_t s = (cudaStream_t)stream;
+#define HB_ARGS (bf16*)out, (const bf16*)q, (const bf16*)kv, block_table, table_stride, row_slot, query_start, kv_len, rows, \
+    heads, kv_heads, head_dim, pages, page_size, scale, window, splits, s
+    if (head_dim <= 64) return launch_decode_cluster<64, 4>(HB_ARGS);
+    if (head_dim <= 128) return launch_decode_cluster<128, 2>(HB_ARGS);
+    return launch_decode_cluster<256, 2>(HB_ARGS);
+#undef HB_ARGS
 }
 
 extern "C" size_t hb_attention_decode_scratch_floats(int rows, int heads, int head_dim, int splits) {

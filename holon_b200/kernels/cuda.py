@@ -66,6 +66,7 @@ class CudaKernels:
         self.decode_attention = os.environ.get("HOLON_B200_DECODE_ATTENTION", "auto")
         if self.decode_attention not in ("auto", "balanced", "splits"):
             raise KernelError(f"HOLON_B200_DECODE_ATTENTION must be auto, balanced or splits, not {self.decode_attention!r}")
+        self.decode_cluster = os.environ.get("HOLON_B200_DECODE_CLUSTER", "1") != "0"   # splits of up to 8 merge in the kernel
         self.decode_pinned = None             # set around a CUDA-graph capture: the captured launches keep this mode
         self.sms = torch.cuda.get_device_properties(self.device).multi_processor_count
         self.decode_ctas = None               # tests: a fixed number of CTAs for the balanced kernel
@@ -184,6 +185,13 @@ class CudaKernels:
                 scratch = torch.empty(floats, dtype=torch.float32, device=self.device)
                 self._call("hb_attention_decode_bf16_balanced", self._p(out), self._p(scratch), self._p(q), self._p(kv),
                            *common, rows.n_decode, *sizes, ctas)
+            elif splits > 1 and self.decode_cluster and (few := self.decode_splits(
+                    rows.n_decode, heads, kv_heads, rows.max_kv, 8)) > 1 and self._split_cost(
+                    rows.n_decode, heads, kv_heads, rows.max_kv, few) <= 1.1 * self._split_cost(
+                    rows.n_decode, heads, kv_heads, rows.max_kv, splits):
+                # up to eight splits cost about as little as the best number: let them merge inside the kernel
+                self._call("hb_attention_decode_bf16_cluster", self._p(out), self._p(q), self._p(kv), *common,
+                           rows.n_decode, *sizes, few)
             else:
                 floats = rows.n_decode * heads * splits * (head_dim + 2) if splits > 1 else 0
                 scratch = torch.empty(floats, dtype=torch.float32, device=self.device) if floats else None
@@ -228,17 +236,22 @@ class CudaKernels:
         longest, total = int(max(kv_lens)), int(sum(int(v) for v in kv_lens))
         return "balanced" if longest >= 4096 and longest * len(kv_lens) >= 8 * total else "splits"
 
-    def decode_splits(self, rows: int, heads: int, kv_heads: int, max_kv: int) -> int:
+    def _split_cost(self, rows: int, heads: int, kv_heads: int, max_kv: int, splits: int) -> int:
+        """Waves x (tiles a CTA walks + 1 for its start): what a launch of `splits` parts a row costs, in tile times."""
+        ctas, tiles, slots = rows * kv_heads * (-(-(heads // kv_heads) // 16)), -(-max_kv // 64), 3 * self.sms
+        return -(-ctas * splits // slots) * (-(-tiles // splits) + 1)
+
+    def decode_splits(self, rows: int, heads: int, kv_heads: int, max_kv: int, most: int = 64) -> int:
         """Parts the keys of a decode row are cut into. Three CTAs fit an SM; a launch of `ctas * parts` CTAs runs in
         waves of 3 x SMs, each CTA walking its share of the longest row's 64-key tiles plus a fixed start-up of
-        about one tile. The number of parts (1 to 64) with the least waves x (tiles + 1) wins. It is a function of
+        about one tile. The number of parts (1 to `most`) with the least waves x (tiles + 1) wins. It is a function of
         the batch's size and the longest length only, as the reference plans its splits
         (plugins/holon_plugins/kernels/triton_attn/plugin.py:40-96)."""
-        key = (rows, heads, kv_heads, -(-max_kv // 64))
+        key = (rows, heads, kv_heads, -(-max_kv // 64), most)
         if key not in self._splits:
-            ctas, tiles, slots = rows * kv_heads * (-(-(heads // kv_heads) // 16)), key[3], 3 * self.sms
-            cost = lambda s: -(-ctas * s // slots) * (-(-tiles // s) + 1)          # noqa: E731
-            self._splits[key] = min(range(1, max(1, min(64, tiles)) + 1), key=lambda s: (cost(s), s))
+            tiles = key[3]
+            self._splits[key] = min(range(1, max(1, min(most, tiles)) + 1),
+                                    key=lambda s: (self._split_cost(rows, heads, kv_heads, max_kv, s), s))
         return self._splits[key]
 
     def _attention_generic(self, out, q, kv, block_table, rows, scale, window) -> None:

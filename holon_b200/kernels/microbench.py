@@ -57,11 +57,17 @@ def decode_attention(k, args) -> None:
         t = timed(call, flush)
         print(f"decode attention rows {rows} context {args.context} balanced: {t:7.1f} us  {moved / t / 1e6:5.2f} TB/s")
         k.decode_attention = "splits"
+        t = timed(call, flush)
+        few = k.decode_splits(rows, heads, kv_heads, args.context, 8)
+        print(f"decode attention rows {rows} context {args.context} as the kernel table runs it (splits {planned}, or {few} "
+              f"merged inside a cluster if that costs about the same): {t:7.1f} us  {moved / t / 1e6:5.2f} TB/s")
+        cluster, k.decode_cluster = k.decode_cluster, False
         for splits in (args.splits or [planned]):
-            k._splits[(rows, heads, kv_heads, -(-args.context // 64))] = splits
+            k._splits[(rows, heads, kv_heads, -(-args.context // 64), 64)] = splits
             t = timed(call, flush)
-            print(f"decode attention rows {rows} context {args.context} splits {splits}: {t:7.1f} us  {moved / t / 1e6:5.2f} TB/s"
+            print(f"decode attention rows {rows} context {args.context} splits {splits}, merge kernel: {t:7.1f} us  {moved / t / 1e6:5.2f} TB/s"
                   + ("  (the planner's choice)" if splits == planned else ""))
+        k.decode_cluster = cluster
         k.decode_attention = "balanced"
         k._splits.clear()
 
