@@ -173,8 +173,22 @@ __global__ void __launch_bounds__(256) qk_norm_rope_kv_write_d128_kernel(
             }
         }
     }
+    // Everything the rotation needs is asked for before the first result is used (the position first: the table row
+    // hangs on it), so that a step of a few tokens pays two trips to memory instead of four.
+    int pos = live && rotate ? positions[t] : 0;
     uint4 ra = make_uint4(0, 0, 0, 0), rb = ra;
     if (dst) { ra = *(const uint4*)(src + sub * 8); rb = *(const uint4*)(src + HALF + sub * 8); }
+    float wa[8], wb[8], c[8], sn[8];
+    if (dst && weight) {
+        load_w8<TW>(weight + sub * 8, wa);
+        load_w8<TW>(weight + HALF + sub * 8, wb);
+    }
+    if (dst && rotate) {
+        pos = pos < 0 ? 0 : (pos >= max_positions ? max_positions - 1 : pos);
+        const float* cs = table + (size_t)pos * D;
+        load_w8<float>(cs + sub * 8, c);
+        load_w8<float>(cs + HALF + sub * 8, sn);
+    }
     if (dst && !rotate) {                             // values: copied as they are
         *(uint4*)(dst + sub * 8) = ra;
         *(uint4*)(dst + HALF + sub * 8) = rb;
@@ -191,21 +205,12 @@ __global__ void __launch_bounds__(256) qk_norm_rope_kv_write_d128_kernel(
     if (!dst || !rotate) return;
     if (weight) {
         const float rstd = rsqrtf(ss / (float)D + eps);
-        float wa[8], wb[8];
-        load_w8<TW>(weight + sub * 8, wa);
-        load_w8<TW>(weight + HALF + sub * 8, wb);
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
             a[i] = rounded<bf16>(a[i] * rstd * (wa[i] + offset));
             b[i] = rounded<bf16>(b[i] * rstd * (wb[i] + offset));
         }
     }
-    int pos = positions[t];
-    pos = pos < 0 ? 0 : (pos >= max_positions ? max_positions - 1 : pos);
-    const float* cs = table + (size_t)pos * D;
-    float c[8], sn[8];
-    load_w8<float>(cs + sub * 8, c);
-    load_w8<float>(cs + HALF + sub * 8, sn);
     float oa[8], ob[8];
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
