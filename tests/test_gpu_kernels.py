@@ -3,6 +3,7 @@ tests use: widths and vocabularies that are no power of two, head sizes in steps
 page edges, windows. Where random inputs would average a fault away, one key is made to dominate."""
 from __future__ import annotations
 
+import ctypes
 import math
 
 import pytest
@@ -367,6 +368,30 @@ def test_attention_finds_one_far_key(K, dtype, page):
                 assert (first_row - 3.0).abs().max() < 0.2, (window, target)
             else:
                 assert first_row.abs().max() < 1.0, (window, target)
+
+
+@pytest.mark.parametrize("geometry", [(32, 8, 128, 64), (40, 2, 64, 16), (6, 1, 48, 4), (16, 4, 256, 128)])
+def test_decode_attention_merged_inside_a_cluster(K, geometry):
+    """2 to 8 splits of a row as a thread-block cluster that merges through distributed shared memory, rows shorter
+    than the number of splits among them, against the plain formula and run to run."""
+    heads, kv_heads, head_dim, page = geometry
+    spec = [(1999, 1), (0, 1), (63, 1), (64, 1), (700, 1), (5, 1), (1300, 1), (128, 1)]
+    q, kv, table, rows = paged_case(heads, kv_heads, head_dim, page, spec, torch.bfloat16, seed=31)
+    scale = 1 / math.sqrt(head_dim)
+    want = torch.empty_like(q)
+    REF.paged_attention(want, q, kv, table, rows, scale, 0)
+    args = (q.to(DEV), kv.to(DEV), table.to(DEV), on_device(rows))
+    for splits in range(2, 9):
+        outs = []
+        for _ in range(2):
+            out = torch.full_like(q, float("nan"), device=DEV)
+            K._call("hb_attention_decode_bf16_cluster", K._p(out), K._p(args[0]), K._p(args[1]), K._i32(args[2], "table"),
+                    args[2].shape[1], K._i32(args[3].row_slot, "slot"), K._i32(args[3].query_start, "start"),
+                    K._i32(args[3].kv_len, "len"), len(spec), heads, kv_heads, head_dim, kv.shape[0], page,
+                    ctypes.c_float(scale), 0, splits)
+            outs.append(out)
+        close(outs[0], want, torch.bfloat16, scale=4)
+        assert torch.equal(outs[0], outs[1]), splits
 
 
 @pytest.mark.parametrize("window", [0, 4096])
