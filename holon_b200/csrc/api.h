@@ -105,6 +105,16 @@ int hb_gemm_bf16_skinny(void* out, int out_f32, const void* x, const void* w, in
                         hb_stream stream);
 
 // bfloat16 product on tcgen05 tensor cores with TMA loads and the accumulator in tensor memory (128 x 256 tiles).
+// The attention's first product for up to 16 tokens with what follows it in one kernel: x [m, k] times
+// w [(heads + 2 kv_heads) * head_dim, k], then per head the q/k RMSNorm (weights bfloat16 or, with weight_f32, float32;
+// null: no norm), the rotation of the whole head by the token's position (table [max_positions, head_dim], cosines
+// then sines) and the write of queries to q_out [m, heads, head_dim] and of keys and values into their cache pages.
+// head_dim 32, 64 or 128. The head_dim / 16 CTAs of a head are a thread-block cluster.
+int hb_qkv_rope_skinny(void* q_out, const void* x, const void* w, int m, int k, const int32_t* positions,
+                       const float* table, int max_positions, const void* q_weight, const void* k_weight, int weight_f32,
+                       float eps, float offset, void* kv, const int32_t* write_index, int pages, int page_size, int heads,
+                       int kv_heads, int head_dim, hb_stream stream);
+
 // Same arguments and modes as hb_gemm_bf16_skinny, any m. hb_gemm_tcgen05_status synchronises the device and
 // returns (and clears) a status word that is non-zero if a bounded wait inside the kernel ever gave up.
 int hb_gemm_bf16_tcgen05(void* out, int out_f32, const void* x, const void* w, int m, int n, int k, int mode, int inter,

@@ -8,6 +8,12 @@
 // 32 rows and add their partial sums through shared memory in a fixed order.
 // mode 1 computes SwiGLU's activation in the epilogue: the CTA's first tile holds 16 gate rows, its second the 16 up
 // rows of the same columns, and it writes silu(gate) * up.
+// mode 2 is the attention's first product with what follows it folded in: w is [q heads; k heads; v heads] x head_dim
+// rows, the head_dim / 16 CTAs of a head form a thread-block cluster, and after the product they norm the head
+// (RMSNorm over head_dim with the q or k weight), rotate it by its token's position (half-split pairs, whole head)
+// and write queries to q_out and keys and values straight into their cache pages. The head's sum of squares and the
+// rotation partner 64 columns away come from the other CTAs' shared memory. Values are rounded to bfloat16 where the
+// separate kernels round them (after the product, after the norm), so the results are theirs.
 #include "common.cuh"
 
 #define SK_WARPS 8
@@ -28,11 +34,36 @@ __device__ __forceinline__ void mma16816(float (&c)[4], uint32_t a0, uint32_t a1
                  : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
+struct RopeEpilogue {                              // what mode 2 needs beyond the product
+    bf16* q_out;                                   // [m, heads, head_dim]
+    const int32_t* positions;                      // [m]
+    const float* table;                            // [max_positions, head_dim]: cosines, then sines
+    const void* q_weight;                          // [head_dim] or null: no norm
+    const void* k_weight;
+    bf16* kv;                                      // [pages, 2, kv_heads, page_size, head_dim] or null: nothing is written
+    const int32_t* write_index;                    // [m]: page * page_size + offset, negative: skip
+    float eps, offset;
+    int max_positions, weight_f32, pages, page_size, heads, kv_heads, head_dim;
+};
+
+__device__ __forceinline__ float ld_peer_f32(const float* local, uint32_t rank) {
+    uint32_t remote;
+    float v;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;\n" : "=r"(remote) : "r"((uint32_t)__cvta_generic_to_shared(local)), "r"(rank));
+    asm volatile("ld.shared::cluster.f32 %0, [%1];\n" : "=f"(v) : "r"(remote) : "memory");
+    return v;
+}
+__device__ __forceinline__ void cluster_barrier_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;\n" ::: "memory");
+}
+
 // MT tiles of 16 weight rows per CTA, NT tiles of 8 rows of x.
 template <int MT, int NT, int SK_UNROLL, int MIN_CTAS>
 __global__ void __launch_bounds__(SK_WARPS * 32, MIN_CTAS) gemm_skinny_kernel(void* __restrict__ out, int out_f32,
                                                                     const bf16* __restrict__ x, const bf16* __restrict__ w,
-                                                                    int m, int n, int k, int mode, int inter) {
+                                                                    int m, int n, int k, int mode, int inter,
+                                                                    const RopeEpilogue ep) {
     __shared__ float red[SK_WARPS][MT * 16][NT * 8 + 1];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, r = lane >> 2, c = lane & 3;
     int row0[MT];                                        // first weight row of each tile
@@ -106,6 +137,79 @@ __global__ void __launch_bounds__(SK_WARPS * 32, MIN_CTAS) gemm_skinny_kernel(vo
             red[warp][a * 16 + r + 8][b * 8 + c * 2 + 1] = acc[a][b][3];
         }
     __syncthreads();
+    if (MT == 1 && mode == 2) {
+        __shared__ float res[NT * 8][16];                            // the product, rounded as the separate kernel's input is
+        __shared__ float psum[NT * 8];                               // this CTA's share of each token's sum of squares
+        const int per_head = ep.head_dim >> 4, rank = blockIdx.x % per_head, item = blockIdx.x / per_head;
+        const bool is_q = item < ep.heads, is_v = item >= ep.heads + ep.kv_heads;
+        for (int i = threadIdx.x; i < 16 * m; i += SK_WARPS * 32) {
+            const int rr = i & 15, tok = i >> 4;
+            float v = 0.f;
+#pragma unroll
+            for (int wv = 0; wv < SK_WARPS; ++wv) v += red[wv][rr][tok];
+            res[tok][rr] = rounded<bf16>(v);
+        }
+        __syncthreads();
+        if (threadIdx.x < m) {
+            float ss = 0.f;
+#pragma unroll
+            for (int j = 0; j < 16; ++j) ss += res[threadIdx.x][j] * res[threadIdx.x][j];
+            psum[threadIdx.x] = ss;
+        }
+        __syncthreads();
+        __syncwarp();
+        cluster_barrier_all();                                       // every CTA of the head has its 16 columns ready
+        const void* weight = is_q ? ep.q_weight : ep.k_weight;
+        const int half = ep.head_dim >> 1;
+        __shared__ float rstd_s[NT * 8];
+        if (threadIdx.x < m && weight && !is_v) {                    // the head's sum of squares, in the order of its CTAs
+            float part[8], ss = 0.f;
+#pragma unroll
+            for (int p2 = 0; p2 < 8; ++p2) part[p2] = p2 < per_head ? ld_peer_f32(&psum[threadIdx.x], p2) : 0.f;
+#pragma unroll
+            for (int p2 = 0; p2 < 8; ++p2) ss += part[p2];
+            rstd_s[threadIdx.x] = rsqrtf(ss / (float)ep.head_dim + ep.eps);
+        }
+        __syncthreads();
+        for (int i = threadIdx.x; i < 16 * m; i += SK_WARPS * 32) {
+            const int rr = i & 15, tok = i >> 4, col = rank * 16 + rr;          // column inside the head
+            const int pair = col < half ? col : col - half, pcol = col < half ? col + half : col - half;
+            float y = res[tok][rr], other = 0.f, w_mine = 1.f, w_other = 1.f, cs = 1.f, sn = 0.f;
+            if (!is_v) {                                             // everything is asked for before anything is used
+                other = ld_peer_f32(&res[tok][rr], rank ^ (per_head >> 1));     // the column half a head away
+                if (weight) {
+                    w_mine = ep.weight_f32 ? ((const float*)weight)[col] : to_f32(((const bf16*)weight)[col]);
+                    w_other = ep.weight_f32 ? ((const float*)weight)[pcol] : to_f32(((const bf16*)weight)[pcol]);
+                }
+                int pos = ep.positions[tok];
+                pos = pos < 0 ? 0 : (pos >= ep.max_positions ? ep.max_positions - 1 : pos);
+                cs = ep.table[(size_t)pos * ep.head_dim + pair];
+                sn = ep.table[(size_t)pos * ep.head_dim + half + pair];
+            }
+            bf16* dst = nullptr;
+            if (is_q) {
+                dst = ep.q_out + ((size_t)tok * ep.heads + item) * ep.head_dim + col;
+            } else if (ep.kv) {
+                const int w = ep.write_index[tok];
+                const int page = w >= 0 ? w / ep.page_size : -1, off = w >= 0 ? w % ep.page_size : 0;
+                const int head = item - ep.heads - (is_v ? ep.kv_heads : 0);
+                if (page >= 0 && page < ep.pages)
+                    dst = ep.kv + ((((size_t)page * 2 + is_v) * ep.kv_heads + head) * ep.page_size + off) * ep.head_dim + col;
+            }
+            if (!is_v) {
+                if (weight) {
+                    const float rstd = rstd_s[tok];
+                    y = rounded<bf16>(y * rstd * (w_mine + ep.offset));
+                    other = rounded<bf16>(other * rstd * (w_other + ep.offset));
+                }
+                y = col < half ? y * cs - other * sn : y * cs + other * sn;
+            }
+            if (dst) *dst = __float2bfloat16_rn(y);
+        }
+        __syncwarp();
+        cluster_barrier_all();                                       // nobody leaves while its shared memory may be read
+        return;
+    }
     const int rows_out = mode == 1 ? HALF * 16 : MT * 16;
     const int width = mode == 1 ? inter : n;
     for (int i = threadIdx.x; i < rows_out * m; i += SK_WARPS * 32) {
@@ -149,19 +253,71 @@ extern "C" int hb_gemm_bf16_skinny(void* out, int out_f32, const void* x, const 
     if (mode == 1) {
         if (inter < 1) HB_REFUSE("gemm_bf16_skinny: inter = %d", inter);
         const int grid = (inter + 15) / 16;
-        if (nt == 1) gemm_skinny_kernel<2, 1, 4, 2><<<grid, SK_WARPS * 32, 0, s>>>(out, out_f32, (const bf16*)x, (const bf16*)w, m, n, k, 1, inter);
-        else gemm_skinny_kernel<2, 2, 4, 2><<<grid, SK_WARPS * 32, 0, s>>>(out, out_f32, (const bf16*)x, (const bf16*)w, m, n, k, 1, inter);
+        if (nt == 1) gemm_skinny_kernel<2, 1, 4, 2><<<grid, SK_WARPS * 32, 0, s>>>(out, out_f32, (const bf16*)x, (const bf16*)w, m, n, k, 1, inter, RopeEpilogue{});
+        else gemm_skinny_kernel<2, 2, 4, 2><<<grid, SK_WARPS * 32, 0, s>>>(out, out_f32, (const bf16*)x, (const bf16*)w, m, n, k, 1, inter, RopeEpilogue{});
     } else {
         if (n < 1) HB_REFUSE("gemm_bf16_skinny: n = %d", n);
         const bool wide = n >= 32 * 2 * sms;             // enough rows to give every SM two CTAs of 32 rows
         const int grid = wide ? (n + 31) / 32 : (n + 15) / 16;
-        if (wide && nt == 1) gemm_skinny_kernel<2, 1, 4, 2><<<grid, SK_WARPS * 32, 0, s>>>(out, out_f32, (const bf16*)x, (const bf16*)w, m, n, k, 0, 0);
-        else if (wide) gemm_skinny_kernel<2, 2, 4, 2><<<grid, SK_WARPS * 32, 0, s>>>(out, out_f32, (const bf16*)x, (const bf16*)w, m, n, k, 0, 0);
+        if (wide && nt == 1) gemm_skinny_kernel<2, 1, 4, 2><<<grid, SK_WARPS * 32, 0, s>>>(out, out_f32, (const bf16*)x, (const bf16*)w, m, n, k, 0, 0, RopeEpilogue{});
+        else if (wide) gemm_skinny_kernel<2, 2, 4, 2><<<grid, SK_WARPS * 32, 0, s>>>(out, out_f32, (const bf16*)x, (const bf16*)w, m, n, k, 0, 0, RopeEpilogue{});
         else if (nt == 1 && grid > 2 * sms && grid <= 3 * sms)       // one wave of three CTAs per SM instead of one and a bit of two
-            gemm_skinny_kernel<1, 1, 4, 3><<<grid, SK_WARPS * 32, 0, s>>>(out, out_f32, (const bf16*)x, (const bf16*)w, m, n, k, 0, 0);
-        else if (nt == 1) gemm_skinny_kernel<1, 1, 8, 2><<<grid, SK_WARPS * 32, 0, s>>>(out, out_f32, (const bf16*)x, (const bf16*)w, m, n, k, 0, 0);
-        else gemm_skinny_kernel<1, 2, 8, 2><<<grid, SK_WARPS * 32, 0, s>>>(out, out_f32, (const bf16*)x, (const bf16*)w, m, n, k, 0, 0);
+            gemm_skinny_kernel<1, 1, 4, 3><<<grid, SK_WARPS * 32, 0, s>>>(out, out_f32, (const bf16*)x, (const bf16*)w, m, n, k, 0, 0, RopeEpilogue{});
+        else if (nt == 1) gemm_skinny_kernel<1, 1, 8, 2><<<grid, SK_WARPS * 32, 0, s>>>(out, out_f32, (const bf16*)x, (const bf16*)w, m, n, k, 0, 0, RopeEpilogue{});
+        else gemm_skinny_kernel<1, 2, 8, 2><<<grid, SK_WARPS * 32, 0, s>>>(out, out_f32, (const bf16*)x, (const bf16*)w, m, n, k, 0, 0, RopeEpilogue{});
     }
     HB_LAUNCH_CHECK("gemm_bf16_skinny");
     return 0;
+}
+
+template <typename Kernel>
+static int launch_head_clusters(Kernel kernel, int grid, int per_head, cudaStream_t s, void* out, const bf16* x, const bf16* w,
+                                int m, int n, int k, const RopeEpilogue& ep) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(grid);
+    cfg.blockDim = dim3(SK_WARPS * 32);
+    cfg.stream = s;
+    cudaLaunchAttribute attr = {};
+    attr.id = cudaLaunchAttributeClusterDimension;
+    attr.val.clusterDim.x = per_head; attr.val.clusterDim.y = 1; attr.val.clusterDim.z = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = 1;
+    HB_CUDA(cudaLaunchKernelEx(&cfg, kernel, out, 0, x, w, m, n, k, 2, 0, ep));
+    return 0;
+}
+
+// The attention's first product for up to 16 tokens with the q/k norm, the rotation and the cache write in its
+// epilogue (mode 2 above): x [m, k], w [(heads + 2 kv_heads) * head_dim, k]; q_out [m, heads, head_dim]; keys and
+// values go to kv [pages, 2, kv_heads, page_size, head_dim] at write_index (kv null: they are dropped). head_dim 32, 64
+// or 128 with the whole head rotated; weights of the norms bfloat16 or float32, or null for no norm.
+extern "C" int hb_qkv_rope_skinny(void* q_out, const void* x, const void* w, int m, int k, const int32_t* positions,
+                                  const float* table, int max_positions, const void* q_weight, const void* k_weight,
+                                  int weight_f32, float eps, float offset, void* kv, const int32_t* write_index,
+                                  int pages, int page_size, int heads, int kv_heads, int head_dim, hb_stream stream) {
+    if (m == 0) return 0;
+    if (m < 0 || m > 16) HB_REFUSE("qkv_rope_skinny: %d rows; this kernel takes 1 to 16", m);
+    if (k < 8 || k % 8) HB_REFUSE("qkv_rope_skinny: k = %d is no multiple of 8", k);
+    if (head_dim != 32 && head_dim != 64 && head_dim != 128) HB_REFUSE("qkv_rope_skinny: head_dim %d (32, 64 or 128)", head_dim);
+    if (heads < 1 || kv_heads < 1) HB_REFUSE("qkv_rope_skinny: %d heads, %d kv heads", heads, kv_heads);
+    if ((((uintptr_t)x | (uintptr_t)w) % 16) != 0) HB_REFUSE("qkv_rope_skinny: x and w must be 16-byte aligned");
+    if (!q_out || !positions || !table || max_positions < 1) HB_REFUSE("qkv_rope_skinny: q_out, positions and the table are needed");
+    if ((q_weight == nullptr) != (k_weight == nullptr)) HB_REFUSE("qkv_rope_skinny: both norm weights or none");
+    static int sms = 0;
+    if (sms == 0) {
+        int device = 0;
+        HB_CUDA(cudaGetDevice(&device));
+        HB_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device));
+    }
+    RopeEpilogue ep;
+    ep.q_out = (bf16*)q_out; ep.positions = positions; ep.table = table; ep.q_weight = q_weight; ep.k_weight = k_weight;
+    ep.kv = (bf16*)kv; ep.write_index = write_index; ep.eps = eps; ep.offset = offset; ep.max_positions = max_positions;
+    ep.weight_f32 = weight_f32; ep.pages = pages; ep.page_size = page_size < 1 ? 1 : page_size; ep.heads = heads;
+    ep.kv_heads = kv_heads; ep.head_dim = head_dim;
+    const int per_head = head_dim / 16, n = (heads + 2 * kv_heads) * head_dim, grid = n / 16;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (m <= 8 && grid > 2 * sms && grid <= 3 * sms)
+        return launch_head_clusters(gemm_skinny_kernel<1, 1, 4, 3>, grid, per_head, s, nullptr, (const bf16*)x, (const bf16*)w, m, n, k, ep);
+    if (m <= 8)
+        return launch_head_clusters(gemm_skinny_kernel<1, 1, 8, 2>, grid, per_head, s, nullptr, (const bf16*)x, (const bf16*)w, m, n, k, ep);
+    return launch_head_clusters(gemm_skinny_kernel<1, 2, 8, 2>, grid, per_head, s, nullptr, (const bf16*)x, (const bf16*)w, m, n, k, ep);
 }

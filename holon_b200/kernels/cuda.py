@@ -67,6 +67,7 @@ class CudaKernels:
         if self.decode_attention not in ("auto", "balanced", "splits"):
             raise KernelError(f"HOLON_B200_DECODE_ATTENTION must be auto, balanced or splits, not {self.decode_attention!r}")
         self.decode_cluster = os.environ.get("HOLON_B200_DECODE_CLUSTER", "1") != "0"   # splits of up to 8 merge in the kernel
+        self.fused_qkv = os.environ.get("HOLON_B200_FUSED_QKV", "1") != "0"   # decode steps: norm, rotation, cache write in the product
         self.decode_pinned = None             # set around a CUDA-graph capture: the captured launches keep this mode
         self.sms = torch.cuda.get_device_properties(self.device).multi_processor_count
         self.decode_ctas = None               # tests: a fixed number of CTAs for the balanced kernel
@@ -158,6 +159,32 @@ class CudaKernels:
                    _code(q_weight) if q_weight is not None else 0, ctypes.c_float(eps), ctypes.c_float(offset),
                    self._p(kv), self._i32(write_index, "write_index"), kv.shape[0] if kv is not None else 0,
                    kv.shape[3] if kv is not None else 1, t, heads, kv_heads, head_dim)
+
+    def qkv_rope(self, q_out, x, weight, positions, table, rotary_dim, q_weight, k_weight, eps, offset, kv,
+                 write_index, heads, kv_heads, head_dim) -> bool:
+        """The product x · weightᵀ with qk_norm_rope_kv_write folded into its epilogue, for the few rows of a decode
+        step (one kernel instead of two). False, with nothing done, where that kernel does not apply: more than
+        SKINNY_ROWS rows, another dtype, a head size other than 32, 64 or 128, a partial rotation or none."""
+        t, k = x.shape
+        if not self.fused_qkv or x.dtype != torch.bfloat16 or t > self.SKINNY_ROWS or k % 8 or table is None \
+                or head_dim not in (32, 64, 128) or rotary_dim != head_dim or (q_weight is None) != (k_weight is None):
+            return False
+        self._check(q_out, x, weight, positions, table, q_weight, k_weight, kv, write_index)
+        if weight.shape != ((heads + 2 * kv_heads) * head_dim, k) or weight.dtype != x.dtype \
+                or q_out.shape != (t, heads, head_dim) or q_out.dtype != x.dtype:
+            raise KernelError("qkv_rope: w must be [(heads + 2 kv_heads) head_dim, k] and q_out [tokens, heads, head_dim], bfloat16")
+        if table.dtype != torch.float32 or table.shape[1] != head_dim:
+            raise KernelError("qkv_rope: the rotation table must be float32 [positions, head_dim]")
+        if kv is not None and (kv.dtype != x.dtype or kv.shape[1:3] != (2, kv_heads) or kv.shape[4] != head_dim):
+            raise KernelError("qkv_rope: kv must be [pages, 2, kv_heads, page_size, head_dim], bfloat16")
+        if q_weight is not None and q_weight.dtype != k_weight.dtype:
+            raise KernelError("qkv_rope: the two norm weights must have one dtype")
+        self._call("hb_qkv_rope_skinny", self._p(q_out), self._p(x), self._p(weight), t, k,
+                   self._i32(positions, "positions"), self._p(table), table.shape[0], self._p(q_weight), self._p(k_weight),
+                   int(q_weight is not None and q_weight.dtype == torch.float32), ctypes.c_float(eps),
+                   ctypes.c_float(offset), self._p(kv), self._i32(write_index, "write_index"),
+                   kv.shape[0] if kv is not None else 0, kv.shape[3] if kv is not None else 1, heads, kv_heads, head_dim)
+        return True
 
     def paged_attention(self, out, q, kv, block_table, rows, scale, window) -> None:
         self._check(out, q, kv, block_table, rows.row_slot, rows.query_start, rows.kv_len)

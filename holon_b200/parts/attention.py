@@ -46,15 +46,16 @@ class GQA(Part):
 
     def forward(self, x: torch.Tensor, step, cache) -> torch.Tensor:
         t, k = x.shape[0], self.ctx.kernels
-        qkv = self.qkv.forward(x)
         q = self.ctx.empty(t, self.heads, self.head_dim)
         norm, pos = self.q_norm, self.position
-        k.qk_norm_rope_kv_write(
-            q, qkv, step.positions, pos.table if pos else None, pos.rotary_dim if pos else 0,
-            norm.weight.tensor if norm else None, self.k_norm.weight.tensor if norm else None,
-            norm.eps if norm else 0.0, norm.offset if norm else 0.0,
-            cache.kv if cache.fills else None, cache.group.write_index if cache.fills else None,
-            self.heads, self.kv_heads, self.head_dim)
+        after = (step.positions, pos.table if pos else None, pos.rotary_dim if pos else 0,
+                 norm.weight.tensor if norm else None, self.k_norm.weight.tensor if norm else None,
+                 norm.eps if norm else 0.0, norm.offset if norm else 0.0,
+                 cache.kv if cache.fills else None, cache.group.write_index if cache.fills else None,
+                 self.heads, self.kv_heads, self.head_dim)
+        fused = getattr(k, "qkv_rope", None)                         # a kernel table may do the product and what follows in one
+        if fused is None or not fused(q, x, self.qkv.weight.tensor, *after):
+            k.qk_norm_rope_kv_write(q, self.qkv.forward(x), *after)
         o = self.ctx.empty(t, self.heads, self.head_dim)
         k.paged_attention(o, q, cache.kv, cache.group.block_table, step.rows, self.scale, self.window)
         return self.o_proj.forward(o.view(t, self.heads * self.head_dim))

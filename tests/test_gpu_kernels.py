@@ -370,6 +370,46 @@ def test_attention_finds_one_far_key(K, dtype, page):
                 assert first_row.abs().max() < 1.0, (window, target)
 
 
+@pytest.mark.parametrize("heads,kv_heads,head_dim,hidden", [(32, 8, 128, 4096), (6, 1, 64, 104), (4, 4, 32, 64), (20, 2, 128, 320)])
+@pytest.mark.parametrize("m", [1, 8, 13])
+@pytest.mark.parametrize("norm", ["bfloat16", "float32", None])
+def test_qkv_product_with_norm_rotation_and_cache_write(K, heads, kv_heads, head_dim, hidden, m, norm):
+    """The decode step's QKV product with q/k norm, rotation and cache write in its epilogue (a cluster of CTAs per
+    head) against the product followed by the separate kernel: queries, and the pages that were written."""
+    g = torch.Generator().manual_seed(heads + m)
+    x = (torch.randn(m, hidden, generator=g) * 0.5).to(torch.bfloat16)
+    w = (torch.randn((heads + 2 * kv_heads) * head_dim, hidden, generator=g) * 0.05).to(torch.bfloat16)
+    wdt = {"bfloat16": torch.bfloat16, "float32": torch.float32, None: None}[norm]
+    qw = (1 + 0.1 * torch.randn(head_dim, generator=g)).to(wdt) if wdt else None
+    kw = (1 + 0.1 * torch.randn(head_dim, generator=g)).to(wdt) if wdt else None
+    positions = torch.randint(0, 500, (m,), generator=g, dtype=torch.int32)
+    inv = 1.0 / (1e4 ** (torch.arange(0, head_dim, 2, dtype=torch.float32) / head_dim))
+    angle = torch.arange(512, dtype=torch.float32)[:, None] * inv[None, :]
+    table = torch.cat((angle.cos(), angle.sin()), dim=-1).contiguous()
+    pages, page = 9, 16
+    write = torch.randperm(pages * page, generator=g)[:m].to(torch.int32)
+    if m > 2:
+        write[1] = -1                                                  # a token whose key and value go nowhere
+    dev = lambda t: None if t is None else t.to(DEV)                   # noqa: E731
+    outs = []
+    for fused in (True, False):
+        kv = torch.full((pages, 2, kv_heads, page, head_dim), 7.0, dtype=torch.bfloat16, device=DEV)
+        q = torch.full((m, heads, head_dim), float("nan"), dtype=torch.bfloat16, device=DEV)
+        args = (dev(positions), dev(table), head_dim, dev(qw), dev(kw), 1e-5, 0.0, kv, dev(write), heads, kv_heads, head_dim)
+        if fused:
+            assert K.qkv_rope(q, dev(x), dev(w), *args)
+        else:
+            qkv = torch.empty(m, w.shape[0], dtype=torch.bfloat16, device=DEV)
+            K.linear(qkv, dev(x), dev(w))
+            K.qk_norm_rope_kv_write(q, qkv, *args)
+        outs.append((q.float().cpu(), kv.float().cpu()))
+    (q1, kv1), (q2, kv2) = outs
+    assert torch.isfinite(q1).all()
+    scale = max(1.0, float(q2.abs().max()))
+    assert (q1 - q2).abs().max() <= 2e-2 * scale and (kv1 - kv2).abs().max() <= 2e-2 * max(scale, float(kv2.abs().max()))
+    assert ((kv1 == 7.0) == (kv2 == 7.0)).all()                        # the same places were written
+
+
 @pytest.mark.parametrize("geometry", [(32, 8, 128, 64), (40, 2, 64, 16), (6, 1, 48, 4), (16, 4, 256, 128)])
 def test_decode_attention_merged_inside_a_cluster(K, geometry):
     """2 to 8 splits of a row as a thread-block cluster that merges through distributed shared memory, rows shorter
