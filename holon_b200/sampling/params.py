@@ -1,5 +1,6 @@
 """Per-request sampling settings; names, defaults and meanings are the reference's `SamplingParams`
-(core/holon/api/batch.py:45-61). Penalties are refused as they are there (core/holon/core/engine.py:346-347)."""
+(core/holon/api/batch.py:45-61). Penalties are refused as they are there (core/holon/core/engine.py:346-347);
+log-probabilities, which the reference returns, are refused too (this engine does not build them)."""
 from __future__ import annotations
 
 import dataclasses
@@ -21,10 +22,14 @@ class SamplingParams:
     ignore_eos: bool = False
     stop_token_ids: tuple[int, ...] = ()
     seed: int | None = None                  # None: the engine draws one
+    logprobs: int | None = None              # the reference's top-k log-probabilities per generated token: not built
+    prompt_logprobs: int | None = None       # and per prompt token: not built
 
     def validate(self) -> None:
         if (self.presence_penalty, self.frequency_penalty, self.repetition_penalty) != (0.0, 0.0, 1.0):
             raise NotImplementedError("presence, frequency and repetition penalties are not implemented")
+        if self.logprobs is not None or self.prompt_logprobs is not None:
+            raise NotImplementedError("logprobs and prompt_logprobs are not implemented")
         if self.n < 1:
             raise ValueError("SamplingParams.n must be >= 1")
         if self.temperature < 0 or not 0 < self.top_p <= 1 or self.top_k < 0 or not 0 <= self.min_p <= 1:

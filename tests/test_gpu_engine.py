@@ -94,6 +94,8 @@ def test_limits_and_errors(model):
         engine.add([config["vocab_size"]])
     with pytest.raises(NotImplementedError):
         engine.add([1], SamplingParams(repetition_penalty=1.1))
+    with pytest.raises(NotImplementedError):
+        engine.add([1], SamplingParams(logprobs=3))
     out = engine.generate([[1, 2, 3]], SamplingParams(temperature=0.0))          # no max_tokens: stops at max_model_len
     assert len(out[0]) == 32 - 3
     rid = engine.add([4, 5, 6], SamplingParams(temperature=0.0, max_tokens=50))
