@@ -16,7 +16,6 @@ import torch
 
 from ..config.engine import EngineConfig
 from ..sampling import Sampler, SamplingParams, sampling_arrays, sequence_seed
-from ..sampling.params import SEED_MASK
 from ..weights import SafetensorsSource
 from .batch import StepEntry
 from .build import build
@@ -31,7 +30,7 @@ class TokenDelta:
 
     rid: str
     token_ids: list[int]
-    index: int                               # how many tokens the request had generated before these
+    index: int = 0                           # which of the request's `n` sequences these belong to
     finish_reason: str | None = None         # "stop" | "length" | "abort" | None
 
 
@@ -62,7 +61,7 @@ class Engine:
         self.eos = frozenset(source.eos_token_ids())
         self.scheduler = Scheduler(b.cache, config.max_step_tokens, config.max_model_len, config.chunk_with_decode)
         self.sampler = Sampler(b.ctx.kernels, self.device)
-        self.requests: dict[str, Request] = {}
+        self.requests: dict[str, list[Request]] = {}          # a request's sequences that have not finished
         self._base_seed = config.seed if config.seed is not None else secrets.randbits(63)
         self._added = 0
         self._graphs: dict[int, tuple] = {}
@@ -82,10 +81,11 @@ class Engine:
 
     # ------------------------------------------------------------------ requests
     def add(self, token_ids: Sequence[int], params: SamplingParams | None = None, rid: str | None = None) -> str:
+        """Queues a request. Its `params.n` sequences stream as TokenDeltas with `index` 0 .. n-1, each sampling from
+        a seed of its own (core/holon/core/engine.py:331-376). Every sequence computes the prompt for itself: there
+        is no index of cached prefixes to adopt it from."""
         params = params or SamplingParams()
         params.validate()
-        if params.n != 1:
-            raise NotImplementedError("n > 1: add the prompt n times with seeds from sampling.sequence_seed")
         tokens = [int(t) for t in token_ids]
         if not tokens:
             raise ValueError("empty prompt")
@@ -98,18 +98,22 @@ class Engine:
         rid = rid if rid is not None else f"r{self._added}"
         if rid in self.requests:
             raise ValueError(f"request id {rid!r} is in use")
-        seed = (params.seed if params.seed is not None else sequence_seed(self._base_seed, self._added + 1)) & SEED_MASK
+        base = params.seed if params.seed is not None else sequence_seed(self._base_seed, self._added + 1)
         self._added += 1
-        self.requests[rid] = request = Request(rid, tokens, len(tokens), params, seed)
-        self.scheduler.add(request)
+        self.requests[rid] = live = []
+        for i in range(params.n):
+            live.append(Request(rid, list(tokens), len(tokens), params, sequence_seed(base, i), index=i))
+            self.scheduler.add(live[-1])
         return rid
 
-    def abort(self, rid: str) -> TokenDelta | None:
-        request = self.requests.pop(rid, None)
-        if request is None:
-            return None
-        self.scheduler.finish(request, "abort", release=request.pending == 0)   # (a row in flight gives the slot back)
-        return TokenDelta(rid, [], request.generated, "abort")
+    def abort(self, rid: str) -> list[TokenDelta]:
+        """Finishes every sequence of request `rid` that is still live, one delta each; none if the id is unknown
+        (core/holon/core/engine.py:391-410)."""
+        deltas = []
+        for request in self.requests.pop(rid, []):
+            self.scheduler.finish(request, "abort", release=request.pending == 0)   # (a row in flight gives the slot back)
+            deltas.append(TokenDelta(rid, [], request.index, "abort"))
+        return deltas
 
     def has_work(self) -> bool:
         return self.scheduler.has_work() or self._inflight is not None
@@ -269,16 +273,22 @@ class Engine:
                     self.built.cache.release(request.slot)
                     request.slot = -1
                 continue
-            index = request.generated
             request.tokens.append(int(token))
             if request.status is not Status.RUNNING:
                 self.scheduler.finished_prefill(request)
             reason = self._finish_reason(request, int(token))
             if reason:
                 self.scheduler.finish(request, reason, release=request.pending == 0)
-                self.requests.pop(request.rid, None)
-            deltas.append(TokenDelta(request.rid, [int(token)], index, reason))
+                self._retire(request)
+            deltas.append(TokenDelta(request.rid, [int(token)], request.index, reason))
         return deltas
+
+    def _retire(self, request: Request) -> None:
+        live = self.requests.get(request.rid)
+        if live is not None and request in live:
+            live.remove(request)
+            if not live:
+                del self.requests[request.rid]
 
     def _finish_reason(self, request: Request, token: int) -> str | None:
         p = request.params
@@ -294,6 +304,8 @@ class Engine:
                  ) -> list[list[int]]:
         """The generated token ids of every prompt (host lists in, host lists out), in the prompts' order."""
         many = isinstance(params, (list, tuple))
+        if any(p is not None and p.n != 1 for p in (params if many else [params])):
+            raise ValueError("generate() returns one sequence per prompt; step() streams n > 1")
         rids = [self.add(p, params[i] if many else params) for i, p in enumerate(prompts)]
         out: dict[str, list[int]] = {rid: [] for rid in rids}
         while any(rid in self.requests for rid in rids):

@@ -36,6 +36,7 @@ class Request:
     prompt_len: int
     params: SamplingParams
     seed: int = 0
+    index: int = 0                          # which of its request's `n` sequences this is
     slot: int = -1
     computed: int = 0                       # tokens whose keys and values the cache holds (or is being given)
     pending: int = 0                        # tokens sampled by steps in flight, not yet read back

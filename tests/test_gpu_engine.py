@@ -62,6 +62,36 @@ def test_greedy_generation(model, dtype, graphs):
         assert again.generate(prompts, params) == got            # other batching, other pages, depth 0: the same tokens
 
 
+def test_the_sequences_of_one_request_stream_under_their_indices(model):
+    """`n` = 3: three sequences under one id, each the same as a request of its own with that sequence's seed; the
+    whole-prompt call refuses n > 1 (core/holon/core/engine.py:331-376, 473-477)."""
+    from holon_b200.sampling.params import sequence_seed
+    folder, config, weights, prompts = model
+    engine = engine_of(folder, "bfloat16")
+    params = SamplingParams(temperature=0.9, max_tokens=6, seed=41, n=3)
+    rid = engine.add([3, 1, 4, 1, 5], params, rid="pi")
+    got = {i: [] for i in range(3)}
+    ended = set()
+    while engine.has_work():
+        for d in engine.step():
+            assert d.rid == rid == "pi" and d.index not in ended
+            got[d.index].extend(d.token_ids)
+            if d.finish_reason:
+                ended.add(d.index)
+    assert ended == {0, 1, 2} and "pi" not in engine.requests and not engine.built.cache.live
+    alone = [engine.generate([[3, 1, 4, 1, 5]], SamplingParams(temperature=0.9, max_tokens=6,
+                                                               seed=sequence_seed(41, i)))[0] for i in range(3)]
+    assert [got[i] for i in range(3)] == alone and len({tuple(a) for a in alone}) > 1
+    with pytest.raises(ValueError, match="one sequence per prompt"):
+        engine.generate([[1, 2]], params)
+    engine.add([1, 2, 3], params, rid="gone")
+    engine.step()
+    assert sorted(d.index for d in engine.abort("gone")) == [0, 1, 2]
+    engine.drain()
+    assert not engine.has_work() and not engine.built.cache.live
+    engine.close()
+
+
 def test_sampled_generation_is_seeded_and_survives_preemption(model):
     folder, config, weights, prompts = model
     params = [SamplingParams(temperature=0.8, max_tokens=10, seed=100 + i, top_k=(0, 20)[i % 2], top_p=(1.0, 0.9)[i // 3],
@@ -100,7 +130,7 @@ def test_limits_and_errors(model):
     assert len(out[0]) == 32 - 3
     rid = engine.add([4, 5, 6], SamplingParams(temperature=0.0, max_tokens=50))
     engine.step()
-    assert engine.abort(rid).finish_reason == "abort"
+    assert [(d.index, d.finish_reason) for d in engine.abort(rid)] == [(0, "abort")] and engine.abort(rid) == []
     engine.drain()                                                   # (its first step was still in flight)
     assert not engine.has_work() and not engine.built.cache.live
     stop = out[0][2]
