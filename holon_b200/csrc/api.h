@@ -62,8 +62,10 @@ int hb_attention_decode_bf16(void* out, float* scratch, const void* q, const voi
                              const int32_t* kv_len, int rows, int heads, int kv_heads, int head_dim, int pages,
                              int page_size, float scale, int window, int splits, hb_stream stream);
 
-// The same rows with 2 to 8 splits whose CTAs form a thread-block cluster and merge through distributed shared memory
-// inside the kernel: no scratch, no second kernel.
+// The same rows with 2 to 16 splits whose CTAs form a thread-block cluster and merge through distributed shared memory
+// inside the kernel: no scratch, no second kernel. hb_attention_decode_cluster_capacity: clusters of that many CTAs
+// that the GPU runs at once for this head size (0: none).
+int hb_attention_decode_cluster_capacity(int head_dim, int splits);
 int hb_attention_decode_bf16_cluster(void* out, const void* q, const void* kv, const int32_t* block_table,
                                      int table_stride, const int32_t* row_slot, const int32_t* query_start,
                                      const int32_t* kv_len, int rows, int heads, int kv_heads, int head_dim, int pages,

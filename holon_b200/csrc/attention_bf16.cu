@@ -489,19 +489,49 @@ static int launch_decode(bf16* out, float* part_o, float* part_ml, const bf16* q
     return 0;
 }
 
+// How many clusters of `splits` CTAs of the cluster kernel the GPU holds at once (0: none, or the size is refused).
+// Sizes beyond the portable 8 are asked for first.
+template <int D_PAD, int STAGES>
+static int decode_cluster_capacity(int splits) {
+    static int known[17] = {};                                       // per size: 0 unknown, else capacity + 1
+    if (known[splits] == 0) {
+        auto kernel = decode_cluster_kernel<D_PAD, STAGES>;
+        const size_t smem = decode_smem<D_PAD>(STAGES);
+        bool ok = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) == cudaSuccess;
+        if (ok && splits > 8)
+            ok = cudaFuncSetAttribute(kernel, cudaFuncAttributeNonPortableClusterSizeAllowed, 1) == cudaSuccess;
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(1, 1, splits);
+        cfg.blockDim = dim3(128);
+        cfg.dynamicSmemBytes = smem;
+        cudaLaunchAttribute attr = {};
+        attr.id = cudaLaunchAttributeClusterDimension;
+        attr.val.clusterDim.x = 1; attr.val.clusterDim.y = 1; attr.val.clusterDim.z = splits;
+        cfg.attrs = &attr;
+        cfg.numAttrs = 1;
+        int clusters = 0;
+        if (!ok || cudaOccupancyMaxActiveClusters(&clusters, kernel, &cfg) != cudaSuccess) {
+            (void)cudaGetLastError();
+            clusters = 0;
+        }
+        known[splits] = clusters + 1;
+    }
+    return known[splits] - 1;
+}
+
 template <int D_PAD, int STAGES>
 static int launch_decode_cluster(bf16* out, const bf16* q, const bf16* kv, const int32_t* block_table, int table_stride,
                                  const int32_t* row_slot, const int32_t* query_start, const int32_t* kv_len, int rows,
                                  int heads, int kv_heads, int head_dim, int pages, int page_size, float scale, int window,
                                  int splits, cudaStream_t s) {
     auto kernel = decode_cluster_kernel<D_PAD, STAGES>;
-    const size_t smem = decode_smem<D_PAD>(STAGES);
-    HB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    if (decode_cluster_capacity<D_PAD, STAGES>(splits) < 1)          // (sets the kernel's attributes at its first call)
+        HB_REFUSE("attention_decode_bf16_cluster: this GPU places no cluster of %d CTAs", splits);
     const int group = heads / kv_heads, m_tiles = (group + 15) / 16;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(rows, kv_heads * m_tiles, splits);
     cfg.blockDim = dim3(128);
-    cfg.dynamicSmemBytes = smem;
+    cfg.dynamicSmemBytes = decode_smem<D_PAD>(STAGES);
     cfg.stream = s;
     cudaLaunchAttribute attr = {};
     attr.id = cudaLaunchAttributeClusterDimension;
@@ -514,7 +544,17 @@ static int launch_decode_cluster(bf16* out, const bf16* q, const bf16* kv, const
     return 0;
 }
 
-// The rows of hb_attention_decode_bf16 with 2 to 8 splits that merge inside the kernel (a cluster per row and kv head).
+// Clusters of `splits` CTAs that run at once for this head size; the planner lets splits merge inside the kernel only
+// while every (row, kv head) has its cluster in that one wave.
+extern "C" int hb_attention_decode_cluster_capacity(int head_dim, int splits) {
+    if (splits < 2 || splits > 16 || head_dim < 16 || head_dim > 256) return 0;
+    if (head_dim <= 64) return decode_cluster_capacity<64, 4>(splits);
+    if (head_dim <= 128) return decode_cluster_capacity<128, 2>(splits);
+    return decode_cluster_capacity<256, 2>(splits);
+}
+
+// The rows of hb_attention_decode_bf16 with 2 to 16 splits that merge inside the kernel (a cluster per row and kv
+// head; more than 8 CTAs a cluster is the size the hardware allows beyond the portable one).
 extern "C" int hb_attention_decode_bf16_cluster(void* out, const void* q, const void* kv, const int32_t* block_table,
                                                 int table_stride, const int32_t* row_slot, const int32_t* query_start,
                                                 const int32_t* kv_len, int rows, int heads, int kv_heads, int head_dim,
@@ -524,7 +564,7 @@ extern "C" int hb_attention_decode_bf16_cluster(void* out, const void* q, const 
     if (head_dim % 16 || head_dim > 256 || head_dim < 16)
         HB_REFUSE("attention_decode_bf16_cluster: head_dim %d is no multiple of 16 up to 256", head_dim);
     if (kv_heads < 1 || heads % kv_heads) HB_REFUSE("attention_decode_bf16_cluster: %d heads, %d kv heads", heads, kv_heads);
-    if (splits < 2 || splits > 8) HB_REFUSE("attention_decode_bf16_cluster: %d splits (2 to 8, a cluster's size)", splits);
+    if (splits < 2 || splits > 16) HB_REFUSE("attention_decode_bf16_cluster: %d splits (2 to 16, a cluster's size)", splits);
     if (!(scale > 0.f)) HB_REFUSE("attention_decode_bf16_cluster: the score scale must be positive");
     if (rows > 65535 * 32) HB_REFUSE("attention_decode_bf16_cluster: %d rows", rows);
     cudaStream_t s = (cudaStream_t)stream;

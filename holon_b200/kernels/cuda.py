@@ -66,7 +66,7 @@ class CudaKernels:
         self.decode_attention = os.environ.get("HOLON_B200_DECODE_ATTENTION", "auto")
         if self.decode_attention not in ("auto", "balanced", "splits"):
             raise KernelError(f"HOLON_B200_DECODE_ATTENTION must be auto, balanced or splits, not {self.decode_attention!r}")
-        self.decode_cluster = os.environ.get("HOLON_B200_DECODE_CLUSTER", "1") != "0"   # splits of up to 8 merge in the kernel
+        self.decode_cluster = os.environ.get("HOLON_B200_DECODE_CLUSTER", "1") != "0"   # splits of up to 16 merge in the kernel
         self.fused_qkv = os.environ.get("HOLON_B200_FUSED_QKV", "1") != "0"   # decode steps: norm, rotation, cache write in the product
         self.decode_pinned = None             # set around a CUDA-graph capture: the captured launches keep this mode
         self.sms = torch.cuda.get_device_properties(self.device).multi_processor_count
@@ -212,14 +212,8 @@ class CudaKernels:
                 scratch = torch.empty(floats, dtype=torch.float32, device=self.device)
                 self._call("hb_attention_decode_bf16_balanced", self._p(out), self._p(scratch), self._p(q), self._p(kv),
                            *common, rows.n_decode, *sizes, ctas)
-            elif splits > 1 and self.decode_cluster and (few := self.decode_splits(
-                    rows.n_decode, heads, kv_heads, rows.max_kv, 8)) > 1 and self._split_cost(
-                    rows.n_decode, heads, kv_heads, rows.max_kv, few) <= 1.1 * self._split_cost(
-                    rows.n_decode, heads, kv_heads, rows.max_kv, splits) \
-                    and rows.n_decode * kv_heads * (-(-(heads // kv_heads) // 16)) * few <= 3 * self.sms:
-                # Up to eight splits cost about as little as the best number, and all CTAs fit the GPU at once: let
-                # them merge inside the kernel. (Over several waves clusters leave holes: at 64 rows 16.6 ms a step
-                # against 15.4 ms with the merge kernel.)
+            elif splits > 1 and (few := self.decode_cluster_splits(rows.n_decode, heads, kv_heads, head_dim,
+                                                                   rows.max_kv, splits)):
                 self._call("hb_attention_decode_bf16_cluster", self._p(out), self._p(q), self._p(kv), *common,
                            rows.n_decode, *sizes, few)
             else:
@@ -282,6 +276,36 @@ class CudaKernels:
             tiles = key[3]
             self._splits[key] = min(range(1, max(1, min(most, tiles)) + 1),
                                     key=lambda s: (self._split_cost(rows, heads, kv_heads, max_kv, s), s))
+        return self._splits[key]
+
+    MERGE_KERNEL_TILES = 6                    # what the second kernel and its scratch cost, in 64-key tile times
+
+    def decode_cluster_splits(self, rows: int, heads: int, kv_heads: int, head_dim: int, max_kv: int, splits: int) -> int:
+        """The number of splits (2 to 16) that merge inside the kernel as one thread-block cluster per (row, kv head),
+        or 0 where `splits` parts and the merge kernel are the better plan. A cluster is taken only while all of them
+        run at once (over several waves clusters leave holes: at 64 rows 16.6 ms a step against 15.4 ms with the merge
+        kernel; the runtime says how many clusters of each size fit, and from 12 CTAs a cluster that is fewer than
+        the CTA slots suggest); of those sizes the one whose CTAs walk the fewest tiles wins. Measured at 8,192 keys
+        and 8 kv heads of 128, that cluster against the best number of splits with the merge kernel: 1 row 20.5 µs
+        (16 CTAs) / 21.4, 3 rows 27.7 (15) / 29.7, 6 rows 38.9 (8) / 44.0, 8 rows 49.2 (6) / 56.2, 16 rows 87.0 (3) /
+        93.2, 24 rows 122.9 (2) / 138.2; from 32 rows on no size fits one wave."""
+        if not self.decode_cluster:
+            return 0
+        key = ("cluster", rows, heads, kv_heads, head_dim, -(-max_kv // 64), splits)
+        if key not in self._splits:
+            pairs, tiles = rows * kv_heads * (-(-(heads // kv_heads) // 16)), -(-max_kv // 64)
+            fitting = [s for s in range(2, min(16, tiles) + 1) if pairs <= self._cluster_capacity(head_dim, s)]
+            best = min(fitting, key=lambda s: (-(-tiles // s), s), default=0)
+            merged = self._split_cost(rows, heads, kv_heads, max_kv, splits) + self.MERGE_KERNEL_TILES
+            self._splits[key] = best if best and -(-tiles // best) + 1 <= merged else 0
+        return self._splits[key]
+
+    def _cluster_capacity(self, head_dim: int, splits: int) -> int:
+        key = ("capacity", -(-head_dim // 64) if head_dim <= 128 else 3, splits)
+        if key not in self._splits:
+            fn = self.lib.hb_attention_decode_cluster_capacity
+            fn.restype = ctypes.c_int
+            self._splits[key] = int(fn(int(head_dim), int(splits)))
         return self._splits[key]
 
     def _attention_generic(self, out, q, kv, block_table, rows, scale, window) -> None:

@@ -10,6 +10,7 @@ Sizes default to Qwen3-8B's (32 query and 8 KV heads of 128, hidden 4096, interm
 from __future__ import annotations
 
 import argparse
+import ctypes
 import math
 
 import torch
@@ -53,14 +54,16 @@ def decode_attention(k, args) -> None:
         moved = rows * args.context * kv_heads * d * 2 * 2
         planned = k.decode_splits(rows, heads, kv_heads, args.context)
         call = lambda: k.paged_attention(out, q, kv, table, batch, 1 / math.sqrt(d), 0)   # noqa: E731
-        k.decode_attention = "balanced"
+        k.decode_attention = "balanced"                    # (the rows keep a step's plan: forget it with every change)
         t = timed(call, flush)
         print(f"decode attention rows {rows} context {args.context} balanced: {t:7.1f} us  {moved / t / 1e6:5.2f} TB/s")
         k.decode_attention = "splits"
+        batch.plan.clear()
         t = timed(call, flush)
-        few = k.decode_splits(rows, heads, kv_heads, args.context, 8)
-        print(f"decode attention rows {rows} context {args.context} as the kernel table runs it (splits {planned}, or {few} "
-              f"merged inside a cluster if that costs about the same): {t:7.1f} us  {moved / t / 1e6:5.2f} TB/s")
+        few = k.decode_cluster_splits(rows, heads, kv_heads, d, args.context, planned)
+        print(f"decode attention rows {rows} context {args.context} as the kernel table runs it ("
+              + (f"a cluster of {few} splits" if few else f"{planned} splits, merge kernel")
+              + f"): {t:7.1f} us  {moved / t / 1e6:5.2f} TB/s")
         cluster, k.decode_cluster = k.decode_cluster, False
         for splits in (args.splits or [planned]):
             k._splits[(rows, heads, kv_heads, -(-args.context // 64), 64)] = splits
@@ -68,6 +71,14 @@ def decode_attention(k, args) -> None:
             print(f"decode attention rows {rows} context {args.context} splits {splits}, merge kernel: {t:7.1f} us  {moved / t / 1e6:5.2f} TB/s"
                   + ("  (the planner's choice)" if splits == planned else ""))
         k.decode_cluster = cluster
+        for splits in args.cluster or []:                  # the cluster kernel itself, whatever the table would choose
+            direct = lambda: k._call(                      # noqa: E731
+                "hb_attention_decode_bf16_cluster", k._p(out), k._p(q), k._p(kv), k._i32(table, "table"), table.shape[1],
+                k._i32(batch.row_slot, "slot"), k._i32(batch.query_start, "start"), k._i32(batch.kv_len, "len"), rows,
+                heads, kv_heads, d, kv.shape[0], page, ctypes.c_float(1 / math.sqrt(d)), 0, splits)
+            t = timed(direct, flush)
+            print(f"decode attention rows {rows} context {args.context} a cluster of {splits} splits: {t:7.1f} us  "
+                  f"{moved / t / 1e6:5.2f} TB/s")
         k.decode_attention = "balanced"
         k._splits.clear()
 
@@ -126,6 +137,7 @@ def main() -> None:
     ap.add_argument("--rows", type=int, nargs="*", default=None)
     ap.add_argument("--context", type=int, default=8192)
     ap.add_argument("--splits", type=int, nargs="*", default=None)
+    ap.add_argument("--cluster", type=int, nargs="*", default=None, help="decode attention: cluster sizes to time")
     ap.add_argument("--shapes", nargs="*", default=list(SHAPES), choices=list(SHAPES))
     ap.add_argument("--device", default="cuda:0")
     args = ap.parse_args()

@@ -412,8 +412,9 @@ def test_qkv_product_with_norm_rotation_and_cache_write(K, heads, kv_heads, head
 
 @pytest.mark.parametrize("geometry", [(32, 8, 128, 64), (40, 2, 64, 16), (6, 1, 48, 4), (16, 4, 256, 128)])
 def test_decode_attention_merged_inside_a_cluster(K, geometry):
-    """2 to 8 splits of a row as a thread-block cluster that merges through distributed shared memory, rows shorter
-    than the number of splits among them, against the plain formula and run to run."""
+    """2 to 16 splits of a row as a thread-block cluster that merges through distributed shared memory, rows shorter
+    than the number of splits among them, against the plain formula and run to run; and the planner takes a cluster
+    only while every (row, kv head) has one in the same wave."""
     heads, kv_heads, head_dim, page = geometry
     spec = [(1999, 1), (0, 1), (63, 1), (64, 1), (700, 1), (5, 1), (1300, 1), (128, 1)]
     q, kv, table, rows = paged_case(heads, kv_heads, head_dim, page, spec, torch.bfloat16, seed=31)
@@ -421,7 +422,8 @@ def test_decode_attention_merged_inside_a_cluster(K, geometry):
     want = torch.empty_like(q)
     REF.paged_attention(want, q, kv, table, rows, scale, 0)
     args = (q.to(DEV), kv.to(DEV), table.to(DEV), on_device(rows))
-    for splits in range(2, 9):
+    for splits in range(2, 17):
+        assert K._cluster_capacity(head_dim, splits) >= 1
         outs = []
         for _ in range(2):
             out = torch.full_like(q, float("nan"), device=DEV)
@@ -432,6 +434,15 @@ def test_decode_attention_merged_inside_a_cluster(K, geometry):
             outs.append(out)
         close(outs[0], want, torch.bfloat16, scale=4)
         assert torch.equal(outs[0], outs[1]), splits
+    for n_rows in (1, 2, 8, 16, 64, 300):
+        planned = K.decode_splits(n_rows, heads, kv_heads, 8192)
+        few = K.decode_cluster_splits(n_rows, heads, kv_heads, head_dim, 8192, planned)
+        pairs = n_rows * kv_heads * (-(-(heads // kv_heads) // 16))
+        assert few == 0 or (2 <= few <= 16 and pairs <= K._cluster_capacity(head_dim, few)), (n_rows, few)
+        if n_rows == 1 and pairs <= K._cluster_capacity(head_dim, 16):
+            assert few == 16                               # one row of 128 tiles: the largest cluster, 8 tiles a CTA
+        if n_rows == 300:
+            assert few == 0                                # several waves: the merge kernel
 
 
 @pytest.mark.parametrize("window", [0, 4096])
