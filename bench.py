@@ -39,6 +39,10 @@ QWEN3_8B = dict(architectures=["Qwen3ForCausalLM"], num_hidden_layers=36, hidden
                 num_key_value_heads=8, head_dim=128, intermediate_size=12288, vocab_size=151936, rope_theta=1000000.0,
                 rms_norm_eps=1e-6, tie_word_embeddings=False, max_position_embeddings=40960)
 FULL_LAYERS = QWEN3_8B["num_hidden_layers"]
+# The other two sizes the benchmark's configurations name, for `--only sizes --sizes ...` (their own workloads).
+QWEN3_06B = dict(QWEN3_8B, num_hidden_layers=28, hidden_size=1024, num_attention_heads=16, intermediate_size=3072,
+                 tie_word_embeddings=True)
+QWEN3_32B = dict(QWEN3_8B, num_hidden_layers=64, hidden_size=5120, num_attention_heads=64, intermediate_size=25600)
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
 
 
@@ -259,12 +263,84 @@ def long_prompt_run(args) -> dict:
             "prompt_tokens_per_s": round(30000 / best, 1), "steps": steps}
 
 
+def sizes_run(args) -> dict:
+    """The workloads of the two other configurations: Qwen3-32B sizes (decode at batch 1 and 64 over 4,096-token
+    prompts, prefill of one 8,192-token prompt, context 16,384) and Qwen3-0.6B sizes (32 requests with prompts uniform
+    in [16, 4096] tokens, prompt portions of 512 beside the decode rows, 128 tokens each, through `Engine.generate`)."""
+    import random
+    import torch
+    from holon_b200.engine import Engine, EngineConfig, SamplingParams
+    from holon_b200.weights import RandomSource
+    peak, peak_kind = peaks()
+    out = {"only": "sizes", "sizes": args.sizes, "peaks": peak_kind}
+    if args.sizes == "32b":
+        cfg, seed = dict(QWEN3_32B), 4
+        engine = Engine(EngineConfig(model="random weights, seed 4", device="cuda:0", dtype="bfloat16", page_size=64,
+                                     max_seqs=64, max_model_len=16384, max_step_tokens=8192, seed=0),
+                        source=RandomSource(cfg, seed=seed, device="cuda:0"))
+        numbers = model_numbers(cfg, cfg["num_hidden_layers"])
+        tokens = 8192
+        ms = prefill_run(engine, tokens, repeats=2, seed=100)
+        flops = 2 * numbers["linear_params"] * tokens - 2 * cfg["vocab_size"] * cfg["hidden_size"] * (tokens - 1) \
+            + numbers["attn_flops_per_pair"] * tokens * (tokens + 1) / 2
+        out["prefill"] = {"value": round(tokens / ms * 1e3, 1), "tokens": tokens, "ms": round(ms, 2),
+                          "frac": round(flops / (ms * 1e-3) / (peak["bf16_tflops"] * 1e12), 4)}
+        steps = max(8, min(args.steps, 64))
+        for b in (1, 64):
+            r = decode_run(engine, b, 4096 + steps + args.warmup + 1, steps, args.warmup, seed=11 + b)
+            ms_step = r["device_ms"] / steps
+            moved = numbers["weight_bytes"] + b * r["mean_context"] * numbers["kv_bytes_per_token"]
+            out[f"decode_b{b}"] = {"value": round(r["tokens"] / r["device_ms"] * 1e3, 1), "ms_per_step": round(ms_step, 3),
+                                   "hbm_frac": round(moved / (ms_step * 1e-3) / 1e9 / peak["hbm_gbs"], 4)}
+    else:
+        cfg, seed = dict(QWEN3_06B), 3
+        engine = Engine(EngineConfig(model="random weights, seed 3", device="cuda:0", dtype="bfloat16", page_size=64,
+                                     max_seqs=32, max_model_len=4352, max_step_tokens=4096, chunk_with_decode=512, seed=0),
+                        source=RandomSource(cfg, seed=seed, device="cuda:0"))
+        rng = random.Random(5)
+        prompts = [[rng.randrange(cfg["vocab_size"]) for _ in range(rng.randint(16, 4096))] for _ in range(32)]
+        params = SamplingParams(temperature=0.0, max_tokens=128, ignore_eos=True)
+        best = float("inf")
+        for rep in range(3):                                         # the first one is a warm-up
+            torch.cuda.synchronize()
+            t0 = time.perf_counter()
+            got = engine.generate(prompts, params)
+            torch.cuda.synchronize()
+            if rep:
+                best = min(best, time.perf_counter() - t0)
+        n_prompt, n_out = sum(map(len, prompts)), sum(map(len, got))
+        out["serve"] = {"requests": 32, "prompt_tokens": n_prompt, "generated_tokens": n_out, "seconds": round(best, 4),
+                        "generated_tokens_per_s": round(n_out / best, 1), "all_tokens_per_s": round((n_prompt + n_out) / best, 1),
+                        "chunk_with_decode": 512, "stats": engine.stats()}
+        engine.close()
+        del engine                                                   # (its cache pool took the free memory)
+        import gc
+        gc.collect()
+        torch.cuda.empty_cache()
+        engine = Engine(EngineConfig(model="random weights, seed 3", device="cuda:0", dtype="bfloat16", page_size=64,
+                                     max_seqs=32, max_model_len=4352, max_step_tokens=4096, seed=0),
+                        source=RandomSource(cfg, seed=seed, device="cuda:0"))
+        numbers = model_numbers(cfg, cfg["num_hidden_layers"])
+        steps = max(8, min(args.steps, 64))
+        for b in (1, 32):
+            r = decode_run(engine, b, 2048 + steps + args.warmup + 1, steps, args.warmup, seed=11 + b)
+            ms_step = r["device_ms"] / steps
+            moved = numbers["weight_bytes"] + b * r["mean_context"] * numbers["kv_bytes_per_token"]
+            out[f"decode_b{b}"] = {"value": round(r["tokens"] / r["device_ms"] * 1e3, 1), "ms_per_step": round(ms_step, 3),
+                                   "hbm_frac": round(moved / (ms_step * 1e-3) / 1e9 / peak["hbm_gbs"], 4)}
+    out["config"] = {k: cfg[k] for k in ("num_hidden_layers", "hidden_size", "num_attention_heads", "num_key_value_heads",
+                                         "head_dim", "intermediate_size", "vocab_size", "tie_word_embeddings")}
+    return out
+
+
 def run_ours(args) -> dict:
     import torch
     from holon_b200.engine import Engine, EngineConfig
     from holon_b200.weights import RandomSource
     if args.only == "long_prompt":
         return long_prompt_run(args)
+    if args.only == "sizes":
+        return sizes_run(args)
     cfg = dict(QWEN3_8B, num_hidden_layers=args.layers)
     context, batch = args.context, args.batch
     engine = Engine(EngineConfig(model="random weights, seed 2", device="cuda:0", dtype="bfloat16", page_size=64,
@@ -342,9 +418,11 @@ def main() -> int:
     ap.add_argument("--layers", type=int, default=FULL_LAYERS, help="fewer layers than the model has (both are reported)")
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--context", type=int, default=8192)
-    ap.add_argument("--only", default="all", choices=("all", "decode", "prefill", "long_prompt"),
+    ap.add_argument("--only", default="all", choices=("all", "decode", "prefill", "long_prompt", "sizes"),
                     help="run one part only (for profiling a small case); the JSON line then lacks the other parts. "
-                         "long_prompt: time to first token of a 30,000-token prompt behind three decoding requests")
+                         "long_prompt: time to first token of a 30,000-token prompt behind three decoding requests; "
+                         "sizes: the workloads of the Qwen3-32B and Qwen3-0.6B configurations (--sizes)")
+    ap.add_argument("--sizes", default="32b", choices=("32b", "0.6b"), help="with --only sizes: which configuration")
     args = ap.parse_args()
     if args.gpus != 1:
         print(f"holon_b200 is a single-GPU engine: --gpus {args.gpus} is not supported")

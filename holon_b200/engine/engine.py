@@ -22,6 +22,7 @@ from .build import build
 from .scheduler import Request, Row, Scheduler, Status
 
 GRAPH_BUCKETS = (1, 2, 4, 8, 16, 24, 32, 48, 64, 96, 128, 192, 256)
+GRAPH_PORTIONS = 2                            # prompt portions beside the decode rows of a step that runs as a graph
 
 
 @dataclasses.dataclass
@@ -44,6 +45,7 @@ class _Inflight:
     host: torch.Tensor | None
     done: object
     decode_only: bool
+    pick: list | None = None                 # where in `host` each sampled row's token lies (None: in their order)
 
 
 class Engine:
@@ -68,7 +70,7 @@ class Engine:
         self._graph_pool = None
         self._use_graphs = config.cuda_graphs and self.device.type == "cuda"
         self._buckets = tuple(x for x in GRAPH_BUCKETS if x < config.max_seqs) + (config.max_seqs,)   # the fullest batch too
-        self._host_tokens = [torch.zeros(config.max_seqs + 1, dtype=torch.int32) for _ in range(2)]
+        self._host_tokens = [torch.zeros(config.max_seqs + 1 + GRAPH_PORTIONS, dtype=torch.int32) for _ in range(2)]
         if self.device.type == "cuda":
             self._host_tokens = [t.pin_memory() for t in self._host_tokens]
         self._flip = 0
@@ -76,7 +78,7 @@ class Engine:
         # the token each request sampled last, by slot, on the device: decode rows of a step that is enqueued before
         # the step ahead of it has been read back take their input from here
         self.last_tokens = torch.zeros(config.max_seqs + 1, dtype=torch.int32, device=self.device)
-        self.steps = self.graph_steps = self._graph_launches = 0
+        self.steps = self.graph_steps = self.mixed_graph_steps = self._graph_launches = 0
         self.h2d_bytes = self.d2h_bytes = 0
 
     # ------------------------------------------------------------------ requests
@@ -181,22 +183,26 @@ class Engine:
         sampled = [r for r in rows if r.samples]
         n = len(sampled)
         runner.check(entries)
-        decode_only = n == len(entries) and all(len(e.tokens) == 1 for e in entries)
-        host = None
+        ones = sum(1 for e in entries if len(e.tokens) == 1)
+        decode_only = n == ones == len(entries)
+        host = pick = None
         if n:
             arrays = sampling_arrays([(r.request.params, r.request.seed, r.request.computed + r.n_tokens)
                                       for r in sampled])
             arrays["sample_slot"] = np.array([r.request.slot for r in sampled], dtype=np.int32)
             filtered = any(r.request.params.filtered for r in sampled)
-            if self._use_graphs and decode_only and not filtered and n <= (self._buckets[-1] if self._buckets else 0):
-                tokens = self._replay(entries, arrays)
+            if self._use_graphs and not filtered and self._graph_fits(entries, ones):
+                tokens, pick = self._replay(entries, [r.samples for r in rows], arrays)
+                m = tokens.shape[0]
+                if pick == list(range(n)):                 # (a plain decode step: its n tokens lie first, in order)
+                    m, pick = n, None
             else:
                 step = runner.context(entries, extra=arrays)
-                tokens = self._forward(step, filtered, n)
-            host = self._host_tokens[self._flip][:n]
+                tokens, m = self._forward(step, filtered, n), n
+            host = self._host_tokens[self._flip][:m]
             self._flip ^= 1
-            host.copy_(tokens[:n], non_blocking=True)
-            self.d2h_bytes += n * 4
+            host.copy_(tokens[:m], non_blocking=True)
+            self.d2h_bytes += m * 4
         else:                                              # every row stops short of its prompt's end: the head is skipped
             step = runner.context(entries)
             self._feed(step)
@@ -211,7 +217,21 @@ class Engine:
             self.scheduler.computed(r)
             r.request.pending += int(r.samples)
         self.steps += 1
-        return _Inflight(rows, sampled, host, done, decode_only)
+        return _Inflight(rows, sampled, host, done, decode_only, pick)
+
+    def _graph_fits(self, entries, ones: int) -> bool:
+        """Whether the step's shape is one that graphs are kept for: rows of one token alone, up to the largest
+        bucket; or such rows beside one or two prompt portions that fill the budget `chunk_with_decode` exactly, which
+        is what a step looks like while prompts wait behind decoding requests. (A graph serves every step with the
+        same counts; other shapes come too rarely to be worth a capture.)"""
+        if ones > self._buckets[-1]:
+            return False
+        portions = len(entries) - ones
+        if portions == 0:
+            return True
+        c = self.config.chunk_with_decode
+        return 0 < c and ones > 0 and portions <= GRAPH_PORTIONS \
+            and sum(len(e.tokens) for e in entries) - ones == c
 
     def _feed(self, step) -> None:
         self.built.ctx.kernels.feed_tokens(step.token_ids, self.last_tokens, step.rows, step.from_last)
@@ -224,30 +244,45 @@ class Engine:
         self.built.ctx.kernels.store_tokens(self.last_tokens, step.extra["sample_slot"], tokens, n)
         return tokens
 
-    def _replay(self, entries, arrays) -> torch.Tensor:
-        """A decode step through the CUDA graph of its batch-size bucket (core/holon/core/executor.py:316-344):
-        rows are padded to the bucket with rows of the padding slot, which read and write the null page."""
-        runner, n = self.built.runner, len(entries)
-        bucket = next(b for b in self._buckets if b >= n)
-        pad = bucket - n
-        fill = {"sample_slot": self.built.cache.padding_slot}
-        padded = {k: np.concatenate([v, np.full(pad, fill.get(k, 0), dtype=v.dtype)]) for k, v in arrays.items()}
+    def _replay(self, entries, samples, arrays) -> tuple[torch.Tensor, list[int]]:
+        """A step through the CUDA graph of its shape (core/holon/core/executor.py:316-344). One-token rows are padded
+        to a bucket with rows of the padding slot, which read and write the null page; prompt portions follow. Every
+        row's last token is sampled (a row that does not want it files the token under the padding slot), so that
+        the work depends on the shape alone. Returns the tokens of all rows and, for each sampling entry in the
+        entries' order, its row."""
+        runner, cache = self.built.runner, self.built.cache
+        single = [i for i, e in enumerate(entries) if len(e.tokens) == 1]
+        portions = [i for i, e in enumerate(entries) if len(e.tokens) != 1]
+        bucket = next(b for b in self._buckets if b >= len(single))
+        pad, m = bucket - len(single), bucket + len(portions)
+        row_of = {i: r for r, i in enumerate(single)} | {i: bucket + r for r, i in enumerate(portions)}
+        wanted = [i for i, s in enumerate(samples) if s]
+        at = np.array([row_of[i] for i in wanted], dtype=np.int64)
+        padded = {}
+        for name, values in arrays.items():
+            full = np.full(m, cache.padding_slot if name == "sample_slot" else 0, dtype=values.dtype)
+            full[at] = values
+            padded[name] = full
         step = runner.context(entries, pad_rows=pad, extra=padded)
         kernels = self.built.ctx.kernels
         lens = step.rows.host_kv_len
-        mode = kernels.decode_mode(lens[:n] if lens is not None else None) if hasattr(kernels, "decode_mode") else None
-        key = (bucket, mode)                                       # a graph per way of sharing out the keys it was captured with
+        mode = kernels.decode_mode(lens[:len(single)] if lens is not None else None) \
+            if hasattr(kernels, "decode_mode") else None
+        prompt_tokens = step.rows.n_tokens - bucket
+        key = (bucket, len(portions), prompt_tokens, mode)         # ... and a graph per way of sharing out the keys
         if key not in self._graphs:
             step.rows.max_kv = self.config.max_model_len          # the captured launch must serve any length
-            out = torch.empty(bucket, dtype=torch.int32, device=self.device)
+            for size in (64, 256):                                 # and any cut of the prompt tokens into the portions:
+                step.rows.plan[size] = prompt_tokens // size + len(portions)   # query tiles beyond a step's own exit at once
+            out = torch.empty(m, dtype=torch.int32, device=self.device)
             kernels.decode_pinned = mode
             try:
-                self._forward(step, False, bucket, out)            # warm-up, not captured
+                self._forward(step, False, m, out)                 # warm-up, not captured
                 torch.cuda.current_stream(self.device).synchronize()
                 graph = torch.cuda.CUDAGraph()
                 before = kernels.launches
                 with torch.cuda.graph(graph, pool=self._graph_pool):
-                    self._forward(step, False, bucket, out)
+                    self._forward(step, False, m, out)
                 captured, kernels.launches = kernels.launches - before, before   # recorded, not run
             finally:
                 kernels.decode_pinned = None
@@ -256,14 +291,17 @@ class Engine:
         graph, out, captured = self._graphs[key]
         graph.replay()
         self.graph_steps += 1
+        self.mixed_graph_steps += bool(portions)
         self._graph_launches += captured
-        return out
+        return out, [row_of[i] for i in wanted]
 
     def _commit(self, inflight: "_Inflight") -> list[TokenDelta]:
         """Waits for a launched step and books its tokens: appended, checked for a finish, reported."""
         if inflight.done is not None:
             inflight.done.synchronize()
         tokens = inflight.host.tolist() if inflight.host is not None else []
+        if inflight.pick is not None:
+            tokens = [tokens[i] for i in inflight.pick]
         deltas = []
         for row, token in zip(inflight.sampled, tokens):
             request = row.request
@@ -325,6 +363,7 @@ class Engine:
         s = self.scheduler
         return {"waiting": len(s.waiting), "running": len(s.running), "preemptions": s.preemptions,
                 "mixed_steps": s.mixed_steps, "steps": self.steps, "graph_steps": self.graph_steps,
+                "mixed_graph_steps": self.mixed_graph_steps,
                 "graphs": len(self._graphs), "free_tokens": self.built.cache.free_tokens()}
 
     def close(self) -> None:

@@ -57,9 +57,10 @@ class Runner:
 
     def context(self, entries: Sequence[StepEntry], pad_rows: int | None = None, extra=None) -> StepContext:
         """Lays the batch out (rows of one token first), uploads it in one copy and returns the device-side view.
-        `pad_rows` (not None: a graph bucket of decode rows): so many rows of one token each for the padding slot
-        follow the entries, and logits are taken at every row, padding included, so that the layout and the work
-        depend on the bucket's size alone.
+        `pad_rows` (not None: the step runs as a CUDA graph): so many rows of one token each for the padding slot
+        follow the entries' one-token rows, and logits are taken at the last token of every row, padding included,
+        so that the layout and the work depend on the counts alone (one-token rows with padding, rows of several
+        tokens, tokens), not on the entries.
         `extra`: {name: int32 array} uploaded alongside; the device views land in `StepContext.extra`."""
         c = self.cache
         order = sorted(range(len(entries)), key=lambda i: len(entries[i].tokens) != 1)       # stable
@@ -67,8 +68,6 @@ class Runner:
         n_decode = sum(1 for n in counts if n == 1)
         bucket = pad_rows is not None
         pad_rows = pad_rows or 0
-        if bucket and n_decode != len(entries):
-            raise StepError("a graph bucket holds rows of one token only")
         if pad_rows:
             counts[n_decode:n_decode] = [1] * pad_rows
         b = len(counts)
@@ -90,7 +89,7 @@ class Runner:
             from_last[r] = int(e.from_last)
             offset_of[i] = a
         if bucket:
-            logits_index = np.arange(b, dtype=np.int32)
+            logits_index = query_start[1:] - 1
         else:
             logits_index = np.array([offset_of[i] + w for i, e in enumerate(entries) for w in e.want], dtype=np.int32)
         up = self.uploader

@@ -205,8 +205,10 @@ class CudaKernels:
             if splits > 1 and mode == "balanced" and rows.n_decode <= self.BALANCED_ROWS:
                 pairs = rows.n_decode * kv_heads * (-(-(heads // kv_heads) // 16))
                 slots = self.sms * (1 if head_dim > 128 else 3)       # CTAs of this kernel that one wave holds
-                if pairs <= slots:                                    # a whole number of CTAs per (row, kv head): rows of
+                if 2 * pairs <= slots:                                # a whole number of CTAs per (row, kv head): rows of
                     slots = pairs * (slots // pairs)                  # equal length are then cut at their own ends only
+                # (with more than half a wave of pairs that rounding would leave one CTA a pair and up to half of the
+                # GPU idle: 29 rows of 8 kv heads, 83 µs against 50 µs with equal cuts)
                 ctas = self.decode_ctas or max(1, min(slots, pairs * (-(-rows.max_kv // 64)) // 2))
                 floats = (ctas + pairs) * min(16, heads // kv_heads) * (head_dim + 2)
                 scratch = torch.empty(floats, dtype=torch.float32, device=self.device)

@@ -54,6 +54,7 @@ def test_greedy_generation(model, dtype, graphs):
         check_teacher_forced(config, weights, prompt, tokens, params, 0, exact=dtype == "float32")
     stats = engine.stats()
     assert stats["mixed_steps"] > 0 and (stats["graph_steps"] > 0) == graphs
+    assert (stats["mixed_graph_steps"] > 0) == graphs          # prompt portions that fill the budget beside decode rows
     engine.built.cache.check()
     assert not engine.built.cache.live
     if dtype == "float32":
@@ -183,10 +184,10 @@ def test_one_long_request_among_short_ones_takes_the_balanced_decode_graph(tmp_p
     kw = dict(page_size=64, max_seqs=12, max_model_len=4608, max_step_tokens=1024, chunk_with_decode=64)
     engine = engine_of(folder, "bfloat16", **kw)
     got = engine.generate(prompts, params)
-    modes = {mode for _, mode in engine._graphs}
+    modes = {key[-1] for key in engine._graphs}                      # (bucket, prompt portions, prompt tokens, mode)
     assert "balanced" in modes, modes
     short = engine.generate(prompts[1:], params)
-    assert {mode for _, mode in engine._graphs} == {"balanced", "splits"}
+    assert {key[-1] for key in engine._graphs} == {"balanced", "splits"}
     plain_run = engine_of(folder, "bfloat16", cuda_graphs=False, **kw)
     kernels = plain_run.built.ctx.kernels                            # (one kernel table per device: put the setting back)
     before, kernels.decode_attention = kernels.decode_attention, "splits"
