@@ -142,6 +142,11 @@ int hb_sample(int32_t* tokens, const float* logits, const float* temperature, co
               const float* top_p, const float* min_p, const int32_t* seed_lo, const int32_t* seed_hi,
               const int32_t* position, int filtered, int rows, int vocab, hb_stream stream);
 
+// Log-probabilities of the raw logits per row: chosen[r] of tokens[r], and the k most likely tokens ranked (equal
+// logits by ascending id) as top_ids / top [rows, k]; places beyond the row's finite entries hold id -1 and -inf.
+int hb_logprobs(float* chosen, int32_t* top_ids, float* top, const float* logits, const int32_t* tokens, int rows,
+                int vocab, int k, hb_stream stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -186,3 +186,92 @@ extern "C" int hb_sample(int32_t* tokens, const float* logits, const float* temp
     HB_LAUNCH_CHECK("sample");
     return 0;
 }
+
+// Log-probabilities of the raw logits (before temperature and filters), one block per row: the chosen token's, and
+// the `k` most likely tokens ranked, equal logits by ascending id (std/holon_std/sampling/sampler.py:118-126:
+// log_softmax, gather, topk). The largest logit and the sum of exponentials come from block reductions in a fixed
+// order; the ranking takes one pass over the row per place, each looking for the best entry after the one before.
+__global__ void __launch_bounds__(SAMPLE_THREADS) logprobs_kernel(
+        float* __restrict__ chosen, int32_t* __restrict__ top_ids, float* __restrict__ top,
+        const float* __restrict__ logits, const int32_t* __restrict__ tokens, int vocab, int k) {
+    __shared__ float fs[SAMPLE_THREADS / 32 + 1];
+    __shared__ int is[SAMPLE_THREADS / 32 + 1];
+    const int r = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const float* x = logits + (size_t)r * vocab;
+    auto block_best = [&](float v, int i) {                         // the largest v, the lowest i among equals
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, v, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, i, o);
+            if (ov > v || (ov == v && oi < i)) { v = ov; i = oi; }
+        }
+        __syncthreads();
+        if (lane == 0) { fs[warp] = v; is[warp] = i; }
+        __syncthreads();
+        if (warp == 0) {
+            v = lane < SAMPLE_THREADS / 32 ? fs[lane] : -INFINITY;
+            i = lane < SAMPLE_THREADS / 32 ? is[lane] : 0x7fffffff;
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) {
+                const float ov = __shfl_xor_sync(0xffffffffu, v, o);
+                const int oi = __shfl_xor_sync(0xffffffffu, i, o);
+                if (ov > v || (ov == v && oi < i)) { v = ov; i = oi; }
+            }
+            if (lane == 0) { fs[SAMPLE_THREADS / 32] = v; is[SAMPLE_THREADS / 32] = i; }
+        }
+        __syncthreads();
+    };
+    float best = -INFINITY;
+    int arg = 0x7fffffff;
+    for (int i = tid; i < vocab; i += SAMPLE_THREADS) {
+        const float v = x[i];
+        if (v > best) { best = v; arg = i; }                        // (ascending i: the first of equals stays)
+    }
+    block_best(best, arg);
+    const float top_v = fs[SAMPLE_THREADS / 32];
+    const int top_i = is[SAMPLE_THREADS / 32];
+    float sum = 0.f;
+    for (int i = tid; i < vocab; i += SAMPLE_THREADS) sum += expf(x[i] - top_v);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+    __syncthreads();
+    if (lane == 0) fs[warp] = sum;
+    __syncthreads();
+    if (tid == 0) {
+        float total = 0.f;
+        for (int w = 0; w < SAMPLE_THREADS / 32; ++w) total += fs[w];
+        fs[SAMPLE_THREADS / 32] = top_v + logf(total);
+    }
+    __syncthreads();
+    const float lse = fs[SAMPLE_THREADS / 32];
+    if (tid == 0) chosen[r] = x[tokens[r]] - lse;
+    float prev_v = top_v;
+    int prev_i = top_i;
+    for (int j = 0; j < k; ++j) {
+        if (j) {
+            best = -INFINITY; arg = 0x7fffffff;
+            for (int i = tid; i < vocab; i += SAMPLE_THREADS) {
+                const float v = x[i];
+                const bool after = v < prev_v || (v == prev_v && i > prev_i);
+                if (after && v > best) { best = v; arg = i; }
+            }
+            block_best(best, arg);
+            prev_v = fs[SAMPLE_THREADS / 32];
+            prev_i = is[SAMPLE_THREADS / 32];
+        }
+        if (tid == 0) {
+            const bool have = prev_i != 0x7fffffff;                  // fewer than k entries (or only NaN) left: -inf, id -1
+            top_ids[(size_t)r * k + j] = have ? prev_i : -1;
+            top[(size_t)r * k + j] = have ? prev_v - lse : -INFINITY;
+        }
+    }
+}
+
+extern "C" int hb_logprobs(float* chosen, int32_t* top_ids, float* top, const float* logits, const int32_t* tokens,
+                           int rows, int vocab, int k, hb_stream stream) {
+    if (rows == 0) return 0;
+    if (vocab < 1 || k < 0 || k > vocab) HB_REFUSE("logprobs: vocab = %d, k = %d", vocab, k);
+    logprobs_kernel<<<rows, SAMPLE_THREADS, 0, (cudaStream_t)stream>>>(chosen, top_ids, top, logits, tokens, vocab, k);
+    HB_LAUNCH_CHECK("logprobs");
+    return 0;
+}

@@ -3,9 +3,9 @@ from ..config.engine import EngineConfig
 from ..sampling.params import SamplingParams
 from .batch import StepEntry
 from .build import Built, build
-from .engine import Engine, TokenDelta
+from .engine import Engine, Logprobs, TokenDelta
 from .runner import Runner, StepError
 from .scheduler import Request, Scheduler
 
 __all__ = ["Built", "Engine", "EngineConfig", "Request", "Runner", "SamplingParams", "Scheduler", "StepEntry",
-           "StepError", "TokenDelta", "build"]
+           "StepError", "TokenDelta", "Logprobs", "build"]

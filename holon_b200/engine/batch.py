@@ -58,6 +58,7 @@ class StepContext:
         self.groups, self._cache = groups, cache
         self.extra: dict = {}
         self.from_last = None        # int32 [rows]: 1 where the row's token is fed from the device
+        self.offset_of: dict = {}    # host: entry index -> offset of its first token among the step's tokens
 
     def layer_cache(self, run) -> LayerCache:
         c = self._cache

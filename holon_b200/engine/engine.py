@@ -26,13 +26,29 @@ GRAPH_PORTIONS = 2                            # prompt portions beside the decod
 
 
 @dataclasses.dataclass
+class Logprobs:
+    """Per position: the chosen token's log-probability and the ranked top-k (ids and log-probabilities as parallel
+    lists), from the raw logits, before temperature and filters. Prompt logprobs cover prompt positions 1 .. n-1: the
+    first token has no context (core/holon/api/frontend.py:25-34)."""
+
+    token: list[float]
+    top_ids: list[list[int]]
+    top: list[list[float]]
+
+
+@dataclasses.dataclass
 class TokenDelta:
-    """What one step added to one request (core/holon/api/frontend.py:17-52)."""
+    """What one step added to one request (core/holon/api/frontend.py:41-52)."""
 
     rid: str
     token_ids: list[int]
     index: int = 0                           # which of the request's `n` sequences these belong to
+    logprobs: Logprobs | None = None         # of these tokens, where the request asked for them
+    prompt_logprobs: Logprobs | None = None  # of the prompt, with the sequence's first delta
     finish_reason: str | None = None         # "stop" | "length" | "abort" | None
+
+
+PROMPT_LOGPROB_ROWS = 256                     # rows of full-vocabulary logits held at once for prompt logprobs
 
 
 @dataclasses.dataclass
@@ -46,6 +62,8 @@ class _Inflight:
     done: object
     decode_only: bool
     pick: list | None = None                 # where in `host` each sampled row's token lies (None: in their order)
+    logprobs: tuple | None = None            # host tensors (chosen, top ids, top) for the sampled rows, in their order
+    prompt: list = dataclasses.field(default_factory=list)   # (request, k, host chosen, host top ids, host top) pieces
 
 
 class Engine:
@@ -64,6 +82,7 @@ class Engine:
         self.scheduler = Scheduler(b.cache, config.max_step_tokens, config.max_model_len, config.chunk_with_decode)
         self.sampler = Sampler(b.ctx.kernels, self.device)
         self.requests: dict[str, list[Request]] = {}          # a request's sequences that have not finished
+        self._prompt_lp: dict[Request, Logprobs] = {}         # sequences whose prompt logprobs are still being gathered
         self._base_seed = config.seed if config.seed is not None else secrets.randbits(63)
         self._added = 0
         self._graphs: dict[int, tuple] = {}
@@ -105,6 +124,8 @@ class Engine:
         self.requests[rid] = live = []
         for i in range(params.n):
             live.append(Request(rid, list(tokens), len(tokens), params, sequence_seed(base, i), index=i))
+            if i == 0 and params.prompt_logprobs is not None:      # once a request (core/holon/core/engine.py:360-366)
+                self._prompt_lp[live[-1]] = Logprobs([], [], [])
             self.scheduler.add(live[-1])
         return rid
 
@@ -114,7 +135,8 @@ class Engine:
         deltas = []
         for request in self.requests.pop(rid, []):
             self.scheduler.finish(request, "abort", release=request.pending == 0)   # (a row in flight gives the slot back)
-            deltas.append(TokenDelta(rid, [], request.index, "abort"))
+            self._prompt_lp.pop(request, None)
+            deltas.append(TokenDelta(rid, [], request.index, finish_reason="abort"))
         return deltas
 
     def has_work(self) -> bool:
@@ -185,28 +207,30 @@ class Engine:
         runner.check(entries)
         ones = sum(1 for e in entries if len(e.tokens) == 1)
         decode_only = n == ones == len(entries)
-        host = pick = None
+        host = pick = lps = None
+        owed = self._prompt_rows(rows) if self._prompt_lp else []
         if n:
             arrays = sampling_arrays([(r.request.params, r.request.seed, r.request.computed + r.n_tokens)
                                       for r in sampled])
             arrays["sample_slot"] = np.array([r.request.slot for r in sampled], dtype=np.int32)
             filtered = any(r.request.params.filtered for r in sampled)
-            if self._use_graphs and not filtered and self._graph_fits(entries, ones):
-                tokens, pick = self._replay(entries, [r.samples for r in rows], arrays)
+            ks = [r.request.params.logprobs for r in sampled if r.request.params.logprobs is not None]
+            if self._use_graphs and not filtered and not ks and not owed and self._graph_fits(entries, ones):
+                tokens, pick = self._replay(entries, [r.samples for r in rows], arrays)      # (graphs return tokens only)
                 m = tokens.shape[0]
                 if pick == list(range(n)):                 # (a plain decode step: its n tokens lie first, in order)
                     m, pick = n, None
             else:
                 step = runner.context(entries, extra=arrays)
-                tokens, m = self._forward(step, filtered, n), n
+                tokens, lps, owed = self._forward(step, filtered, n, logprobs=max(ks) if ks else None, prompt=owed)
+                m = n
             host = self._host_tokens[self._flip][:m]
             self._flip ^= 1
             host.copy_(tokens[:m], non_blocking=True)
             self.d2h_bytes += m * 4
         else:                                              # every row stops short of its prompt's end: the head is skipped
             step = runner.context(entries)
-            self._feed(step)
-            runner.model.forward(step)
+            _, _, owed = self._forward(step, False, 0, prompt=owed)
         self.h2d_bytes += runner.uploader.bytes_last
         done = None
         if self.device.type == "cuda":
@@ -217,7 +241,22 @@ class Engine:
             self.scheduler.computed(r)
             r.request.pending += int(r.samples)
         self.steps += 1
-        return _Inflight(rows, sampled, host, done, decode_only, pick)
+        return _Inflight(rows, sampled, host, done, decode_only, pick, lps, owed)
+
+    def _prompt_rows(self, rows: list[Row]) -> list[tuple]:
+        """The prompt logprobs this step's rows owe: (entry, request, first and end offset among its tokens, targets)
+        for the prompt positions they compute that predict a prompt token, except those already recorded (a request
+        preempted in mid-prompt computes them again) (core/holon/core/engine.py:588-602)."""
+        out = []
+        for i, r in enumerate(rows):
+            q = r.request
+            acc = self._prompt_lp.get(q)
+            if acc is None or q.pending:
+                continue
+            lo, hi = max(q.computed, len(acc.token)), min(q.computed + r.n_tokens, q.prompt_len - 1)
+            if lo < hi:
+                out.append((i, q, lo - q.computed, hi - q.computed, q.tokens[lo + 1:hi + 1]))
+        return out
 
     def _graph_fits(self, entries, ones: int) -> bool:
         """Whether the step's shape is one that graphs are kept for: rows of one token alone, up to the largest
@@ -236,13 +275,40 @@ class Engine:
     def _feed(self, step) -> None:
         self.built.ctx.kernels.feed_tokens(step.token_ids, self.last_tokens, step.rows, step.from_last)
 
-    def _forward(self, step, filtered: bool, n: int, out: torch.Tensor | None = None) -> torch.Tensor:
-        """feed -> model -> sample -> store, all enqueued; returns the device tensor of sampled tokens."""
+    def _forward(self, step, filtered: bool, n: int, out: torch.Tensor | None = None, logprobs: int | None = None,
+                 prompt: list | None = None):
+        """feed -> model -> sample -> store, all enqueued. Returns the device tensor of the `n` sampled tokens (None
+        when nothing is sampled: the head is skipped), the sampled rows' logprobs on their way to the host (`logprobs`
+        not None: that many top entries), and the pieces of `prompt`'s logprobs on their way to the host."""
         self._feed(step)
-        logits = self.built.runner.model.forward(step)
-        tokens = self.sampler.sample(logits, step.extra, filtered, out)
-        self.built.ctx.kernels.store_tokens(self.last_tokens, step.extra["sample_slot"], tokens, n)
-        return tokens
+        model = self.built.runner.model
+        stream = model.trunk(step)
+        tokens = lps = None
+        if n:
+            logits = model.logits_at(stream, step.logits_index)
+            tokens = self.sampler.sample(logits, step.extra, filtered, out)
+            self.built.ctx.kernels.store_tokens(self.last_tokens, step.extra["sample_slot"], tokens, n)
+            if logprobs is not None:
+                lps = self._to_host(self.sampler.logprobs(logits, tokens, logprobs))
+        pieces = []
+        for i, q, a, b, targets in prompt or []:           # a bounded number of full-vocabulary rows at a time
+            k, at = q.params.prompt_logprobs, step.offset_of[i]
+            for c in range(a, b, PROMPT_LOGPROB_ROWS):
+                d = min(b, c + PROMPT_LOGPROB_ROWS)
+                index = torch.arange(at + c, at + d, dtype=torch.int32, device=self.device)
+                want = torch.tensor(targets[c - a:d - a], dtype=torch.int32).to(self.device, non_blocking=True)
+                got = self.sampler.logprobs(model.logits_at(stream, index), want, k)
+                pieces.append((q, *self._to_host(got)))
+        return tokens, lps, pieces
+
+    def _to_host(self, tensors) -> tuple:
+        out = []
+        for t in tensors:
+            host = torch.empty(t.shape, dtype=t.dtype, pin_memory=self.device.type == "cuda")
+            host.copy_(t, non_blocking=True)
+            self.d2h_bytes += t.numel() * t.element_size()
+            out.append(host)
+        return tuple(out)
 
     def _replay(self, entries, samples, arrays) -> tuple[torch.Tensor, list[int]]:
         """A step through the CUDA graph of its shape (core/holon/core/executor.py:316-344). One-token rows are padded
@@ -302,8 +368,15 @@ class Engine:
         tokens = inflight.host.tolist() if inflight.host is not None else []
         if inflight.pick is not None:
             tokens = [tokens[i] for i in inflight.pick]
+        for request, chosen, ids, top in inflight.prompt:   # before any delta: a prompt's last piece and its first token
+            acc = self._prompt_lp.get(request)             # come from the same step
+            if acc is not None:
+                acc.token += chosen.tolist()
+                acc.top_ids += ids.tolist()
+                acc.top += top.tolist()
+        lps = [t.tolist() for t in inflight.logprobs] if inflight.logprobs is not None else None
         deltas = []
-        for row, token in zip(inflight.sampled, tokens):
+        for j, (row, token) in enumerate(zip(inflight.sampled, tokens)):
             request = row.request
             request.pending -= 1
             if request.status is Status.FINISHED:          # it stopped a step ago; this row was already in flight
@@ -318,7 +391,10 @@ class Engine:
             if reason:
                 self.scheduler.finish(request, reason, release=request.pending == 0)
                 self._retire(request)
-            deltas.append(TokenDelta(request.rid, [int(token)], request.index, reason))
+            k = request.params.logprobs
+            own = None if k is None or lps is None else Logprobs([lps[0][j]], [lps[1][j][:k]], [lps[2][j][:k]])
+            deltas.append(TokenDelta(request.rid, [int(token)], request.index, own, self._prompt_lp.pop(request, None),
+                                     reason))
         return deltas
 
     def _retire(self, request: Request) -> None:

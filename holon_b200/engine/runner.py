@@ -113,6 +113,7 @@ class Runner:
         step = StepContext(dev["token_ids"], dev["positions"], dev["logits_index"], rows_, groups, c)
         step.extra = {name: dev[name] for name in (extra or {})}
         step.from_last = dev["from_last"]
+        step.offset_of = offset_of                    # entry index -> where its tokens start among the step's
         return step
 
     # ------------------------------------------------------------------ the step

@@ -401,6 +401,18 @@ class CudaKernels:
         self._call("hb_store_tokens", self._i32(last_tokens, "last_tokens"), self._i32(slots, "slots"),
                    self._i32(tokens, "tokens"), int(n))
 
+    def logprobs(self, chosen, top_ids, top, logits, tokens) -> None:
+        """chosen [rows] float32: log softmax(logits)[tokens]; top_ids int32 / top float32 [rows, k]: the k most likely."""
+        self._check(chosen, top_ids, top, logits, tokens)
+        r, v = logits.shape
+        k = top.shape[1]
+        if logits.dtype != torch.float32 or chosen.dtype != torch.float32 or top.dtype != torch.float32 \
+                or top_ids.dtype != torch.int32 or tokens.dtype != torch.int32:
+            raise KernelError("logprobs: logits, chosen, top float32; top_ids, tokens int32")
+        if chosen.shape[0] < r or tokens.shape[0] < r or top.shape != (r, k) or top_ids.shape != (r, k):
+            raise KernelError("logprobs: chosen and tokens [rows], top_ids and top [rows, k]")
+        self._call("hb_logprobs", self._p(chosen), self._p(top_ids), self._p(top), self._p(logits), self._p(tokens), r, v, k)
+
     def sample(self, tokens, logits, temperature, top_k, top_p, min_p, seed_lo, seed_hi, position, filtered) -> None:
         self._check(tokens, logits, temperature, top_k, top_p, min_p, seed_lo, seed_hi, position)
         r, v = logits.shape

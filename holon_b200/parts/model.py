@@ -67,7 +67,10 @@ class Model(Part):
 
     def forward(self, step) -> torch.Tensor | None:
         """Logits [R, V] in 32-bit at the step's wanted places; None if the step wants none (the head is skipped)."""
-        stream = self.trunk(step)
-        if step.logits_index.shape[0] == 0:
+        return self.logits_at(self.trunk(step), step.logits_index)
+
+    def logits_at(self, stream, index: torch.Tensor) -> torch.Tensor | None:
+        """Logits [R, V] in 32-bit of the step's tokens `index` (int32 [R]) from the trunk's residual stream."""
+        if index.shape[0] == 0:
             return None
-        return self.head.forward(self.norm.gather(stream, step.logits_index))
+        return self.head.forward(self.norm.gather(stream, index))

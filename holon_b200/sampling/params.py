@@ -22,14 +22,16 @@ class SamplingParams:
     ignore_eos: bool = False
     stop_token_ids: tuple[int, ...] = ()
     seed: int | None = None                  # None: the engine draws one
-    logprobs: int | None = None              # the reference's top-k log-probabilities per generated token: not built
-    prompt_logprobs: int | None = None       # and per prompt token: not built
+    logprobs: int | None = None              # top-k log-probabilities per generated token (0: the token's own alone)
+    prompt_logprobs: int | None = None       # and per prompt token
 
     def validate(self) -> None:
         if (self.presence_penalty, self.frequency_penalty, self.repetition_penalty) != (0.0, 0.0, 1.0):
             raise NotImplementedError("presence, frequency and repetition penalties are not implemented")
-        if self.logprobs is not None or self.prompt_logprobs is not None:
-            raise NotImplementedError("logprobs and prompt_logprobs are not implemented")
+        for name in ("logprobs", "prompt_logprobs"):
+            k = getattr(self, name)
+            if k is not None and (not isinstance(k, int) or k < 0):
+                raise ValueError(f"SamplingParams.{name} must be None or a count >= 0, got {k!r}")
         if self.n < 1:
             raise ValueError("SamplingParams.n must be >= 1")
         if self.temperature < 0 or not 0 < self.top_p <= 1 or self.top_k < 0 or not 0 <= self.min_p <= 1:

@@ -40,3 +40,14 @@ class Sampler:
         self.kernels.sample(tokens, logits, f32("temperature"), dev["top_k"], f32("top_p"), f32("min_p"),
                             dev["seed_lo"], dev["seed_hi"], dev["sample_position"], filtered)
         return tokens
+
+    def logprobs(self, logits: torch.Tensor, tokens: torch.Tensor, k: int):
+        """Of the raw logits, before temperature and filters (std/holon_std/sampling/sampler.py:118-126): float32 [rows]
+        log softmax(logits)[tokens], and the `k` most likely per row as int32 ids and float32 log-probabilities
+        [rows, k], ranked, equal logits by ascending id."""
+        r = logits.shape[0]
+        chosen = torch.empty(r, dtype=torch.float32, device=self.device)
+        top_ids = torch.empty((r, k), dtype=torch.int32, device=self.device)
+        top = torch.empty((r, k), dtype=torch.float32, device=self.device)
+        self.kernels.logprobs(chosen, top_ids, top, logits, tokens)
+        return chosen, top_ids, top

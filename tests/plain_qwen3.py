@@ -205,6 +205,14 @@ def sample(logits, temperature, seed, position, top_k=0, top_p=1.0, min_p=0.0) -
     return draw(distribution(logits, temperature, top_k, top_p, min_p), uniform(seed, position))
 
 
+def logprobs(logits, token: int, k: int):
+    """(log-probability of `token`, ids of the k most likely, their log-probabilities) from the raw logits of one
+    position: log_softmax, gather, topk (std/holon_std/sampling/sampler.py:118-126)."""
+    lp = logits.double().log_softmax(-1)
+    order = sorted(range(lp.numel()), key=lambda i: (-float(lp[i]), i))[:k]      # ranked; equal ones by ascending id
+    return float(lp[token]), order, [float(lp[i]) for i in order]
+
+
 def generate(config, w, prompt, max_tokens, temperature=0.0, seed=0, top_k=0, top_p=1.0, min_p=0.0):
     """Tokens generated after `prompt`, each step a whole forward pass (no cache)."""
     ids = list(prompt)

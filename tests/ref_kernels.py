@@ -108,6 +108,16 @@ class RefKernels:
     def store_tokens(self, last_tokens, slots, tokens, n):
         last_tokens[slots[:n].long()] = tokens[:n]
 
+    def logprobs(self, chosen, top_ids, top, logits, tokens):
+        """log softmax of the raw logits: the given token's, and the k most likely ranked (equal ones by ascending id)."""
+        k = top.shape[1]
+        for r in range(logits.shape[0]):
+            lp = logits[r].double().log_softmax(-1)
+            chosen[r] = lp[int(tokens[r])]
+            order = torch.tensor(sorted(range(lp.numel()), key=lambda i: (-float(lp[i]), i))[:k], dtype=torch.long)
+            top_ids[r] = order.to(torch.int32)
+            top[r] = lp[order].float()
+
     def sample(self, tokens, logits, temperature, top_k, top_p, min_p, seed_lo, seed_hi, position, filtered):
         """temperature 0: arg max. Else softmax(logits / T) filtered by top-k, top-p, min-p, drawn by inverse CDF in
         vocabulary order with the uniform of (seed, position)."""

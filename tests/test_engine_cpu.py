@@ -70,3 +70,52 @@ def test_generate_matches_plain(tmp_path, name, temperature):
         assert g == plain.generate(config, weights, p, 8, temperature, sp.seed)
     engine.built.cache.check()
     assert not engine.built.cache.live and engine.stats()["mixed_steps"] > 0
+
+
+
+def test_logprobs_of_generated_and_prompt_tokens(tmp_path):
+    """`logprobs` and `prompt_logprobs` (core/holon/api/frontend.py:25-34): the chosen token's log-probability and the
+    ranked top-k from the raw logits at every generated token; the prompt's positions 1 .. n-1 with the first delta,
+    gathered over portions (and once only when the request is preempted in mid-prompt and starts again)."""
+    folder = make_folder(tmp_path, "b")
+    config, weights = plain.read_folder(folder)
+    prompts = [random_prompt(config["vocab_size"], n, 40 + n) for n in (23, 9, 1)]
+    engine = Engine(EngineConfig(model=str(folder), device="cpu", dtype="float32", page_size=4, max_seqs=3,
+                                 max_model_len=64, max_step_tokens=16, chunk_with_decode=8, state_memory=1 << 20),
+                    kernels=RefKernels())
+    params = [SamplingParams(temperature=0.8, max_tokens=5, seed=3, logprobs=3, prompt_logprobs=2),
+              SamplingParams(temperature=0.0, max_tokens=5, logprobs=0),
+              SamplingParams(temperature=0.0, max_tokens=5, prompt_logprobs=0, n=2)]
+    rids = [engine.add(p, sp) for p, sp in zip(prompts, params)]
+    seen: dict = {}
+    while engine.has_work():
+        for d in engine.step():
+            seen.setdefault((d.rid, d.index), []).append(d)
+    for rid, prompt, sp in zip(rids, prompts, params):
+        for index in range(sp.n):
+            deltas = seen[(rid, index)]
+            ids = list(prompt)
+            first = deltas[0].prompt_logprobs
+            assert all(d.prompt_logprobs is None for d in deltas[1:])
+            if sp.prompt_logprobs is None or index:
+                assert first is None
+            else:
+                whole = plain.forward(config, weights, ids)
+                assert len(first.token) == len(first.top) == len(first.top_ids) == len(ids) - 1
+                for at in range(len(ids) - 1):
+                    own, top_ids, top = plain.logprobs(whole[at], ids[at + 1], sp.prompt_logprobs)
+                    assert abs(first.token[at] - own) < 1e-4 and first.top_ids[at] == top_ids
+                    assert all(abs(a - b) < 1e-4 for a, b in zip(first.top[at], top))
+            for d in deltas:
+                logits = plain.forward(config, weights, ids)[-1]
+                if sp.logprobs is None:
+                    assert d.logprobs is None
+                else:
+                    own, top_ids, top = plain.logprobs(logits, d.token_ids[0], sp.logprobs)
+                    assert abs(d.logprobs.token[0] - own) < 1e-4 and d.logprobs.top_ids == [top_ids]
+                    assert all(abs(a - b) < 1e-4 for a, b in zip(d.logprobs.top[0], top))
+                ids += d.token_ids
+    with pytest.raises(ValueError, match="logprobs"):
+        engine.add([1], SamplingParams(logprobs=-1))
+    engine.built.cache.check()
+    assert not engine.built.cache.live and not engine._prompt_lp

@@ -3,6 +3,8 @@ plain implementation: greedy and seeded temperature sampling, with prompt portio
 CUDA graphs on and off, and in a pool so small that requests are preempted and computed again."""
 from __future__ import annotations
 
+import dataclasses
+
 import pytest
 import torch
 
@@ -93,6 +95,50 @@ def test_the_sequences_of_one_request_stream_under_their_indices(model):
     engine.close()
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_logprobs_beside_requests_that_ask_for_none(model, dtype):
+    """Generated-token and prompt logprobs through the CUDA kernels: steps that owe them run outside the graphs and
+    give the tokens the same requests get without them; values against the plain implementation."""
+    folder, config, weights, prompts = model
+    engine = engine_of(folder, dtype)
+    base = [SamplingParams(temperature=0.0, max_tokens=6) for _ in prompts]
+    plain_tokens = engine.generate(prompts, base)
+    asked = [dataclasses.replace(p, logprobs=(4, None, 0)[i % 3], prompt_logprobs=(None, 3)[i % 2]) for i, p in enumerate(base)]
+    rids = [engine.add(p, sp) for p, sp in zip(prompts, asked)]
+    seen = {rid: [] for rid in rids}
+    while engine.has_work():
+        for d in engine.step():
+            seen[d.rid].append(d)
+    tol = 1e-4 if dtype == "float32" else 0.08
+    for rid, prompt, sp, want in zip(rids, prompts, asked, plain_tokens):
+        deltas = seen[rid]
+        if dtype == "float32":
+            assert [t for d in deltas for t in d.token_ids] == want
+        else:                                                      # (another batch shape may flip a near-tie in bfloat16)
+            check_teacher_forced(config, weights, prompt, [t for d in deltas for t in d.token_ids], sp, 0, exact=False)
+        first = deltas[0].prompt_logprobs
+        if sp.prompt_logprobs is None:
+            assert first is None
+        else:
+            whole = plain.forward(config, weights, list(prompt))
+            assert len(first.token) == len(prompt) - 1
+            for at in range(0, len(prompt) - 1, 5):
+                own, _, top = plain.logprobs(whole[at], prompt[at + 1], sp.prompt_logprobs)
+                assert abs(first.token[at] - own) < tol and len(first.top_ids[at]) == sp.prompt_logprobs
+                assert all(abs(a - b) < tol for a, b in zip(first.top[at], top))
+        ids = list(prompt)
+        for d in deltas:
+            if sp.logprobs is None:
+                assert d.logprobs is None
+            else:
+                own, _, top = plain.logprobs(plain.forward(config, weights, ids)[-1], d.token_ids[0], sp.logprobs)
+                assert abs(d.logprobs.token[0] - own) < tol and len(d.logprobs.top[0]) == sp.logprobs
+                assert all(abs(a - b) < tol for a, b in zip(d.logprobs.top[0], top))
+            ids += d.token_ids
+    assert not engine._prompt_lp and not engine.built.cache.live
+    engine.close()
+
+
 def test_sampled_generation_is_seeded_and_survives_preemption(model):
     folder, config, weights, prompts = model
     params = [SamplingParams(temperature=0.8, max_tokens=10, seed=100 + i, top_k=(0, 20)[i % 2], top_p=(1.0, 0.9)[i // 3],
@@ -125,8 +171,8 @@ def test_limits_and_errors(model):
         engine.add([config["vocab_size"]])
     with pytest.raises(NotImplementedError):
         engine.add([1], SamplingParams(repetition_penalty=1.1))
-    with pytest.raises(NotImplementedError):
-        engine.add([1], SamplingParams(logprobs=3))
+    with pytest.raises(ValueError, match="logprobs"):
+        engine.add([1], SamplingParams(logprobs=-3))
     out = engine.generate([[1, 2, 3]], SamplingParams(temperature=0.0))          # no max_tokens: stops at max_model_len
     assert len(out[0]) == 32 - 3
     rid = engine.add([4, 5, 6], SamplingParams(temperature=0.0, max_tokens=50))

@@ -501,6 +501,32 @@ def test_sample_greedy_and_temperature(K):
     assert got[2] == got[5]                                        # same seed, position and logits: same token
 
 
+@pytest.mark.parametrize("vocab,k", [(1531, 5), (151936, 20), (37, 37), (600, 0)])
+def test_logprobs_of_the_raw_logits(K, vocab, k):
+    """The chosen token's log-probability and the ranked top-k against log_softmax in float64; equal logits rank by
+    ascending id, and a row with fewer finite entries than k fills the rest with id -1 and -inf."""
+    rows = 5
+    logits = rand(rows, vocab, seed=5 + k, scale=3.0)
+    logits[1, 3] = logits[1, vocab - 1] = logits[1, 17] = 50.0          # three equal maxima
+    if vocab == 37:
+        logits[2, 5:] = float("-inf")                                 # five finite entries
+    tokens = torch.tensor([0, vocab - 1, 3, vocab // 2, 7], dtype=torch.int32)
+    chosen = torch.empty(rows, dtype=torch.float32, device=DEV)
+    top_ids = torch.full((rows, k), -7, dtype=torch.int32, device=DEV)
+    top = torch.full((rows, k), float("nan"), dtype=torch.float32, device=DEV)
+    K.logprobs(chosen, top_ids, top, logits.to(DEV), tokens.to(DEV))
+    for r in range(rows):
+        own, ids, values = plain.logprobs(logits[r], int(tokens[r]), k)
+        assert abs(float(chosen[r]) - own) < 2e-5 * max(1.0, abs(own)), (r, float(chosen[r]), own)
+        finite = [i for i, v in zip(ids, values) if v != float("-inf")]
+        got = top_ids[r].cpu().tolist()
+        assert got[:len(finite)] == finite and all(i == -1 for i in got[len(finite):]), (r, got, ids)
+        for a, b in zip(top[r].cpu().tolist(), values):
+            assert (a == b == float("-inf")) or abs(a - b) < 2e-5 * max(1.0, abs(b))
+    if k >= 3:
+        assert top_ids[1, :3].cpu().tolist() == [3, 17, vocab - 1]
+
+
 def test_sample_follows_the_distribution(K):
     """4096 draws of one row at positions 0..4095, against the plain implementation's float64 distribution, with and
     without filters: total variation small, filtered-out tokens never drawn."""
