@@ -106,6 +106,15 @@ int hb_gemm_f32(float* out, const float* x, const float* w, int m, int n, int k,
 int hb_gemm_bf16_skinny(void* out, int out_f32, const void* x, const void* w, int m, int n, int k, int mode, int inter,
                         hb_stream stream);
 
+// The same kernel with the norms around the product folded in. mode 3: h [m, n] (float32) += bfloat16(x · wᵀ),
+// out [m, n] = bfloat16(h · (next_weight + next_offset)), ss_out [ceil(n / 16), 16] = sums of squares of the new h
+// per 16 columns and token. ss_in (any mode; null: none): x is such an `out` and lacks its row scale
+// rsqrt(sum of ss_in [parts_in, 16] over parts / dim_in + eps_in), which is applied to the product's sums.
+int hb_gemm_bf16_skinny_linked(void* out, int out_f32, const void* x, const void* w, int m, int n, int k, int mode,
+                               int inter, float* h, const void* next_weight, int next_weight_f32, float next_offset,
+                               float* ss_out, const float* ss_in, int parts_in, float eps_in, int dim_in,
+                               hb_stream stream);
+
 // bfloat16 product on tcgen05 tensor cores with TMA loads and the accumulator in tensor memory (128 x 256 tiles).
 // The attention's first product for up to 16 tokens with what follows it in one kernel: x [m, k] times
 // w [(heads + 2 kv_heads) * head_dim, k], then per head the q/k RMSNorm (weights bfloat16 or, with weight_f32, float32;
@@ -116,6 +125,11 @@ int hb_qkv_rope_skinny(void* q_out, const void* x, const void* w, int m, int k, 
                        const float* table, int max_positions, const void* q_weight, const void* k_weight, int weight_f32,
                        float eps, float offset, void* kv, const int32_t* write_index, int pages, int page_size, int heads,
                        int kv_heads, int head_dim, hb_stream stream);
+int hb_qkv_rope_skinny_linked(void* q_out, const void* x, const void* w, int m, int k, const int32_t* positions,
+                              const float* table, int max_positions, const void* q_weight, const void* k_weight,
+                              int weight_f32, float eps, float offset, void* kv, const int32_t* write_index, int pages,
+                              int page_size, int heads, int kv_heads, int head_dim, const float* ss_in, int parts_in,
+                              float eps_in, int dim_in, hb_stream stream);
 
 // Same arguments and modes as hb_gemm_bf16_skinny, any m. hb_gemm_tcgen05_status synchronises the device and
 // returns (and clears) a status word that is non-zero if a bounded wait inside the kernel ever gave up.

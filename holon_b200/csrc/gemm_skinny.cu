@@ -14,6 +14,12 @@
 // and write queries to q_out and keys and values straight into their cache pages. The head's sum of squares and the
 // rotation partner 64 columns away come from the other CTAs' shared memory. Values are rounded to bfloat16 where the
 // separate kernels round them (after the product, after the norm), so the results are theirs.
+// mode 3 folds the residual sum and the next RMSNorm into a product that ends a mixer or a feed-forward: the CTA adds
+// its 16 columns (rounded to bfloat16, as the separate product's output is) into the 32-bit stream h, writes the new
+// stream times the next norm's weight as bfloat16, and leaves the sum of squares of its columns per token. The
+// product that consumes those rows (any mode, `NormLink::ss_in`) adds the partial sums up in a fixed order and scales
+// its sums by rsqrt(mean + eps) per token: x · rstd · w == (x · w) · rstd, so the norm costs no kernel and no pass
+// over the stream of its own.
 #include "common.cuh"
 
 #define SK_WARPS 8
@@ -46,6 +52,15 @@ struct RopeEpilogue {                              // what mode 2 needs beyond t
     int max_positions, weight_f32, pages, page_size, heads, kv_heads, head_dim;
 };
 
+struct NormLink {                                  // the residual stream and the norms around a product
+    float* h;                                      // mode 3: [m, n] 32-bit stream, added into
+    const void* next_weight;                       // mode 3: the next norm's weight [n]
+    float* ss_out;                                 // mode 3: [grid, 16] sums of squares of the new stream, per CTA and token
+    const float* ss_in;                            // any mode: [parts_in, 16] of the product that made x (null: x is normed)
+    float next_offset, eps_in;
+    int next_weight_f32, parts_in, dim_in;
+};
+
 __device__ __forceinline__ float ld_peer_f32(const float* local, uint32_t rank) {
     uint32_t remote;
     float v;
@@ -63,8 +78,10 @@ template <int MT, int NT, int SK_UNROLL, int MIN_CTAS>
 __global__ void __launch_bounds__(SK_WARPS * 32, MIN_CTAS) gemm_skinny_kernel(void* __restrict__ out, int out_f32,
                                                                     const bf16* __restrict__ x, const bf16* __restrict__ w,
                                                                     int m, int n, int k, int mode, int inter,
-                                                                    const RopeEpilogue ep) {
+                                                                    const RopeEpilogue ep, const NormLink link) {
     __shared__ float red[SK_WARPS][MT * 16][NT * 8 + 1];
+    __shared__ float scale_part[16][17];
+    __shared__ float scale_in[16];                       // per token: what the rows of x still lack (1 without a link)
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, r = lane >> 2, c = lane & 3;
     int row0[MT];                                        // first weight row of each tile
     int limit[MT];                                       // rows below this exist
@@ -127,6 +144,10 @@ __global__ void __launch_bounds__(SK_WARPS * 32, MIN_CTAS) gemm_skinny_kernel(vo
                     mma16816(acc[a][b], wr[u][a][0].z, wr[u][a][1].z, wr[u][a][0].w, wr[u][a][1].w, xr[u][b].z, xr[u][b].w);
                 }
     }
+    float ss_mine = 0.f;                                 // token (thread & 15): every 16th partial sum, in ascending order
+    if (link.ss_in)
+        for (int p2 = threadIdx.x >> 4; p2 < link.parts_in; p2 += 16) ss_mine += link.ss_in[p2 * 16 + (threadIdx.x & 15)];
+    scale_part[threadIdx.x >> 4][threadIdx.x & 15] = ss_mine;
 #pragma unroll
     for (int a = 0; a < MT; ++a)
 #pragma unroll
@@ -136,6 +157,13 @@ __global__ void __launch_bounds__(SK_WARPS * 32, MIN_CTAS) gemm_skinny_kernel(vo
             red[warp][a * 16 + r + 8][b * 8 + c * 2] = acc[a][b][2];
             red[warp][a * 16 + r + 8][b * 8 + c * 2 + 1] = acc[a][b][3];
         }
+    __syncthreads();
+    if (threadIdx.x < 16) {
+        float total = 0.f;
+#pragma unroll
+        for (int j = 0; j < 16; ++j) total += scale_part[j][threadIdx.x];
+        scale_in[threadIdx.x] = link.ss_in ? rsqrtf(total / (float)link.dim_in + link.eps_in) : 1.f;
+    }
     __syncthreads();
     if (MT == 1 && mode == 2) {
         __shared__ float res[NT * 8][16];                            // the product, rounded as the separate kernel's input is
@@ -147,7 +175,7 @@ __global__ void __launch_bounds__(SK_WARPS * 32, MIN_CTAS) gemm_skinny_kernel(vo
             float v = 0.f;
 #pragma unroll
             for (int wv = 0; wv < SK_WARPS; ++wv) v += red[wv][rr][tok];
-            res[tok][rr] = rounded<bf16>(v);
+            res[tok][rr] = rounded<bf16>(v * scale_in[tok]);
         }
         __syncthreads();
         if (threadIdx.x < m) {
@@ -210,6 +238,26 @@ __global__ void __launch_bounds__(SK_WARPS * 32, MIN_CTAS) gemm_skinny_kernel(vo
         cluster_barrier_all();                                       // nobody leaves while its shared memory may be read
         return;
     }
+    if (MT == 1 && NT <= 2 && mode == 3) {                           // 16 columns x up to 16 tokens: one thread each
+        const int rr = threadIdx.x & 15, tok = threadIdx.x >> 4, col = row0[0] + rr;
+        const bool live = tok < m && col < n;
+        float hn = 0.f;
+        if (live) {
+            const float before = link.h[(size_t)tok * n + col];
+            const float wn = link.next_weight_f32 ? ((const float*)link.next_weight)[col] : to_f32(((const bf16*)link.next_weight)[col]);
+            float v = 0.f;
+#pragma unroll
+            for (int wv = 0; wv < SK_WARPS; ++wv) v += red[wv][rr][tok];
+            hn = before + rounded<bf16>(v * scale_in[tok]);
+            link.h[(size_t)tok * n + col] = hn;
+            ((bf16*)out)[(size_t)tok * n + col] = __float2bfloat16_rn(hn * (wn + link.next_offset));
+        }
+        float sq = hn * hn;                                          // over the token's 16 columns: lanes 0-15 or 16-31
+#pragma unroll
+        for (int o = 8; o > 0; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
+        if (rr == 0) link.ss_out[blockIdx.x * 16 + tok] = sq;        // (tokens beyond m: 0)
+        return;
+    }
     const int rows_out = mode == 1 ? HALF * 16 : MT * 16;
     const int width = mode == 1 ? inter : n;
     for (int i = threadIdx.x; i < rows_out * m; i += SK_WARPS * 32) {
@@ -217,13 +265,14 @@ __global__ void __launch_bounds__(SK_WARPS * 32, MIN_CTAS) gemm_skinny_kernel(vo
         float v = 0.f;
 #pragma unroll
         for (int wv = 0; wv < SK_WARPS; ++wv) v += red[wv][rr][tok];
+        v *= scale_in[tok];
         int col = row0[0] + rr;
         if (MT > 1 && rr >= 16) col = row0[rr >> 4] + (rr & 15);
         if (mode == 1) {
             float u = 0.f;
 #pragma unroll
             for (int wv = 0; wv < SK_WARPS; ++wv) u += red[wv][HALF * 16 + rr][tok];
-            v = v / (1.f + expf(-v)) * u;
+            v = v / (1.f + expf(-v)) * (u * scale_in[tok]);
         }
         if (col < width) {
             if (out_f32) ((float*)out)[(size_t)tok * width + col] = v;
@@ -234,14 +283,25 @@ __global__ void __launch_bounds__(SK_WARPS * 32, MIN_CTAS) gemm_skinny_kernel(vo
 
 // mode 0: out [m, n] (bfloat16, or float32 when out_f32) = x [m, k] · w [n, k]ᵀ.
 // mode 1: w is [2 * inter, k] with gate rows first; out [m, inter] = silu(x · gateᵀ) * (x · upᵀ); n is ignored.
+// mode 3: h [m, n] (float32) += bfloat16(x · wᵀ); out [m, n] = bfloat16(h · (next_weight + next_offset));
+//         ss_out [ceil(n / 16), 16] = per CTA and token the sum of squares of the CTA's 16 columns of the new h.
+// ss_in (any mode; null: none): x lacks its norm's row scale, rsqrt(sum of ss_in [parts_in, 16] over parts / dim_in +
+// eps_in) per token; the product's sums are scaled by it.
 // m at most 16, k a multiple of 8, all pointers 16-byte aligned.
-extern "C" int hb_gemm_bf16_skinny(void* out, int out_f32, const void* x, const void* w, int m, int n, int k, int mode,
-                                   int inter, hb_stream stream) {
+extern "C" int hb_gemm_bf16_skinny_linked(void* out, int out_f32, const void* x, const void* w, int m, int n, int k,
+                                          int mode, int inter, float* h, const void* next_weight, int next_weight_f32,
+                                          float next_offset, float* ss_out, const float* ss_in, int parts_in,
+                                          float eps_in, int dim_in, hb_stream stream) {
     if (m == 0) return 0;
     if (m < 0 || m > 16) HB_REFUSE("gemm_bf16_skinny: %d rows; this kernel takes 1 to 16", m);
     if (k < 8 || k % 8) HB_REFUSE("gemm_bf16_skinny: k = %d is no multiple of 8", k);
     if ((((uintptr_t)out | (uintptr_t)x | (uintptr_t)w) % 16) != 0) HB_REFUSE("gemm_bf16_skinny: pointers must be 16-byte aligned");
-    if (mode != 0 && mode != 1) HB_REFUSE("gemm_bf16_skinny: mode %d", mode);
+    if (mode != 0 && mode != 1 && mode != 3) HB_REFUSE("gemm_bf16_skinny: mode %d", mode);
+    if (mode == 3 && (!h || !next_weight || !ss_out || out_f32)) HB_REFUSE("gemm_bf16_skinny: mode 3 needs h, the next norm's weight and ss_out, and writes bfloat16");
+    if (ss_in && (parts_in < 1 || dim_in < 1)) HB_REFUSE("gemm_bf16_skinny: %d partial sums over %d columns", parts_in, dim_in);
+    NormLink link = {};
+    link.h = h; link.next_weight = next_weight; link.ss_out = ss_out; link.ss_in = ss_in; link.next_offset = next_offset;
+    link.eps_in = eps_in; link.next_weight_f32 = next_weight_f32; link.parts_in = parts_in; link.dim_in = dim_in;
     cudaStream_t s = (cudaStream_t)stream;
     static int sms = 0;
     if (sms == 0) {
@@ -250,29 +310,38 @@ extern "C" int hb_gemm_bf16_skinny(void* out, int out_f32, const void* x, const 
         HB_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device));
     }
     const int nt = m <= 8 ? 1 : 2;
+#define HB_SK_ARGS(md, it) out, out_f32, (const bf16*)x, (const bf16*)w, m, n, k, md, it, RopeEpilogue{}, link
     if (mode == 1) {
         if (inter < 1) HB_REFUSE("gemm_bf16_skinny: inter = %d", inter);
         const int grid = (inter + 15) / 16;
-        if (nt == 1) gemm_skinny_kernel<2, 1, 4, 2><<<grid, SK_WARPS * 32, 0, s>>>(out, out_f32, (const bf16*)x, (const bf16*)w, m, n, k, 1, inter, RopeEpilogue{});
-        else gemm_skinny_kernel<2, 2, 4, 2><<<grid, SK_WARPS * 32, 0, s>>>(out, out_f32, (const bf16*)x, (const bf16*)w, m, n, k, 1, inter, RopeEpilogue{});
+        if (nt == 1) gemm_skinny_kernel<2, 1, 4, 2><<<grid, SK_WARPS * 32, 0, s>>>(HB_SK_ARGS(1, inter));
+        else gemm_skinny_kernel<2, 2, 4, 2><<<grid, SK_WARPS * 32, 0, s>>>(HB_SK_ARGS(1, inter));
     } else {
         if (n < 1) HB_REFUSE("gemm_bf16_skinny: n = %d", n);
-        const bool wide = n >= 32 * 2 * sms;             // enough rows to give every SM two CTAs of 32 rows
+        const bool wide = mode == 0 && n >= 32 * 2 * sms;    // enough rows to give every SM two CTAs of 32 rows
         const int grid = wide ? (n + 31) / 32 : (n + 15) / 16;
-        if (wide && nt == 1) gemm_skinny_kernel<2, 1, 4, 2><<<grid, SK_WARPS * 32, 0, s>>>(out, out_f32, (const bf16*)x, (const bf16*)w, m, n, k, 0, 0, RopeEpilogue{});
-        else if (wide) gemm_skinny_kernel<2, 2, 4, 2><<<grid, SK_WARPS * 32, 0, s>>>(out, out_f32, (const bf16*)x, (const bf16*)w, m, n, k, 0, 0, RopeEpilogue{});
+        if (wide && nt == 1) gemm_skinny_kernel<2, 1, 4, 2><<<grid, SK_WARPS * 32, 0, s>>>(HB_SK_ARGS(0, 0));
+        else if (wide) gemm_skinny_kernel<2, 2, 4, 2><<<grid, SK_WARPS * 32, 0, s>>>(HB_SK_ARGS(0, 0));
         else if (nt == 1 && grid > 2 * sms && grid <= 3 * sms)       // one wave of three CTAs per SM instead of one and a bit of two
-            gemm_skinny_kernel<1, 1, 4, 3><<<grid, SK_WARPS * 32, 0, s>>>(out, out_f32, (const bf16*)x, (const bf16*)w, m, n, k, 0, 0, RopeEpilogue{});
-        else if (nt == 1) gemm_skinny_kernel<1, 1, 8, 2><<<grid, SK_WARPS * 32, 0, s>>>(out, out_f32, (const bf16*)x, (const bf16*)w, m, n, k, 0, 0, RopeEpilogue{});
-        else gemm_skinny_kernel<1, 2, 8, 2><<<grid, SK_WARPS * 32, 0, s>>>(out, out_f32, (const bf16*)x, (const bf16*)w, m, n, k, 0, 0, RopeEpilogue{});
+            gemm_skinny_kernel<1, 1, 4, 3><<<grid, SK_WARPS * 32, 0, s>>>(HB_SK_ARGS(mode, 0));
+        else if (nt == 1) gemm_skinny_kernel<1, 1, 8, 2><<<grid, SK_WARPS * 32, 0, s>>>(HB_SK_ARGS(mode, 0));
+        else gemm_skinny_kernel<1, 2, 8, 2><<<grid, SK_WARPS * 32, 0, s>>>(HB_SK_ARGS(mode, 0));
     }
+#undef HB_SK_ARGS
     HB_LAUNCH_CHECK("gemm_bf16_skinny");
     return 0;
 }
 
+extern "C" int hb_gemm_bf16_skinny(void* out, int out_f32, const void* x, const void* w, int m, int n, int k, int mode,
+                                   int inter, hb_stream stream) {
+    if (mode == 3) HB_REFUSE("gemm_bf16_skinny: mode 3 goes through hb_gemm_bf16_skinny_linked");
+    return hb_gemm_bf16_skinny_linked(out, out_f32, x, w, m, n, k, mode, inter, nullptr, nullptr, 0, 0.f, nullptr, nullptr,
+                                      0, 0.f, 0, stream);
+}
+
 template <typename Kernel>
 static int launch_head_clusters(Kernel kernel, int grid, int per_head, cudaStream_t s, void* out, const bf16* x, const bf16* w,
-                                int m, int n, int k, const RopeEpilogue& ep) {
+                                int m, int n, int k, const RopeEpilogue& ep, const NormLink& link) {
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(grid);
     cfg.blockDim = dim3(SK_WARPS * 32);
@@ -282,7 +351,7 @@ static int launch_head_clusters(Kernel kernel, int grid, int per_head, cudaStrea
     attr.val.clusterDim.x = per_head; attr.val.clusterDim.y = 1; attr.val.clusterDim.z = 1;
     cfg.attrs = &attr;
     cfg.numAttrs = 1;
-    HB_CUDA(cudaLaunchKernelEx(&cfg, kernel, out, 0, x, w, m, n, k, 2, 0, ep));
+    HB_CUDA(cudaLaunchKernelEx(&cfg, kernel, out, 0, x, w, m, n, k, 2, 0, ep, link));
     return 0;
 }
 
@@ -290,10 +359,12 @@ static int launch_head_clusters(Kernel kernel, int grid, int per_head, cudaStrea
 // epilogue (mode 2 above): x [m, k], w [(heads + 2 kv_heads) * head_dim, k]; q_out [m, heads, head_dim]; keys and
 // values go to kv [pages, 2, kv_heads, page_size, head_dim] at write_index (kv null: they are dropped). head_dim 32, 64
 // or 128 with the whole head rotated; weights of the norms bfloat16 or float32, or null for no norm.
-extern "C" int hb_qkv_rope_skinny(void* q_out, const void* x, const void* w, int m, int k, const int32_t* positions,
-                                  const float* table, int max_positions, const void* q_weight, const void* k_weight,
-                                  int weight_f32, float eps, float offset, void* kv, const int32_t* write_index,
-                                  int pages, int page_size, int heads, int kv_heads, int head_dim, hb_stream stream) {
+// ss_in, parts_in, eps_in, dim_in: as for hb_gemm_bf16_skinny_linked (x lacks its norm's row scale).
+extern "C" int hb_qkv_rope_skinny_linked(void* q_out, const void* x, const void* w, int m, int k, const int32_t* positions,
+                                         const float* table, int max_positions, const void* q_weight, const void* k_weight,
+                                         int weight_f32, float eps, float offset, void* kv, const int32_t* write_index,
+                                         int pages, int page_size, int heads, int kv_heads, int head_dim,
+                                         const float* ss_in, int parts_in, float eps_in, int dim_in, hb_stream stream) {
     if (m == 0) return 0;
     if (m < 0 || m > 16) HB_REFUSE("qkv_rope_skinny: %d rows; this kernel takes 1 to 16", m);
     if (k < 8 || k % 8) HB_REFUSE("qkv_rope_skinny: k = %d is no multiple of 8", k);
@@ -302,6 +373,9 @@ extern "C" int hb_qkv_rope_skinny(void* q_out, const void* x, const void* w, int
     if ((((uintptr_t)x | (uintptr_t)w) % 16) != 0) HB_REFUSE("qkv_rope_skinny: x and w must be 16-byte aligned");
     if (!q_out || !positions || !table || max_positions < 1) HB_REFUSE("qkv_rope_skinny: q_out, positions and the table are needed");
     if ((q_weight == nullptr) != (k_weight == nullptr)) HB_REFUSE("qkv_rope_skinny: both norm weights or none");
+    if (ss_in && (parts_in < 1 || dim_in < 1)) HB_REFUSE("qkv_rope_skinny: %d partial sums over %d columns", parts_in, dim_in);
+    NormLink link = {};
+    link.ss_in = ss_in; link.parts_in = parts_in; link.eps_in = eps_in; link.dim_in = dim_in;
     static int sms = 0;
     if (sms == 0) {
         int device = 0;
@@ -316,8 +390,17 @@ extern "C" int hb_qkv_rope_skinny(void* q_out, const void* x, const void* w, int
     const int per_head = head_dim / 16, n = (heads + 2 * kv_heads) * head_dim, grid = n / 16;
     cudaStream_t s = (cudaStream_t)stream;
     if (m <= 8 && grid > 2 * sms && grid <= 3 * sms)
-        return launch_head_clusters(gemm_skinny_kernel<1, 1, 4, 3>, grid, per_head, s, nullptr, (const bf16*)x, (const bf16*)w, m, n, k, ep);
+        return launch_head_clusters(gemm_skinny_kernel<1, 1, 4, 3>, grid, per_head, s, nullptr, (const bf16*)x, (const bf16*)w, m, n, k, ep, link);
     if (m <= 8)
-        return launch_head_clusters(gemm_skinny_kernel<1, 1, 8, 2>, grid, per_head, s, nullptr, (const bf16*)x, (const bf16*)w, m, n, k, ep);
-    return launch_head_clusters(gemm_skinny_kernel<1, 2, 8, 2>, grid, per_head, s, nullptr, (const bf16*)x, (const bf16*)w, m, n, k, ep);
+        return launch_head_clusters(gemm_skinny_kernel<1, 1, 8, 2>, grid, per_head, s, nullptr, (const bf16*)x, (const bf16*)w, m, n, k, ep, link);
+    return launch_head_clusters(gemm_skinny_kernel<1, 2, 8, 2>, grid, per_head, s, nullptr, (const bf16*)x, (const bf16*)w, m, n, k, ep, link);
+}
+
+extern "C" int hb_qkv_rope_skinny(void* q_out, const void* x, const void* w, int m, int k, const int32_t* positions,
+                                  const float* table, int max_positions, const void* q_weight, const void* k_weight,
+                                  int weight_f32, float eps, float offset, void* kv, const int32_t* write_index,
+                                  int pages, int page_size, int heads, int kv_heads, int head_dim, hb_stream stream) {
+    return hb_qkv_rope_skinny_linked(q_out, x, w, m, k, positions, table, max_positions, q_weight, k_weight, weight_f32,
+                                     eps, offset, kv, write_index, pages, page_size, heads, kv_heads, head_dim, nullptr, 0,
+                                     0.f, 0, stream);
 }

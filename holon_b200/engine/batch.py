@@ -57,6 +57,7 @@ class StepContext:
         self.token_ids, self.positions, self.logits_index, self.rows = token_ids, positions, logits_index, rows
         self.groups, self._cache = groups, cache
         self.extra: dict = {}
+        self.link = None             # parts.base.Link: a block's offer to the product that ends its mixer or feed-forward
         self.from_last = None        # int32 [rows]: 1 where the row's token is fed from the device
         self.offset_of: dict = {}    # host: entry index -> offset of its first token among the step's tokens
 

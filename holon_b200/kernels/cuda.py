@@ -68,6 +68,7 @@ class CudaKernels:
             raise KernelError(f"HOLON_B200_DECODE_ATTENTION must be auto, balanced or splits, not {self.decode_attention!r}")
         self.decode_cluster = os.environ.get("HOLON_B200_DECODE_CLUSTER", "1") != "0"   # splits of up to 16 merge in the kernel
         self.fused_qkv = os.environ.get("HOLON_B200_FUSED_QKV", "1") != "0"   # decode steps: norm, rotation, cache write in the product
+        self.fused_norm = os.environ.get("HOLON_B200_FUSED_NORM", "1") != "0"   # decode steps: residual sum and next norm in the product before
         self.decode_pinned = None             # set around a CUDA-graph capture: the captured launches keep this mode
         self.sms = torch.cuda.get_device_properties(self.device).multi_processor_count
         self.decode_ctas = None               # tests: a fixed number of CTAs for the balanced kernel
@@ -165,6 +166,7 @@ class CudaKernels:
         """The product x · weightᵀ with qk_norm_rope_kv_write folded into its epilogue, for the few rows of a decode
         step (one kernel instead of two). False, with nothing done, where that kernel does not apply: more than
         SKINNY_ROWS rows, another dtype, a head size other than 32, 64 or 128, a partial rotation or none."""
+        scaled, x = (x, x.y) if hasattr(x, "ss") else (None, x)      # rows that lack their norm's scale (parts.base.Scaled)
         t, k = x.shape
         if not self.fused_qkv or x.dtype != torch.bfloat16 or t > self.SKINNY_ROWS or k % 8 or table is None \
                 or head_dim not in (32, 64, 128) or rotary_dim != head_dim or (q_weight is None) != (k_weight is None):
@@ -179,11 +181,13 @@ class CudaKernels:
             raise KernelError("qkv_rope: kv must be [pages, 2, kv_heads, page_size, head_dim], bfloat16")
         if q_weight is not None and q_weight.dtype != k_weight.dtype:
             raise KernelError("qkv_rope: the two norm weights must have one dtype")
-        self._call("hb_qkv_rope_skinny", self._p(q_out), self._p(x), self._p(weight), t, k,
+        self._call("hb_qkv_rope_skinny_linked", self._p(q_out), self._p(x), self._p(weight), t, k,
                    self._i32(positions, "positions"), self._p(table), table.shape[0], self._p(q_weight), self._p(k_weight),
                    int(q_weight is not None and q_weight.dtype == torch.float32), ctypes.c_float(eps),
                    ctypes.c_float(offset), self._p(kv), self._i32(write_index, "write_index"),
-                   kv.shape[0] if kv is not None else 0, kv.shape[3] if kv is not None else 1, heads, kv_heads, head_dim)
+                   kv.shape[0] if kv is not None else 0, kv.shape[3] if kv is not None else 1, heads, kv_heads, head_dim,
+                   self._p(scaled.ss) if scaled else None, scaled.ss.shape[0] if scaled else 0,
+                   ctypes.c_float(scaled.eps if scaled else 0.0), scaled.dim if scaled else 0)
         return True
 
     def paged_attention(self, out, q, kv, block_table, rows, scale, window) -> None:
@@ -317,7 +321,49 @@ class CudaKernels:
                    self._i32(rows.query_start, "query_start"), self._i32(rows.kv_len, "kv_len"), rows.n_rows, t,
                    heads, kv.shape[2], head_dim, kv.shape[0], kv.shape[3], ctypes.c_float(scale), int(window))
 
+    # ---- the residual sum and the next norm inside the product that ends a part (decode steps)
+    def can_link(self, rows: int, hidden: int, norm) -> bool:
+        """Whether a product of `rows` rows may add itself into the stream and leave `norm`'s rows unscaled for the
+        next product: both run in the weight-streaming kernel, which takes SKINNY_ROWS rows."""
+        w = getattr(norm, "weight", None)
+        return self.fused_norm and 0 < rows <= self.SKINNY_ROWS and hidden % 8 == 0 and w is not None \
+            and w.tensor.dtype in (torch.bfloat16, torch.float32) and w.tensor.shape == (hidden,)
+
+    def linear_link(self, h, x, weight, norm_weight, eps: float, offset: float):
+        """h [m, n] (float32) += bfloat16(x · weightᵀ) and, returned as parts.base.Scaled, the new h times
+        (norm_weight + offset) in bfloat16 with the partial sums of squares its RMSNorm still needs. None, with
+        nothing done, where the kernel does not apply (another dtype, k no multiple of 8, more rows)."""
+        from ..parts.base import Scaled
+        m, k = x.shape
+        n = weight.shape[0]
+        if x.dtype != torch.bfloat16 or weight.dtype != torch.bfloat16 or h.dtype != torch.float32 or k % 8 \
+                or not 0 < m <= self.SKINNY_ROWS or tuple(h.shape) != (m, n) or weight.shape != (n, k):
+            return None
+        self._check(h, x, weight, norm_weight)
+        y = torch.empty((m, n), dtype=torch.bfloat16, device=self.device)
+        parts = -(-n // 16)
+        ss = torch.empty((parts, 16), dtype=torch.float32, device=self.device)
+        self._call("hb_gemm_bf16_skinny_linked", self._p(y), 0, self._p(x), self._p(weight), m, n, k, 3, 0, self._p(h),
+                   self._p(norm_weight), int(norm_weight.dtype == torch.float32), ctypes.c_float(offset), self._p(ss),
+                   None, 0, ctypes.c_float(0.0), 0)
+        return Scaled(y, ss, float(eps), n)
+
+    def _scaled_product(self, out, x, weight, mode: int, inter: int) -> None:
+        """A product whose x is parts.base.Scaled: the weight-streaming kernel applies the row scale to its sums."""
+        y = x.y
+        self._check(out, y, x.ss, weight)
+        m, k = y.shape
+        if m > self.SKINNY_ROWS or k % 8 or y.dtype != torch.bfloat16 or weight.dtype != torch.bfloat16 or weight.shape[1] != k:
+            raise KernelError("a product of unscaled rows takes up to SKINNY_ROWS bfloat16 rows of a multiple of 8 columns")
+        self._call("hb_gemm_bf16_skinny_linked", self._p(out), int(out.dtype == torch.float32), self._p(y), self._p(weight),
+                   m, weight.shape[0], k, mode, inter, None, None, 0, ctypes.c_float(0.0), None, self._p(x.ss),
+                   x.ss.shape[0], ctypes.c_float(x.eps), x.dim)
+
     def linear(self, out, x, weight) -> None:
+        if hasattr(x, "ss"):                             # rows that lack their norm's scale (parts.base.Scaled)
+            if weight.shape[1] != x.shape[1] or out.shape != (x.shape[0], weight.shape[0]):
+                raise KernelError(f"linear: x {tuple(x.shape)} · w {tuple(weight.shape)}ᵀ -> out {tuple(out.shape)} do not fit")
+            return self._scaled_product(out, x, weight, 0, 0)
         self._check(out, x, weight)
         m, k = x.shape
         n = weight.shape[0]
@@ -366,6 +412,10 @@ class CudaKernels:
     def swiglu_gate_up(self, out, x, weight) -> None:
         """out [tokens, inter] = silu(x · gateᵀ) · (x · upᵀ) with gate's rows first in `weight` [2 inter, k]: for a
         few tokens one kernel with the activation in its epilogue, else the product and the activation kernel."""
+        if hasattr(x, "ss"):                             # rows that lack their norm's scale (parts.base.Scaled)
+            if weight.shape != (2 * out.shape[1], x.shape[1]) or out.shape[0] != x.shape[0] or out.dtype != torch.bfloat16:
+                raise KernelError("swiglu_gate_up: x [tokens, k], weight [2 inter, k], out [tokens, inter], one dtype")
+            return self._scaled_product(out, x, weight, 1, out.shape[1])
         self._check(out, x, weight)
         m, k = x.shape
         inter = out.shape[1]

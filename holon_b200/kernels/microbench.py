@@ -109,25 +109,37 @@ def prefill_attention(k, args) -> None:
 
 
 def gemm(k, args) -> None:
-    m = args.rows[0]
-    for name in args.shapes:
-        n, kk = SHAPES[name]
-        x = torch.randn(m, kk, device=k.device, dtype=torch.bfloat16)
-        w = torch.randn(n, kk, device=k.device, dtype=torch.bfloat16) * 0.02
-        out = torch.empty(m, n, device=k.device, dtype=torch.bfloat16)
-        flops = 2 * m * n * kk
-        t_lib = timed(lambda: torch.mm(x, w.t(), out=out), None, 20)
-        t_own = timed(lambda: k.linear_tcgen05(out, x, w, pair=False), None, 20)
-        t_pair = timed(lambda: k.linear_tcgen05(out, x, w, pair=True), None, 20)
-        line = (f"{name:8s} rows {m}: cuBLAS {t_lib:7.1f} us ({flops / t_lib / 1e6:5.0f} TFLOP/s)  tcgen05 {t_own:7.1f} us "
-                f"({flops / t_own / 1e6:5.0f})  tcgen05 CTA pairs {t_pair:7.1f} us ({flops / t_pair / 1e6:5.0f})")
-        if name == "gate_up":
-            act = torch.empty(m, n // 2, device=k.device, dtype=torch.bfloat16)
-            t_fused = timed(lambda: k.linear_tcgen05(act, x, w, swiglu=True, pair=False), None, 20)
-            t_fused_pair = timed(lambda: k.linear_tcgen05(act, x, w, swiglu=True, pair=True), None, 20)
-            t_act = timed(lambda: k.silu_mul(act, out), None, 20)
-            line += (f"  with SwiGLU {t_fused:7.1f} us, by pairs {t_fused_pair:7.1f} us; activation kernel alone {t_act:5.1f} us")
-        print(line)
+    """A layer's products at each of `--rows`: the library, both tcgen05 kernels and, up to its row limit, the
+    weight-streaming kernel of decode steps. Below 512 rows the product is bound by reading the weight, so the L2 is
+    replaced by reading 256 MB before every run, and the weight's bytes over the time are printed as well."""
+    flush_buffer = torch.zeros(256 << 20, device=k.device, dtype=torch.uint8)
+    for m in args.rows:
+        flush, runs = (flush_buffer, 6) if m < 512 else (None, 20)
+        for name in args.shapes:
+            n, kk = SHAPES[name]
+            x = torch.randn(m, kk, device=k.device, dtype=torch.bfloat16)
+            w = torch.randn(n, kk, device=k.device, dtype=torch.bfloat16) * 0.02
+            out = torch.empty(m, n, device=k.device, dtype=torch.bfloat16)
+            flops = 2 * m * n * kk
+            rate = (lambda t: f"{flops / t / 1e6:5.0f} TFLOP/s") if flush is None else (lambda t: f"{2 * n * kk / t / 1e6:5.2f} TB/s")
+            t_lib = timed(lambda: torch.mm(x, w.t(), out=out), flush, runs)
+            t_own = timed(lambda: k.linear_tcgen05(out, x, w, pair=False), flush, runs)
+            t_pair = timed(lambda: k.linear_tcgen05(out, x, w, pair=True), flush, runs)
+            line = (f"{name:8s} rows {m}: cuBLAS {t_lib:7.1f} us ({rate(t_lib)})  tcgen05 {t_own:7.1f} us "
+                    f"({rate(t_own)})  tcgen05 CTA pairs {t_pair:7.1f} us ({rate(t_pair)})")
+            if m <= k.SKINNY_ROWS:
+                t_skinny = timed(lambda: k.linear(out, x, w), flush, runs)
+                line += f"  weight-streaming {t_skinny:7.1f} us ({rate(t_skinny)})"
+            if name == "gate_up":
+                act = torch.empty(m, n // 2, device=k.device, dtype=torch.bfloat16)
+                t_fused = timed(lambda: k.linear_tcgen05(act, x, w, swiglu=True, pair=False), flush, runs)
+                t_fused_pair = timed(lambda: k.linear_tcgen05(act, x, w, swiglu=True, pair=True), flush, runs)
+                t_act = timed(lambda: k.silu_mul(act, out), flush, runs)
+                line += (f"  with SwiGLU {t_fused:7.1f} us, by pairs {t_fused_pair:7.1f} us; activation kernel alone {t_act:5.1f} us")
+                if m <= k.SKINNY_ROWS:
+                    t_sw = timed(lambda: k.swiglu_gate_up(act, x, w), flush, runs)
+                    line += f"; weight-streaming with SwiGLU {t_sw:7.1f} us"
+            print(line)
     print("tcgen05 status", k.tcgen05_status())
 
 

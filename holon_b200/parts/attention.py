@@ -11,7 +11,7 @@ from __future__ import annotations
 import torch
 
 from ..config.spec import PartRef
-from .base import BuildContext, PagedKV, Part
+from .base import BuildContext, PagedKV, Part, take_link
 from .linear import Linear
 
 
@@ -38,6 +38,8 @@ class GQA(Part):
         for name, p, rows in super().loadables(prefix):
             yield name.replace(prefix + "qkv.", prefix, 1), p, rows
 
+    takes_scaled = True                      # x may be base.Scaled: both first products apply the row scale
+
     def cache(self) -> PagedKV:
         return PagedKV(self.kv_heads, self.head_dim, self.window)
 
@@ -58,4 +60,4 @@ class GQA(Part):
             k.qk_norm_rope_kv_write(q, self.qkv.forward(x), *after)
         o = self.ctx.empty(t, self.heads, self.head_dim)
         k.paged_attention(o, q, cache.kv, cache.group.block_table, step.rows, self.scale, self.window)
-        return self.o_proj.forward(o.view(t, self.heads * self.head_dim))
+        return self.o_proj.forward(o.view(t, self.heads * self.head_dim), link=take_link(step))

@@ -129,9 +129,52 @@ class BuildContext:
 
 class Residual:
     """The residual stream between blocks: `h` [T, H] in 32-bit, and `delta`, a part's output that has not been
-    added yet. The next norm adds it while it normalises, in one kernel."""
+    added yet. The next norm adds it while it normalises, in one kernel. Or the product that ended the part has
+    added its output itself and left the next norm's rows behind (`normed`, made with the weight of `normed_by`):
+    then that norm has nothing left to launch."""
 
-    __slots__ = ("h", "delta")
+    __slots__ = ("h", "delta", "normed", "normed_by")
 
     def __init__(self, h: torch.Tensor, delta: torch.Tensor | None = None) -> None:
         self.h, self.delta = h, delta
+        self.normed, self.normed_by = None, None
+
+
+class Scaled:
+    """Rows of a norm that still lack their row scale: `y` [T, dim] = stream · (weight + offset) in the engine's
+    dtype, and `ss` [parts, 16] float32, partial sums of squares of the stream per token (16 to a part, unused ones 0).
+    x = y · rsqrt(sum(ss) / dim + eps) row by row; a product that takes these rows applies the scale to its sums
+    instead, since (y · s) · Wᵀ = (y · Wᵀ) · s. Only parts that say `takes_scaled` are handed one."""
+
+    __slots__ = ("y", "ss", "eps", "dim")
+
+    def __init__(self, y: torch.Tensor, ss: torch.Tensor, eps: float, dim: int) -> None:
+        self.y, self.ss, self.eps, self.dim = y, ss, eps, dim
+
+    @property
+    def shape(self):
+        return self.y.shape
+
+    @property
+    def dtype(self):
+        return self.y.dtype
+
+
+class Link:
+    """An offer to the product that ends a mixer or a feed-forward: add your output into `stream` yourself and leave
+    the rows of `norm` behind (`Linear.forward(x, link=...)`). A part that takes it from `step.link` returns None in
+    place of its output; a part that knows nothing of it returns its output as ever."""
+
+    __slots__ = ("stream", "norm")
+
+    def __init__(self, stream: Residual, norm) -> None:
+        self.stream, self.norm = stream, norm
+
+
+def take_link(step):
+    """The block's offer for the product that ends the part that calls this (None: there is none); taken, it is gone
+    from the step, which is how the block sees that the part has used it."""
+    link = getattr(step, "link", None)
+    if link is not None:
+        step.link = None
+    return link

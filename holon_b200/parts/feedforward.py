@@ -4,7 +4,7 @@ from __future__ import annotations
 
 import torch
 
-from .base import BuildContext, Part
+from .base import BuildContext, Part, take_link
 from .linear import Linear
 
 
@@ -20,7 +20,9 @@ class SwiGLU(Part):
         for name, p, rows in super().loadables(prefix):
             yield name.replace(prefix + "gate_up.", prefix, 1), p, rows
 
-    def forward(self, x: torch.Tensor, step) -> torch.Tensor:
+    takes_scaled = True                      # x may be base.Scaled: the first product applies the row scale
+
+    def forward(self, x: torch.Tensor, step) -> torch.Tensor | None:
         act = self.ctx.empty(x.shape[0], self.inter)
         self.ctx.kernels.swiglu_gate_up(act, x, self.gate_up.weight.tensor)
-        return self.down.forward(act)
+        return self.down.forward(act, link=take_link(step))

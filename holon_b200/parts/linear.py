@@ -18,7 +18,16 @@ class Linear(Part):
         self.width_out = at
         self.weight = self.add_param(name, (at, width_in), "matrix", rows)
 
-    def forward(self, x: torch.Tensor, out_dtype: torch.dtype | None = None) -> torch.Tensor:
+    def forward(self, x: torch.Tensor, out_dtype: torch.dtype | None = None, link=None) -> torch.Tensor | None:
+        """x · Wᵀ. With `link` (base.Link): the product is added into the link's stream, the rows of the link's norm
+        are left on the stream, and None is returned; where the kernel table has no such product for these sizes, the
+        plain product is returned as ever."""
+        if link is not None:
+            stream, norm = link.stream, link.norm
+            rows = self.ctx.kernels.linear_link(stream.h, x, self.weight.tensor, norm.weight.tensor, norm.eps, norm.offset)
+            if rows is not None:                           # (None: that kernel does not take these sizes or this dtype)
+                stream.normed, stream.normed_by = rows, norm
+                return None
         out = self.ctx.empty(x.shape[0], self.width_out, dtype=out_dtype)
         self.ctx.kernels.linear(out, x, self.weight.tensor)
         return out

@@ -61,8 +61,10 @@ class Model(Part):
     def trunk(self, step):
         """The residual stream after the last run, for every token of the step."""
         stream = self.embed.forward(step.token_ids)
-        for run in self.spec.order:
-            stream = self.layers[run.layer].forward(stream, step, step.layer_cache(run))
+        order = self.spec.order
+        for i, run in enumerate(order):
+            after = self.layers[order[i + 1].layer] if i + 1 < len(order) else None
+            stream = self.layers[run.layer].forward(stream, step, step.layer_cache(run), after)
         return stream
 
     def forward(self, step) -> torch.Tensor | None:

@@ -20,7 +20,12 @@ class RMSNorm(Part):
         return out
 
     def add(self, stream: Residual) -> torch.Tensor:
-        """Adds the stream's pending output into it and returns the norm of the sum."""
+        """Adds the stream's pending output into it and returns the norm of the sum; or, where the product before
+        has done both, the rows it left (base.Scaled)."""
+        if stream.normed is not None:
+            rows, by, stream.normed, stream.normed_by = stream.normed, stream.normed_by, None, None
+            if by is self:
+                return rows                                # (made for another norm: dropped, the stream itself is whole)
         out = self.ctx.empty(*stream.h.shape)
         self.ctx.kernels.add_rmsnorm(out, stream.h, stream.delta, self.weight.tensor, self.eps, self.offset, None)
         stream.delta = None

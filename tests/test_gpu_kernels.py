@@ -5,6 +5,7 @@ from __future__ import annotations
 
 import ctypes
 import math
+import types
 
 import pytest
 import torch
@@ -408,6 +409,71 @@ def test_qkv_product_with_norm_rotation_and_cache_write(K, heads, kv_heads, head
     scale = max(1.0, float(q2.abs().max()))
     assert (q1 - q2).abs().max() <= 2e-2 * scale and (kv1 - kv2).abs().max() <= 2e-2 * max(scale, float(kv2.abs().max()))
     assert ((kv1 == 7.0) == (kv2 == 7.0)).all()                        # the same places were written
+
+
+@pytest.mark.parametrize("hidden,wide", [(4096, 4096), (96, 192), (200, 72), (1024, 3072)])
+@pytest.mark.parametrize("m", [1, 8, 16])
+@pytest.mark.parametrize("norm", ["bfloat16", "float32"])
+def test_residual_sum_and_norm_inside_the_products_around_them(K, hidden, wide, m, norm):
+    """A product that adds itself into the 32-bit stream and leaves the next norm's rows unscaled, and the three
+    products that take such rows (plain, SwiGLU, QKV with rotation), against the separate kernels: product,
+    add_rmsnorm, product. The stream itself must come out the same to the bit."""
+    g = torch.Generator().manual_seed(hidden + m)
+    dev = lambda t: t.to(DEV)                                          # noqa: E731
+    x = dev((torch.randn(m, wide, generator=g) * 0.5).to(torch.bfloat16))
+    w = dev((torch.randn(hidden, wide, generator=g) * 0.05).to(torch.bfloat16))
+    h0 = dev(torch.randn(m, hidden, generator=g) * 2.0)
+    gain = dev((1 + 0.1 * torch.randn(hidden, generator=g)).to(getattr(torch, norm)))
+    eps, offset = 1e-5, 0.25
+    norm_part = types.SimpleNamespace(weight=types.SimpleNamespace(tensor=gain))
+    assert K.can_link(m, hidden, norm_part) and not K.can_link(17, hidden, norm_part)
+    # the separate kernels
+    delta = torch.empty(m, hidden, dtype=torch.bfloat16, device=DEV)
+    K.linear(delta, x, w)
+    h_want, xn = h0.clone(), torch.empty(m, hidden, dtype=torch.bfloat16, device=DEV)
+    K.add_rmsnorm(xn, h_want, delta, gain, eps, offset, None)
+    # the linked product
+    h_got = h0.clone()
+    rows = K.linear_link(h_got, x, w, gain, eps, offset)
+    assert rows is not None and rows.shape == (m, hidden) and rows.ss.shape == (-(-hidden // 16), 16)
+    assert torch.equal(h_got, h_want)
+    ss = rows.ss.double().sum(0)[:m].cpu()
+    assert torch.allclose(ss, h_want.double().pow(2).sum(-1).cpu(), rtol=1e-5)
+    assert (rows.ss[:, m:] == 0).all()
+    # 1. a plain product of the rows
+    w2 = dev((torch.randn(176, hidden, generator=g) * 0.05).to(torch.bfloat16))
+    want, got = (torch.empty(m, 176, dtype=torch.bfloat16, device=DEV) for _ in range(2))
+    K.linear(want, xn, w2)
+    K.linear(got, rows, w2)
+    close(got, want.cpu(), torch.bfloat16, scale=2 * max(1.0, float(want.abs().max())))
+    # 2. SwiGLU's first product
+    w3 = dev((torch.randn(2 * 208, hidden, generator=g) * 0.05).to(torch.bfloat16))
+    want, got = (torch.empty(m, 208, dtype=torch.bfloat16, device=DEV) for _ in range(2))
+    K.swiglu_gate_up(want, xn, w3)
+    K.swiglu_gate_up(got, rows, w3)
+    close(got, want.cpu(), torch.bfloat16, scale=2 * max(1.0, float(want.abs().max())))
+    # 3. the attention's first product with q/k norm, rotation and cache write
+    heads, kv_heads, head_dim = 4, 2, 64
+    w4 = dev((torch.randn((heads + 2 * kv_heads) * head_dim, hidden, generator=g) * 0.05).to(torch.bfloat16))
+    qw, kw = (dev((1 + 0.1 * torch.randn(head_dim, generator=g)).to(torch.bfloat16)) for _ in range(2))
+    inv = 1.0 / (1e4 ** (torch.arange(0, head_dim, 2, dtype=torch.float32) / head_dim))
+    angle = torch.arange(64, dtype=torch.float32)[:, None] * inv[None, :]
+    table = dev(torch.cat((angle.cos(), angle.sin()), dim=-1).contiguous())
+    positions = dev(torch.randint(0, 64, (m,), generator=g, dtype=torch.int32))
+    write = dev(torch.randperm(48, generator=g)[:m].to(torch.int32))
+    outs = []
+    for source in (xn, rows):
+        kv = torch.full((3, 2, kv_heads, 16, head_dim), 1024.0, dtype=torch.bfloat16, device=DEV)
+        q = torch.full((m, heads, head_dim), float("nan"), dtype=torch.bfloat16, device=DEV)
+        assert K.qkv_rope(q, source, w4, positions, table, head_dim, qw, kw, 1e-6, 0.0, kv, write, heads, kv_heads, head_dim)
+        outs.append((q.float().cpu(), kv.float().cpu()))
+    (q1, kv1), (q2, kv2) = outs
+    assert torch.isfinite(q2).all() and (q1 - q2).abs().max() <= 4e-2 * max(1.0, float(q1.abs().max()))
+    written = kv1 != 1024.0
+    assert (written == (kv2 != 1024.0)).all() and written.sum() == 2 * m * kv_heads * head_dim
+    assert (kv1 - kv2)[written].abs().max() <= 4e-2 * max(1.0, float(kv1[written].abs().max()))
+    # where the kernel does not apply, nothing is done
+    assert K.linear_link(h_got.double().float()[:, :hidden], x.float(), w.float(), gain, eps, offset) is None
 
 
 @pytest.mark.parametrize("geometry", [(32, 8, 128, 64), (40, 2, 64, 16), (6, 1, 48, 4), (16, 4, 256, 128)])
