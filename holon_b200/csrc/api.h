@@ -89,12 +89,13 @@ int hb_attention_prefill_bf16(void* out, const void* q, const void* kv, const in
                               float scale, int window, hb_stream stream);
 
 // The same rows on tcgen05 tensor cores (scores and output in tensor memory, operands by TMA): head_dim 128, page
-// sizes that are multiples of 64. q_tiles: the sum over the rows of ceil(tokens / 256); tokens: all tokens of the step.
+// sizes that are multiples of 64. q_tiles: the sum over the rows of ceil(tokens / tile_q); tokens: all tokens of the
+// step; tile_q: 256, or 128 for twice the CTAs at half the work each (steps with few query tiles).
 // hb_attention_tcgen05_status synchronises the device and returns (and clears) the kernel's bounded-wait status word.
 int hb_attention_prefill_tcgen05(void* out, const void* q, const void* kv, const int32_t* block_table, int table_stride,
                                  const int32_t* row_slot, const int32_t* query_start, const int32_t* kv_len, int row0,
                                  int rows, int q_tiles, int tokens, int heads, int kv_heads, int head_dim, int pages,
-                                 int page_size, float scale, int window, hb_stream stream);
+                                 int page_size, float scale, int window, int tile_q, hb_stream stream);
 int hb_attention_tcgen05_status(unsigned int* status);
 
 // out[m, n] = sum_k x[m, k] * w[n, k], all float32, sums in a fixed order that does not depend on m's neighbours.

@@ -72,7 +72,7 @@ __global__ void __launch_bounds__(AT_THREADS, 1) prefill_tcgen05_kernel(
         const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_kv, bf16* __restrict__ out,
         const int32_t* __restrict__ block_table, int table_stride, const int32_t* __restrict__ row_slot,
         const int32_t* __restrict__ query_start, const int32_t* __restrict__ kv_len, int row0, int rows, int heads,
-        int kv_heads, int pages, int page_size, float scale_log2, int window) {
+        int kv_heads, int pages, int page_size, float scale_log2, int window, int tile_q) {
     extern __shared__ unsigned char smem_raw[];
     const uint32_t base = (smem_addr(smem_raw) + 1023u) & ~1023u;
     const uint32_t q_s = base, kv_s = q_s + AT_GROUPS * AT_Q_BYTES;
@@ -88,8 +88,8 @@ __global__ void __launch_bounds__(AT_THREADS, 1) prefill_tcgen05_kernel(
         int left = (int)blockIdx.y, found = -1, q0 = 0;      // blocks are handed out x first: every head's late query
                                                              // tiles (the longest walks) start before any short one
         for (int b = rows - 1; b >= row0; --b) {
-            const int tiles = (query_start[b + 1] - query_start[b] + AT_GROUPS * AT_BM - 1) / (AT_GROUPS * AT_BM);
-            if (left < tiles) { found = b; q0 = (tiles - 1 - left) * AT_GROUPS * AT_BM; break; }
+            const int tiles = (query_start[b + 1] - query_start[b] + tile_q - 1) / tile_q;
+            if (left < tiles) { found = b; q0 = (tiles - 1 - left) * tile_q; break; }
             left -= tiles;
         }
         s_row = found; s_q0 = q0;
@@ -125,7 +125,7 @@ __global__ void __launch_bounds__(AT_THREADS, 1) prefill_tcgen05_kernel(
         tile_lo = lo / AT_BN;
 #pragma unroll
         for (int g = 0; g < AT_GROUPS; ++g) {
-            g_qn[g] = max(0, min(AT_BM, nq - s_q0 - g * AT_BM));     // queries of this group
+            g_qn[g] = max(0, min(AT_BM, min(nq - s_q0, tile_q) - g * AT_BM));   // queries of this group
             g_hi[g] = g_qn[g] ? min(n, p0 + g * AT_BM + g_qn[g]) : 0;   // keys below this are visible to some of them
             g_tiles[g] = g_qn[g] ? (g_hi[g] + AT_BN - 1) / AT_BN - tile_lo : 0;
         }
@@ -355,13 +355,16 @@ extern "C" int hb_attention_tcgen05_status(unsigned int* status) {
     return 0;
 }
 
-// Rows row0 .. rows - 1 of the batch; q_tiles is the sum of ceil(queries / 256) over them; tokens the step's token count.
+// Rows row0 .. rows - 1 of the batch; q_tiles is the sum of ceil(queries / tile_q) over them; tokens the step's token
+// count. tile_q: 256 (both groups of a CTA at work) or 128 (one group: twice the CTAs, for steps whose tiles of 256
+// would leave SMs idle).
 extern "C" int hb_attention_prefill_tcgen05(void* out, const void* q, const void* kv, const int32_t* block_table,
                                             int table_stride, const int32_t* row_slot, const int32_t* query_start,
                                             const int32_t* kv_len, int row0, int rows, int q_tiles, int tokens, int heads,
                                             int kv_heads, int head_dim, int pages, int page_size, float scale, int window,
-                                            hb_stream stream) {
+                                            int tile_q, hb_stream stream) {
     if (rows <= row0 || q_tiles == 0) return 0;
+    if (tile_q != AT_BM && tile_q != AT_GROUPS * AT_BM) HB_REFUSE("attention_prefill_tcgen05: query tiles of %d (128 or 256)", tile_q);
     if (head_dim != AT_D) HB_REFUSE("attention_prefill_tcgen05: head_dim %d; this kernel is for %d", head_dim, AT_D);
     if (page_size % AT_BN) HB_REFUSE("attention_prefill_tcgen05: page size %d is no multiple of %d", page_size, AT_BN);
     if (kv_heads < 1 || heads % kv_heads) HB_REFUSE("attention_prefill_tcgen05: %d heads, %d kv heads", heads, kv_heads);
@@ -378,7 +381,7 @@ extern "C" int hb_attention_prefill_tcgen05(void* out, const void* q, const void
     HB_CUDA(cudaFuncSetAttribute(prefill_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, AT_SMEM));
     prefill_tcgen05_kernel<<<dim3(heads, q_tiles), AT_THREADS, AT_SMEM, (cudaStream_t)stream>>>(
         map_q, map_kv, (bf16*)out, block_table, table_stride, row_slot, query_start, kv_len, row0, rows, heads, kv_heads,
-        pages, page_size, scale * 1.4426950408889634f, window);
+        pages, page_size, scale * 1.4426950408889634f, window, tile_q);
     HB_LAUNCH_CHECK("attention_prefill_tcgen05");
     return 0;
 }

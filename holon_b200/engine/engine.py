@@ -338,7 +338,7 @@ class Engine:
         key = (bucket, len(portions), prompt_tokens, mode)         # ... and a graph per way of sharing out the keys
         if key not in self._graphs:
             step.rows.max_kv = self.config.max_model_len          # the captured launch must serve any length
-            for size in (64, 256):                                 # and any cut of the prompt tokens into the portions:
+            for size in (64, 128, 256):                            # and any cut of the prompt tokens into the portions:
                 step.rows.plan[size] = prompt_tokens // size + len(portions)   # query tiles beyond a step's own exit at once
             out = torch.empty(m, dtype=torch.int32, device=self.device)
             kernels.decode_pinned = mode

@@ -72,6 +72,7 @@ class CudaKernels:
         self.decode_pinned = None             # set around a CUDA-graph capture: the captured launches keep this mode
         self.sms = torch.cuda.get_device_properties(self.device).multi_processor_count
         self.decode_ctas = None               # tests: a fixed number of CTAs for the balanced kernel
+        self.prefill_tile = None              # tests, microbench: 128 or 256 queries a CTA of the tcgen05 prefill kernel
 
     # ------------------------------------------------------------------ plumbing
     def _call(self, name: str, *args) -> None:
@@ -229,8 +230,11 @@ class CudaKernels:
                            rows.n_decode, *sizes, splits)
         if rows.n_rows > rows.n_decode:
             if self.prefill_attention == "tcgen05" and head_dim == 128 and kv.shape[3] % 64 == 0:
+                tile_q, tiles = 256, self._query_tiles(rows, 256)
+                if self.prefill_tile == 128 or (self.prefill_tile is None and 4 * heads * tiles < 3 * self.sms):              # tiles of 256 queries would leave SMs idle: one group of
+                    tile_q, tiles = 128, self._query_tiles(rows, 128)   # 128 a CTA, twice the CTAs
                 self._call("hb_attention_prefill_tcgen05", self._p(out), self._p(q), self._p(kv), *common,
-                           rows.n_decode, rows.n_rows, self._query_tiles(rows, 256), t, *sizes)
+                           rows.n_decode, rows.n_rows, tiles, t, *sizes, tile_q)
             else:
                 self._call("hb_attention_prefill_bf16", self._p(out), self._p(q), self._p(kv), *common, rows.n_decode,
                            rows.n_rows, self._query_tiles(rows, 64), *sizes)

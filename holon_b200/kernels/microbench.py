@@ -97,14 +97,17 @@ def prefill_attention(k, args) -> None:
         dev = lambda v: torch.tensor(v, device=k.device, dtype=torch.int32)   # noqa: E731
         batch = Rows(dev([0]), dev([0, t]), dev([n]), 1, t, 0, t, n, [0, t], [n])
         flops = 4 * heads * d * (t * (n - t) + t * (t + 1) // 2)
-        for name in ("tcgen05", "mma"):
-            k.prefill_attention = name
+        for name, tile in (("tcgen05", 256), ("tcgen05", 128), ("mma", None)):
+            k.prefill_attention, k.prefill_tile = name, tile
+            batch.plan.clear()
 
             def ten():
                 for _ in range(10):
                     k.paged_attention(out, q, kv, table, batch, 1 / math.sqrt(d), 0)
             us = timed(ten, None, 4) / 10
-            print(f"prefill attention {name:8s} tokens {t} keys {n}: {us:7.1f} us  {flops / us / 1e6:6.0f} TFLOP/s (causal)")
+            label = name + (f" tile {tile}" if tile else "")
+            print(f"prefill attention {label:16s} tokens {t} keys {n}: {us:7.1f} us  {flops / us / 1e6:6.0f} TFLOP/s (causal)")
+        k.prefill_tile = None
     print("tcgen05 status", k.tcgen05_status())
 
 
