@@ -9,7 +9,6 @@ holon's own CPU model on a tiny random model, recorded once by `tests/golden/mak
 from __future__ import annotations
 
 import json
-import math
 import pathlib
 
 import torch

@@ -6,7 +6,7 @@ import pytest
 import torch
 
 import plain_qwen3 as plain
-from helpers import TINY, make_folder, random_prompt
+from helpers import make_folder, random_prompt
 from holon_b200.engine import Engine, EngineConfig, SamplingParams, StepEntry, StepError, build
 from holon_b200.weights import SafetensorsSource
 from ref_kernels import RefKernels

@@ -6,7 +6,6 @@ from __future__ import annotations
 import dataclasses
 
 import pytest
-import torch
 
 import plain_qwen3 as plain
 from helpers import make_folder, random_prompt

@@ -2,7 +2,6 @@
 own that is defined here, registered, built into a model and stepped without any change to the framework."""
 from __future__ import annotations
 
-import math
 
 import pytest
 import torch
@@ -12,7 +11,7 @@ from holon_b200.cache import CacheManager
 from holon_b200.config import LayerSpec, ModelSpec, PartRef, Run, WeightRule, register_architecture, unregister_architecture
 from holon_b200.engine import StepEntry, build
 from holon_b200.engine.runner import Runner
-from holon_b200.parts import BuildContext, CacheEntry, Model, Part, Residual, SlotState, register_part, unregister_part
+from holon_b200.parts import BuildContext, CacheEntry, Part, Residual, SlotState, register_part, unregister_part
 from holon_b200.weights import RandomSource
 
 pytestmark = pytest.mark.gpu

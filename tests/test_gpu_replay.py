@@ -14,7 +14,7 @@ import pytest
 import torch
 
 import plain_qwen3 as plain
-from helpers import TINY, make_folder, random_prompt
+from helpers import make_folder, random_prompt
 from holon_b200.replay import Replayer
 
 pytestmark = pytest.mark.gpu
