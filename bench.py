@@ -8,8 +8,8 @@ request ending at a context of 8,192 tokens. It prints ONE JSON line:
 
   value            decoded tokens per second, timed on the device with CUDA events around exactly K steps
   e2e              decode throughput through the public entry point `Engine.generate` (host token lists in and out), by
-                   wall clock, as batch * K / (t(K + 1 tokens) - t(1 token)); every step copies its inputs from pinned
-                   host memory and its tokens back (bytes per step are reported)
+                   wall clock, as batch * K / (t(K + 1 tokens) - t(1 token)), each time the faster of two runs; every step
+                   copies its inputs from pinned host memory and its tokens back (bytes per step are reported)
   prefill          one prompt of 2,048 tokens: tokens per second, milliseconds, flops / time / bf16 peak
   roofline         the decode step's bytes (every weight once, the live requests' cache) / its time against the
                    measured copy bandwidth
@@ -192,20 +192,21 @@ def generate_run(engine, batch: int, context: int, steps: int, seed: int) -> dic
     from holon_b200.engine import SamplingParams
     vocab = engine.built.model.spec.vocab
     prompt_len = context - steps - 2
+    import torch
     times = {}
-    for n, s in ((1, seed), (steps + 1, seed + 1)):
-        prompts = prompts_of(vocab, batch, prompt_len, s)
-        import torch
-        torch.cuda.synchronize()
-        h2d0, d2h0, steps0 = engine.h2d_bytes, engine.d2h_bytes, engine.steps
-        t0 = time.perf_counter()
-        out = engine.generate(prompts, SamplingParams(temperature=0.0, max_tokens=n, ignore_eos=True))
-        times[n] = time.perf_counter() - t0
-        assert all(len(o) == n for o in out)
-        if n > 1:
-            decode_steps = steps
-            prefill_steps = engine.steps - steps0 - decode_steps
-            io = (engine.h2d_bytes - h2d0, engine.d2h_bytes - d2h0, prefill_steps)
+    for rep in range(2):                                             # each of the two runs twice, the faster one counts:
+        for n, s in ((1, seed + 2 * rep), (steps + 1, seed + 2 * rep + 1)):   # the prompts' prefill (most of either run)
+            prompts = prompts_of(vocab, batch, prompt_len, s)        # varies by more than a decode step from run to run
+            torch.cuda.synchronize()
+            h2d0, d2h0, steps0 = engine.h2d_bytes, engine.d2h_bytes, engine.steps
+            t0 = time.perf_counter()
+            out = engine.generate(prompts, SamplingParams(temperature=0.0, max_tokens=n, ignore_eos=True))
+            times[n] = min(times.get(n, float("inf")), time.perf_counter() - t0)
+            assert all(len(o) == n for o in out)
+            if n > 1:
+                decode_steps = steps
+                prefill_steps = engine.steps - steps0 - decode_steps
+                io = (engine.h2d_bytes - h2d0, engine.d2h_bytes - d2h0, prefill_steps)
     return {"value": batch * steps / (times[steps + 1] - times[1]), "seconds": times, "io": io}
 
 
@@ -385,7 +386,7 @@ def run_ours(args) -> dict:
                    "cuda_graphs": True, "overlap": engine.config.overlap, "peaks": peak_kind,
                    "gemm": engine.built.ctx.kernels.gemm},
         "e2e": {"value": round(e2e["value"], 1), "unit": "tok/s", "h2d_bytes_per_step": main["h2d_bytes_per_step"],
-                "d2h_bytes_per_step": main["d2h_bytes_per_step"], "method": "Engine.generate: t(K+1 tokens) - t(1 token)",
+                "d2h_bytes_per_step": main["d2h_bytes_per_step"], "method": "Engine.generate: t(K+1 tokens) - t(1 token), each the faster of two runs",
                 "step_loop_wall_value": round(main["tokens"] / main["wall_ms"] * 1e3, 1)},
         "gpu_launches": main["launches"],
         "prefill": {"value": round(prefill_tokens / prefill_ms * 1e3, 1), "tokens": prefill_tokens,
