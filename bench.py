@@ -345,7 +345,8 @@ def run_ours(args) -> dict:
     cfg = dict(QWEN3_8B, num_hidden_layers=args.layers)
     context, batch = args.context, args.batch
     engine = Engine(EngineConfig(model="random weights, seed 2", device="cuda:0", dtype="bfloat16", page_size=64,
-                                 max_seqs=64, max_model_len=context, max_step_tokens=8192, seed=0),
+                                 max_seqs=64, max_model_len=context, max_step_tokens=8192, seed=0,
+                                 memory_fraction=args.memory_fraction),
                     source=RandomSource(cfg, seed=2, device="cuda:0"))
     numbers = model_numbers(cfg, args.layers)
     peak, peak_kind = peaks()
@@ -417,6 +418,9 @@ def main() -> int:
     ap.add_argument("--warmup", type=int, default=4)
     ap.add_argument("--impl", default="ours", choices=("ours", "reference"))
     ap.add_argument("--layers", type=int, default=FULL_LAYERS, help="fewer layers than the model has (both are reported)")
+    ap.add_argument("--memory-fraction", type=float, default=0.9,
+                    help="share of the free device memory for weights and cache pool; a run under a profiler that takes "
+                         "several passes should hold a few GB only (e.g. 0.03 with --layers 4 --batch 8)")
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--context", type=int, default=8192)
     ap.add_argument("--only", default="all", choices=("all", "decode", "prefill", "long_prompt", "sizes"),

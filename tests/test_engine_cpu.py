@@ -119,3 +119,24 @@ def test_logprobs_of_generated_and_prompt_tokens(tmp_path):
         engine.add([1], SamplingParams(logprobs=-1))
     engine.built.cache.check()
     assert not engine.built.cache.live and not engine._prompt_lp
+
+
+def test_which_steps_are_kept_as_graphs(tmp_path):
+    """The shapes `Engine._graph_fits` accepts: one-token rows alone up to the largest bucket, or beside one or two
+    prompt portions that fill `chunk_with_decode` exactly."""
+    folder = make_folder(tmp_path, "a")
+    engine = Engine(EngineConfig(model=str(folder), device="cpu", dtype="float32", page_size=4, max_seqs=3,
+                                 max_model_len=64, max_step_tokens=16, chunk_with_decode=8, state_memory=1 << 20),
+                    kernels=RefKernels())
+    one = lambda slot: StepEntry(slot, [1], 0)                       # noqa: E731
+    part = lambda slot, n: StepEntry(slot, list(range(n)), 0)        # noqa: E731
+    fits = lambda entries: engine._graph_fits(entries, sum(len(e.tokens) == 1 for e in entries))   # noqa: E731
+    assert engine._buckets == (1, 2, 3)                              # max_seqs itself is the last bucket
+    assert fits([one(0)]) and fits([one(0), one(1), one(2)])
+    assert not fits([one(0), one(1), one(2), one(3)])               # more rows than the largest bucket
+    assert fits([one(0), part(1, 8)]) and fits([one(0), part(1, 5), part(2, 3)])
+    assert not fits([one(0), part(1, 7)])                           # the budget is not filled
+    assert not fits([part(1, 8)])                                   # no decode row beside it: a plain prefill step
+    assert not fits([one(0), part(1, 2), part(2, 3), part(3, 3)])   # three portions
+    engine.config.chunk_with_decode = 0
+    assert not fits([one(0), part(1, 8)]) and fits([one(0)])
