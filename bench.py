@@ -238,7 +238,7 @@ def long_prompt_run(args) -> dict:
     from holon_b200.weights import RandomSource
     cfg = dict(QWEN3_8B, num_hidden_layers=args.layers)
     engine = Engine(EngineConfig(model="random weights, seed 2", device="cuda:0", dtype="bfloat16", page_size=64,
-                                 max_seqs=8, max_model_len=32768, max_step_tokens=4096, chunk_with_decode=2048, seed=0),
+                                 max_seqs=8, max_model_len=32768, max_step_tokens=4096, chunk_with_decode=2048, seed=0, prefix_cache=False),
                     source=RandomSource(cfg, seed=2, device="cuda:0"))
     vocab, best = engine.built.model.spec.vocab, float("inf")
     streams = SamplingParams(temperature=0.0, max_tokens=400, ignore_eos=True)
@@ -277,7 +277,7 @@ def sizes_run(args) -> dict:
     if args.sizes == "32b":
         cfg, seed = dict(QWEN3_32B), 4
         engine = Engine(EngineConfig(model="random weights, seed 4", device="cuda:0", dtype="bfloat16", page_size=64,
-                                     max_seqs=64, max_model_len=16384, max_step_tokens=8192, seed=0),
+                                     max_seqs=64, max_model_len=16384, max_step_tokens=8192, seed=0, prefix_cache=False),
                         source=RandomSource(cfg, seed=seed, device="cuda:0"))
         numbers = model_numbers(cfg, cfg["num_hidden_layers"])
         tokens = 8192
@@ -296,7 +296,7 @@ def sizes_run(args) -> dict:
     else:
         cfg, seed = dict(QWEN3_06B), 3
         engine = Engine(EngineConfig(model="random weights, seed 3", device="cuda:0", dtype="bfloat16", page_size=64,
-                                     max_seqs=32, max_model_len=4352, max_step_tokens=4096, chunk_with_decode=512, seed=0),
+                                     max_seqs=32, max_model_len=4352, max_step_tokens=4096, chunk_with_decode=512, seed=0, prefix_cache=False),
                         source=RandomSource(cfg, seed=seed, device="cuda:0"))
         rng = random.Random(5)
         prompts = [[rng.randrange(cfg["vocab_size"]) for _ in range(rng.randint(16, 4096))] for _ in range(32)]
@@ -319,7 +319,7 @@ def sizes_run(args) -> dict:
         gc.collect()
         torch.cuda.empty_cache()
         engine = Engine(EngineConfig(model="random weights, seed 3", device="cuda:0", dtype="bfloat16", page_size=64,
-                                     max_seqs=32, max_model_len=4352, max_step_tokens=4096, seed=0),
+                                     max_seqs=32, max_model_len=4352, max_step_tokens=4096, seed=0, prefix_cache=False),
                         source=RandomSource(cfg, seed=seed, device="cuda:0"))
         numbers = model_numbers(cfg, cfg["num_hidden_layers"])
         steps = max(8, min(args.steps, 64))
@@ -346,7 +346,7 @@ def run_ours(args) -> dict:
     context, batch = args.context, args.batch
     engine = Engine(EngineConfig(model="random weights, seed 2", device="cuda:0", dtype="bfloat16", page_size=64,
                                  max_seqs=64, max_model_len=context, max_step_tokens=8192, seed=0,
-                                 memory_fraction=args.memory_fraction),
+                                 memory_fraction=args.memory_fraction, prefix_cache=False),
                     source=RandomSource(cfg, seed=2, device="cuda:0"))
     numbers = model_numbers(cfg, args.layers)
     peak, peak_kind = peaks()
@@ -384,7 +384,7 @@ def run_ours(args) -> dict:
                    "kv_heads": cfg["num_key_value_heads"], "head_dim": cfg["head_dim"],
                    "intermediate": cfg["intermediate_size"], "vocab": cfg["vocab_size"], "global_batch": batch,
                    "seq_len": context, "page_size": 64, "parallelism": "single GPU", "l2": "inputs larger than L2",
-                   "cuda_graphs": True, "overlap": engine.config.overlap, "peaks": peak_kind,
+                   "cuda_graphs": True, "overlap": engine.config.overlap, "prefix_cache": False, "peaks": peak_kind,
                    "gemm": engine.built.ctx.kernels.gemm},
         "e2e": {"value": round(e2e["value"], 1), "unit": "tok/s", "h2d_bytes_per_step": main["h2d_bytes_per_step"],
                 "d2h_bytes_per_step": main["d2h_bytes_per_step"], "method": "Engine.generate: t(K+1 tokens) - t(1 token), each the faster of two runs",

@@ -9,6 +9,10 @@ request ends, or, in a group with a window, when every position in it lies befor
 (core/holon/core/state.py:398-418, 499-517). The last page of each pool's tensor is the null page: never handed
 out, it stands in every unused block-table cell (memory.py:49-54).
 
+With `prefix_cache` (and one group of full attention, no state of fixed size) whole pages of prompts are shared
+between requests through `prefix.PrefixIndex`: `admit(tokens)` starts a request on the pages of the longest known
+prefix of its tokens, `publish(slot, tokens)` enters the pages its computed tokens have filled.
+
 Slots: a request holds one slot from admission to release; the slot is its row in every block table and in every
 per-request tensor (state.py:154, 183-186). Mixers may declare state of fixed size (`SlotState`); it is zeroed when
 a request takes the slot.
@@ -22,6 +26,7 @@ import torch
 
 from ..parts.base import PagedKV
 from .pages import OutOfPages, PagePool
+from .prefix import ROOT, PrefixIndex
 
 
 class CacheGroup:
@@ -88,7 +93,7 @@ class CacheGroup:
 
     def release(self, slot: int) -> None:
         first, count = int(self.first[slot]), int(self.count[slot])
-        self.pool.give(self.table[slot, first:count].tolist(), slot)
+        self.pool.give(self.table[slot, first:count].tolist()[::-1], slot)     # the last block first: kept leaves go first
         self.table[slot, :count] = self.null_page
         self.first[slot] = self.count[slot] = 0
         self.dirty.add(slot)
@@ -107,9 +112,11 @@ class CacheGroup:
 
 class CacheManager:
     def __init__(self, entries, page_size: int, max_seqs: int, max_model_len: int, dtype: torch.dtype, device,
-                 state_memory: int | None = None, pages: int | None = None) -> None:
+                 state_memory: int | None = None, pages: int | None = None, prefix_cache: bool = False) -> None:
         """`entries`: the model's `CacheEntry` list. Give either `state_memory` (bytes for all pools together) or
-        `pages` (pages per pool)."""
+        `pages` (pages per pool). `prefix_cache`: share whole pages of equal prompt prefixes between requests; it
+        takes effect only for one group of full attention without state of fixed size (a window lets go of early
+        pages, and a fixed-size state cannot be entered in the middle of a prompt)."""
         self.page_size, self.max_seqs, self.max_model_len = page_size, max_seqs, max_model_len
         self.dtype, self.device = dtype, torch.device(device)
         by_decl: dict[PagedKV, list[int]] = {}
@@ -141,18 +148,54 @@ class CacheManager:
             for s in e.slot_states:
                 self.slot_states[(e.entry, s.name)] = torch.zeros((max_seqs + 1, *s.shape),
                                                                   dtype=getattr(torch, s.dtype), device=device)
+        self.prefix: PrefixIndex | None = None
+        if prefix_cache and len(self.groups) == 1 and self.groups[0].decl.window <= 0 and not self.slot_states:
+            self.prefix = PrefixIndex(page_size)
+            self.groups[0].pool.on_evict = self.prefix.evicted
+        self._chain_node = np.full(max_seqs + 1, ROOT, dtype=np.int64)    # per slot: the index node of its last known block
+        self._chain_blocks = np.zeros(max_seqs + 1, dtype=np.int64)      # and how many blocks lead there
 
     # ---- slots
-    def admit(self) -> int | None:
-        """A free slot (lowest first), its fixed-size state zeroed; None if every slot is taken."""
+    def admit(self, tokens=None) -> int | None:
+        """A free slot (lowest first), its fixed-size state zeroed; None if every slot is taken. With a prefix index
+        and the request's `tokens`, the slot starts on the pages of the longest known prefix: `computed[slot]` says
+        how many tokens those hold (whole pages, at least one token is left to compute)."""
         if not self._free_slots:
             return None
         slot = self._free_slots.pop()
         self.live.add(slot)
         self.computed[slot] = 0
+        self._chain_node[slot], self._chain_blocks[slot] = ROOT, 0
         for t in self.slot_states.values():
             t[slot].zero_()
+        if self.prefix is not None and tokens is not None:
+            g = self.groups[0]
+            pages, node = self.prefix.match(tokens)
+            for i, page in enumerate(pages):
+                g.pool.share(page, slot)
+                g.table[slot, i] = page
+            if pages:
+                g.count[slot] = len(pages)
+                g.dirty.add(slot)
+                self.computed[slot] = len(pages) * self.page_size
+                self._chain_node[slot], self._chain_blocks[slot] = node, len(pages)
         return slot
+
+    def publish(self, slot: int, tokens) -> None:
+        """Enters the pages that the request's computed tokens have filled into the prefix index. `tokens`: the
+        request's tokens as far as the host knows them (a token still on the device is left for the next call)."""
+        if self.prefix is None:
+            return
+        g, p = self.groups[0], self.page_size
+        known = min(len(tokens), int(self.computed[slot]))
+        i, node = int(self._chain_blocks[slot]), int(self._chain_node[slot])
+        while (i + 1) * p <= known:
+            page = int(g.table[slot, i])
+            node, new = self.prefix.extend(node, tokens[i * p:(i + 1) * p], page)
+            if new:
+                g.pool.register(page)
+            i += 1
+        self._chain_node[slot], self._chain_blocks[slot] = node, i
 
     def release(self, slot: int) -> None:
         if slot not in self.live:
@@ -188,8 +231,11 @@ class CacheManager:
 
     def could_fit(self, slot: int | None, tokens: int, releasing=()) -> bool:
         """Whether `reserve(slot, tokens)` would succeed once the slots in `releasing` were released."""
+        gone = set(releasing)
         for g in self.groups:
-            have = g.pool.available + sum(int(g.count[s] - g.first[s]) for s in releasing)
+            freed = {page for s in gone for page in g.table[s, int(g.first[s]):int(g.count[s])].tolist()
+                     if g.pool.holders(page) <= gone}             # (a page shared with a request that stays is not freed)
+            have = g.pool.available + len(freed)
             need = math.ceil(tokens / g.page_size) - (int(g.count[slot]) if slot is not None else 0)
             if need > have:
                 return False
@@ -204,9 +250,11 @@ class CacheManager:
 
     # ---- checks (tests call this after every operation)
     def check(self) -> None:
-        """No page lost, none held twice, none both free and held; tables agree with the pools."""
+        """No page lost, none both free and held; a page held by two requests is one the prefix index knows; tables
+        agree with the pools."""
         for g in self.groups:
-            held: dict[int, int] = {}
+            g.pool.check()
+            held: dict[int, set[int]] = {}
             for slot in range(self.max_seqs + 1):
                 first, count = int(g.first[slot]), int(g.count[slot])
                 row = g.table[slot]
@@ -214,11 +262,16 @@ class CacheManager:
                     assert count == 0 and (row == g.null_page).all(), f"slot {slot} is free but holds pages"
                     continue
                 assert (row[:first] == g.null_page).all() and (row[count:] == g.null_page).all()
-                for page in row[first:count].tolist():
+                pages = row[first:count].tolist()
+                assert len(set(pages)) == len(pages), f"slot {slot} holds a page twice"
+                for page in pages:
                     assert 0 <= page < g.pool.pages, f"slot {slot} holds page {page}"
-                    assert page not in held, f"page {page} held by slots {held[page]} and {slot}"
-                    assert g.pool.holder(page) == slot
-                    held[page] = slot
-            assert len(held) + g.pool.available == g.pool.pages, "a page is neither free nor held"
-            assert len(set(g.pool._free)) == len(g.pool._free), "a page is twice in the free list"
-            assert not set(g.pool._free) & set(held), "a page is both free and held"
+                    held.setdefault(page, set()).add(slot)
+            for page, slots in held.items():
+                assert g.pool.holders(page) == slots, f"page {page}: table says {slots}, pool says {g.pool.holders(page)}"
+                assert len(slots) == 1 or g.pool.registered(page), f"page {page} is shared by {slots} but not registered"
+            assert len(held) + g.pool.available == g.pool.pages, "a page is neither available nor held"
+            assert all(not g.pool.holders(p) for p in range(g.pool.pages) if p not in held), "a page is held by no table"
+        if self.prefix is not None:
+            pool = self.groups[0].pool
+            assert all(pool.registered(p) for p in self.prefix.pages()), "the index names a page that is not registered"

@@ -22,6 +22,7 @@ class EngineConfig:
     max_model_len: int = _setting(8192, "prompt + generated tokens per request; the cache always holds one")
     max_step_tokens: int = _setting(4096, "tokens one step computes at most")
     chunk_with_decode: int = _setting(0, "prefill tokens a step with decode rows may also carry (0: none)")
+    prefix_cache: bool = _setting(True, "share whole cache pages of equal prompt prefixes between requests")
     memory_fraction: float = _setting(0.9, "of the memory left after the weights, for the cache and activations")
     state_memory: int | None = _setting(None, "bytes for the cache pools; default: from memory_fraction")
     overlap: bool = _setting(True, "schedule step N while step N-1 runs (depth 1); off: depth 0")

@@ -27,7 +27,7 @@ class Built:
 
 def build(source, *, dtype: str, device, kernels=None, page_size: int, max_seqs: int, max_model_len: int,
           max_step_tokens: int, state_memory: int | None = None, pages: int | None = None,
-          memory_fraction: float = 0.9) -> Built:
+          memory_fraction: float = 0.9, prefix_cache: bool = False) -> Built:
     """`kernels=None` loads the compiled CUDA kernels and fails if they cannot be had. With neither `state_memory`
     nor `pages` the cache takes `memory_fraction` of the device memory left after the weights, less room for the
     largest step's activations."""
@@ -52,5 +52,5 @@ def build(source, *, dtype: str, device, kernels=None, page_size: int, max_seqs:
         activations = max_step_tokens * (widest * 3 + spec.hidden * 8) * 4 + min(max_step_tokens, max_seqs) * spec.vocab * 8
         state_memory = int(free * memory_fraction) - activations
     cache = CacheManager(model.entries, page_size, max_seqs, max_model_len, tdtype, device,
-                         state_memory=state_memory, pages=pages)
+                         state_memory=state_memory, pages=pages, prefix_cache=prefix_cache)
     return Built(config, model, cache, Runner(model, cache, ctx, max_step_tokens), ctx, weight_bytes)

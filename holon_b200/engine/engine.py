@@ -46,6 +46,7 @@ class TokenDelta:
     logprobs: Logprobs | None = None         # of these tokens, where the request asked for them
     prompt_logprobs: Logprobs | None = None  # of the prompt, with the sequence's first delta
     finish_reason: str | None = None         # "stop" | "length" | "abort" | None
+    cached_tokens: int | None = None         # on a sequence's first delta: prompt tokens the prefix cache served
 
 
 PROMPT_LOGPROB_ROWS = 256                     # rows of full-vocabulary logits held at once for prompt logprobs
@@ -75,7 +76,7 @@ class Engine:
         self.built = build(source, dtype=config.dtype, device=config.device, kernels=kernels,
                            page_size=config.page_size, max_seqs=config.max_seqs, max_model_len=config.max_model_len,
                            max_step_tokens=config.max_step_tokens, state_memory=config.state_memory,
-                           memory_fraction=config.memory_fraction)
+                           memory_fraction=config.memory_fraction, prefix_cache=config.prefix_cache)
         b = self.built
         self.device = b.ctx.device
         self.eos = frozenset(source.eos_token_ids())
@@ -83,6 +84,7 @@ class Engine:
         self.sampler = Sampler(b.ctx.kernels, self.device)
         self.requests: dict[str, list[Request]] = {}          # a request's sequences that have not finished
         self._prompt_lp: dict[Request, Logprobs] = {}         # sequences whose prompt logprobs are still being gathered
+        self._siblings: dict[Request, list[Request]] = {}     # sequences that wait for their request's first one's prompt
         self._base_seed = config.seed if config.seed is not None else secrets.randbits(63)
         self._added = 0
         self._graphs: dict[int, tuple] = {}
@@ -103,8 +105,8 @@ class Engine:
     # ------------------------------------------------------------------ requests
     def add(self, token_ids: Sequence[int], params: SamplingParams | None = None, rid: str | None = None) -> str:
         """Queues a request. Its `params.n` sequences stream as TokenDeltas with `index` 0 .. n-1, each sampling from
-        a seed of its own (core/holon/core/engine.py:331-376). Every sequence computes the prompt for itself: there
-        is no index of cached prefixes to adopt it from."""
+        a seed of its own (core/holon/core/engine.py:331-376). With the prefix cache the sequences after the first
+        wait until the first one's prompt is cached and start on its pages; without it each computes the prompt."""
         params = params or SamplingParams()
         params.validate()
         tokens = [int(t) for t in token_ids]
@@ -126,15 +128,23 @@ class Engine:
             live.append(Request(rid, list(tokens), len(tokens), params, sequence_seed(base, i), index=i))
             if i == 0 and params.prompt_logprobs is not None:      # once a request (core/holon/core/engine.py:360-366)
                 self._prompt_lp[live[-1]] = Logprobs([], [], [])
-            self.scheduler.add(live[-1])
+            if i == 0 or self.built.cache.prefix is None:
+                self.scheduler.add(live[-1])
+            else:                  # siblings wait until the first sequence's prompt is cached, then start on its pages
+                self._siblings.setdefault(live[0], []).append(live[-1])
         return rid
 
     def abort(self, rid: str) -> list[TokenDelta]:
         """Finishes every sequence of request `rid` that is still live, one delta each; none if the id is unknown
         (core/holon/core/engine.py:391-410)."""
         deltas = []
-        for request in self.requests.pop(rid, []):
-            self.scheduler.finish(request, "abort", release=request.pending == 0)   # (a row in flight gives the slot back)
+        live = self.requests.pop(rid, [])
+        held = {id(r) for r in live for r in self._siblings.pop(r, [])}          # never started: nothing to release
+        for request in live:
+            if id(request) in held:
+                request.status, request.finish_reason = Status.FINISHED, "abort"
+            else:
+                self.scheduler.finish(request, "abort", release=request.pending == 0)   # (a row in flight gives the slot back)
             self._prompt_lp.pop(request, None)
             deltas.append(TokenDelta(rid, [], request.index, finish_reason="abort"))
         return deltas
@@ -238,6 +248,7 @@ class Engine:
             done.record()
         runner.commit(entries)                             # the cache's books: these tokens are (being) computed
         for r in rows:
+            self.built.cache.publish(r.request.slot, r.request.tokens)   # whole pages of known tokens: shareable from now on
             self.scheduler.computed(r)
             r.request.pending += int(r.samples)
         self.steps += 1
@@ -385,8 +396,13 @@ class Engine:
                     request.slot = -1
                 continue
             request.tokens.append(int(token))
+            cached = None
             if request.status is not Status.RUNNING:
                 self.scheduler.finished_prefill(request)
+                if request.generated == 1:                 # its first token, not a return from preemption
+                    cached = request.cached
+                for sibling in self._siblings.pop(request, []):
+                    self.scheduler.add(sibling)
             reason = self._finish_reason(request, int(token))
             if reason:
                 self.scheduler.finish(request, reason, release=request.pending == 0)
@@ -394,7 +410,7 @@ class Engine:
             k = request.params.logprobs
             own = None if k is None or lps is None else Logprobs([lps[0][j]], [lps[1][j][:k]], [lps[2][j][:k]])
             deltas.append(TokenDelta(request.rid, [int(token)], request.index, own, self._prompt_lp.pop(request, None),
-                                     reason))
+                                     reason, cached))
         return deltas
 
     def _retire(self, request: Request) -> None:
@@ -436,11 +452,12 @@ class Engine:
         return getattr(self.built.ctx.kernels, "launches", 0) + self._graph_launches
 
     def stats(self) -> dict[str, int]:
-        s = self.scheduler
+        s, p = self.scheduler, self.built.cache.prefix
         return {"waiting": len(s.waiting), "running": len(s.running), "preemptions": s.preemptions,
                 "mixed_steps": s.mixed_steps, "steps": self.steps, "graph_steps": self.graph_steps,
                 "mixed_graph_steps": self.mixed_graph_steps,
-                "graphs": len(self._graphs), "free_tokens": self.built.cache.free_tokens()}
+                "graphs": len(self._graphs), "free_tokens": self.built.cache.free_tokens(),
+                "prefix_hit_tokens": p.hits if p is not None else 0, "prefix_query_tokens": p.queries if p is not None else 0}
 
     def close(self) -> None:
         for rid in list(self.requests):

@@ -37,6 +37,7 @@ class Request:
     params: SamplingParams
     seed: int = 0
     index: int = 0                          # which of its request's `n` sequences this is
+    cached: int | None = None               # tokens the prefix cache served when it was first admitted
     slot: int = -1
     computed: int = 0                       # tokens whose keys and values the cache holds (or is being given)
     pending: int = 0                        # tokens sampled by steps in flight, not yet read back
@@ -124,9 +125,13 @@ class Scheduler:
         lower-ranked admitted requests, lowest first, while releasing them can make room."""
         while True:
             if tokens is None:
-                slot = self.cache.admit()
+                # (prompt logprobs need every prompt position computed: such a request starts on no cached prefix)
+                wants_all = request.index == 0 and request.params.prompt_logprobs is not None
+                slot = self.cache.admit(None if wants_all else request.tokens)
                 if slot is not None:
-                    request.slot, request.computed = slot, 0
+                    request.slot, request.computed = slot, int(self.cache.computed[slot])
+                    if request.cached is None:
+                        request.cached = request.computed            # what the prefix cache served at its first admission
                     return True
             elif self.cache.reserve(request.slot, tokens):
                 return True

@@ -25,7 +25,7 @@ def test_pool_hands_out_low_pages_first_and_reuses_freed_ones():
     assert pool.take(4, holder=1) is None and pool.available == 3          # all or nothing
     pool.give([1], holder=0)
     assert pool.take(2, holder=1) == [1, 3]                                # the freed page is used again first
-    with pytest.raises(PageError, match="held by 1"):
+    with pytest.raises(PageError, match=r"held by \[1\]"):
         pool.give([1], holder=0)
     pool.give([0, 2], holder=0)
     with pytest.raises(PageError):
@@ -132,3 +132,122 @@ def test_random_traffic_keeps_the_books(seed):
         m.release(slot)
     m.check()
     assert all(g.pool.available == g.pool.pages for g in m.groups) and m.admit() is not None
+
+
+def one_group(**kw):
+    return manager([CacheEntry(i, i, PagedKV(2, 16), ()) for i in range(2)], prefix_cache=True, **kw)
+
+
+def test_equal_prefixes_share_whole_pages():
+    """A request starts on the pages that another one published for the same tokens: whole pages only, at least one
+    token left to compute; the shared pages have both as holders and are kept, not freed, when both have gone."""
+    m = one_group()
+    g = m.groups[0]
+    prompt = list(range(100, 111))                                    # 11 tokens: two whole pages and three tokens
+    a = m.admit(prompt)
+    assert int(m.computed[a]) == 0 and m.reserve(a, 11)
+    m.advance(a, 11)
+    m.publish(a, prompt)
+    m.check()
+    assert len(m.prefix) == 2 and all(g.pool.registered(p) for p in g.table[a, :2].tolist())
+    assert not g.pool.registered(int(g.table[a, 2]))                  # the page that is not full stays private
+    b = m.admit(prompt + [7, 8])
+    assert int(m.computed[b]) == 8 and g.table[b, :2].tolist() == g.table[a, :2].tolist()
+    assert g.pool.holders(int(g.table[a, 0])) == {a, b}
+    c = m.admit(prompt[:8])                                           # all of it is cached: one token must be computed still
+    assert int(m.computed[c]) == 4
+    d = m.admit([1, 2, 3, 4] + prompt)                                # the same tokens elsewhere are another prefix
+    assert int(m.computed[d]) == 0
+    m.check()
+    assert m.reserve(b, 13) and g.table[b, 2] != g.table[a, 2]        # b's own third page
+    m.advance(b, 13)
+    m.publish(b, prompt + [7, 8])                                     # its third block differs from nothing known: entered
+    assert len(m.prefix) == 3
+    free = g.pool.available
+    for slot in (a, b, c, d):
+        m.release(slot)
+        m.check()
+    assert g.pool.available == g.pool.pages and len(g.pool._kept) == 3 and free < g.pool.pages
+    e = m.admit(prompt + [7, 8, 9])                                   # the kept pages serve the next request
+    assert int(m.computed[e]) == 12 and len(g.pool._kept) == 0
+    m.release(e)
+    with pytest.raises(PageError):
+        g.pool.share(int(g.table[e, 0]), 3)                           # (the null page: nothing to share)
+
+
+def test_kept_pages_are_evicted_oldest_first_and_forgotten():
+    m = one_group(pages=16, max_model_len=32)
+    g = m.groups[0]
+    first, second = list(range(50, 59)), list(range(70, 83))          # 2 and 3 whole pages
+    for prompt in (first, second):
+        s = m.admit(prompt)
+        assert m.reserve(s, len(prompt))
+        m.advance(s, len(prompt))
+        m.publish(s, prompt)
+        m.release(s)
+    assert len(m.prefix) == 5 and len(g.pool._kept) == 5 and g.pool.available == 16
+    s = m.admit([9] * 30)
+    assert m.reserve(s, 30) and g.pool.available == 8                 # 8 pages: the 11 free ones sufficed
+    assert len(m.prefix) == 5
+    t = m.admit([8] * 32)
+    assert m.reserve(t, 16) and len(g.pool._kept) == 4                # 4 pages: 3 free, then the one kept longest
+    m.check()
+    assert int(m.computed[m.admit(first)]) == 4                       # its leaf went first; the parent still serves
+    assert len(m.prefix) == 3 + 1 and m.prefix.match(second)[0] != []
+    assert not m.reserve(t, 32) and m.reserve(t, 28) and len(g.pool._kept) == 0   # everything else is taken now
+    assert m.prefix.match(second)[0] == [] and len(m.prefix) == 1
+    m.check()
+
+
+def test_no_prefix_index_where_pages_cannot_be_shared():
+    window = [CacheEntry(0, 0, PagedKV(2, 16), ()), CacheEntry(1, 1, PagedKV(2, 16, window=8), ())]
+    state = [CacheEntry(0, 0, PagedKV(2, 16), (SlotState("sum", (4,), "float32"),))]
+    assert manager(window, prefix_cache=True).prefix is None
+    assert manager(state, prefix_cache=True).prefix is None
+    assert manager(prefix_cache=False).prefix is None and one_group().prefix is not None
+
+
+@pytest.mark.parametrize("seed", range(6))
+def test_random_traffic_with_shared_prefixes_keeps_the_books(seed):
+    """Requests drawn from a few prompt families (equal beginnings) come and go in random order in a pool too small
+    for all of them: after every operation the books are right, every position a request may read has a page, and a
+    request's shared pages are exactly those of its family's beginning."""
+    rng = random.Random(100 + seed)
+    m = one_group(pages=rng.choice([18, 24, 40]), max_seqs=5)
+    g = m.groups[0]
+    families = [[rng.randrange(1000) for _ in range(40)] for _ in range(3)]
+    live: dict[int, tuple[list[int], int]] = {}
+    for _ in range(500):
+        op = rng.random()
+        if op < 0.3 and len(live) < 5:
+            tokens = families[rng.randrange(3)][:rng.choice([4, 9, 16, 23, 40])] + [rng.randrange(1000) for _ in range(rng.randrange(6))]
+            slot = m.admit(tokens)
+            hit = int(m.computed[slot])
+            assert hit % 4 == 0 and hit < len(tokens)
+            live[slot] = (tokens, hit)
+        elif op < 0.8 and live:
+            slot = rng.choice(list(live))
+            tokens, have = live[slot]
+            want = min(len(tokens), have + rng.choice([1, 2, 5, 17]))
+            if want > have and m.reserve(slot, want):
+                m.advance(slot, want)
+                m.publish(slot, tokens)
+                live[slot] = (tokens, want)
+        elif live:
+            slot = rng.choice(list(live))
+            m.release(slot)
+            del live[slot]
+        m.check()
+        for slot, (tokens, have) in live.items():
+            assert all(p != g.null_page for p in g.table[slot, :-(-have // 4)])
+        for page in range(g.pool.pages):                           # a page with two holders holds the same tokens for both
+            holders = sorted(g.pool.holders(page))
+            if len(holders) > 1:
+                at = [g.table[s, :int(g.count[s])].tolist().index(page) for s in holders]
+                assert len(set(at)) == 1
+                blocks = {tuple(live[s][0][:(at[0] + 1) * 4]) for s in holders}
+                assert len(blocks) == 1, "two requests share a page but not the tokens up to it"
+    for slot in list(live):
+        m.release(slot)
+    m.check()
+    assert g.pool.available == g.pool.pages

@@ -140,3 +140,64 @@ def test_which_steps_are_kept_as_graphs(tmp_path):
     assert not fits([one(0), part(1, 2), part(2, 3), part(3, 3)])   # three portions
     engine.config.chunk_with_decode = 0
     assert not fits([one(0), part(1, 8)]) and fits([one(0)])
+
+
+def test_prefix_cache_gives_the_same_tokens_and_skips_the_shared_pages(tmp_path):
+    """Prompts with equal beginnings through an engine with the prefix cache and one without: the same tokens (32-bit),
+    fewer prompt tokens computed, `cached_tokens` on every request's first delta; the sequences of an `n` = 3
+    request start on the first one's pages; a pool too small for all requests (preemption, eviction) changes nothing."""
+    folder = make_folder(tmp_path, "b")
+    config, weights = plain.read_folder(folder)
+    stem = random_prompt(config["vocab_size"], 22, 3)
+    prompts = [stem + random_prompt(config["vocab_size"], n, 50 + n) for n in (1, 6, 13)] + [stem[:9], stem]
+    params = SamplingParams(temperature=0.7, max_tokens=6, seed=5)
+
+    def run(prompts=prompts, params=params, **kw):
+        args = dict(model=str(folder), device="cpu", dtype="float32", page_size=4, max_seqs=3, max_model_len=64,
+                    max_step_tokens=16, chunk_with_decode=8, state_memory=1 << 20)
+        args.update(kw)
+        engine = Engine(EngineConfig(**args), kernels=RefKernels())
+        out, cached = {}, {}
+        for round_ in range(2):                                      # the second round finds the first one's pages kept
+            rids = [engine.add(p, params) for p in prompts]
+            while engine.has_work():
+                for d in engine.step():
+                    out.setdefault((round_, d.rid), []).extend(d.token_ids)
+                    if d.cached_tokens is not None:
+                        assert (round_, d.rid) not in cached
+                        cached[(round_, d.rid)] = d.cached_tokens
+            engine.built.cache.check()
+            assert not engine.built.cache.live
+        return engine, [out[k] for k in sorted(out)], cached
+
+    plain_engine, want, cached = run(prefix_cache=False)
+    assert plain_engine.built.cache.prefix is None and set(cached.values()) == {0}
+    for p, got in zip(prompts, want[:len(prompts)]):
+        assert got == plain.generate(config, weights, p, 6, 0.7, 5)
+    engine, got, cached = run()
+    assert got == want
+    stats = engine.stats()
+    assert stats["prefix_hit_tokens"] > 0 and len(cached) == 2 * len(prompts)
+    assert all(c % 4 == 0 for c in cached.values()) and max(cached.values()) >= 20
+    second_round = [c for (r, _), c in cached.items() if r == 1]
+    assert all(c >= 8 for c in second_round)                         # everyone finds at least the stem's beginning
+    long = SamplingParams(temperature=0.7, max_tokens=30, seed=5)     # 16 pages of 4,608 bytes: one request of 64 tokens
+    small, got_small, _ = run(prompts[:3], long, state_memory=17 * 4608)
+    assert small.built.cache.pages == 16 and small.stats()["preemptions"] > 0 and small.stats()["prefix_hit_tokens"] > 0
+    assert got_small == run(prompts[:3], long, prefix_cache=False)[1]
+
+    engine = Engine(EngineConfig(model=str(folder), device="cpu", dtype="float32", page_size=4, max_seqs=3,
+                                 max_model_len=64, max_step_tokens=16, chunk_with_decode=8, state_memory=1 << 20),
+                    kernels=RefKernels())
+    rid = engine.add(stem, SamplingParams(temperature=0.7, max_tokens=4, seed=9, n=3))
+    first: dict[int, int] = {}
+    while engine.has_work():
+        for d in engine.step():
+            if d.cached_tokens is not None:
+                first[d.index] = d.cached_tokens
+    assert first == {0: 0, 1: 20, 2: 20} and rid not in engine.requests
+    engine.add(stem, SamplingParams(max_tokens=4, n=2), rid="gone")
+    engine.step()
+    assert sorted(d.index for d in engine.abort("gone")) == [0, 1]   # the second sequence had not started
+    engine.drain()
+    assert not engine.has_work() and not engine.built.cache.live and not engine._siblings
