@@ -138,6 +138,29 @@ def test_logprobs_beside_requests_that_ask_for_none(model, dtype):
     engine.close()
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_prefix_cache_on_the_device(model, dtype):
+    """Prompts with an equal beginning, twice over: requests start on pages that earlier ones filled (CUDA graphs and
+    prompt portions beside decode rows included) and generate what an engine without the prefix cache generates."""
+    folder, config, weights, _ = model
+    stem = random_prompt(config["vocab_size"], 70, 3)
+    prompts = [stem + random_prompt(config["vocab_size"], n, 90 + n) for n in (1, 9, 30)] + [stem[:33], stem]
+    params = SamplingParams(temperature=0.0, max_tokens=8)
+    engine = engine_of(folder, dtype)
+    assert engine.built.cache.prefix is not None
+    first, second = engine.generate(prompts, params), engine.generate(prompts, params)
+    stats = engine.stats()
+    assert stats["prefix_hit_tokens"] >= 5 * 64 and stats["mixed_graph_steps"] > 0
+    engine.built.cache.check()
+    without = engine_of(folder, dtype, prefix_cache=False).generate(prompts, params)
+    if dtype == "float32":
+        assert first == second == without
+    else:                                                          # (another batch shape may flip a near-tie in bfloat16)
+        for prompt, a, b in zip(prompts, first, second):
+            check_teacher_forced(config, weights, prompt, a, params, 0, exact=False)
+            check_teacher_forced(config, weights, prompt, b, params, 0, exact=False)
+
+
 def test_sampled_generation_is_seeded_and_survives_preemption(model):
     folder, config, weights, prompts = model
     params = [SamplingParams(temperature=0.8, max_tokens=10, seed=100 + i, top_k=(0, 20)[i % 2], top_p=(1.0, 0.9)[i // 3],
