@@ -139,7 +139,7 @@ class Engine:
         (core/holon/core/engine.py:391-410)."""
         deltas = []
         live = self.requests.pop(rid, [])
-        held = {id(r) for r in live for r in self._siblings.pop(r, [])}          # never started: nothing to release
+        held = {id(sibling) for first in live for sibling in self._siblings.pop(first, [])}   # never started: nothing to release
         for request in live:
             if id(request) in held:
                 request.status, request.finish_reason = Status.FINISHED, "abort"
