@@ -48,12 +48,32 @@ def cmd_generate(args) -> int:
     from .engine import Engine, SamplingParams
     params = SamplingParams(temperature=args.temperature, top_p=args.top_p, top_k=args.top_k, min_p=args.min_p,
                             max_tokens=args.max_tokens, ignore_eos=args.ignore_eos, seed=args.sampling_seed,
-                            stop_token_ids=tuple(args.stop_token_ids or ()))
+                            stop_token_ids=tuple(args.stop_token_ids or ()), n=args.n, logprobs=args.logprobs,
+                            prompt_logprobs=args.prompt_logprobs)
     with torch.inference_mode():
         engine = Engine(_engine_config(args))
         prompts = _prompts(args)
-        for prompt, tokens in zip(prompts, engine.generate(prompts, params)):
-            print(json.dumps({"prompt_ids": prompt, "token_ids": tokens}), flush=True)
+        if args.n == 1 and args.logprobs is None and args.prompt_logprobs is None:
+            for prompt, tokens in zip(prompts, engine.generate(prompts, params)):
+                print(json.dumps({"prompt_ids": prompt, "token_ids": tokens}), flush=True)
+        else:                                  # several sequences a prompt, or log-probabilities: the streaming calls
+            out = {(engine.add(p, params, rid=str(i)), j): {"prompt": i, "index": j, "token_ids": []}
+                   for i, p in enumerate(prompts) for j in range(args.n)}
+            while engine.has_work():
+                for d in engine.step():
+                    o = out[(d.rid, d.index)]
+                    o["token_ids"] += d.token_ids
+                    o["finish_reason"] = d.finish_reason
+                    if d.cached_tokens is not None:
+                        o["cached_tokens"] = d.cached_tokens
+                    for name, lp in (("logprobs", d.logprobs), ("prompt_logprobs", d.prompt_logprobs)):
+                        if lp is not None:
+                            have = o.setdefault(name, {"token": [], "top_ids": [], "top": []})
+                            have["token"] += lp.token
+                            have["top_ids"] += lp.top_ids
+                            have["top"] += lp.top
+            for key in sorted(out, key=lambda k: (int(k[0]), k[1])):
+                print(json.dumps(out[key]), flush=True)
         print(f"holon-b200: {json.dumps(engine.stats())}", file=sys.stderr)
         engine.close()
     return 0
@@ -97,6 +117,10 @@ def main(argv=None) -> int:
     g.add_argument("--sampling-seed", type=int, default=None, help="SamplingParams.seed of every prompt")
     g.add_argument("--ignore-eos", action="store_true")
     g.add_argument("--stop-token-ids", type=int, nargs="*")
+    g.add_argument("--n", type=int, default=1, help="sequences per prompt (SamplingParams.n); more than one prints one "
+                                                    "line a sequence with its index")
+    g.add_argument("--logprobs", type=int, default=None, help="top-k log-probabilities per generated token (0: the token's own)")
+    g.add_argument("--prompt-logprobs", type=int, default=None, help="the same per prompt token")
     g.set_defaults(run=cmd_generate)
     r = sub.add_parser("random-model", help="write a model folder (config.json, model.safetensors) with seeded random weights")
     r.add_argument("config", help="a config.json to take the sizes from")
