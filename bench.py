@@ -334,6 +334,43 @@ def sizes_run(args) -> dict:
     return out
 
 
+def shared_prompt_run(args) -> dict:
+    """16 requests whose prompts share their first 2,048 tokens (64 tokens of their own follow), 32 tokens generated
+    each, through `Engine.generate`, with the prefix cache and without it: seconds for all of them, second pass (the
+    first pass of the engine with the cache leaves the shared pages behind, as a system prompt does in serving)."""
+    import gc
+    import torch
+    from holon_b200.engine import Engine, EngineConfig, SamplingParams
+    from holon_b200.weights import RandomSource
+    cfg = dict(QWEN3_8B, num_hidden_layers=args.layers)
+    out = {"only": "shared_prompt", "layers": args.layers, "requests": 16, "shared_tokens": 2048, "own_tokens": 64,
+           "generated_each": 32}
+    params = SamplingParams(temperature=0.0, max_tokens=32, ignore_eos=True)
+    for cached in (True, False):
+        engine = Engine(EngineConfig(model="random weights, seed 2", device="cuda:0", dtype="bfloat16", page_size=64,
+                                     max_seqs=16, max_model_len=4096, max_step_tokens=4096, chunk_with_decode=1024,
+                                     seed=0, prefix_cache=cached, memory_fraction=0.5),
+                        source=RandomSource(cfg, seed=2, device="cuda:0"))
+        vocab, times = engine.built.model.spec.vocab, []
+        for rep in range(3):                                         # other tokens every pass: only passes of one engine
+            stem = prompts_of(vocab, 1, 2048, 500)[0]                # share the stem
+            prompts = [stem + tail for tail in prompts_of(vocab, 16, 64, 600 + rep)]
+            torch.cuda.synchronize()
+            t0 = time.perf_counter()
+            got = engine.generate(prompts, params)
+            times.append(time.perf_counter() - t0)
+            assert all(len(g) == 32 for g in got)
+        stats = engine.stats()
+        out["prefix_cache" if cached else "no_prefix_cache"] = {
+            "first_pass_s": round(times[0], 4), "later_pass_s": round(min(times[1:]), 4),
+            "prefix_hit_tokens": stats["prefix_hit_tokens"], "steps": stats["steps"]}
+        engine.close()
+        del engine
+        gc.collect()
+        torch.cuda.empty_cache()
+    return out
+
+
 def run_ours(args) -> dict:
     import torch
     from holon_b200.engine import Engine, EngineConfig
@@ -342,6 +379,8 @@ def run_ours(args) -> dict:
         return long_prompt_run(args)
     if args.only == "sizes":
         return sizes_run(args)
+    if args.only == "shared_prompt":
+        return shared_prompt_run(args)
     cfg = dict(QWEN3_8B, num_hidden_layers=args.layers)
     context, batch = args.context, args.batch
     engine = Engine(EngineConfig(model="random weights, seed 2", device="cuda:0", dtype="bfloat16", page_size=64,
@@ -423,10 +462,11 @@ def main() -> int:
                          "several passes should hold a few GB only (e.g. 0.03 with --layers 4 --batch 8)")
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--context", type=int, default=8192)
-    ap.add_argument("--only", default="all", choices=("all", "decode", "prefill", "long_prompt", "sizes"),
+    ap.add_argument("--only", default="all", choices=("all", "decode", "prefill", "long_prompt", "sizes", "shared_prompt"),
                     help="run one part only (for profiling a small case); the JSON line then lacks the other parts. "
                          "long_prompt: time to first token of a 30,000-token prompt behind three decoding requests; "
-                         "sizes: the workloads of the Qwen3-32B and Qwen3-0.6B configurations (--sizes)")
+                         "sizes: the workloads of the Qwen3-32B and Qwen3-0.6B configurations (--sizes); "
+                         "shared_prompt: 16 requests with a common 2,048-token beginning, with and without the prefix cache")
     ap.add_argument("--sizes", default="32b", choices=("32b", "0.6b"), help="with --only sizes: which configuration")
     args = ap.parse_args()
     if args.gpus != 1:

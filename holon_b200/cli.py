@@ -57,8 +57,8 @@ def cmd_generate(args) -> int:
             for prompt, tokens in zip(prompts, engine.generate(prompts, params)):
                 print(json.dumps({"prompt_ids": prompt, "token_ids": tokens}), flush=True)
         else:                                  # several sequences a prompt, or log-probabilities: the streaming calls
-            out = {(engine.add(p, params, rid=str(i)), j): {"prompt": i, "index": j, "token_ids": []}
-                   for i, p in enumerate(prompts) for j in range(args.n)}
+            rids = [engine.add(p, params, rid=str(i)) for i, p in enumerate(prompts)]
+            out = {(rid, j): {"prompt": i, "index": j, "token_ids": []} for i, rid in enumerate(rids) for j in range(args.n)}
             while engine.has_work():
                 for d in engine.step():
                     o = out[(d.rid, d.index)]

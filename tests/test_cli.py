@@ -66,3 +66,29 @@ def test_generate_on_the_command_line(tmp_path, capsys):
         assert len(o["logprobs"]["token"]) == 5 and all(len(t) == 2 for t in o["logprobs"]["top_ids"])
         assert ("prompt_logprobs" in o) == (o["index"] == 0)
     assert len(lines[0]["prompt_logprobs"]["token"]) == 2 and lines[0]["token_ids"] != lines[1]["token_ids"]
+
+
+def test_generate_streams_sequences_and_logprobs_with_the_plain_kernel_table(tmp_path, capsys, monkeypatch):
+    """The command's two ways of generating (whole prompts; `add` / `step` for --n and log-probabilities) on the CPU,
+    the engine built with the plain torch kernel table in place of the CUDA kernels."""
+    import holon_b200.engine as engine_module
+    from ref_kernels import RefKernels
+
+    class CpuEngine(engine_module.Engine):
+        def __init__(self, config):
+            config.device, config.state_memory = "cpu", 1 << 20
+            super().__init__(config, kernels=RefKernels())
+    monkeypatch.setattr(engine_module, "Engine", CpuEngine)
+    folder = make_folder(tmp_path, "b")
+    config, weights = plain.read_folder(folder)
+    common = ["generate", str(folder), "--prompt-ids", "5,17,3", "--prompt-ids", "9 8 7 6", "--max-tokens", "5", "--dtype",
+              "float32", "--max-model-len", "64", "--max-seqs", "4", "--max-step-tokens", "64", "--page-size", "16"]
+    assert cli.main(common) == 0
+    lines = [json.loads(line) for line in capsys.readouterr().out.splitlines()]
+    assert [o["token_ids"] for o in lines] == [plain.generate(config, weights, p, 5) for p in ([5, 17, 3], [9, 8, 7, 6])]
+    assert cli.main(common + ["--n", "2", "--temperature", "0.8", "--sampling-seed", "3", "--logprobs", "2",
+                              "--prompt-logprobs", "0"]) == 0
+    lines = [json.loads(line) for line in capsys.readouterr().out.splitlines()]
+    assert [(o["prompt"], o["index"]) for o in lines] == [(0, 0), (0, 1), (1, 0), (1, 1)]
+    assert lines[0]["token_ids"] == plain.generate(config, weights, [5, 17, 3], 5, 0.8, 3)
+    assert all(len(o["logprobs"]["token"]) == 5 and ("prompt_logprobs" in o) == (o["index"] == 0) for o in lines)
