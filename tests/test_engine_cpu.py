@@ -201,3 +201,49 @@ def test_prefix_cache_gives_the_same_tokens_and_skips_the_shared_pages(tmp_path)
     assert sorted(d.index for d in engine.abort("gone")) == [0, 1]   # the second sequence had not started
     engine.drain()
     assert not engine.has_work() and not engine.built.cache.live and not engine._siblings
+
+
+@pytest.mark.parametrize("seed", range(3))
+def test_random_arrivals_aborts_and_a_small_pool(tmp_path, seed):
+    """Requests from a few prompt families arrive at random steps, some are aborted in mid-flight, the pool holds one
+    request of the longest length and a little more: whatever is preempted, evicted or shared, every request that
+    finishes has the plain implementation's tokens, and in the end nothing is held."""
+    import random
+    rng = random.Random(seed)
+    folder = make_folder(tmp_path, "a")
+    config, weights = plain.read_folder(folder)
+    page_bytes = 2 * 2 * 2 * 4 * 16 * 4                              # layers x (k, v) x kv heads x page x head size x 4 bytes
+    engine = Engine(EngineConfig(model=str(folder), device="cpu", dtype="float32", page_size=4, max_seqs=4,
+                                 max_model_len=48, max_step_tokens=24, chunk_with_decode=rng.choice([0, 8]),
+                                 state_memory=(12 + rng.choice([1, 4, 9])) * page_bytes + page_bytes),
+                    kernels=RefKernels())
+    families = [random_prompt(config["vocab_size"], 30, 70 + i) for i in range(3)]
+    pending = []
+    for i in range(14):
+        prompt = families[rng.randrange(3)][:rng.choice([3, 8, 13, 21, 30])] + random_prompt(config["vocab_size"], rng.randrange(4), 200 + i)
+        pending.append((rng.randrange(25), f"q{i}", prompt, SamplingParams(temperature=0.6, seed=i, max_tokens=rng.choice([1, 5, 12]))))
+    got: dict[str, list[int]] = {}
+    done, aborted, asked, step = set(), set(), {}, 0
+    while pending or engine.has_work():
+        for item in [p for p in pending if p[0] <= step]:
+            pending.remove(item)
+            asked[engine.add(item[2], item[3], rid=item[1])] = item
+        if asked and rng.random() < 0.08:
+            victim = rng.choice(sorted(asked))
+            if victim not in done and victim not in aborted and engine.abort(victim):
+                aborted.add(victim)
+        for d in engine.step():
+            assert d.rid not in aborted
+            got.setdefault(d.rid, []).extend(d.token_ids)
+            if d.finish_reason:
+                done.add(d.rid)
+        engine.built.cache.check()
+        step += 1
+        assert step < 2000
+    assert done | aborted == set(asked) and not done & aborted
+    for rid in done:
+        _, _, prompt, sp = asked[rid]
+        assert got[rid] == plain.generate(config, weights, prompt, sp.max_tokens, 0.6, sp.seed), rid
+    assert not engine.built.cache.live and engine.built.cache.free_tokens() == engine.built.cache.pages * 4
+    stats = engine.stats()
+    assert stats["preemptions"] > 0 and stats["prefix_hit_tokens"] > 0      # (seeds chosen so that both happen)
