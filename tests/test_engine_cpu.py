@@ -247,3 +247,29 @@ def test_random_arrivals_aborts_and_a_small_pool(tmp_path, seed):
     assert not engine.built.cache.live and engine.built.cache.free_tokens() == engine.built.cache.pages * 4
     stats = engine.stats()
     assert stats["preemptions"] > 0 and stats["prefix_hit_tokens"] > 0      # (seeds chosen so that both happen)
+
+
+def test_layout_of_a_step_that_runs_as_a_graph(tmp_path):
+    """`Runner.context(entries, pad_rows=...)`: one-token rows first in their order, then the padding rows (padding
+    slot, position 0, kv_len 1), then the prompt portions; logits at the last token of every row."""
+    b = built(make_folder(tmp_path, "a"), max_seqs=6)
+    slots = [b.cache.admit() for _ in range(4)]
+    for slot, n in zip(slots, (9, 1, 30, 12)):
+        assert b.cache.reserve(slot, n)
+    b.cache.advance(slots[0], 8)                                     # slot 0 holds 8 tokens and decodes
+    b.cache.advance(slots[2], 20)                                    # slot 2 is in mid-prompt
+    entries = [StepEntry(slots[2], list(range(5)), 20, ()), StepEntry(slots[0], [7], 8, (0,)),
+               StepEntry(slots[3], list(range(3)), 0, (2,)), StepEntry(slots[1], [9], 0, (0,))]
+    step = b.runner.context(entries, pad_rows=2, extra={"sample_slot": torch.arange(6, dtype=torch.int32).numpy()})
+    rows = step.rows
+    assert (rows.n_rows, rows.n_tokens, rows.n_decode, rows.max_q) == (6, 12, 4, 5)
+    assert rows.row_slot.tolist() == [slots[0], slots[1], b.cache.padding_slot, b.cache.padding_slot, slots[2], slots[3]]
+    assert rows.query_start.tolist() == [0, 1, 2, 3, 4, 9, 12] and rows.kv_len.tolist() == [9, 1, 1, 1, 25, 3]
+    assert step.token_ids.tolist() == [7, 9, 0, 0, 0, 1, 2, 3, 4, 0, 1, 2]
+    assert step.positions.tolist() == [8, 0, 0, 0, 20, 21, 22, 23, 24, 0, 1, 2]
+    assert step.logits_index.tolist() == [0, 1, 2, 3, 8, 11]
+    assert step.offset_of == {1: 0, 3: 1, 0: 4, 2: 9}
+    null = b.cache.groups[0].null_page * 4
+    write = step.groups[0].write_index.tolist()
+    assert write[2] // 4 * 4 == null and write[3] // 4 * 4 == null   # the padding rows write into the null page
+    assert write[0] == int(b.cache.groups[0].table[slots[0], 2]) * 4 + 0
