@@ -36,16 +36,13 @@ class CacheGroup:
         self.max_pages = math.ceil(max_model_len / page_size)
         self.pool = PagePool(pages)
         self.null_page = pages
-        self._staging = torch.full((max_seqs + 1, self.max_pages), self.null_page, dtype=torch.int32)
-        if torch.device(device).type == "cuda":
-            self._staging = self._staging.pin_memory()
-        self.table = self._staging.numpy()                         # the host block table, in page-locked memory
+        self.table = np.full((max_seqs + 1, self.max_pages), self.null_page, dtype=np.int32)   # the host block table
         self.first = np.zeros(max_seqs + 1, dtype=np.int64)       # first logical page still held
         self.count = np.zeros(max_seqs + 1, dtype=np.int64)       # logical pages reserved so far
         self.dirty: set[int] = set()
         self.kv = torch.zeros((len(entries), pages + 1, 2, decl.kv_heads, page_size, decl.head_dim), dtype=dtype,
                               device=device)
-        self.table_device = self._staging.to(device)
+        self.table_device = torch.from_numpy(self.table).to(device)
 
     @staticmethod
     def page_bytes(decl: PagedKV, entries: int, page_size: int, itemsize: int) -> int:
@@ -98,11 +95,14 @@ class CacheGroup:
         self.first[slot] = self.count[slot] = 0
         self.dirty.add(slot)
 
-    def sync(self) -> None:
-        """Copies the block-table rows that changed since the last call to the device."""
-        for slot in sorted(self.dirty):
-            self.table_device[slot].copy_(self._staging[slot], non_blocking=True)
+    def take_dirty(self) -> tuple[np.ndarray, np.ndarray]:
+        """(slots [n], rows [n, max_pages]) of the block-table rows that changed since the last call, as copies: the
+        host table may change again at once (a window lets go of pages, a request ends) while the step that these
+        rows were taken for is still on its way to the device. The caller uploads them with the step's other arrays
+        and scatters them into `table_device` ahead of the step's kernels."""
+        slots = np.array(sorted(self.dirty), dtype=np.int32)
         self.dirty.clear()
+        return slots, self.table[slots]
 
     def write_index(self, slots: np.ndarray, positions: np.ndarray) -> np.ndarray:
         """page · page_size + offset for each (slot, position) of a step's tokens."""
@@ -144,8 +144,10 @@ class CacheManager:
         self.computed = np.zeros(max_seqs + 1, dtype=np.int64)
         self.padding_slot = max_seqs
         self.slot_states: dict[tuple[int, str], torch.Tensor] = {}
-        for e in entries:
+        self.chunk = 1                       # prompts are cut at multiples of this: the least common multiple of the
+        for e in entries:                    # chunks that the fixed-size states ask for
             for s in e.slot_states:
+                self.chunk = math.lcm(self.chunk, max(1, int(getattr(s, "chunk", 1))))
                 self.slot_states[(e.entry, s.name)] = torch.zeros((max_seqs + 1, *s.shape),
                                                                   dtype=getattr(torch, s.dtype), device=device)
         self.prefix: PrefixIndex | None = None
@@ -243,10 +245,6 @@ class CacheManager:
 
     def free_tokens(self) -> int:
         return min((g.pool.available * g.page_size for g in self.groups), default=self.max_model_len)
-
-    def sync(self) -> None:
-        for g in self.groups:
-            g.sync()
 
     # ---- checks (tests call this after every operation)
     def check(self) -> None:

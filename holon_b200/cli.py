@@ -52,6 +52,7 @@ def cmd_generate(args) -> int:
                             prompt_logprobs=args.prompt_logprobs)
     with torch.inference_mode():
         engine = Engine(_engine_config(args))
+        print(f"holon-b200: {engine.memory_report()}", file=sys.stderr, flush=True)
         prompts = _prompts(args)
         if args.n == 1 and args.logprobs is None and args.prompt_logprobs is None:
             for prompt, tokens in zip(prompts, engine.generate(prompts, params)):

@@ -1,6 +1,6 @@
 """Engine settings. Field names and meanings follow the reference's `EngineConfig`
 (core/holon/core/engine.py:61-100), one command-line flag per field; fields of features this engine does not have
-(prefix cache, drafts, kernel pins, tiers) are absent."""
+(drafts, kernel pins and preferences, memory tiers, plugin options) are absent."""
 from __future__ import annotations
 
 import dataclasses

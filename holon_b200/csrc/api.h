@@ -116,7 +116,6 @@ int hb_gemm_bf16_skinny_linked(void* out, int out_f32, const void* x, const void
                                float* ss_out, const float* ss_in, int parts_in, float eps_in, int dim_in,
                                hb_stream stream);
 
-// bfloat16 product on tcgen05 tensor cores with TMA loads and the accumulator in tensor memory (128 x 256 tiles).
 // The attention's first product for up to 16 tokens with what follows it in one kernel: x [m, k] times
 // w [(heads + 2 kv_heads) * head_dim, k], then per head the q/k RMSNorm (weights bfloat16 or, with weight_f32, float32;
 // null: no norm), the rotation of the whole head by the token's position (table [max_positions, head_dim], cosines
@@ -132,6 +131,7 @@ int hb_qkv_rope_skinny_linked(void* q_out, const void* x, const void* w, int m, 
                               int page_size, int heads, int kv_heads, int head_dim, const float* ss_in, int parts_in,
                               float eps_in, int dim_in, hb_stream stream);
 
+// bfloat16 product on tcgen05 tensor cores with TMA loads and the accumulator in tensor memory (128 x 256 tiles).
 // Same arguments and modes as hb_gemm_bf16_skinny, any m. hb_gemm_tcgen05_status synchronises the device and
 // returns (and clears) a status word that is non-zero if a bounded wait inside the kernel ever gave up.
 int hb_gemm_bf16_tcgen05(void* out, int out_f32, const void* x, const void* w, int m, int n, int k, int mode, int inter,
@@ -145,11 +145,23 @@ int hb_gemm_bf16_tcgen05_pair(void* out, int out_f32, const void* x, const void*
 int hb_gemm_tcgen05_pair_status(unsigned int* status);
 int hb_gemm_tcgen05_pair_width(int bn);             // tests: fix the tile width (0: chosen per launch)
 
+// The waits inside the tcgen05 kernels are bounded; one that gives up records (place << 28) | (block + 1) in its
+// kernel file's status word (the *_status functions above read those, synchronising) and in one word of page-locked
+// host memory that hb_status_word hands out: the host reads it without a copy or a synchronisation, after a step's
+// completion event, and may write 0 to it. hb_status_selftest enqueues a wait of `polls` polls on a barrier nobody
+// arrives at (place 15): it runs out within microseconds and lets tests see what the host does then.
+int hb_status_word(unsigned int** host);
+int hb_status_selftest(int polls, hb_stream stream);
+
 // The token each request sampled last, kept on the device by slot. feed: for every row r with from_last[r] != 0,
 // token_ids[query_start[r]] = last_tokens[row_slot[r]]. store: last_tokens[slots[i]] = tokens[i] for i < n.
 int hb_feed_tokens(int32_t* token_ids, const int32_t* last_tokens, const int32_t* row_slot, const int32_t* query_start,
                    const int32_t* from_last, int rows, hb_stream stream);
 int hb_store_tokens(int32_t* last_tokens, const int32_t* slots, const int32_t* tokens, int n, hb_stream stream);
+
+// Block-table rows that changed on the host, uploaded packed: table[slots[i], :] = rows[i, :] for i < n.
+int hb_scatter_rows(int32_t* table, const int32_t* slots, const int32_t* rows, int n, int width, int table_rows,
+                    hb_stream stream);
 
 // One token per logits row: arg max where temperature is 0, else a draw from softmax(logits / temperature) after the
 // filters (when `filtered`), by inverse CDF in vocabulary order with the uniform of (seed, position).

@@ -347,6 +347,7 @@ static int encode_2d(CUtensorMap* map, const void* ptr, uint64_t cols, uint64_t 
     return 0;
 }
 
+HB_DEFINE_STATUS_MIRROR(hb_attention_tcgen05_status_mirror)
 extern "C" int hb_attention_tcgen05_status(unsigned int* status) {
     HB_CUDA(cudaDeviceSynchronize());
     HB_CUDA(cudaMemcpyFromSymbol(status, g_tc_status, sizeof(unsigned int)));

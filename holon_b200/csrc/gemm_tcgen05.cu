@@ -197,6 +197,7 @@ static int encode_map(CUtensorMap* map, const void* ptr, int rows, int k, int bo
 
 // Reads and clears the status word: 0, or (place << 28) | (block + 1) of the first wait that gave up
 // (place 1 producer, 2 MMA, 3 epilogue). Synchronises the device.
+HB_DEFINE_STATUS_MIRROR(hb_gemm_tcgen05_status_mirror)
 extern "C" int hb_gemm_tcgen05_status(unsigned int* status) {
     HB_CUDA(cudaDeviceSynchronize());
     HB_CUDA(cudaMemcpyFromSymbol(status, g_tc_status, sizeof(unsigned int)));

@@ -247,6 +247,7 @@ static int encode_pair_map(CUtensorMap* map, const void* ptr, int rows, int k, i
 
 // Reads and clears this kernel's status word: 0, or (place << 28) | (block + 1) of the first wait that gave up
 // (place 1 producer, 2 and 4 MMA, 3 epilogue). Synchronises the device.
+HB_DEFINE_STATUS_MIRROR(hb_gemm_tcgen05_pair_status_mirror)
 extern "C" int hb_gemm_tcgen05_pair_status(unsigned int* status) {
     HB_CUDA(cudaDeviceSynchronize());
     HB_CUDA(cudaMemcpyFromSymbol(status, g_tc_status, sizeof(unsigned int)));

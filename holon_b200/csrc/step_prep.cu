@@ -16,6 +16,22 @@ __global__ void store_tokens_kernel(int32_t* __restrict__ last_tokens, const int
     if (i < n) last_tokens[slots[i]] = tokens[i];
 }
 
+__global__ void scatter_rows_kernel(int32_t* __restrict__ table, const int32_t* __restrict__ slots,
+                                    const int32_t* __restrict__ rows, int width, int table_rows) {
+    const int slot = slots[blockIdx.x];
+    if (slot < 0 || slot >= table_rows) return;
+    for (int i = threadIdx.x; i < width; i += blockDim.x) table[(size_t)slot * width + i] = rows[(size_t)blockIdx.x * width + i];
+}
+
+// table[slots[i], :] = rows[i, :] for i < n (rows of `width` int32; slots outside [0, table_rows) are skipped).
+extern "C" int hb_scatter_rows(int32_t* table, const int32_t* slots, const int32_t* rows, int n, int width, int table_rows,
+                               hb_stream stream) {
+    if (n == 0 || width == 0) return 0;
+    scatter_rows_kernel<<<n, 128, 0, (cudaStream_t)stream>>>(table, slots, rows, width, table_rows);
+    HB_LAUNCH_CHECK("scatter_rows");
+    return 0;
+}
+
 // For every row r with from_last[r] != 0: token_ids[query_start[r]] = last_tokens[row_slot[r]].
 extern "C" int hb_feed_tokens(int32_t* token_ids, const int32_t* last_tokens, const int32_t* row_slot,
                               const int32_t* query_start, const int32_t* from_last, int rows, hb_stream stream) {

@@ -8,8 +8,11 @@
 #define HB_SPIN_LIMIT (1u << 22)
 
 // One status word per translation unit that includes this header: 0 fine; else (place << 28) | (block + 1) of the
-// first wait that gave up.
+// first wait that gave up. `g_tc_mirror` (null: none) points at a word of page-locked host memory that the device can
+// write: a wait that gives up stores its code there too, so the host learns of it by reading its own memory, without
+// a copy, a launch or a synchronisation of its own (the step's completion event orders the store before the read).
 static __device__ unsigned int g_tc_status = 0;
+static __device__ unsigned int* g_tc_mirror = nullptr;
 
 __device__ __forceinline__ uint32_t smem_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
@@ -18,17 +21,37 @@ __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
 __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(bar), "r"(bytes) : "memory");
 }
-// Waits until the phase of the given parity has completed; false if it gave up.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, unsigned place) {
-    for (unsigned spin = 0; spin < HB_SPIN_LIMIT; ++spin) {
+// Records that a wait gave up: in the status word (the first one stays) and in the host's mirror of it.
+__device__ __forceinline__ void tc_give_up(unsigned place) {
+    const unsigned code = (place << 28) | ((blockIdx.y * gridDim.x + blockIdx.x + 1) & 0x0FFFFFFFu);
+    atomicCAS(&g_tc_status, 0u, code);
+    unsigned int* mirror = g_tc_mirror;
+    if (mirror != nullptr) {
+        *(volatile unsigned int*)mirror = code;
+        __threadfence_system();
+    }
+}
+// Waits until the phase of the given parity has completed; false if it gave up after `limit` polls.
+__device__ __forceinline__ bool mbar_wait_limit(uint32_t bar, uint32_t parity, unsigned place, unsigned limit) {
+    for (unsigned spin = 0; spin < limit; ++spin) {
         uint32_t done;
         asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.b32 %0, 1, 0, p;\n\t}\n"
                      : "=r"(done) : "r"(bar), "r"(parity) : "memory");
         if (done) return true;
     }
-    atomicCAS(&g_tc_status, 0u, (place << 28) | (blockIdx.y * gridDim.x + blockIdx.x + 1));
+    tc_give_up(place);
     return false;
 }
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, unsigned place) {
+    return mbar_wait_limit(bar, parity, place, HB_SPIN_LIMIT);
+}
+// Host side, once per translation unit: an exported `name`(word) that points this unit's mirror at `word`, a device-
+// visible address of page-locked host memory (null: no mirror).
+#define HB_DEFINE_STATUS_MIRROR(name) \
+    extern "C" int name(unsigned int* word) { \
+        HB_CUDA(cudaMemcpyToSymbol(g_tc_mirror, &word, sizeof(word))); \
+        return 0; \
+    }
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y) {
     asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];\n"
                  ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y) : "memory");

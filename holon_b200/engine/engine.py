@@ -76,7 +76,8 @@ class Engine:
         self.built = build(source, dtype=config.dtype, device=config.device, kernels=kernels,
                            page_size=config.page_size, max_seqs=config.max_seqs, max_model_len=config.max_model_len,
                            max_step_tokens=config.max_step_tokens, state_memory=config.state_memory,
-                           memory_fraction=config.memory_fraction, prefix_cache=config.prefix_cache)
+                           memory_fraction=config.memory_fraction, prefix_cache=config.prefix_cache,
+                           chunk_with_decode=config.chunk_with_decode, cuda_graphs=config.cuda_graphs)
         b = self.built
         self.device = b.ctx.device
         self.eos = frozenset(source.eos_token_ids())
@@ -87,7 +88,8 @@ class Engine:
         self._siblings: dict[Request, list[Request]] = {}     # sequences that wait for their request's first one's prompt
         self._base_seed = config.seed if config.seed is not None else secrets.randbits(63)
         self._added = 0
-        self._graphs: dict[int, tuple] = {}
+        self._graphs: dict[tuple, tuple] = {}
+        self._captured_ahead: set[tuple] = set()               # keys of graphs captured with rows fed from the device
         self._graph_pool = None
         self._use_graphs = config.cuda_graphs and self.device.type == "cuda"
         self._buckets = tuple(x for x in GRAPH_BUCKETS if x < config.max_seqs) + (config.max_seqs,)   # the fullest batch too
@@ -96,6 +98,7 @@ class Engine:
             self._host_tokens = [t.pin_memory() for t in self._host_tokens]
         self._flip = 0
         self._inflight: _Inflight | None = None
+        self._stopped: str | None = None                       # why the engine stopped: a kernel's bounded wait gave up
         # the token each request sampled last, by slot, on the device: decode rows of a step that is enqueued before
         # the step ahead of it has been read back take their input from here
         self.last_tokens = torch.zeros(config.max_seqs + 1, dtype=torch.int32, device=self.device)
@@ -107,6 +110,8 @@ class Engine:
         """Queues a request. Its `params.n` sequences stream as TokenDeltas with `index` 0 .. n-1, each sampling from
         a seed of its own (core/holon/core/engine.py:331-376). With the prefix cache the sequences after the first
         wait until the first one's prompt is cached and start on its pages; without it each computes the prompt."""
+        if self._stopped:
+            raise RuntimeError(f"the engine stopped: {self._stopped}")
         params = params or SamplingParams()
         params.validate()
         tokens = [int(t) for t in token_ids]
@@ -157,6 +162,8 @@ class Engine:
         """Runs one step and returns what became known. With `overlap`, the step launched here stays in flight and
         the deltas are those of the step before it: the host schedules and enqueues step N + 1 while step N runs,
         decode rows reading their input token from the device (core/holon/core/engine.py:492-524)."""
+        if self._stopped:
+            raise RuntimeError(f"the engine stopped: {self._stopped}")
         deltas: list[TokenDelta] = []
         prev, self._inflight = self._inflight, None
         if prev is not None and not self._may_run_ahead(prev):
@@ -342,29 +349,28 @@ class Engine:
             padded[name] = full
         step = runner.context(entries, pad_rows=pad, extra=padded)
         kernels = self.built.ctx.kernels
-        lens = step.rows.host_kv_len
-        mode = kernels.decode_mode(lens[:len(single)] if lens is not None else None) \
-            if hasattr(kernels, "decode_mode") else None
-        prompt_tokens = step.rows.n_tokens - bucket
-        key = (bucket, len(portions), prompt_tokens, mode)         # ... and a graph per way of sharing out the keys
+        # what the mixers' kernels pin for a captured step is part of the key: a graph per plan
+        key = (bucket, len(portions), step.rows.n_tokens - bucket, runner.model.capture_plan(step, self.config.max_model_len))
         if key not in self._graphs:
-            step.rows.max_kv = self.config.max_model_len          # the captured launch must serve any length
-            for size in (64, 128, 256):                            # and any cut of the prompt tokens into the portions:
-                step.rows.plan[size] = prompt_tokens // size + len(portions)   # query tiles beyond a step's own exit at once
+            # The first step of a shape runs eagerly (which also warms up what the capture must not do for the first
+            # time) and is then recorded for the steps to come. Its results are the eager run's: replaying the new
+            # graph on top would run the step twice, and the second run would feed on what the first one stored.
             out = torch.empty(m, dtype=torch.int32, device=self.device)
-            kernels.decode_pinned = mode
-            try:
-                self._forward(step, False, m, out)                 # warm-up, not captured
-                torch.cuda.current_stream(self.device).synchronize()
-                graph = torch.cuda.CUDAGraph()
-                before = kernels.launches
-                with torch.cuda.graph(graph, pool=self._graph_pool):
-                    self._forward(step, False, m, out)
+            self._forward(step, False, m, out)
+            torch.cuda.current_stream(self.device).synchronize()
+            graph = torch.cuda.CUDAGraph()
+            before = getattr(kernels, "launches", 0)
+            with torch.cuda.graph(graph, pool=self._graph_pool):
+                self._forward(step, False, m, out)
+            if hasattr(kernels, "launches"):
                 captured, kernels.launches = kernels.launches - before, before   # recorded, not run
-            finally:
-                kernels.decode_pinned = None
+            else:
+                captured = 0
             self._graph_pool = self._graph_pool or graph.pool()
             self._graphs[key] = (graph, out, captured)
+            if any(e.from_last for e in entries):      # captured while the step before was still in flight
+                self._captured_ahead.add(key)
+            return out, [row_of[i] for i in wanted]
         graph, out, captured = self._graphs[key]
         graph.replay()
         self.graph_steps += 1
@@ -376,6 +382,7 @@ class Engine:
         """Waits for a launched step and books its tokens: appended, checked for a finish, reported."""
         if inflight.done is not None:
             inflight.done.synchronize()
+        self._check_kernels()
         tokens = inflight.host.tolist() if inflight.host is not None else []
         if inflight.pick is not None:
             tokens = [tokens[i] for i in inflight.pick]
@@ -412,6 +419,19 @@ class Engine:
             deltas.append(TokenDelta(request.rid, [int(token)], request.index, own, self._prompt_lp.pop(request, None),
                                      reason, cached))
         return deltas
+
+    def _check_kernels(self) -> None:
+        """Every wait inside the kernels is bounded; one that gave up left a code in a word of host memory, and what
+        its kernel wrote is not to be trusted. Read here, after a step's completion event and before any of its
+        tokens is handed out: the engine stops with the reason and refuses further work, as the reference stops when
+        a step's commit fails (core/holon/core/engine.py:498-499, 607-612)."""
+        status = getattr(self.built.ctx.kernels, "status", None)
+        code = status() if status is not None else 0
+        if code:
+            self._stopped = (f"a bounded wait inside a kernel gave up (status {code:#010x}: place {code >> 28}, "
+                             f"block {(code & 0x0FFFFFFF) - 1}); the step's results were dropped")
+            self._inflight = None
+            raise RuntimeError(f"the engine stopped: {self._stopped}")
 
     def _retire(self, request: Request) -> None:
         live = self.requests.get(request.rid)
@@ -459,8 +479,15 @@ class Engine:
                 "graphs": len(self._graphs), "free_tokens": self.built.cache.free_tokens(),
                 "prefix_hit_tokens": p.hits if p is not None else 0, "prefix_query_tokens": p.queries if p is not None else 0}
 
+    def memory_report(self) -> str:
+        """One line: what the weights, the largest step's activations, the graphs' pool and the cache pools take of
+        the device's memory, and what is left (measured when the engine was built)."""
+        return self.built.memory.line()
+
     def close(self) -> None:
         for rid in list(self.requests):
             self.abort(rid)
-        self.drain()
+        if not self._stopped:
+            self.drain()
+        self._inflight = None
         self._graphs.clear()

@@ -23,7 +23,8 @@ class Runner:
         self.model, self.cache, self.ctx = model, cache, build_ctx
         self.device, self.max_step_tokens = build_ctx.device, max_step_tokens
         s, t, g = cache.max_seqs + 1, max_step_tokens, len(cache.groups)
-        self.uploader = Uploader(t * (3 + g) + 16 * s + 64, self.device)
+        tables = sum(s * (group.max_pages + 1) + 8 for group in cache.groups)     # every block-table row changed at once
+        self.uploader = Uploader(t * (3 + g) + 16 * s + 64 + tables, self.device)
         self.vocab = model.spec.vocab
 
     # ------------------------------------------------------------------ host half
@@ -105,8 +106,16 @@ class Runner:
             up.put(f"write_index.{g.index}", g.write_index(token_slot, positions).astype(np.int32))
         for name, array in (extra or {}).items():
             up.put(name, array)
-        c.sync()
+        changed = []
+        for g in c.groups:                            # block-table rows that changed, behind everything a graph reads
+            slots, table_rows = g.take_dirty()        # (copies: the host table may change before the upload is read)
+            if len(slots):
+                up.put(f"table_slots.{g.index}", slots)
+                up.put(f"table_rows.{g.index}", table_rows.reshape(-1))
+                changed.append(g)
         dev = up.end()
+        for g in changed:
+            self.ctx.kernels.scatter_rows(g.table_device, dev[f"table_slots.{g.index}"], dev[f"table_rows.{g.index}"])
         rows_ = Rows(dev["row_slot"], dev["query_start"], dev["kv_len"], b, t, n_decode + pad_rows,
                      max(counts), int(kv_len.max()), query_start, kv_len)
         groups = [GroupStep(g.table_device, dev[f"write_index.{g.index}"], g.page_size) for g in c.groups]

@@ -96,6 +96,11 @@ class Scheduler:
             if request.slot < 0 and not self._fit(request, None):
                 break
             n = min(len(request.tokens) - request.computed, budget)
+            chunk = getattr(self.cache, "chunk", 1)
+            if chunk > 1 and request.computed + n < len(request.tokens):
+                n -= (request.computed + n) % chunk          # a portion that does not end the prompt ends on a multiple
+                if n <= 0:                                   # (the budget left is too small for one chunk: next step)
+                    break
             if not self._fit(request, request.computed + n):
                 break
             rows.append(Row(request, n, request.computed + n == len(request.tokens)))

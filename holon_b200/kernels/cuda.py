@@ -69,10 +69,15 @@ class CudaKernels:
         self.decode_cluster = os.environ.get("HOLON_B200_DECODE_CLUSTER", "1") != "0"   # splits of up to 16 merge in the kernel
         self.fused_qkv = os.environ.get("HOLON_B200_FUSED_QKV", "1") != "0"   # decode steps: norm, rotation, cache write in the product
         self.fused_norm = os.environ.get("HOLON_B200_FUSED_NORM", "1") != "0"   # decode steps: residual sum and next norm in the product before
-        self.decode_pinned = None             # set around a CUDA-graph capture: the captured launches keep this mode
         self.sms = torch.cuda.get_device_properties(self.device).multi_processor_count
         self.decode_ctas = None               # tests: a fixed number of CTAs for the balanced kernel
         self.prefill_tile = None              # tests, microbench: 128 or 256 queries a CTA of the tcgen05 prefill kernel
+        # One word of page-locked host memory that a kernel's bounded wait writes when it gives up (csrc/status.cu)
+        word = ctypes.POINTER(ctypes.c_uint)()
+        with torch.cuda.device(self.device):
+            if self.lib.hb_status_word(ctypes.byref(word)):
+                raise KernelError(f"hb_status_word: {self.lib.hb_last_error().decode()}")
+        self._status_word = word
 
     # ------------------------------------------------------------------ plumbing
     def _call(self, name: str, *args) -> None:
@@ -206,7 +211,7 @@ class CudaKernels:
         sizes = (heads, kv_heads, head_dim, kv.shape[0], kv.shape[3], ctypes.c_float(scale), int(window))
         if rows.n_decode:
             splits = self.decode_splits(rows.n_decode, heads, kv_heads, rows.max_kv)
-            mode = self.decode_pinned or self._decode_mode_of(rows)
+            mode = self._decode_mode_of(rows)
             if splits > 1 and mode == "balanced" and rows.n_decode <= self.BALANCED_ROWS:
                 pairs = rows.n_decode * kv_heads * (-(-(heads // kv_heads) // 16))
                 slots = self.sms * (1 if head_dim > 128 else 3)       # CTAs of this kernel that one wave holds
@@ -238,6 +243,30 @@ class CudaKernels:
             else:
                 self._call("hb_attention_prefill_bf16", self._p(out), self._p(q), self._p(kv), *common, rows.n_decode,
                            rows.n_rows, self._query_tiles(rows, 64), *sizes)
+
+    KV_BUCKET_MIN = 512                       # the smallest number of keys a captured decode launch is planned for
+
+    def attention_capture_plan(self, rows, max_model_len: int):
+        """For a step that runs as a CUDA graph: what of the attention's launch plan a captured launch keeps, as a
+        hashable key, pinned on `rows` so that every layer's launch is planned with it. The keys of a row are cut for
+        a power-of-two bucket of the longest row (a graph of that bucket serves every batch whose longest row fits
+        it; planning every graph for the longest request the engine takes would cut 2,000-token rows like 8,000-token
+        ones), the one-token rows' keys are shared out in the mode their lengths call for, and rows of several tokens
+        get the most query tiles any cut of their tokens into that many rows can have (tiles beyond a step's own exit
+        at once)."""
+        lens = rows.host_kv_len
+        bucket = self.KV_BUCKET_MIN
+        longest = int(lens.max()) if lens is not None and len(lens) else max_model_len
+        while bucket < longest:
+            bucket *= 2
+        bucket = min(bucket, max(max_model_len, longest))
+        mode = self.decode_mode(lens[:rows.n_decode] if lens is not None else None) if rows.n_decode else None
+        rows.max_kv = bucket
+        rows.plan["mode"] = mode
+        portions, tokens = rows.n_rows - rows.n_decode, rows.n_tokens - rows.n_decode
+        for size in (64, 128, 256):
+            rows.plan[size] = tokens // size + portions
+        return mode, bucket
 
     # Every layer of a step asks the same questions about the step's rows: the answers are kept on the rows.
     def _decode_mode_of(self, rows) -> str:
@@ -403,14 +432,28 @@ class CudaKernels:
         self._call(name, self._p(out), int(out.dtype == torch.float32), self._p(x), self._p(weight), m, n, k,
                    int(swiglu), inter)
 
+    def status(self) -> int:
+        """0, or the code of a bounded wait inside a kernel that gave up: (place << 28) | (block + 1). A read of host
+        memory, no synchronisation: it tells of every kernel that has finished (wait for the step's event first)."""
+        return int(self._status_word[0])
+
+    def clear_status(self) -> None:
+        self._status_word[0] = 0
+
+    def status_selftest(self, polls: int = 1000) -> None:
+        """Enqueues a wait of `polls` polls on a barrier nobody arrives at: it runs out and `status()` turns non-zero."""
+        self._call("hb_status_selftest", int(polls))
+
     def tcgen05_status(self) -> int:
-        """0, or which bounded wait inside a tcgen05 kernel (product or attention) gave up (synchronises the device)."""
+        """0, or which bounded wait inside a tcgen05 kernel (product or attention) gave up (synchronises the device;
+        clears the kernels' words and the host's)."""
         out = 0
         for name in ("hb_gemm_tcgen05_status", "hb_gemm_tcgen05_pair_status", "hb_attention_tcgen05_status"):
             status = ctypes.c_uint(0)
             if getattr(self.lib, name)(ctypes.byref(status)):
                 raise KernelError(self.lib.hb_last_error().decode())
             out = out or status.value
+        self.clear_status()
         return out
 
     def swiglu_gate_up(self, out, x, weight) -> None:
@@ -448,6 +491,15 @@ class CudaKernels:
         self._call("hb_feed_tokens", self._i32(token_ids, "token_ids"), self._i32(last_tokens, "last_tokens"),
                    self._i32(rows.row_slot, "row_slot"), self._i32(rows.query_start, "query_start"),
                    self._i32(from_last, "from_last"), rows.n_rows)
+
+    def scatter_rows(self, table, slots, rows) -> None:
+        """table[slots[i], :] = rows[i, :]: block-table rows that changed on the host, packed in the step's upload."""
+        self._check(table, slots, rows)
+        n, width = slots.shape[0], table.shape[1]
+        if rows.shape[0] != n * width:
+            raise KernelError(f"scatter_rows: {n} rows of {width} need {n * width} values, not {rows.shape[0]}")
+        self._call("hb_scatter_rows", self._i32(table, "table"), self._i32(slots, "slots"), self._i32(rows, "rows"),
+                   n, width, table.shape[0])
 
     def store_tokens(self, last_tokens, slots, tokens, n) -> None:
         """last_tokens[slots[i]] = tokens[i] for i < n."""

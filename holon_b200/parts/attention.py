@@ -46,6 +46,16 @@ class GQA(Part):
     def slot_states(self):
         return ()
 
+    @property
+    def plan_group(self):
+        """Mixers with equal answers here plan a captured step alike: one of them is asked."""
+        return "gqa", self.heads, self.kv_heads, self.head_dim, self.window
+
+    def capture_plan(self, step, max_model_len: int):
+        """What the attention kernels pin for a step that is captured as a CUDA graph (see base.Part)."""
+        plan = getattr(self.ctx.kernels, "attention_capture_plan", None)
+        return plan(step.rows, max_model_len) if plan is not None else None
+
     def forward(self, x: torch.Tensor, step, cache) -> torch.Tensor:
         t, k = x.shape[0], self.ctx.kernels
         q = self.ctx.empty(t, self.heads, self.head_dim)

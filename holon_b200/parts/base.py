@@ -81,11 +81,15 @@ class PagedKV:
 @dataclasses.dataclass(frozen=True)
 class SlotState:
     """State of fixed size per request: one tensor [requests + 1, *shape] per layer that declares it, zeroed when a
-    request takes the slot."""
+    request takes the slot. `chunk` > 1: the mixer updates this state in chunks of that many tokens, so a prompt may
+    be cut only at positions that are multiples of it (the scheduler shortens a portion to the last such position;
+    the portion that ends the prompt ends where the prompt ends), as the reference cuts where a recurrent state wants
+    its checkpoints (core/holon/core/sched.py:150; core/holon/core/state.py:311-318)."""
 
     name: str
     shape: tuple[int, ...]
     dtype: str = "float32"
+    chunk: int = 1
 
 
 # ---------------------------------------------------------------- registries

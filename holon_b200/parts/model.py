@@ -45,6 +45,12 @@ class Model(Part):
         self.norm = self.add_child("norm", ctx.part(spec.norm, dim=spec.hidden))
         self.head = self.add_child("head", ctx.part(spec.head, vocab=spec.vocab, hidden=spec.hidden, embed=self.embed))
         self.entries = self._entries()
+        planners: dict = {}                                   # one mixer of each kind that plans captured steps
+        for layer in self.layers:
+            mixer = getattr(layer, "mixer", None)
+            if hasattr(mixer, "capture_plan"):
+                planners.setdefault(getattr(mixer, "plan_group", id(mixer)), mixer)
+        self._planners = tuple(planners.values())
 
     def _entries(self) -> tuple[CacheEntry, ...]:
         entries: dict[int, CacheEntry] = {}
@@ -57,6 +63,16 @@ class Model(Part):
                 raise ValueError(f"layer {run.layer} reads cache entry {run.cache}, filled by layer "
                                  f"{entries[run.cache].layer} with other sizes: {entries[run.cache].decl} vs {decl}")
         return tuple(entries[k] for k in sorted(entries))
+
+    def capture_plan(self, step, max_model_len: int) -> tuple:
+        """A step that is to run as a CUDA graph is replayed for every later step of the same shape: whatever a
+        mixer's kernels decide from the rows' lengths on the host (how keys are shared out over CTAs, how many tiles a
+        launch has) is frozen at the capture. Each mixer that makes such decisions answers `capture_plan(step,
+        max_model_len)`: it pins them on the step in a form that serves every step with the same answer, and returns
+        that answer, hashable. The answers of all mixers are part of the graph's key, so a step whose rows call for
+        another plan gets another graph (core/holon/api/mixer.py:20-28 splits a mixer's planning the same way, into
+        bounds known on the host and metadata made on the device)."""
+        return tuple(mixer.capture_plan(step, max_model_len) for mixer in self._planners)
 
     def trunk(self, step):
         """The residual stream after the last run, for every token of the step."""

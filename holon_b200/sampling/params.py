@@ -1,6 +1,6 @@
 """Per-request sampling settings; names, defaults and meanings are the reference's `SamplingParams`
 (core/holon/api/batch.py:45-61). Penalties are refused as they are there (core/holon/core/engine.py:346-347);
-log-probabilities, which the reference returns, are refused too (this engine does not build them)."""
+`logprobs` and `prompt_logprobs` ask for the top-k log-probabilities of generated and of prompt tokens."""
 from __future__ import annotations
 
 import dataclasses

@@ -105,6 +105,9 @@ class RefKernels:
             if int(from_last[r]):
                 token_ids[int(rows.query_start[r])] = last_tokens[int(rows.row_slot[r])]
 
+    def scatter_rows(self, table, slots, rows):
+        table[slots.long()] = rows.view(slots.shape[0], table.shape[1])
+
     def store_tokens(self, last_tokens, slots, tokens, n):
         last_tokens[slots[:n].long()] = tokens[:n]
 

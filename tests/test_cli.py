@@ -53,7 +53,9 @@ def test_generate_on_the_command_line(tmp_path, capsys):
     common = ["generate", str(folder), "--prompt-ids", "5,17,3", "--prompt-ids", "9 8 7 6", "--max-tokens", "5", "--dtype",
               "float32", "--max-model-len", "64", "--max-seqs", "4", "--max-step-tokens", "64", "--page-size", "16"]
     assert cli.main(common) == 0
-    lines = [json.loads(line) for line in capsys.readouterr().out.splitlines()]
+    captured = capsys.readouterr()
+    assert "holon-b200: memory: weights" in captured.err and "cache pools" in captured.err   # the account, at the start
+    lines = [json.loads(line) for line in captured.out.splitlines()]
     assert [o["prompt_ids"] for o in lines] == [[5, 17, 3], [9, 8, 7, 6]]
     for o in lines:
         assert o["token_ids"] == plain.generate(config, weights, o["prompt_ids"], 5)

@@ -273,3 +273,52 @@ def test_layout_of_a_step_that_runs_as_a_graph(tmp_path):
     write = step.groups[0].write_index.tolist()
     assert write[2] // 4 * 4 == null and write[3] // 4 * 4 == null   # the padding rows write into the null page
     assert write[0] == int(b.cache.groups[0].table[slots[0], 2]) * 4 + 0
+
+
+def test_the_engine_stops_when_a_kernel_reports_a_wait_that_gave_up(tmp_path):
+    """The kernel table's `status()` is read after every step's completion and before its tokens are handed out: a
+    non-zero word stops the engine with the reason, and it takes no further work
+    (core/holon/core/engine.py:498-499, 607-612)."""
+    class Flaky(RefKernels):
+        word = 0
+
+        def status(self):
+            return self.word
+
+    kernels = Flaky()
+    engine = Engine(EngineConfig(model=str(make_folder(tmp_path, "a")), device="cpu", dtype="float32", page_size=4,
+                                 max_seqs=3, max_model_len=64, max_step_tokens=16, state_memory=1 << 20),
+                    kernels=kernels)
+    engine.add([1, 2, 3], SamplingParams(temperature=0.0, max_tokens=8))
+    engine.step()                                                    # (depth 1: its tokens come a step later)
+    assert [d.token_ids for d in engine.step()]
+    kernels.word = (2 << 28) | 6
+    with pytest.raises(RuntimeError, match=r"stopped: a bounded wait.*place 2, block 5"):
+        for _ in range(3):
+            engine.step()
+    with pytest.raises(RuntimeError, match="the engine stopped"):
+        engine.step()
+    with pytest.raises(RuntimeError, match="the engine stopped"):
+        engine.add([4, 5])
+    engine.close()                                                   # still closes
+
+
+def test_block_table_rows_travel_as_copies_with_the_step(tmp_path):
+    """Rows of the block table that changed go to the device inside the step's own upload, as copies taken when the
+    step is laid out: what the host does to its table afterwards (a window letting go of pages, a request ending)
+    cannot reach a step that is already on its way."""
+    b = built(make_folder(tmp_path, "a"))
+    group = b.cache.groups[0]
+    slot = b.cache.admit()
+    assert b.cache.reserve(slot, 10)
+    slots, rows = group.take_dirty()
+    assert slots.tolist() == [slot] and rows[0, :3].tolist() == group.table[slot, :3].tolist()
+    before = rows.copy()
+    b.cache.release(slot)                                            # the host table moves on
+    assert (rows == before).all() and (group.table[slot] == group.null_page).all()
+    assert group.take_dirty()[0].tolist() == [slot] and group.take_dirty()[0].tolist() == []
+    slot = b.cache.admit()
+    assert b.cache.reserve(slot, 6)
+    b.runner.step([StepEntry(slot, [1, 2, 3, 4, 5, 6], 0)])
+    assert group.table_device[slot].tolist() == group.table[slot].tolist()
+    assert b.runner.uploader.bytes_last >= 4 * (1 + group.max_pages)  # counted with the step's upload

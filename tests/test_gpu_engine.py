@@ -252,10 +252,9 @@ def test_one_long_request_among_short_ones_takes_the_balanced_decode_graph(tmp_p
     kw = dict(page_size=64, max_seqs=12, max_model_len=4608, max_step_tokens=1024, chunk_with_decode=64)
     engine = engine_of(folder, "bfloat16", **kw)
     got = engine.generate(prompts, params)
-    modes = {key[-1] for key in engine._graphs}                      # (bucket, prompt portions, prompt tokens, mode)
-    assert "balanced" in modes, modes
+    assert "balanced" in modes_of(engine._graphs)
     short = engine.generate(prompts[1:], params)
-    assert {key[-1] for key in engine._graphs} == {"balanced", "splits"}
+    assert modes_of(engine._graphs) == {"balanced", "splits"}
     plain_run = engine_of(folder, "bfloat16", cuda_graphs=False, **kw)
     kernels = plain_run.built.ctx.kernels                            # (one kernel table per device: put the setting back)
     before, kernels.decode_attention = kernels.decode_attention, "splits"
@@ -264,3 +263,98 @@ def test_one_long_request_among_short_ones_takes_the_balanced_decode_graph(tmp_p
     finally:
         kernels.decode_attention = before
     engine.built.cache.check()
+
+
+def modes_of(keys):
+    """How the decode rows' keys are shared out in the graphs of `keys`: a key is (bucket, prompt portions, prompt
+    tokens, the mixers' plans), and the attention's plan is (mode, bucket of the longest row)."""
+    return {plan[0] for key in keys for plan in key[3] if plan is not None and plan[0] is not None}
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_a_graph_captured_while_a_step_is_in_flight_runs_that_step_once(tmp_path, dtype):
+    """In steady decode the host runs one step ahead: rows take their input token from the device. When the rows'
+    lengths then call for another graph (the longest row passes 4,096 tokens beside short ones: the keys are shared
+    out evenly from there on; short rows pass 512 tokens: the launch is planned for the next bucket), the first step
+    of the new shape runs eagerly and is recorded, and must run once only: a replay on top would feed on the token the
+    eager run has just stored. Tokens are sampled, so that a step that ran twice shows; they must equal those of an
+    engine that commits every step before the next (same graphs, same plans: bit for bit), and in float32 those of
+    an engine without graphs."""
+    folder = make_folder(tmp_path, "b")
+    config, _ = plain.read_folder(folder)
+    vocab = config["vocab_size"]
+    long_batch = [random_prompt(vocab, n, 7 + n) for n in (4088, 30, 12, 55, 9, 21, 40, 3, 17, 26, 33, 8)]
+    short_batch = [random_prompt(vocab, 500 + n, 11 + n) for n in range(6)]
+    kw = dict(page_size=64, max_seqs=12, max_model_len=4608, max_step_tokens=4608, chunk_with_decode=0,
+              state_memory=24 << 20, prefix_cache=False)
+
+    def run(**more):
+        engine = engine_of(folder, dtype, **kw, **more)
+        out = []
+        for batch in (long_batch, short_batch):
+            params = [SamplingParams(temperature=1.0, max_tokens=20, seed=500 + i) for i in range(len(batch))]
+            out.append(engine.generate(batch, params))
+        return engine, out
+
+    ahead, got = run()
+    assert modes_of(ahead._captured_ahead) == {"balanced", "splits"}, ahead._captured_ahead
+    assert any(len(set(tokens)) > 3 for tokens in got[0])            # tokens vary: feeding a wrong one would show
+    in_turn, want = run(overlap=False)
+    assert not in_turn._captured_ahead and set(in_turn._graphs) == set(ahead._graphs)
+    assert got == want
+    if dtype == "float32":
+        assert run(cuda_graphs=False)[1] == got
+    ahead.built.cache.check()
+
+
+def test_a_wait_that_gives_up_stops_the_engine(model):
+    """Every wait inside the tcgen05 kernels is bounded and leaves a code in a word of host memory when it gives up.
+    A test-only kernel makes such a wait run out (a thousand polls of a barrier at which nobody arrives: microseconds,
+    and the device stays as it was); the engine reads the word after the step's completion, hands out none of the
+    step's tokens, stops with the reason and refuses further work."""
+    folder, config, weights, prompts = model
+    engine = engine_of(folder, "bfloat16")
+    kernels = engine.built.ctx.kernels
+    assert kernels.status() == 0
+    try:
+        engine.add(prompts[0], SamplingParams(temperature=0.0, max_tokens=30))
+        for _ in range(4):
+            engine.step()
+        kernels.status_selftest(1000)
+        with pytest.raises(RuntimeError, match=r"the engine stopped: a bounded wait inside a kernel gave up .*place 15, block 0"):
+            for _ in range(3):
+                engine.step()
+        assert kernels.status() == (15 << 28) | 1
+        with pytest.raises(RuntimeError, match="the engine stopped"):
+            engine.step()
+        with pytest.raises(RuntimeError, match="the engine stopped"):
+            engine.add([1, 2, 3])
+    finally:
+        assert kernels.tcgen05_status() == 0                        # (the products' and the attention's own words)
+        kernels.clear_status()
+    engine.close()
+    healthy = engine_of(folder, "bfloat16")                         # the device and the library go on as before
+    assert len(healthy.generate([prompts[0]], SamplingParams(temperature=0.0, max_tokens=4))[0]) == 4
+
+
+def test_memory_is_measured_at_the_start(model):
+    """Without a given size the cache pools take `memory_fraction` of what is free after the weights, less the measured
+    activation peak of the largest step and of the largest step that graphs replay; the engine reports the account."""
+    import torch
+    folder, config, _, prompts = model
+    free, _ = torch.cuda.mem_get_info()
+    engine = engine_of(folder, "bfloat16", state_memory=None, memory_fraction=0.02, max_step_tokens=256, max_seqs=8,
+                       chunk_with_decode=32)
+    memory = engine.built.memory
+    assert memory.activations > 0 and memory.graphs > 0 and memory.free_before <= free
+    # logits of the rows that may sample in one step are the floor of what such a step allocates
+    assert memory.activations >= 8 * config["vocab_size"] * 4
+    assert memory.cache <= int(memory.free_before * 0.02) - memory.activations - memory.graphs
+    assert memory.cache >= 0.9 * (int(memory.free_before * 0.02) - memory.activations - memory.graphs) - (1 << 20)
+    line = engine.memory_report()
+    for word in ("weights", "activations", "graph pool", "cache pools", "free"):
+        assert word in line
+    assert "not measured" not in line
+    assert len(engine.generate([prompts[1]], SamplingParams(temperature=0.0, max_tokens=4))[0]) == 4
+    fixed = engine_of(folder, "bfloat16")
+    assert fixed.built.memory.activations is None and "not measured" in fixed.memory_report()

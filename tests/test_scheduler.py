@@ -142,3 +142,32 @@ def test_random_traffic_finishes_every_request(seed):
         assert steps < 5000
     assert len(done) == 25 and all(r.generated >= 1 for r in done)
     assert not cache.live and cache.groups[0].pool.available == cache.groups[0].pool.pages
+
+
+def test_a_state_that_wants_chunks_moves_the_cuts_to_their_multiples():
+    """A mixer whose fixed-size state is updated in chunks of 8 tokens (`SlotState.chunk`): a portion that does not
+    end its prompt ends at a multiple of 8, wherever the budget would have cut it; the portion that ends the prompt
+    ends where the prompt ends; a budget too small for a whole chunk leaves the request for the next step."""
+    from holon_b200.parts import SlotState
+    entries = [CacheEntry(0, 0, PagedKV(1, 16), ()), CacheEntry(1, 1, None, (SlotState("sum", (4,), chunk=8),))]
+    cache = CacheManager(entries, page_size=4, max_seqs=4, max_model_len=64, dtype=torch.float32, device="cpu", pages=40)
+    assert cache.chunk == 8
+    s = Scheduler(cache, 21, 64, 0)
+    for rid, n in (("a", 30), ("b", 13), ("c", 9)):
+        s.add(request(rid, n))
+    rows = s.schedule()
+    assert shape(rows) == [("a", 16, False)]                    # 21 tokens of budget: cut back to 16; 5 left are too few
+    run_step(s, rows)                                           # for one chunk of b, whose prompt would not end there
+    rows = s.schedule()
+    assert shape(rows) == [("a", 14, True)]                     # the prompt's end needs no multiple; b's 7 would be none
+    run_step(s, rows)
+    rows = s.schedule()
+    assert shape(rows) == [("b", 13, True), ("c", 8, False)]
+    seen = []
+    while rows:
+        seen += [(r.request.rid, r.request.computed, r.n_tokens, r.samples) for r in rows]
+        run_step(s, rows)
+        rows = s.schedule() if s.waiting else None
+    for rid, start, n, ends in seen:                            # every cut inside a prompt lies on a multiple of 8
+        assert ends or (start + n) % 8 == 0, (rid, start, n)
+    assert {rid for rid, _, _, ends in seen if ends} == {"b", "c"} and not s.waiting

@@ -4,7 +4,8 @@ exported C symbol, against the entry point that takes scratch from the caller.
 Some users of the library cannot allocate when they call it: a server that gave all free device memory to its cache
 at start, or a program in another language that sees only the C symbols. For them the library carries its own scratch
 array. This test makes two calls in a row with different inputs and different splits (the array keeps the first
-call's contents, which must not leak into the second), and checks that a launch too large for the array is refused
+call's contents, which must not leak into the second: each result must equal the other entry point's bit for bit, and
+the plain attention within the kernel tests' bound), and checks that a launch too large for the array is refused
 with a message instead of run. The file sorts last on purpose: a run that stops at the first failure has then already
 run every other test.
 """
@@ -12,9 +13,12 @@ from __future__ import annotations
 
 import ctypes
 import math
+import types
 
 import pytest
 import torch
+
+from ref_kernels import RefKernels
 
 pytestmark = pytest.mark.gpu
 DEV = "cuda:0"
@@ -62,7 +66,13 @@ def test_static_scratch_entry_point_matches_the_one_that_takes_scratch():
         assert lib.hb_attention_decode_bf16_static(p(got), *common) == 0, lib.hb_last_error()
         torch.cuda.synchronize()
         assert torch.isfinite(got.float()).all()
-        assert (got.float() - want.float()).abs().max().item() <= 1.6e-2 * 4     # the kernel tests' bfloat16 bound
+        assert torch.equal(got, want)            # the same launch with other scratch, a fixed-order merge: bit for bit
+        rows = types.SimpleNamespace(query_start=c["query_start"].cpu(), row_slot=c["row_slot"].cpu(),
+                                     kv_len=c["kv_len"].cpu(), n_rows=c["rows"])
+        plain = torch.empty(c["q"].shape, dtype=torch.float32)
+        RefKernels().paged_attention(plain, c["q"].float().cpu(), c["kv"].float().cpu(), c["table"].cpu(), rows,
+                                     1 / math.sqrt(c["head_dim"]), window)
+        assert (got.float().cpu() - plain).abs().max().item() <= 1.6e-2 * 4      # the kernel tests' bfloat16 bound
         return got
 
     first = both(case(1, 5, 8, 2, 128, 16, [700, 64, 1, 333, 1500]), splits=5, window=0)
