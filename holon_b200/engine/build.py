@@ -49,15 +49,16 @@ class Built:
 
 
 def _peak_of(device, run) -> int:
-    """Bytes the allocator took from the device at most while `run()` ran, beyond what it held before (its own
-    rounding and splitting of blocks included: that is what the cache pools must leave room for)."""
+    """Bytes `run()` needed at most beyond what was held before: what the allocator took from the device meanwhile
+    (its own rounding and splitting of blocks included: that is what the cache pools must leave room for), and at
+    least what it handed out (a small step may fit into blocks the allocator already holds)."""
     torch.cuda.synchronize(device)
     torch.cuda.empty_cache()
     torch.cuda.reset_peak_memory_stats(device)
-    before = torch.cuda.memory_reserved(device)
+    reserved, allocated = torch.cuda.memory_reserved(device), torch.cuda.memory_allocated(device)
     run()
     torch.cuda.synchronize(device)
-    return max(0, torch.cuda.max_memory_reserved(device) - before)
+    return max(0, torch.cuda.max_memory_reserved(device) - reserved, torch.cuda.max_memory_allocated(device) - allocated)
 
 
 def _measure(model, ctx, entries, *, page_size: int, max_seqs: int, max_model_len: int, max_step_tokens: int,

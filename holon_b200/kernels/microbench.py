@@ -4,8 +4,9 @@
     python -m holon_b200.kernels.microbench gemm [--rows 2048] [--shapes qkv o gate_up down]
     python -m holon_b200.kernels.microbench prefill_attention [--rows 2048] [--context 2048]
 
-Sizes default to Qwen3-8B's (32 query and 8 KV heads of 128, hidden 4096, intermediate 12288). The numbers under
-`profiles/` that are not ncu captures come from here.
+Sizes default to Qwen3-8B's (32 query and 8 KV heads of 128, hidden 4096, intermediate 12288). `layer_table` times
+every kernel of one decode layer and of one prefill layer the same way and sets each time against the bytes or the
+flops the kernel has to move or do; `bench.py` prints it as its `kernels` block.
 """
 from __future__ import annotations
 
@@ -144,6 +145,105 @@ def gemm(k, args) -> None:
                     line += f"; weight-streaming with SwiGLU {t_sw:7.1f} us"
             print(line)
     print("tcgen05 status", k.tcgen05_status())
+
+
+def layer_table(k, cfg: dict, batch: int, context: int, prefill_tokens: int, hbm_gbs: float, bf16_tflops: float) -> dict:
+    """Every kernel of one layer (and the head) alone, with CUDA events, at the sizes of `cfg` (config.json keys):
+    a decode step of `batch` rows that hold `context` tokens, where a kernel's measure is the bytes it must read
+    (weights once, the rows' cache) over its time against the copy bandwidth `hbm_gbs`; and a prompt of
+    `prefill_tokens` tokens, where it is flops over time against `bf16_tflops`. The L2 is replaced before every run of
+    a decode kernel. {"decode": {kernel: {"us", "mb", "gbs", "frac"}}, "prefill": {kernel: {"us", "gflop", "tflops",
+    "frac"}}}; the decode products run as the engine runs them (norm, rotation, cache write, SwiGLU and the residual
+    sum folded in where the kernel table folds them)."""
+    from ..parts.base import Scaled
+    h, d, hq, hkv, inter, vocab = (cfg[x] for x in ("hidden_size", "head_dim", "num_attention_heads", "num_key_value_heads",
+                                                    "intermediate_size", "vocab_size"))
+    eps, page, dev, bf = float(cfg["rms_norm_eps"]), 64, k.device, torch.bfloat16
+    flush = torch.zeros(256 << 20, device=dev, dtype=torch.uint8)
+    g = torch.Generator(device=dev).manual_seed(1)
+    rand = lambda *shape, scale=1.0: (torch.randn(*shape, device=dev, generator=g) * scale).to(bf)   # noqa: E731
+    w_qkv, w_o = rand((hq + 2 * hkv) * d, h, scale=0.02), rand(h, hq * d, scale=0.02)
+    w_gu, w_down, w_head = rand(2 * inter, h, scale=0.02), rand(h, inter, scale=0.02), rand(vocab, h, scale=0.02)
+    gain_h, gain_d = torch.ones(h, device=dev, dtype=bf), torch.ones(d, device=dev, dtype=bf)
+    positions_max = max(context, prefill_tokens) + 1
+    inv = 1.0 / (float(cfg["rope_theta"]) ** (torch.arange(0, d, 2, dtype=torch.float32) / d))
+    angle = torch.arange(positions_max, dtype=torch.float32)[:, None] * inv[None, :]
+    table = torch.cat((angle.cos(), angle.sin()), dim=-1).contiguous().to(dev)
+    i32 = lambda v: torch.tensor(v, device=dev, dtype=torch.int32)   # noqa: E731
+
+    def rows_of(n_rows: int, tokens_each: int, kv_each: int):
+        per = -(-kv_each // page)
+        kv = rand(n_rows * per + 1, 2, hkv, page, d)
+        block = torch.arange(n_rows * per, device=dev, dtype=torch.int32).view(n_rows, per).contiguous()
+        starts = list(range(0, n_rows * tokens_each + 1, tokens_each))
+        rows = Rows(i32(list(range(n_rows))), i32(starts), i32([kv_each] * n_rows), n_rows, n_rows * tokens_each,
+                    n_rows if tokens_each == 1 else 0, tokens_each, kv_each, starts, [kv_each] * n_rows)
+        pos = torch.cat([torch.arange(kv_each - tokens_each, kv_each, dtype=torch.int32) for _ in range(n_rows)]).to(dev)
+        write = torch.cat([block[r].repeat_interleave(page)[kv_each - tokens_each:kv_each] * page
+                           + (torch.arange(kv_each - tokens_each, kv_each, device=dev, dtype=torch.int32) % page)
+                           for r in range(n_rows)]).to(torch.int32).contiguous()
+        return kv, block, rows, pos.contiguous(), write
+
+    out: dict = {"decode": {}, "prefill": {}}
+
+    # ---- one decode layer: `batch` rows of one token
+    m = batch
+    kv, block, rows, pos, write = rows_of(m, 1, context)
+    stream = torch.randn(m, h, device=dev, generator=g)
+    x = rand(m, h)
+    ss = torch.full((-(-h // 16), 16), float(h) / (-(-h // 16) * 16), device=dev)       # sums of squares of unit rows
+    q, o = torch.empty(m, hq, d, device=dev, dtype=bf), torch.empty(m, hq, d, device=dev, dtype=bf)
+    act, logits = torch.empty(m, inter, device=dev, dtype=bf), torch.empty(m, vocab, device=dev, dtype=torch.float32)
+    scaled = Scaled(x, ss, eps, h) if m <= k.SKINNY_ROWS else x
+    scale = 1 / math.sqrt(d)
+
+    def first_product():
+        if not k.qkv_rope(q, scaled, w_qkv, pos, table, d, gain_d, gain_d, eps, 0.0, kv, write, hq, hkv, d):
+            qkv = torch.empty(m, w_qkv.shape[0], device=dev, dtype=bf)
+            k.linear(qkv, x, w_qkv)
+            k.qk_norm_rope_kv_write(q, qkv, pos, table, d, gain_d, gain_d, eps, 0.0, kv, write, hq, hkv, d)
+
+    def closing(x_in, w):
+        if k.linear_link(stream, x_in, w, gain_h, eps, 0.0) is None:
+            y = torch.empty(m, w.shape[0], device=dev, dtype=bf)
+            k.linear(y, x_in, w)
+            k.add_rmsnorm(torch.empty(m, h, device=dev, dtype=bf), stream, y, gain_h, eps, 0.0, None)
+
+    decode = (("qkv+norm+rope+write", first_product, w_qkv.numel() * 2),
+              ("attention", lambda: k.paged_attention(o, q, kv, block, rows, scale, 0), m * context * hkv * d * 4),
+              ("o_proj+add+norm", lambda: closing(o.view(m, hq * d), w_o), w_o.numel() * 2),
+              ("gate_up+swiglu", lambda: k.swiglu_gate_up(act, scaled, w_gu), w_gu.numel() * 2),
+              ("down+add+norm", lambda: closing(act, w_down), w_down.numel() * 2),
+              ("lm_head", lambda: k.linear(logits, x, w_head), w_head.numel() * 2))
+    for name, fn, moved in decode:
+        us = timed(fn, flush)
+        out["decode"][name] = {"us": round(us, 1), "mb": round(moved / 1e6, 1), "gbs": round(moved / us / 1e3, 0),
+                               "frac": round(moved / us / 1e3 / hbm_gbs, 3)}
+    del kv, block, rows
+
+    # ---- one prefill layer: one prompt of `prefill_tokens` tokens
+    t = prefill_tokens
+    kv, block, rows, pos, write = rows_of(1, t, t)
+    stream = torch.randn(t, h, device=dev, generator=g)
+    x, delta = rand(t, h), rand(t, h)
+    qkv = torch.empty(t, w_qkv.shape[0], device=dev, dtype=bf)
+    q, o = torch.empty(t, hq, d, device=dev, dtype=bf), torch.empty(t, hq, d, device=dev, dtype=bf)
+    act, y, normed = torch.empty(t, inter, device=dev, dtype=bf), torch.empty(t, h, device=dev, dtype=bf), torch.empty(t, h, device=dev, dtype=bf)
+    prefill = (("add+norm", lambda: k.add_rmsnorm(normed, stream, delta, gain_h, eps, 0.0, None), 0),
+               ("qkv", lambda: k.linear(qkv, x, w_qkv), 2 * t * w_qkv.numel()),
+               ("norm+rope+write", lambda: k.qk_norm_rope_kv_write(q, qkv, pos, table, d, gain_d, gain_d, eps, 0.0, kv, write, hq, hkv, d), 0),
+               ("attention", lambda: k.paged_attention(o, q, kv, block, rows, scale, 0), 4 * hq * d * t * (t + 1) // 2),
+               ("o_proj", lambda: k.linear(y, o.view(t, hq * d), w_o), 2 * t * w_o.numel()),
+               ("gate_up+swiglu", lambda: k.swiglu_gate_up(act, x, w_gu), 2 * t * w_gu.numel()),
+               ("down", lambda: k.linear(y, act, w_down), 2 * t * w_down.numel()))
+    for name, fn, flops in prefill:
+        def ten(fn=fn):
+            for _ in range(10):
+                fn()
+        us = timed(ten, None, 4) / 10
+        out["prefill"][name] = {"us": round(us, 1), "gflop": round(flops / 1e9, 1), "tflops": round(flops / us / 1e6, 0),
+                                "frac": round(flops / us / 1e6 / bf16_tflops, 3)}
+    return out
 
 
 def main() -> None:
