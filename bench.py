@@ -1,4 +1,5 @@
-"""Measures decode and prefill throughput of holon_b200 at Qwen3-8B sizes with random weights on one B200.
+"""Measures decode and prefill throughput at Qwen3-8B sizes with random weights on one B200, for this engine and,
+with `--impl reference`, for mxinO/holon itself through the same loops.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
 
@@ -6,21 +7,29 @@ A "step" is one decode step of the whole batch. The default run: the layer sizes
 4096, 32 query heads, 8 KV heads, head size 128, intermediate 12288, vocabulary 151936), bfloat16, batch 8, each
 request ending at a context of 8,192 tokens. It prints ONE JSON line:
 
-  value            decoded tokens per second, timed on the device with CUDA events around exactly K steps
-  e2e              decode throughput through the public entry point `Engine.generate` (host token lists in and out), by
-                   wall clock, as batch * K / (t(K + 1 tokens) - t(1 token)), each time the faster of two runs; every step
-                   copies its inputs from pinned host memory and its tokens back (bytes per step are reported)
+  value            decoded tokens per second, timed on the device with CUDA events around exactly K steps of the
+                   engine's `step()`, after W untimed ones
+  e2e              the same through the public streaming calls a user makes (`add` with host token lists, `step`,
+                   `has_work`; token ids back on the host with every step): tokens that arrive after every request's
+                   first token, over the wall time from that moment to the last arrival, as the reference's own
+                   benchmark takes it (bench/llama_bench.py:90-128). Every step copies its inputs from pinned host
+                   memory and its tokens back; the bytes per step are counted from the tensors copied
   prefill          one prompt of 2,048 tokens: tokens per second, milliseconds, flops / time / bf16 peak
   roofline         the decode step's bytes (every weight once, the live requests' cache) / its time against the
                    measured copy bandwidth
-  points           decode tokens per second at batch 1 and 64
+  points           decode tokens per second at batch 1 and 64, and at batch 1, 8 and 64 with 2,048-token prompts and
+                   256 decoded tokens; `point_rooflines` gives each point's bytes, milliseconds a step and fraction
+  kernels          every kernel of one decode layer and of one prefill layer alone, with CUDA events: microseconds,
+                   bytes or flops, and the fraction of the copy bandwidth or of the bf16 peak (this engine only)
   clocks           SM clocks sampled with nvidia-smi during the timed steps
 
 Every decode step reads 15 GB of weights and the requests' cache, far more than the 126 MB L2, so consecutive steps
-cannot reuse cached data ("l2": "inputs larger than L2"). Peaks come from MEASURED_PEAKS.json when the driver wrote
-it, else from an earlier measurement on this pool (6.65 TB/s copy, 1.59 PFLOP/s bf16).
-The method is the reference's own: decode throughput from first to last generated token of a batch of equal
-prompts, prefill as prompt tokens over time to first token (bench/holon_tg.py:51-63, bench/llama_bench.py:90-128).
+cannot reuse cached data ("l2": "inputs larger than L2"). Peaks come from MEASURED_PEAKS.json beside this file if it
+is there, else from an earlier measurement of a B200 (6.65 TB/s copy, 1.59 PFLOP/s bf16).
+
+`--impl reference` runs the unmodified reference from baseline/_ref (see baseline/install_ref.py) through its own
+`Engine`, `EngineConfig` and `SamplingParams`, on the same weights (written once to a temporary model folder), the
+same prompts, batch, context, K and W, and prints the same keys with "impl": "reference".
 """
 from __future__ import annotations
 
@@ -142,19 +151,64 @@ def prompts_of(vocab: int, batch: int, length: int, seed: int) -> list[list[int]
     return torch.randint(1000, vocab // 2, (batch, length), generator=g).tolist()
 
 
-def decode_run(engine, batch: int, context: int, steps: int, warmup: int, seed: int, clocks: Clocks | None = None) -> dict:
+class Arm:
+    """An engine under the benchmark's loops. This engine and the reference answer the same calls (`add`, `step`,
+    `has_work`, `abort`, `drain`: the reference's names, core/holon/core/engine.py:332-524), so one set of loops times
+    both; what differs is gathered here."""
+
+    impl = "holon_b200"
+
+    def __init__(self, engine) -> None:
+        self.engine = engine
+
+    def params(self, max_tokens: int):
+        from holon_b200.engine import SamplingParams
+        return SamplingParams(temperature=0.0, max_tokens=max_tokens, ignore_eos=True)
+
+    @property
+    def sched(self):
+        return self.engine.scheduler
+
+    @property
+    def vocab(self) -> int:
+        return self.engine.built.model.spec.vocab
+
+    def counters(self):
+        """(bytes copied to the device, bytes copied back, kernels of this package launched) so far."""
+        e = self.engine
+        return e.h2d_bytes, e.d2h_bytes, e.launches()
+
+
+class ReferenceArm(Arm):
+    impl = "reference"
+
+    def params(self, max_tokens: int):
+        from holon.api import SamplingParams
+        return SamplingParams(temperature=0.0, max_tokens=max_tokens, ignore_eos=True)
+
+    @property
+    def sched(self):
+        return self.engine.sched
+
+    @property
+    def vocab(self) -> int:
+        return self.engine.spec.vocab
+
+    def counters(self):
+        return None                                                  # the reference does not count its copies
+
+
+def decode_run(arm: Arm, batch: int, context: int, steps: int, warmup: int, seed: int, clocks: Clocks | None = None) -> dict:
     """`batch` equal prompts, prefilled (untimed) so that the last timed step ends at `context` tokens; then `warmup`
-    untimed and `steps` timed decode steps through `Engine.step`."""
+    untimed and `steps` timed decode steps through the engine's `step`."""
     import torch
-    from holon_b200.engine import SamplingParams
+    engine = arm.engine
     prompt_len = context - (steps + warmup) - 1
-    vocab = engine.built.model.spec.vocab
-    params = SamplingParams(temperature=0.0, max_tokens=steps + warmup + 1, ignore_eos=True)
-    for p in prompts_of(vocab, batch, prompt_len, seed):
-        engine.add(p, params)
-    while engine.scheduler.waiting:                                  # prefill, in portions under the token budget
+    params = arm.params(steps + warmup + 1)
+    rids = [engine.add(p, params) for p in prompts_of(arm.vocab, batch, prompt_len, seed)]
+    while arm.sched.waiting:                                         # prefill, in portions under the token budget
         engine.step()
-    assert len(engine.scheduler.running) == batch
+    assert len(arm.sched.running) == batch
     if clocks:
         clocks.start()                                              # (nvidia-smi needs a moment before its first sample)
     for _ in range(warmup):
@@ -162,62 +216,86 @@ def decode_run(engine, batch: int, context: int, steps: int, warmup: int, seed: 
     torch.cuda.synchronize()
     if clocks:
         clocks.mark()
-    h2d0, d2h0, launches0 = engine.h2d_bytes, engine.d2h_bytes, engine.launches()
+    before = arm.counters()
     start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     t0 = time.perf_counter()
     start.record()
     produced = 0
     for _ in range(steps):
-        produced += len(engine.step())
+        produced += sum(len(d.token_ids) for d in engine.step())
     end.record()
     torch.cuda.synchronize()
     wall = time.perf_counter() - t0
     device_ms = start.elapsed_time(end)
     clock = clocks.stop() if clocks else None
     assert produced == batch * steps, (produced, batch, steps)
-    out = {"device_ms": device_ms, "wall_ms": wall * 1e3, "tokens": produced,
-           "h2d_bytes_per_step": (engine.h2d_bytes - h2d0) // steps, "d2h_bytes_per_step": (engine.d2h_bytes - d2h0) // steps,
-           "launches": engine.launches() - launches0, "mean_context": context - (steps + 1) / 2, "clocks": clock}
-    for rid in list(engine.requests):
+    out = {"device_ms": device_ms, "wall_ms": wall * 1e3, "tokens": produced, "mean_context": context - (steps + 1) / 2,
+           "clocks": clock, "h2d_bytes_per_step": None, "d2h_bytes_per_step": None, "launches": None}
+    if before is not None:
+        after = arm.counters()
+        out |= {"h2d_bytes_per_step": (after[0] - before[0]) // steps, "d2h_bytes_per_step": (after[1] - before[1]) // steps,
+                "launches": after[2] - before[2]}
+    for rid in rids:
         engine.abort(rid)
     engine.drain()
     return out
 
 
-def generate_run(engine, batch: int, context: int, steps: int, seed: int) -> dict:
-    """Decode throughput end to end through `Engine.generate` (host token lists in, host token lists out), the
-    reference's way (bench/holon_tg.py:51-63): batch * steps / (t(generate steps + 1 tokens) - t(generate 1 token)) over
-    equal-length prompts, so that the prompts' prefill cancels. Every decode step inside copies its inputs from pinned
-    host memory and its sampled tokens back."""
-    from holon_b200.engine import SamplingParams
-    vocab = engine.built.model.spec.vocab
-    prompt_len = context - steps - 2
+def stream_run(arm: Arm, batch: int, context: int, steps: int, warmup: int, seed: int) -> dict:
+    """Decode throughput end to end, through the calls a user streams with: host token lists go in with `add`, every
+    `step` brings the new token ids back to the host, and the wall clock is read when they arrive (the reference's
+    benchmark times the same loop: bench/llama_bench.py:35-49, 118-121). Each request generates `warmup` + `steps` + 1
+    tokens and ends at `context`. Two passes with fresh prompts:
+
+    - `after_prefill`: `batch * steps` tokens over the time from the moment every request has its first token to the
+      arrival of the `steps`-th token after it: decoding straight after the prompts' computation, which runs under the
+      power cap and leaves the SM clocks low for the first tens of milliseconds (`gaps_ms` shows the ramp);
+    - `value`: the protocol of the device-timed run, by wall clock: when every request has its first token the clock
+      sampler is started, then `warmup` arrivals pass untimed and `batch * steps` tokens are timed from the `warmup`-th
+      arrival to the last; the clocks sampled meanwhile are returned."""
     import torch
-    times = {}
-    for rep in range(2):                                             # each of the two runs twice, the faster one counts:
-        for n, s in ((1, seed + 2 * rep), (steps + 1, seed + 2 * rep + 1)):   # the prompts' prefill (most of either run)
-            prompts = prompts_of(vocab, batch, prompt_len, s)        # varies by more than a decode step from run to run
-            torch.cuda.synchronize()
-            h2d0, d2h0, steps0 = engine.h2d_bytes, engine.d2h_bytes, engine.steps
-            t0 = time.perf_counter()
-            out = engine.generate(prompts, SamplingParams(temperature=0.0, max_tokens=n, ignore_eos=True))
-            times[n] = min(times.get(n, float("inf")), time.perf_counter() - t0)
-            assert all(len(o) == n for o in out)
-            if n > 1:
-                decode_steps = steps
-                prefill_steps = engine.steps - steps0 - decode_steps
-                io = (engine.h2d_bytes - h2d0, engine.d2h_bytes - d2h0, prefill_steps)
-    return {"value": batch * steps / (times[steps + 1] - times[1]), "seconds": times, "io": io}
+    engine, out = arm.engine, {}
+    prompt_len = context - (steps + warmup) - 1
+    for sampled in (False, True):
+        prompts = prompts_of(arm.vocab, batch, prompt_len, seed + sampled)
+        params = arm.params(steps + warmup + 1)
+        clocks = Clocks() if sampled else None
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        rids = [engine.add(p, params) for p in prompts]
+        first, moments, began = {}, [], None
+        while engine.has_work():
+            deltas = engine.step()
+            now = time.perf_counter() - t0
+            arrived = [d for d in deltas if d.token_ids]
+            for d in arrived:
+                first.setdefault(d.rid, now)
+            if began is not None and arrived:
+                moments.append(now)
+            if began is None and len(first) == len(rids):
+                began = now
+                if clocks:
+                    clocks.start()
+                    clocks.mark()
+        clock = clocks.stop() if clocks else None
+        assert began is not None and len(moments) == steps + warmup, (began, len(moments))
+        if sampled:
+            seconds = moments[warmup + steps - 1] - moments[warmup - 1]
+            out |= {"value": batch * steps / seconds, "seconds": seconds, "tokens": batch * steps, "clocks": clock}
+        else:
+            seconds = moments[steps - 1] - began
+            out["after_prefill"] = {"value": round(batch * steps / seconds, 1), "seconds": round(seconds, 5),
+                                    "gaps_ms": [round((b - a) * 1e3, 2) for a, b in zip([began] + moments, moments)]}
+    return out
 
 
-def prefill_run(engine, tokens: int, repeats: int, seed: int) -> float:
+def prefill_run(arm: Arm, tokens: int, repeats: int, seed: int) -> float:
     """Milliseconds (device, best of `repeats`) of one step that computes a whole prompt of `tokens` tokens and samples
     its first token."""
     import torch
-    from holon_b200.engine import SamplingParams
-    vocab, best = engine.built.model.spec.vocab, float("inf")
+    engine, best = arm.engine, float("inf")
     for i in range(repeats + 1):                                     # the first one is a warm-up
-        engine.add(prompts_of(vocab, 1, tokens, seed + i)[0], SamplingParams(temperature=0.0, max_tokens=1, ignore_eos=True))
+        engine.add(prompts_of(arm.vocab, 1, tokens, seed + i)[0], arm.params(1))
         torch.cuda.synchronize()
         start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         start.record()
@@ -281,14 +359,14 @@ def sizes_run(args) -> dict:
                         source=RandomSource(cfg, seed=seed, device="cuda:0"))
         numbers = model_numbers(cfg, cfg["num_hidden_layers"])
         tokens = 8192
-        ms = prefill_run(engine, tokens, repeats=2, seed=100)
+        ms = prefill_run(Arm(engine), tokens, repeats=2, seed=100)
         flops = 2 * numbers["linear_params"] * tokens - 2 * cfg["vocab_size"] * cfg["hidden_size"] * (tokens - 1) \
             + numbers["attn_flops_per_pair"] * tokens * (tokens + 1) / 2
         out["prefill"] = {"value": round(tokens / ms * 1e3, 1), "tokens": tokens, "ms": round(ms, 2),
                           "frac": round(flops / (ms * 1e-3) / (peak["bf16_tflops"] * 1e12), 4)}
         steps = max(8, min(args.steps, 64))
         for b in (1, 64):
-            r = decode_run(engine, b, 4096 + steps + args.warmup + 1, steps, args.warmup, seed=11 + b)
+            r = decode_run(Arm(engine), b, 4096 + steps + args.warmup + 1, steps, args.warmup, seed=11 + b)
             ms_step = r["device_ms"] / steps
             moved = numbers["weight_bytes"] + b * r["mean_context"] * numbers["kv_bytes_per_token"]
             out[f"decode_b{b}"] = {"value": round(r["tokens"] / r["device_ms"] * 1e3, 1), "ms_per_step": round(ms_step, 3),
@@ -324,7 +402,7 @@ def sizes_run(args) -> dict:
         numbers = model_numbers(cfg, cfg["num_hidden_layers"])
         steps = max(8, min(args.steps, 64))
         for b in (1, 32):
-            r = decode_run(engine, b, 2048 + steps + args.warmup + 1, steps, args.warmup, seed=11 + b)
+            r = decode_run(Arm(engine), b, 2048 + steps + args.warmup + 1, steps, args.warmup, seed=11 + b)
             ms_step = r["device_ms"] / steps
             moved = numbers["weight_bytes"] + b * r["mean_context"] * numbers["kv_bytes_per_token"]
             out[f"decode_b{b}"] = {"value": round(r["tokens"] / r["device_ms"] * 1e3, 1), "ms_per_step": round(ms_step, 3),
@@ -371,6 +449,67 @@ def shared_prompt_run(args) -> dict:
     return out
 
 
+def headline(arm: Arm, args, cfg: dict, engine_facts: dict) -> dict:
+    """The benchmark's line for one engine: the loops above at the sizes of `cfg`."""
+    context, batch = args.context, args.batch
+    numbers = model_numbers(cfg, cfg["num_hidden_layers"])
+    peak, peak_kind = peaks()
+    prefill_tokens = 2048
+    prefill_ms = prefill_run(arm, prefill_tokens, repeats=3, seed=100)
+    prefill_flops = 2 * numbers["linear_params"] * prefill_tokens - 2 * cfg["vocab_size"] * cfg["hidden_size"] * (prefill_tokens - 1) \
+        + numbers["attn_flops_per_pair"] * prefill_tokens * (prefill_tokens + 1) / 2
+    clocks = Clocks()
+    main = decode_run(arm, batch, context, args.steps, args.warmup, seed=7, clocks=clocks)
+    e2e = stream_run(arm, batch, context, args.steps, args.warmup, seed=31)
+
+    def roofline_of(run: dict, rows: int, steps: int) -> dict:
+        ms = run["device_ms"] / steps
+        moved = numbers["weight_bytes"] + rows * run["mean_context"] * numbers["kv_bytes_per_token"]
+        achieved = moved / (ms * 1e-3) / 1e9
+        return {"gb": round(moved / 1e9, 3), "ms_per_step": round(ms, 4), "achieved": round(achieved, 1),
+                "frac": round(achieved / peak["hbm_gbs"], 4), "mean_context": run["mean_context"]}
+
+    points, point_rooflines = {}, {}
+    few = max(8, min(args.steps, 64))
+    workloads = [(f"decode_b{b}", b, context, few) for b in (1, 64)] if not args.no_points else []
+    # the same with 2,048-token prompts and 256 decoded tokens a request: the steps timed are the last ones of the 256
+    workloads += [(f"decode_b{b}_prompt2048", b, 2048 + 256, min(256 - args.warmup, max(8, args.steps)))
+                  for b in (1, 8, 64)] if not args.no_points else []
+    for name, b, ctx, steps in workloads:
+        r = decode_run(arm, b, ctx, steps, args.warmup, seed=11 + b + ctx)
+        points[name] = round(r["tokens"] / r["device_ms"] * 1e3, 1)
+        point_rooflines[name] = roofline_of(r, b, steps)
+    ms_per_step = main["device_ms"] / args.steps
+    main_roofline = roofline_of(main, batch, args.steps)
+    return {
+        "metric": f"decode tok/s at batch {batch} (Qwen3-8B bf16, context {context}); points: batch 1/64 there, and batch "
+                  "1/8/64 with 2,048-token prompts + 256 decoded; prefill of 2,048 tokens",
+        "value": round(main["tokens"] / main["device_ms"] * 1e3, 1), "unit": "tok/s",
+        "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms_per_step, 4),
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+        "data": "synthetic: uniform random token ids, seeded random weights", "impl": arm.impl,
+        "config": {"model": "Qwen3-8B sizes", "layers": cfg["num_hidden_layers"], "layers_full": FULL_LAYERS,
+                   "hidden": cfg["hidden_size"], "heads": cfg["num_attention_heads"],
+                   "kv_heads": cfg["num_key_value_heads"], "head_dim": cfg["head_dim"],
+                   "intermediate": cfg["intermediate_size"], "vocab": cfg["vocab_size"], "global_batch": batch,
+                   "seq_len": context, "parallelism": "single GPU", "l2": "inputs larger than L2", "peaks": peak_kind,
+                   **engine_facts},
+        "e2e": {"value": round(e2e["value"], 1), "unit": "tok/s", "h2d_bytes_per_step": main["h2d_bytes_per_step"],
+                "d2h_bytes_per_step": main["d2h_bytes_per_step"],
+                "method": "add / step / has_work with host token lists, wall clock at the arrivals: W arrivals untimed "
+                          "after every request's first token, then batch * K tokens from the W-th arrival to the last",
+                "tokens": e2e["tokens"], "seconds": round(e2e["seconds"], 5), "clocks": e2e["clocks"],
+                "after_prefill": e2e["after_prefill"],
+                "step_loop_wall_value": round(main["tokens"] / main["wall_ms"] * 1e3, 1)},
+        "gpu_launches": main["launches"],
+        "prefill": {"value": round(prefill_tokens / prefill_ms * 1e3, 1), "tokens": prefill_tokens,
+                    "ms": round(prefill_ms, 3), "frac": round(prefill_flops / (prefill_ms * 1e-3) / (peak["bf16_tflops"] * 1e12), 4)},
+        "roofline": {"bound": "hbm", "achieved": main_roofline["achieved"], "peak": peak["hbm_gbs"], "unit": "GB/s",
+                     "frac": main_roofline["frac"], "gb": main_roofline["gb"]},
+        "points": points, "point_rooflines": point_rooflines, "clocks": main["clocks"],
+    }
+
+
 def run_ours(args) -> dict:
     import torch
     from holon_b200.engine import Engine, EngineConfig
@@ -387,67 +526,108 @@ def run_ours(args) -> dict:
                                  max_seqs=64, max_model_len=context, max_step_tokens=8192, seed=0,
                                  memory_fraction=args.memory_fraction, prefix_cache=False),
                     source=RandomSource(cfg, seed=2, device="cuda:0"))
-    numbers = model_numbers(cfg, args.layers)
-    peak, peak_kind = peaks()
-    prefill_tokens = 2048
+    print(f"bench: {engine.memory_report()}", file=sys.stderr, flush=True)
+    arm = Arm(engine)
     if args.only == "decode":
-        main = decode_run(engine, batch, context, args.steps, args.warmup, seed=7)
+        main = decode_run(arm, batch, context, args.steps, args.warmup, seed=7)
         return {"only": "decode", "layers": args.layers, "ms_per_step": round(main["device_ms"] / args.steps, 4)}
-    prefill_ms = prefill_run(engine, prefill_tokens, repeats=3, seed=100)
     if args.only == "prefill":
-        return {"only": "prefill", "layers": args.layers, "ms": round(prefill_ms, 3)}
-    prefill_flops = 2 * numbers["linear_params"] * prefill_tokens - 2 * cfg["vocab_size"] * cfg["hidden_size"] * (prefill_tokens - 1) \
-        + numbers["attn_flops_per_pair"] * prefill_tokens * (prefill_tokens + 1) / 2
-    clocks = Clocks()
-    main = decode_run(engine, batch, context, args.steps, args.warmup, seed=7, clocks=clocks)
-    e2e = generate_run(engine, batch, context, args.steps, seed=31)
-    points = {}
-    for b in (1, 64):
-        r = decode_run(engine, b, context, max(8, args.steps // 2), args.warmup, seed=11 + b)
-        points[f"decode_b{b}"] = round(r["tokens"] / r["device_ms"] * 1e3, 1)
-    for b in (1, 8, 64):                                             # the same with 2,048-token prompts and 256 decoded tokens
-        r = decode_run(engine, b, 2048 + 256, max(8, args.steps // 2), args.warmup, seed=41 + b)
-        points[f"decode_b{b}_prompt2048"] = round(r["tokens"] / r["device_ms"] * 1e3, 1)
-    ms_per_step = main["device_ms"] / args.steps
-    value = main["tokens"] / main["device_ms"] * 1e3
-    step_bytes = numbers["weight_bytes"] + batch * main["mean_context"] * numbers["kv_bytes_per_token"]
-    achieved = step_bytes / (ms_per_step * 1e-3) / 1e9
-    free, total = torch.cuda.mem_get_info()
-    return {
-        "metric": "decode tok/s at batch 8 (Qwen3-8B bf16, context 8192)", "value": round(value, 1), "unit": "tok/s",
-        "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms_per_step, 4),
-        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
-        "data": "synthetic: uniform random token ids, seeded random weights", "impl": "holon_b200",
-        "config": {"model": "Qwen3-8B sizes", "layers": args.layers, "layers_full": FULL_LAYERS,
-                   "hidden": cfg["hidden_size"], "heads": cfg["num_attention_heads"],
-                   "kv_heads": cfg["num_key_value_heads"], "head_dim": cfg["head_dim"],
-                   "intermediate": cfg["intermediate_size"], "vocab": cfg["vocab_size"], "global_batch": batch,
-                   "seq_len": context, "page_size": 64, "parallelism": "single GPU", "l2": "inputs larger than L2",
-                   "cuda_graphs": True, "overlap": engine.config.overlap, "prefix_cache": False, "peaks": peak_kind,
-                   "gemm": engine.built.ctx.kernels.gemm},
-        "e2e": {"value": round(e2e["value"], 1), "unit": "tok/s", "h2d_bytes_per_step": main["h2d_bytes_per_step"],
-                "d2h_bytes_per_step": main["d2h_bytes_per_step"], "method": "Engine.generate: t(K+1 tokens) - t(1 token), each the faster of two runs",
-                "step_loop_wall_value": round(main["tokens"] / main["wall_ms"] * 1e3, 1)},
-        "gpu_launches": main["launches"],
-        "prefill": {"value": round(prefill_tokens / prefill_ms * 1e3, 1), "tokens": prefill_tokens,
-                    "ms": round(prefill_ms, 3), "frac": round(prefill_flops / (prefill_ms * 1e-3) / (peak["bf16_tflops"] * 1e12), 4)},
-        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peak["hbm_gbs"], "unit": "GB/s",
-                     "frac": round(achieved / peak["hbm_gbs"], 4)},
-        "points": points, "clocks": main["clocks"],
-        "memory": {"weights_gb": round(engine.built.weight_bytes / 1e9, 2), "cache_gb": round(engine.built.cache.bytes / 1e9, 2),
-                   "device_free_gb": round(free / 1e9, 2)},
-    }
+        return {"only": "prefill", "layers": args.layers, "ms": round(prefill_run(arm, 2048, repeats=3, seed=100), 3)}
+    out = headline(arm, args, cfg, {"page_size": 64, "cuda_graphs": True, "overlap": engine.config.overlap,
+                                    "prefix_cache": False, "gemm": engine.built.ctx.kernels.gemm})
+    if not args.no_kernels:
+        from holon_b200.kernels.microbench import layer_table
+        peak, _ = peaks()
+        out["kernels"] = layer_table(engine.built.ctx.kernels, cfg, batch, context, 2048, peak["hbm_gbs"], peak["bf16_tflops"])
+    memory = engine.built.memory
+    free, _ = torch.cuda.mem_get_info()
+    out["memory"] = {"weights_gb": round(memory.weights / 1e9, 2), "cache_gb": round(memory.cache / 1e9, 2),
+                     "activations_gb": round((memory.activations or 0) / 1e9, 3), "graphs_gb": round((memory.graphs or 0) / 1e9, 3),
+                     "device_free_gb": round(free / 1e9, 2)}
+    return out
+
+
+def write_model_shards(cfg: dict, seed: int, folder: pathlib.Path, shard_bytes: int = 2 << 30) -> None:
+    """config.json and the seeded random weights of `cfg` as safetensors shards of about `shard_bytes` each (the
+    tensors are made on the GPU one by one, so the host never holds more than a shard)."""
+    import torch
+    from safetensors.torch import save_file
+    from holon_b200.weights import RandomSource
+    folder.mkdir(parents=True, exist_ok=True)
+    (folder / "config.json").write_text(json.dumps(cfg))
+    shard, held, index = {}, 0, 0
+    for name, tensor in RandomSource(cfg, seed=seed, device="cuda:0" if torch.cuda.is_available() else "cpu").tensors():
+        shard[name] = tensor.cpu().contiguous()
+        held += tensor.numel() * tensor.element_size()
+        if held >= shard_bytes:
+            save_file(shard, str(folder / f"model-{index:05d}.safetensors"))
+            shard, held, index = {}, 0, index + 1
+    if shard:
+        save_file(shard, str(folder / f"model-{index:05d}.safetensors"))
+
+
+def reference_plugins(ref: pathlib.Path, testing: bool = False):
+    """The reference's plugin set, made from the `plugin.toml` manifests of its installed packages (its own
+    `discover()` reads the same manifests through entry points, which a plain copy of the packages does not have).
+    Its test-only plugins (CPU oracle kernels) stay out unless `testing`: a user's install has none of them."""
+    from holon.api import Manifest
+    from holon.core.plugins import Installed, PluginSet
+    installed = {}
+    for root in (ref / "holon_std", ref / "holon_plugins") + ((ref / "holon_testing",) if testing else ()):
+        for toml in sorted(root.rglob("plugin.toml")):
+            if "vendor" in toml.parts:
+                continue
+            manifest = Manifest.load(toml)
+            installed[manifest.name] = Installed(manifest, ".".join(toml.parent.relative_to(root.parent).parts), toml.parent)
+    return PluginSet(installed)
 
 
 def run_reference(args) -> dict:
-    """The reference arm. mxinO/holon cannot be installed offline here (its build backend, hatchling, is neither
-    installed nor in the wheelhouse), so there is nothing under baseline/_ref to run."""
+    """The reference arm: the unmodified reference from baseline/_ref, driven through its own `Engine`, `EngineConfig`
+    and `SamplingParams` by the loops that time this engine, on the same weights, prompts and sizes. Nothing of this
+    package is on its path but the weight files, written once to a temporary folder."""
+    import shutil
+    import tempfile
     ref = ROOT / "baseline" / "_ref"
     if not (ref / "holon").is_dir():
-        return {"impl": "reference", "unavailable": "mxinO/holon is not installed under baseline/_ref: the offline "
-                                                    "pip install fails for want of its build backend (hatchling)"}
-    return {"impl": "reference", "unavailable": "baseline/_ref exists but this benchmark has no driver for it; the "
-                                                "offline install was not possible when bench.py was written"}
+        return {"impl": "reference", "unavailable": "baseline/_ref holds no copy of mxinO/holon: run "
+                                                    "`python baseline/install_ref.py <checkout of the reference>` first"}
+    if args.only != "all":
+        return {"impl": "reference", "unavailable": f"--only {args.only} is a mode of this engine's arm alone"}
+    folder = pathlib.Path(tempfile.mkdtemp(prefix="holon_b200_reference_model_"))
+    engine = None
+    stage = "importing the reference"
+    try:
+        import torch
+        sys.path.insert(0, str(ref))
+        from holon.core.engine import Engine, EngineConfig
+        plugins = reference_plugins(ref)
+        stage = "writing the model folder"
+        cfg = dict(QWEN3_8B, num_hidden_layers=args.layers)
+        write_model_shards(cfg, 2, folder)
+        torch.cuda.empty_cache()
+        stage = "building the reference's engine"
+        engine = Engine(EngineConfig(model=str(folder), device="cuda:0", dtype=torch.bfloat16, max_seqs=64,
+                                     max_model_len=args.context, max_step_tokens=8192, prefix_cache=False,
+                                     memory_fraction=args.memory_fraction), plugins)
+        stage = "running the reference's engine"
+        facts = {"page_size": engine.cfg.page_size, "cuda_graphs": engine.cfg.cuda_graphs, "overlap": engine.cfg.overlap,
+                 "prefix_cache": engine.cfg.prefix_cache}
+        out = headline(ReferenceArm(engine), args, cfg, facts)     # (its own calls switch gradients off)
+        selected = getattr(getattr(engine, "ctx", None), "selected", None)
+        if selected:
+            out["reference_kernels"] = {str(k): str(v) for k, v in dict(selected).items()}
+        return out
+    except Exception as e:                                           # what the reference raised here, in its own words
+        text = " ".join(f"{type(e).__name__}: {e}".split())
+        return {"impl": "reference", "unavailable": f"{stage} failed on this machine: {text[:600]}"}
+    finally:
+        try:
+            if engine is not None:
+                engine.close()
+        except Exception:
+            pass
+        shutil.rmtree(folder, ignore_errors=True)
 
 
 def main() -> int:
@@ -468,9 +648,11 @@ def main() -> int:
                          "sizes: the workloads of the Qwen3-32B and Qwen3-0.6B configurations (--sizes); "
                          "shared_prompt: 16 requests with a common 2,048-token beginning, with and without the prefix cache")
     ap.add_argument("--sizes", default="32b", choices=("32b", "0.6b"), help="with --only sizes: which configuration")
+    ap.add_argument("--no-points", action="store_true", help="leave out the points at other batch sizes and contexts")
+    ap.add_argument("--no-kernels", action="store_true", help="leave out the per-kernel table")
     args = ap.parse_args()
     if args.gpus != 1:
-        print(f"holon_b200 is a single-GPU engine: --gpus {args.gpus} is not supported")
+        print(f"this benchmark measures one GPU: --gpus {args.gpus} is not supported (holon_b200 is a single-GPU engine)")
         return 2
     if args.warmup < 3:
         args.warmup = 3

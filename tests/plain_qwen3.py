@@ -162,10 +162,14 @@ def _mix32(x: int) -> int:
 
 
 def uniform(seed: int, position: int) -> float:
-    """The one uniform of (seed, position of the token being drawn) (std/holon_std/sampling/sampler.py:33-40)."""
+    """The one uniform of (seed, position of the token being drawn) (std/holon_std/sampling/sampler.py:33-40). The
+    reference adds the half in 32-bit floating point: from 2^23 on the sum is a tie and rounds to the even neighbour,
+    so the value is the reference's bit for bit only if the sum is taken in 32-bit here too."""
+    import numpy as np
     h = _mix32(seed & _M32) ^ ((seed >> 32) & _M32) ^ _mix32(position & _M32)
     h = _mix32(h)
-    return min(((h >> 8) + 0.5) * 2.0 ** -24, 1 - 2.0 ** -24)
+    u = (np.float32(h >> 8) + np.float32(0.5)) * np.float32(2.0 ** -24)
+    return min(float(u), 1 - 2.0 ** -24)
 
 
 def distribution(logits, temperature, top_k=0, top_p=1.0, min_p=0.0):

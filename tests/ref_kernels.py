@@ -144,7 +144,7 @@ class RefKernels:
             q = torch.where(keep, x, float("-inf")).softmax(-1)
             lo, hi, pos = int(seed_lo[r]) & _M32, int(seed_hi[r]) & _M32, int(position[r]) & _M32
             h = _mix32(_mix32(lo) ^ hi ^ _mix32(pos))
-            u = min(((h >> 8) + 0.5) * 2.0 ** -24, 1 - 2.0 ** -24)
+            u = min(float((torch.tensor(float(h >> 8), dtype=torch.float32) + 0.5) * 2.0 ** -24), 1 - 2.0 ** -24)
             c = q.cumsum(-1)
             i = int(torch.searchsorted(c, torch.tensor([u * float(c[-1])], dtype=c.dtype), right=True)[0])
             tokens[r] = min(i, q.numel() - 1)

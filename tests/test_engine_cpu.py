@@ -322,3 +322,25 @@ def test_block_table_rows_travel_as_copies_with_the_step(tmp_path):
     b.runner.step([StepEntry(slot, [1, 2, 3, 4, 5, 6], 0)])
     assert group.table_device[slot].tolist() == group.table[slot].tolist()
     assert b.runner.uploader.bytes_last >= 4 * (1 + group.max_pages)  # counted with the step's upload
+
+
+@pytest.mark.parametrize("name", ["a", "b"])
+def test_the_engine_generates_what_the_reference_engine_generated(tmp_path, name):
+    """The workloads that the reference's own engine ran on the CPU (tests/golden/make_engine_golden.py): the same
+    weights, prompts, pages, portions beside decoding requests and seeded temperature sampling give the same tokens,
+    also in a pool so small that requests are preempted and computed again."""
+    from helpers import golden_engine, golden_folder
+    golden = golden_engine()
+    folder, config, _ = golden_folder(tmp_path, name, golden)
+    work = golden["engine"][name]
+    w = work["workload"]
+    page_bytes = config["num_hidden_layers"] * 2 * config["num_key_value_heads"] * w["page_size"] * config["head_dim"] * 4
+    for pages, overlap in ((64, False), (-(-w["max_model_len"] // w["page_size"]) + 2, True)):
+        engine = Engine(EngineConfig(model=str(folder), device="cpu", dtype="float32", page_size=w["page_size"],
+                                     max_seqs=w["max_seqs"], max_model_len=w["max_model_len"], prefix_cache=False,
+                                     max_step_tokens=w["max_step_tokens"], chunk_with_decode=w["chunk_with_decode"],
+                                     state_memory=page_bytes * (pages + 1), overlap=overlap), kernels=RefKernels())
+        params = [SamplingParams(temperature=w["temperature"], seed=s, max_tokens=w["max_tokens"]) for s in w["seeds"]]
+        assert engine.generate(work["prompts"], params) == work["tokens"]
+        assert engine.stats()["mixed_steps"] > 0
+        engine.built.cache.check()

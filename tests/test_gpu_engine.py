@@ -357,3 +357,44 @@ def test_memory_is_measured_at_the_start(model):
     assert len(engine.generate([prompts[1]], SamplingParams(temperature=0.0, max_tokens=4))[0]) == 4
     fixed = engine_of(folder, "bfloat16")
     assert fixed.built.memory.activations is None and "not measured" in fixed.memory_report()
+
+
+@pytest.mark.parametrize("name", ["a", "b"])
+@pytest.mark.parametrize("graphs", [True, False])
+def test_the_engine_generates_what_the_reference_engine_generated(tmp_path, name, graphs):
+    """The workloads that the reference's own engine ran on its CPU path (tests/golden/make_engine_golden.py), here on
+    the GPU in true 32-bit: the same weights, prompts, pages, portions beside decoding requests and seeded temperature
+    sampling give the same tokens, with the sampling kernel's hash and inverse-CDF draw."""
+    from helpers import golden_engine, golden_folder
+    golden = golden_engine()
+    folder, config, _ = golden_folder(tmp_path, name, golden)
+    work = golden["engine"][name]
+    w = work["workload"]
+    engine = Engine(EngineConfig(model=str(folder), dtype="float32", page_size=w["page_size"], max_seqs=w["max_seqs"],
+                                 max_model_len=w["max_model_len"], max_step_tokens=w["max_step_tokens"], prefix_cache=False,
+                                 chunk_with_decode=w["chunk_with_decode"], state_memory=4 << 20, cuda_graphs=graphs))
+    params = [SamplingParams(temperature=w["temperature"], seed=s, max_tokens=w["max_tokens"]) for s in w["seeds"]]
+    assert engine.generate(work["prompts"], params) == work["tokens"]
+    engine.built.cache.check()
+
+
+def test_the_sampling_kernel_draws_what_the_reference_sampler_drew():
+    """`hb_sample` on the logits rows, temperatures, seeds and positions of the recorded draws."""
+    import sys
+    import pathlib
+    import torch
+    from helpers import golden_engine
+    from holon_b200.kernels import load_kernels
+    sys.path.insert(0, str(pathlib.Path(__file__).resolve().parent / "golden"))
+    import make_engine_golden as recorded
+    golden, kernels = golden_engine(), load_kernels("cuda:0")
+    logits = recorded.draw_logits().to("cuda:0")
+    rows = logits.shape[0]
+    full = lambda v, dt: torch.full((rows,), v, dtype=dt, device="cuda:0")               # noqa: E731
+    as_i32 = lambda v: torch.tensor([v], dtype=torch.int64).to(torch.int32).repeat(rows).to("cuda:0")   # noqa: E731
+    for case in golden["draws"]:
+        tokens = torch.zeros(rows, dtype=torch.int32, device="cuda:0")
+        kernels.sample(tokens, logits, full(case["temperature"], torch.float32), full(0, torch.int32),
+                       full(1.0, torch.float32), full(0.0, torch.float32), as_i32(case["seed"] & 0xFFFFFFFF),
+                       as_i32(case["seed"] >> 32), full(case["position"], torch.int32), False)
+        assert tokens.tolist() == case["tokens"], case

@@ -60,3 +60,46 @@ def test_distribution_filters():
     assert (p > 0).tolist() == [True, False, False, False, True]
     assert plain.draw(torch.tensor([0.0, 0.5, 0.0, 0.5]), 0.25) == 1
     assert plain.draw(torch.tensor([0.0, 0.5, 0.0, 0.5]), 0.75) == 3
+
+
+# ---------------------------------------------------------------- sampling and generation against the reference's own
+
+def test_uniform_and_draws_match_the_reference_sampler():
+    """`plain.uniform` and `plain.sample` against the values the reference's sampler produced (tests/golden/
+    make_engine_golden.py): the hash of (seed, position) for seeds on both sides of 2^32, and the inverse-CDF draw at
+    two temperatures. The plain kernel table's sampler is held to the same draws."""
+    import sys
+    from helpers import golden_engine
+    sys.path.insert(0, str(GOLDEN))
+    import make_engine_golden as recorded
+    from ref_kernels import RefKernels
+    golden = golden_engine()
+    table = iter(golden["uniform"])
+    for seed in golden["seeds"]:
+        for position in golden["positions"]:
+            assert abs(plain.uniform(seed, position) - next(table)) < 1e-12, (seed, position)
+    logits = recorded.draw_logits()
+    rows = logits.shape[0]
+    kernels = RefKernels()
+    for case in golden["draws"]:
+        t, seed, position = case["temperature"], case["seed"], case["position"]
+        assert [plain.sample(row, t, seed, position) for row in logits] == case["tokens"], case
+        tokens = torch.zeros(rows, dtype=torch.int32)
+        full = lambda v, dt: torch.full((rows,), v, dtype=dt)                   # noqa: E731
+        as_i32 = lambda v: torch.tensor([v], dtype=torch.int64).to(torch.int32).repeat(rows)   # noqa: E731
+        kernels.sample(tokens, logits, full(t, torch.float32), full(0, torch.int32), full(1.0, torch.float32),
+                       full(0.0, torch.float32), as_i32(seed & 0xFFFFFFFF), as_i32(seed >> 32), full(position, torch.int32), False)
+        assert tokens.tolist() == case["tokens"], case
+
+
+@pytest.mark.parametrize("name", ["a", "b"])
+def test_plain_generation_matches_the_reference_engine(name, tmp_path):
+    """Whole forward passes and `plain.sample`, token by token, against what the reference's engine generated with its
+    paged cache, prompt portions beside decoding requests and seeded temperature sampling."""
+    from helpers import golden_engine, golden_folder
+    golden = golden_engine()
+    _, config, weights = golden_folder(tmp_path, name, golden)
+    work = golden["engine"][name]
+    for prompt, seed, want in zip(work["prompts"], work["workload"]["seeds"], work["tokens"]):
+        got = plain.generate(config, weights, prompt, work["workload"]["max_tokens"], work["workload"]["temperature"], seed)
+        assert got == want
