@@ -1,6 +1,6 @@
 """Trace replay: feeds given token ids through the model step by step and writes logits. It samples nothing.
 
-    bin/trace_run --model DIR --dtype bfloat16|float32 --out DIR --max-tokens N
+    bin/trace_run --model DIR --dtype bfloat16|float32 --out DIR --max-tokens N [--page-size P]
 
 Standard input brings one JSON object a line:
 
@@ -11,7 +11,8 @@ ones generation uses; this file has no forward pass of its own). A request is ad
 and continues where it stopped; ids listed under `end` give back what they hold after the step. For a step that
 wants logits, `DIR/<step>.f32` receives them as little-endian float32 [wanted, vocab], in the order of the entries
 and of each entry's `want`. After every step a line `done <step>` is printed and flushed. The cache pool holds
-`--max-tokens` tokens, each live request's count rounded up to whole pages of 64, so pages are used again.
+`--max-tokens` tokens, each live request's count rounded up to whole pages of `--page-size` tokens (64 unless given),
+so pages are used again.
 
 The reference has no such program; the nearest are its teacher-forced scoring and its per-step snapshot trace
 (judge/holon_judge/engine.py:49-80, judge/holon_judge/snapshot.py:59-99).
@@ -71,13 +72,16 @@ def main(argv=None) -> int:
     ap.add_argument("--out", required=True, help="folder that receives <step>.f32")
     ap.add_argument("--max-tokens", required=True, type=int,
                     help="the most tokens live requests hold at any time (each rounded up to a multiple of 64)")
+    ap.add_argument("--page-size", type=int, default=PAGE_SIZE, help="tokens per page of the cache (default: 64)")
     ap.add_argument("--device", default="cuda:0")
     args = ap.parse_args(argv)
+    if args.page_size < 1:
+        ap.error("--page-size must be at least 1")
     out = pathlib.Path(args.out)
     out.mkdir(parents=True, exist_ok=True)
     import torch
     with torch.inference_mode():
-        replayer = Replayer(args.model, args.dtype, args.max_tokens, args.device)
+        replayer = Replayer(args.model, args.dtype, args.max_tokens, args.device, page_size=args.page_size)
         for line in sys.stdin:
             line = line.strip()
             if not line:

@@ -14,7 +14,7 @@ from holon_b200.engine import Engine, EngineConfig, SamplingParams
 pytestmark = pytest.mark.gpu
 
 
-@pytest.fixture(scope="module", params=["a", "b"])
+@pytest.fixture(scope="module", params=["a", "b", "c"])
 def model(request, tmp_path_factory):
     folder = make_folder(tmp_path_factory.mktemp("models"), request.param)
     config, weights = plain.read_folder(folder)

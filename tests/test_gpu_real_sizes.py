@@ -70,3 +70,68 @@ def test_prompt_portions_and_decoding_at_real_sizes(case, dtype):
         assert diff.mean() <= 1.5 * floor.mean(), (float(diff.mean()), float(floor.mean()))
     b.cache.release(slot)
     b.cache.check()
+
+
+@pytest.fixture(scope="module")
+def mixed_case():
+    source = Held(CONFIG, seed=2)
+    prompts = {rid: random_prompt(CONFIG["vocab_size"], n, 20 + i) for i, (rid, n) in
+               enumerate((("a", 268), ("b", 207), ("c", 40), ("d", 60)))}
+    weights = {k: v.float() for k, v in source.kept.items()}
+    want = {}
+    for rid, ids in prompts.items():
+        exact = plain.forward(CONFIG, weights, ids)
+        with plain.rounding(torch.bfloat16):
+            want[rid] = (exact, plain.forward(CONFIG, weights, ids))
+    del weights
+    return source, prompts, want
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_mixed_steps_at_real_sizes(mixed_case, dtype):
+    """Up to four live requests at the production layer sizes, decode rows beside prompt portions in one step, on pages
+    of 64 in a pool of eleven, so that the last request runs in a page another one gave back. The steps are cut to
+    meet the kernels' own borders: a portion of 260 tokens (more than the 256 queries of the largest attention tile),
+    one of 200 beside a decode row (more than the 192 rows from which SwiGLU's product runs on CTA pairs), steps of
+    16 and of 17 tokens in all (the row limit of the weight-streaming products), and portions of two tokens."""
+    from replay_tools import compare
+    source, p, want = mixed_case
+    b = build(source, dtype=dtype, device="cuda:0", page_size=64, max_seqs=4, max_model_len=320, max_step_tokens=320,
+              pages=11)
+    trace = [
+        ([("a", 260)], []),
+        ([("a", 1), ("b", 200)], []),
+        ([("a", 1), ("b", 1), ("c", 14)], []),                       # 16 tokens in all
+        ([("a", 1), ("b", 1), ("c", 15)], []),                       # 17
+        ([("a", 1), ("b", 1), ("c", 11)], ["c"]),
+        ([("a", 1), ("b", 1), ("d", 2)], []),                        # d takes the page c gave back
+        ([("a", 1), ("b", 1), ("d", 30)], []),
+        ([("a", 1), ("b", 1), ("d", 28)], ["d"]),
+        ([("a", 1), ("b", 1)], ["a", "b"]),
+    ]
+    slots, at, got = {}, {rid: 0 for rid in p}, {}
+    pages_of_c = None
+    for step, end in trace:
+        entries = []
+        for rid, n in step:
+            if rid not in slots:
+                slots[rid] = b.cache.admit()
+            assert b.cache.reserve(slots[rid], at[rid] + n)
+            entries.append(StepEntry(slots[rid], p[rid][at[rid]:at[rid] + n], at[rid], range(n)))
+        logits = b.runner.step(entries).float().cpu()
+        k = 0
+        for rid, n in step:
+            for _ in range(n):
+                got[(rid, at[rid])] = logits[k]
+                at[rid], k = at[rid] + 1, k + 1
+        group = b.cache.groups[0]
+        if "c" in end:
+            pages_of_c = set(group.table[slots["c"], :1].tolist())
+        if ("d", 2) in step:
+            assert set(group.table[slots["d"], :1].tolist()) == pages_of_c
+        for rid in end:
+            b.cache.release(slots.pop(rid))
+        b.cache.check()
+    assert at == {rid: len(ids) for rid, ids in p.items()} and not b.cache.live
+    compare(got, want, dtype)
+    assert b.ctx.kernels.tcgen05_status() == 0
