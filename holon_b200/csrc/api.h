@@ -131,6 +131,21 @@ int hb_qkv_rope_skinny_linked(void* q_out, const void* x, const void* w, int m, 
                               int page_size, int heads, int kv_heads, int head_dim, const float* ss_in, int parts_in,
                               float eps_in, int dim_in, hb_stream stream);
 
+// Several products of the same few rows, one after the other, as phases of ONE persistent kernel (csrc/gemm_chain.cu):
+// the weight stream keeps running across them. A phase is a product of hb_gemm_bf16_skinny_linked (modes 0, 1, 3, same
+// meanings of the fields); a phase may read what an earlier phase wrote. sync: two words, zero before the first
+// launch; scratch: `slots` x 512 floats; flags: `slots` words, zero before the first launch; none of them may be
+// shared with a launch that runs at the same time. hb_gemm_chain_capacity: the most CTAs a launch can have.
+typedef struct {
+    const void* w; const void* x; void* out; float* h; const void* next_weight; float* ss_out; const float* ss_in;
+    int n, k, mode, inter, out_f32, next_weight_f32, parts_in, dim_in;
+    float next_offset, eps_in;
+} hb_chain_phase;
+int hb_gemm_chain_capacity(void);
+int hb_gemm_chain(const hb_chain_phase* phases, int n_phases, int m, unsigned int* sync, float* scratch,
+                  unsigned int* flags, int slots, int cooperative, hb_stream stream);
+int hb_gemm_chain_status(unsigned int* status);
+
 // bfloat16 product on tcgen05 tensor cores with TMA loads and the accumulator in tensor memory (128 x 256 tiles).
 // Same arguments and modes as hb_gemm_bf16_skinny, any m. hb_gemm_tcgen05_status synchronises the device and
 // returns (and clears) a status word that is non-zero if a bounded wait inside the kernel ever gave up.

@@ -1,5 +1,6 @@
-// The host's view of the kernels' bounded waits. Every wait on an mbarrier inside the tcgen05 kernels gives up after a
-// fixed number of polls and records where (tcgen05.cuh). Reading those words needs a copy from the device; a serving
+// The host's view of the kernels' bounded waits. Every wait inside a kernel (on an mbarrier in the tcgen05 kernels, on
+// the grid barrier and the hand-over flags of the chained products) gives up after a fixed number of polls and records
+// where (tcgen05.cuh). Reading those words needs a copy from the device; a serving
 // loop cannot afford one per step. So one word of page-locked host memory, mapped into the device's address space, is
 // handed to every kernel file as its mirror: a wait that gives up writes its code there as well, and the host reads
 // that word, in its own memory, whenever a step's completion event has fired.
@@ -8,6 +9,7 @@
 extern "C" int hb_attention_tcgen05_status_mirror(unsigned int* word);
 extern "C" int hb_gemm_tcgen05_status_mirror(unsigned int* word);
 extern "C" int hb_gemm_tcgen05_pair_status_mirror(unsigned int* word);
+extern "C" int hb_gemm_chain_status_mirror(unsigned int* word);
 HB_DEFINE_STATUS_MIRROR(hb_status_selftest_mirror)
 
 static unsigned int* g_word_host = nullptr;
@@ -23,7 +25,8 @@ extern "C" int hb_status_word(unsigned int** host) {
         unsigned int* device = nullptr;
         HB_CUDA(cudaHostGetDevicePointer((void**)&device, word, 0));
         if (hb_attention_tcgen05_status_mirror(device) || hb_gemm_tcgen05_status_mirror(device) ||
-            hb_gemm_tcgen05_pair_status_mirror(device) || hb_status_selftest_mirror(device))
+            hb_gemm_tcgen05_pair_status_mirror(device) || hb_gemm_chain_status_mirror(device) ||
+            hb_status_selftest_mirror(device))
             return HB_ERR_CUDA;
         g_word_host = word;
     }

@@ -29,6 +29,14 @@ def _code(t: torch.Tensor) -> int:
         raise KernelError(f"kernels take float32 and bfloat16 tensors, not {t.dtype}") from None
 
 
+class _ChainPhase(ctypes.Structure):
+    """hb_chain_phase of csrc/api.h."""
+
+    _fields_ = [(name, ctypes.c_void_p) for name in ("w", "x", "out", "h", "next_weight", "ss_out", "ss_in")] \
+        + [(name, ctypes.c_int) for name in ("n", "k", "mode", "inter", "out_f32", "next_weight_f32", "parts_in", "dim_in")] \
+        + [("next_offset", ctypes.c_float), ("eps_in", ctypes.c_float)]
+
+
 class CudaKernels:
     name = "cuda sm_100a"
 
@@ -72,6 +80,22 @@ class CudaKernels:
         self.sms = torch.cuda.get_device_properties(self.device).multi_processor_count
         self.decode_ctas = None               # tests: a fixed number of CTAs for the balanced kernel
         self.prefill_tile = None              # tests, microbench: 128 or 256 queries a CTA of the tcgen05 prefill kernel
+        # Decode steps, with HOLON_B200_CHAIN=1: the products of a layer that follow one another on the same few rows
+        # (the mixer's last, the feed-forward's two, the next mixer's first) are queued and run as phases of one
+        # persistent kernel (csrc/gemm_chain.cu); every other call of this table runs what is queued first. Default: every
+        # product its own launch, which is faster as measured (102 us against 89 us for a layer's four at 8B sizes).
+        self.chain = os.environ.get("HOLON_B200_CHAIN", "0") != "0"
+        self.chain_cooperative = os.environ.get("HOLON_B200_CHAIN_COOPERATIVE", "1") != "0"
+        self._pending: list = []              # (phase, tensors it names) of products queued, in order
+        self.chain_launches = self.chain_phases = 0
+        self.lib.hb_gemm_chain_capacity.restype = ctypes.c_int
+        with torch.cuda.device(self.device):
+            self._chain_slots = int(self.lib.hb_gemm_chain_capacity())
+        if self._chain_slots < 1:
+            raise KernelError("hb_gemm_chain_capacity: the device runs no CTA of the chained products' kernel")
+        self._chain_sync = torch.zeros(2, dtype=torch.int32, device=self.device)
+        self._chain_flags = torch.zeros(self._chain_slots, dtype=torch.int32, device=self.device)
+        self._chain_scratch = torch.empty(self._chain_slots * 512, dtype=torch.float32, device=self.device)
         # One word of page-locked host memory that a kernel's bounded wait writes when it gives up (csrc/status.cu)
         word = ctypes.POINTER(ctypes.c_uint)()
         with torch.cuda.device(self.device):
@@ -81,6 +105,11 @@ class CudaKernels:
 
     # ------------------------------------------------------------------ plumbing
     def _call(self, name: str, *args) -> None:
+        if self._pending:                      # what is queued comes first: this call may read what it writes
+            self.flush()
+        self._launch(name, *args)
+
+    def _launch(self, name: str, *args) -> None:
         fn = self._fn.get(name)
         if fn is None:
             fn = self._fn[name] = getattr(self.lib, name)
@@ -89,6 +118,45 @@ class CudaKernels:
         self.launches += 1
         if code:
             raise KernelError(f"{name}: {self.lib.hb_last_error().decode()}")
+
+    # ---- products queued for one persistent kernel (decode steps)
+    MAX_CHAIN = 8                              # phases a launch takes (csrc/gemm_chain.cu)
+
+    def _queue(self, *, w, x, out, mode: int, n: int, inter: int = 0, h=None, next_weight=None, next_offset: float = 0.0,
+               ss_out=None, scaled=None) -> None:
+        if len(self._pending) >= self.MAX_CHAIN:
+            self.flush()
+        y = scaled.y if scaled is not None else x
+        phase = _ChainPhase(w=w.data_ptr(), x=y.data_ptr(), out=out.data_ptr(), h=h.data_ptr() if h is not None else None,
+                            next_weight=next_weight.data_ptr() if next_weight is not None else None,
+                            ss_out=ss_out.data_ptr() if ss_out is not None else None,
+                            ss_in=scaled.ss.data_ptr() if scaled is not None else None, n=n, k=y.shape[1], mode=mode,
+                            inter=inter, out_f32=int(out.dtype == torch.float32),
+                            next_weight_f32=int(next_weight is not None and next_weight.dtype == torch.float32),
+                            parts_in=scaled.ss.shape[0] if scaled is not None else 0,
+                            dim_in=scaled.dim if scaled is not None else 0, next_offset=float(next_offset),
+                            eps_in=float(scaled.eps) if scaled is not None else 0.0)
+        keep = (w, x, out, h, next_weight, ss_out, scaled)            # (the tensors stay alive until the launch)
+        if self._pending and self._pending[0][2] != y.shape[0]:
+            self.flush()
+        self._pending.append((phase, keep, y.shape[0]))
+
+    def flush(self) -> None:
+        """Launches what is queued: one persistent kernel for all of it. Everything this table's other calls do comes
+        after it; whoever reads a queued product's output by other means (torch operations) calls this first."""
+        if not self._pending:
+            return
+        pending, self._pending = self._pending, []
+        phases = (_ChainPhase * len(pending))(*[p for p, _, _ in pending])
+        self._launch("hb_gemm_chain", phases, len(pending), pending[0][2], self._p(self._chain_sync),
+                     self._p(self._chain_scratch), self._p(self._chain_flags), self._chain_slots, int(self.chain_cooperative))
+        self.chain_launches += 1
+        self.chain_phases += len(pending)
+
+    def _chains(self, m: int, k: int, *tensors) -> bool:
+        """Whether a product of `m` rows over `k` columns of these bfloat16 tensors may be queued."""
+        return self.chain and 0 < m <= self.SKINNY_ROWS and k % 8 == 0 \
+            and all(t.dtype == torch.bfloat16 and t.data_ptr() % 16 == 0 for t in tensors)
 
     def _stream(self) -> int:
         """The handle of torch's current stream on the device (a few hundred kernels a step ask for it)."""
@@ -187,6 +255,14 @@ class CudaKernels:
             raise KernelError("qkv_rope: kv must be [pages, 2, kv_heads, page_size, head_dim], bfloat16")
         if q_weight is not None and q_weight.dtype != k_weight.dtype:
             raise KernelError("qkv_rope: the two norm weights must have one dtype")
+        if self._pending and scaled is not None and self._chains(t, k, x, weight):
+            # the product that made these rows is still queued: this one joins it as a plain product, so that the
+            # weights of both stream through one kernel, and the norm, rotation and cache write run behind it
+            qkv = torch.empty((t, weight.shape[0]), dtype=torch.bfloat16, device=self.device)
+            self._queue(w=weight, x=x, out=qkv, mode=0, n=weight.shape[0], scaled=scaled)
+            self.qk_norm_rope_kv_write(q_out, qkv, positions, table, rotary_dim, q_weight, k_weight, eps, offset, kv,
+                                       write_index, heads, kv_heads, head_dim)
+            return True
         self._call("hb_qkv_rope_skinny_linked", self._p(q_out), self._p(x), self._p(weight), t, k,
                    self._i32(positions, "positions"), self._p(table), table.shape[0], self._p(q_weight), self._p(k_weight),
                    int(q_weight is not None and q_weight.dtype == torch.float32), ctypes.c_float(eps),
@@ -376,6 +452,9 @@ class CudaKernels:
         y = torch.empty((m, n), dtype=torch.bfloat16, device=self.device)
         parts = -(-n // 16)
         ss = torch.empty((parts, 16), dtype=torch.float32, device=self.device)
+        if self._chains(m, k, x, weight, y) and norm_weight.dtype in (torch.bfloat16, torch.float32):
+            self._queue(w=weight, x=x, out=y, mode=3, n=n, h=h, next_weight=norm_weight, next_offset=offset, ss_out=ss)
+            return Scaled(y, ss, float(eps), n)
         self._call("hb_gemm_bf16_skinny_linked", self._p(y), 0, self._p(x), self._p(weight), m, n, k, 3, 0, self._p(h),
                    self._p(norm_weight), int(norm_weight.dtype == torch.float32), ctypes.c_float(offset), self._p(ss),
                    None, 0, ctypes.c_float(0.0), 0)
@@ -388,6 +467,9 @@ class CudaKernels:
         m, k = y.shape
         if m > self.SKINNY_ROWS or k % 8 or y.dtype != torch.bfloat16 or weight.dtype != torch.bfloat16 or weight.shape[1] != k:
             raise KernelError("a product of unscaled rows takes up to SKINNY_ROWS bfloat16 rows of a multiple of 8 columns")
+        if self._chains(m, k, y, weight) and out.dtype in (torch.bfloat16, torch.float32) and (mode == 0 or out.dtype == torch.bfloat16):
+            self._queue(w=weight, x=x, out=out, mode=mode, n=weight.shape[0], inter=inter, scaled=x)
+            return
         self._call("hb_gemm_bf16_skinny_linked", self._p(out), int(out.dtype == torch.float32), self._p(y), self._p(weight),
                    m, weight.shape[0], k, mode, inter, None, None, 0, ctypes.c_float(0.0), None, self._p(x.ss),
                    x.ss.shape[0], ctypes.c_float(x.eps), x.dim)
@@ -402,6 +484,11 @@ class CudaKernels:
         n = weight.shape[0]
         if weight.shape != (n, k) or out.shape != (m, n) or x.dtype != weight.dtype:
             raise KernelError(f"linear: x {tuple(x.shape)} · w {tuple(weight.shape)}ᵀ -> out {tuple(out.shape)} do not fit")
+        if self._pending:
+            if self._chains(m, k, x, weight) and out.data_ptr() % 16 == 0 and self._pending[0][2] == m:
+                self._queue(w=weight, x=x, out=out, mode=0, n=n)   # (the last of a run of products: with them, then out)
+                return self.flush()
+            self.flush()
         if x.dtype == torch.float32:
             if out.dtype != torch.float32:
                 raise KernelError("linear: a float32 product writes float32")
@@ -445,15 +532,20 @@ class CudaKernels:
         self._call("hb_status_selftest", int(polls))
 
     def tcgen05_status(self) -> int:
-        """0, or which bounded wait inside a tcgen05 kernel (product or attention) gave up (synchronises the device;
-        clears the kernels' words and the host's)."""
+        """0, or which bounded wait inside a kernel (a tcgen05 product or attention, the chained products) gave up
+        (synchronises the device; clears the kernels' words and the host's). After a wait of the chained products gave
+        up their barrier and flags are put back to zero, so that the next launch starts clean."""
         out = 0
-        for name in ("hb_gemm_tcgen05_status", "hb_gemm_tcgen05_pair_status", "hb_attention_tcgen05_status"):
+        for name in ("hb_gemm_tcgen05_status", "hb_gemm_tcgen05_pair_status", "hb_attention_tcgen05_status",
+                     "hb_gemm_chain_status"):
             status = ctypes.c_uint(0)
             if getattr(self.lib, name)(ctypes.byref(status)):
                 raise KernelError(self.lib.hb_last_error().decode())
             out = out or status.value
         self.clear_status()
+        if out:
+            self._chain_sync.zero_()
+            self._chain_flags.zero_()
         return out
 
     def swiglu_gate_up(self, out, x, weight) -> None:

@@ -246,9 +246,51 @@ def layer_table(k, cfg: dict, batch: int, context: int, prefill_tokens: int, hbm
     return out
 
 
+def chain(k, args) -> None:
+    """A decode layer's four products on `--rows` rows (o_proj + residual + norm, gate/up + SwiGLU, down + residual +
+    norm, next QKV) as launches of their own and as phases of one persistent kernel; the L2 replaced before each."""
+    h, d, hq, hkv, inter = 4096, 128, 32, 8, 12288
+    flush = torch.zeros(256 << 20, device=k.device, dtype=torch.uint8)
+    bf = torch.bfloat16
+    rand = lambda *shape: (torch.randn(*shape, device=k.device) * 0.02).to(bf)   # noqa: E731
+    w_o, w_gu, w_down, w_qkv = rand(h, hq * d), rand(2 * inter, h), rand(h, inter), rand((hq + 2 * hkv) * d, h)
+    gain = torch.ones(h, device=k.device, dtype=bf)
+    moved = 2 * (w_o.numel() + w_gu.numel() + w_down.numel() + w_qkv.numel())
+    for m in args.rows:
+        o = torch.randn(m, hq * d, device=k.device).to(bf)
+        stream = torch.randn(m, h, device=k.device)
+        act, qkv = torch.empty(m, inter, device=k.device, dtype=bf), torch.empty(m, w_qkv.shape[0], device=k.device, dtype=bf)
+
+        def layer():
+            rows = k.linear_link(stream, o, w_o, gain, 1e-6, 0.0)
+            k.swiglu_gate_up(act, rows, w_gu)
+            rows2 = k.linear_link(stream, act, w_down, gain, 1e-6, 0.0)
+            k.linear(qkv, rows2, w_qkv)
+            k.flush()
+        for chained, cooperative in ((False, True), (True, True), (True, False)):
+            k.chain, k.chain_cooperative = chained, cooperative
+            t = timed(layer, flush)
+            label = "four launches" if not chained else "one persistent kernel" + ("" if cooperative else ", plain launch")
+            print(f"four products, rows {m}, {label:36s}: {t:7.1f} us  {moved / t / 1e6:5.2f} TB/s")
+        k.chain, k.chain_cooperative = True, True
+        singles = (("o_proj+add+norm", lambda: k.linear_link(stream, o, w_o, gain, 1e-6, 0.0), w_o),
+                   ("down+add+norm", lambda: k.linear_link(stream, act, w_down, gain, 1e-6, 0.0), w_down))
+        for name, fn, w in singles:
+            for chained in (False, True):
+                k.chain = chained
+
+                def one(fn=fn):
+                    fn()
+                    k.flush()
+                t = timed(one, flush)
+                print(f"  {name:16s} rows {m} {'as a chain of one' if chained else 'its own kernel':18s}: {t:6.1f} us  {2 * w.numel() / t / 1e6:5.2f} TB/s")
+        k.chain = False
+    print("status", k.tcgen05_status())
+
+
 def main() -> None:
     ap = argparse.ArgumentParser(description=__doc__.split("\n\n")[0])
-    ap.add_argument("what", choices=("decode_attention", "gemm", "prefill_attention"))
+    ap.add_argument("what", choices=("decode_attention", "gemm", "prefill_attention", "chain"))
     ap.add_argument("--rows", type=int, nargs="*", default=None)
     ap.add_argument("--context", type=int, default=8192)
     ap.add_argument("--splits", type=int, nargs="*", default=None)
@@ -261,6 +303,9 @@ def main() -> None:
         if args.what == "decode_attention":
             args.rows = args.rows or [8, 64, 1]
             decode_attention(k, args)
+        elif args.what == "chain":
+            args.rows = args.rows or [1, 8, 16]
+            chain(k, args)
         elif args.what == "prefill_attention":
             args.rows = args.rows or [2048]
             prefill_attention(k, args)

@@ -81,6 +81,9 @@ class Model(Part):
         for i, run in enumerate(order):
             after = self.layers[order[i + 1].layer] if i + 1 < len(order) else None
             stream = self.layers[run.layer].forward(stream, step, step.layer_cache(run), after)
+        flush = getattr(self.ctx.kernels, "flush", None)
+        if flush is not None:                          # a kernel table may queue launches: the stream is whole from here on
+            flush()
         return stream
 
     def forward(self, step) -> torch.Tensor | None:

@@ -414,10 +414,12 @@ def test_qkv_product_with_norm_rotation_and_cache_write(K, heads, kv_heads, head
 @pytest.mark.parametrize("hidden,wide", [(4096, 4096), (96, 192), (200, 72), (1024, 3072)])
 @pytest.mark.parametrize("m", [1, 8, 16])
 @pytest.mark.parametrize("norm", ["bfloat16", "float32"])
-def test_residual_sum_and_norm_inside_the_products_around_them(K, hidden, wide, m, norm):
+def test_residual_sum_and_norm_inside_the_products_around_them(K, hidden, wide, m, norm, monkeypatch):
     """A product that adds itself into the 32-bit stream and leaves the next norm's rows unscaled, and the three
     products that take such rows (plain, SwiGLU, QKV with rotation), against the separate kernels: product,
-    add_rmsnorm, product. The stream itself must come out the same to the bit."""
+    add_rmsnorm, product. The stream itself must come out the same to the bit. (Every product its own launch here;
+    the same products as phases of one kernel: test_products_chained_in_one_kernel.)"""
+    monkeypatch.setattr(K, "chain", False)
     g = torch.Generator().manual_seed(hidden + m)
     dev = lambda t: t.to(DEV)                                          # noqa: E731
     x = dev((torch.randn(m, wide, generator=g) * 0.5).to(torch.bfloat16))
@@ -474,6 +476,62 @@ def test_residual_sum_and_norm_inside_the_products_around_them(K, hidden, wide, 
     assert (kv1 - kv2)[written].abs().max() <= 4e-2 * max(1.0, float(kv1[written].abs().max()))
     # where the kernel does not apply, nothing is done
     assert K.linear_link(h_got.double().float()[:, :hidden], x.float(), w.float(), gain, eps, offset) is None
+
+
+@pytest.mark.parametrize("hidden,inter,heads,kv_heads,head_dim", [(4096, 12288, 32, 8, 128), (1024, 3072, 16, 8, 128),
+                                                                  (96, 176, 6, 1, 48), (64, 128, 4, 2, 16), (200, 72, 2, 2, 24)])
+@pytest.mark.parametrize("m", [1, 7, 16])
+def test_products_chained_in_one_kernel(K, hidden, inter, heads, kv_heads, head_dim, m, monkeypatch):
+    """A decode layer's products on the same few rows (attention output -> o_proj + residual + post norm -> gate/up with
+    SwiGLU -> down + residual + next input norm -> next QKV, twice over) queued and run as phases of one persistent
+    kernel, against the same products as launches of their own. The weights are cut into equal shares of chunks
+    whatever their shapes, so tiles are summed across CTAs: sums may differ in the last bits, never more; the odd
+    sizes leave CTAs without work and tiles with ragged ends."""
+    from holon_b200.parts.base import Scaled
+    g = torch.Generator().manual_seed(hidden + 3 * m)
+    dev = lambda t: t.to(DEV)                                          # noqa: E731
+    mat = lambda n, k: dev((torch.randn(n, k, generator=g) * 0.05).to(torch.bfloat16))   # noqa: E731
+    gain = lambda n: dev((1 + 0.1 * torch.randn(n, generator=g)).to(torch.bfloat16))     # noqa: E731
+    qkv_rows = (heads + 2 * kv_heads) * head_dim
+    layers = [dict(o=mat(hidden, heads * head_dim), gate_up=mat(2 * inter, hidden), down=mat(hidden, inter), qkv=mat(qkv_rows, hidden),
+                   post=gain(hidden), after=gain(hidden)) for _ in range(2)]
+    attn = [dev((torch.randn(m, heads * head_dim, generator=g) * 0.5).to(torch.bfloat16)) for _ in range(2)]
+    h0 = dev(torch.randn(m, hidden, generator=g))
+    eps = 1e-6
+
+    def run(chain: bool):
+        monkeypatch.setattr(K, "chain", chain)
+        h, outs, before = h0.clone(), [], (K.chain_launches, K.chain_phases)
+        for layer, o in zip(layers, attn):
+            rows = K.linear_link(h, o, layer["o"], layer["post"], eps, 0.0)
+            act = torch.empty(m, inter, dtype=torch.bfloat16, device=DEV)
+            K.swiglu_gate_up(act, rows, layer["gate_up"])
+            rows2 = K.linear_link(h, act, layer["down"], layer["after"], eps, 0.0)
+            qkv = torch.empty(m, qkv_rows, dtype=torch.bfloat16, device=DEV)
+            K.linear(qkv, rows2, layer["qkv"])
+            assert isinstance(rows, Scaled) and isinstance(rows2, Scaled)
+            if chain:
+                assert len(K._pending) == 4
+            K.flush()                                                  # (the engine's next call, the rotation kernel, does this)
+            outs.append((act.float().cpu(), qkv.float().cpu(), rows.y.float().cpu(), rows2.ss.double().sum(0).cpu()))
+        counted = (K.chain_launches - before[0], K.chain_phases - before[1])
+        return h.cpu(), outs, counted
+
+    h_want, want, none = run(False)
+    h_got, got, counted = run(True)
+    assert none == (0, 0) and counted == (2, 8)
+    assert K.tcgen05_status() == 0
+    assert torch.isfinite(h_got).all()
+    # the stream: each product is rounded to bfloat16 before it is added, so a last-bit difference of a sum shows
+    # either not at all or as one bfloat16 step of that product (and the second layer's products start from it)
+    step = 2.0 ** -7 * (h_want - h0.cpu()).abs().max().item()
+    assert (h_got - h_want).abs().max().item() <= 2 * step
+    first_want, first_got = want[0][2], got[0][2]                      # the first product's rows: same inputs on both sides
+    assert (first_got != first_want).float().mean().item() < 0.02
+    for (act1, qkv1, y1, ss1), (act2, qkv2, y2, ss2) in zip(want, got):
+        for a, b in ((act1, act2), (qkv1, qkv2), (y1, y2)):
+            assert (a - b).abs().max().item() <= 1.6e-2 * max(1.0, a.abs().max().item())
+        assert torch.allclose(ss1[:m], ss2[:m], rtol=1e-3)
 
 
 @pytest.mark.parametrize("geometry", [(32, 8, 128, 64), (40, 2, 64, 16), (6, 1, 48, 4), (16, 4, 256, 128)])

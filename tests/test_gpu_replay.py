@@ -158,3 +158,19 @@ def test_weights_stored_in_32_bits(tmp_path, dtype):
     assert set(norms) == {torch.float32}
     got = run(r, [([("x", ids[:61])], []), ([("x", ids[61:63])], [])] + [([("x", [t])], []) for t in ids[63:]])
     compare(got, want, dtype)
+
+
+def test_products_chained_in_one_kernel_through_the_engine(model, monkeypatch):
+    """With HOLON_B200_CHAIN=1 the kernel table queues a decode step's consecutive products (o_proj, gate/up, down, the
+    next layer's QKV) and runs them as phases of one persistent kernel: the mixed trace (steps of up to 16 tokens take
+    that path, larger ones the usual one) must give the same logits as ever."""
+    from holon_b200.kernels import load_kernels
+    folder, config, prompts, want = model
+    kernels = load_kernels("cuda:0")
+    monkeypatch.setattr(kernels, "chain", True)
+    before = kernels.chain_launches
+    r = Replayer(str(folder), "bfloat16", max_tokens=448)
+    got = run(r, mixed_trace(prompts))
+    assert kernels.chain_launches - before > 50 and not kernels._pending
+    compare(got, want, "bfloat16")
+    assert kernels.tcgen05_status() == 0
