@@ -146,6 +146,12 @@ int hb_gemm_chain(const hb_chain_phase* phases, int n_phases, int m, unsigned in
                   unsigned int* flags, int slots, int cooperative, hb_stream stream);
 int hb_gemm_chain_status(unsigned int* status);
 
+// The same products in one launch whose CTAs each take one tile of one product, in the products' order (tickets drawn
+// at the start; csrc/gemm_tickets.cu): a product's CTAs start while the one before ends, ask for their weights and
+// wait for its last tile. Up to 4 products; state: 6 words, zero before the first launch.
+int hb_gemm_tickets(const hb_chain_phase* phases, int n_phases, int m, unsigned int* state, hb_stream stream);
+int hb_gemm_tickets_status(unsigned int* status);
+
 // bfloat16 product on tcgen05 tensor cores with TMA loads and the accumulator in tensor memory (128 x 256 tiles).
 // Same arguments and modes as hb_gemm_bf16_skinny, any m. hb_gemm_tcgen05_status synchronises the device and
 // returns (and clears) a status word that is non-zero if a bounded wait inside the kernel ever gave up.

@@ -80,11 +80,14 @@ class CudaKernels:
         self.sms = torch.cuda.get_device_properties(self.device).multi_processor_count
         self.decode_ctas = None               # tests: a fixed number of CTAs for the balanced kernel
         self.prefill_tile = None              # tests, microbench: 128 or 256 queries a CTA of the tcgen05 prefill kernel
-        # Decode steps, with HOLON_B200_CHAIN=1: the products of a layer that follow one another on the same few rows
-        # (the mixer's last, the feed-forward's two, the next mixer's first) are queued and run as phases of one
-        # persistent kernel (csrc/gemm_chain.cu); every other call of this table runs what is queued first. Default: every
-        # product its own launch, which is faster as measured (102 us against 89 us for a layer's four at 8B sizes).
-        self.chain = os.environ.get("HOLON_B200_CHAIN", "0") != "0"
+        # Decode steps: the products of a layer that follow one another on the same few rows (the mixer's last, the
+        # feed-forward's two, the next mixer's first) can be queued and run in one launch; every other call of this table
+        # runs what is queued first. HOLON_B200_CHAIN: "tickets" (csrc/gemm_tickets.cu: every CTA a tile of one of the
+        # products, drawn in order, so that a product starts while the one before ends), "ring" (csrc/gemm_chain.cu: one
+        # persistent kernel with a shared-memory ring; slower as measured) or "0" (every product its own launch).
+        self.chain = {"0": "", "1": "tickets"}.get(os.environ.get("HOLON_B200_CHAIN", "0"), os.environ.get("HOLON_B200_CHAIN", "0"))
+        if self.chain not in ("", "tickets", "ring"):
+            raise KernelError(f"HOLON_B200_CHAIN must be 0, tickets or ring, not {self.chain!r}")
         self.chain_cooperative = os.environ.get("HOLON_B200_CHAIN_COOPERATIVE", "1") != "0"
         self._pending: list = []              # (phase, tensors it names) of products queued, in order
         self.chain_launches = self.chain_phases = 0
@@ -96,6 +99,7 @@ class CudaKernels:
         self._chain_sync = torch.zeros(2, dtype=torch.int32, device=self.device)
         self._chain_flags = torch.zeros(self._chain_slots, dtype=torch.int32, device=self.device)
         self._chain_scratch = torch.empty(self._chain_slots * 512, dtype=torch.float32, device=self.device)
+        self._ticket_state = torch.zeros(8, dtype=torch.int32, device=self.device)
         # One word of page-locked host memory that a kernel's bounded wait writes when it gives up (csrc/status.cu)
         word = ctypes.POINTER(ctypes.c_uint)()
         with torch.cuda.device(self.device):
@@ -121,10 +125,11 @@ class CudaKernels:
 
     # ---- products queued for one persistent kernel (decode steps)
     MAX_CHAIN = 8                              # phases a launch takes (csrc/gemm_chain.cu)
+    MAX_TICKETS = 4                            # products a launch takes (csrc/gemm_tickets.cu)
 
     def _queue(self, *, w, x, out, mode: int, n: int, inter: int = 0, h=None, next_weight=None, next_offset: float = 0.0,
                ss_out=None, scaled=None) -> None:
-        if len(self._pending) >= self.MAX_CHAIN:
+        if len(self._pending) >= (self.MAX_CHAIN if self.chain == "ring" else self.MAX_TICKETS):
             self.flush()
         y = scaled.y if scaled is not None else x
         phase = _ChainPhase(w=w.data_ptr(), x=y.data_ptr(), out=out.data_ptr(), h=h.data_ptr() if h is not None else None,
@@ -148,14 +153,17 @@ class CudaKernels:
             return
         pending, self._pending = self._pending, []
         phases = (_ChainPhase * len(pending))(*[p for p, _, _ in pending])
-        self._launch("hb_gemm_chain", phases, len(pending), pending[0][2], self._p(self._chain_sync),
-                     self._p(self._chain_scratch), self._p(self._chain_flags), self._chain_slots, int(self.chain_cooperative))
+        if self.chain == "ring":
+            self._launch("hb_gemm_chain", phases, len(pending), pending[0][2], self._p(self._chain_sync),
+                         self._p(self._chain_scratch), self._p(self._chain_flags), self._chain_slots, int(self.chain_cooperative))
+        else:
+            self._launch("hb_gemm_tickets", phases, len(pending), pending[0][2], self._p(self._ticket_state))
         self.chain_launches += 1
         self.chain_phases += len(pending)
 
     def _chains(self, m: int, k: int, *tensors) -> bool:
         """Whether a product of `m` rows over `k` columns of these bfloat16 tensors may be queued."""
-        return self.chain and 0 < m <= self.SKINNY_ROWS and k % 8 == 0 \
+        return bool(self.chain) and 0 < m <= self.SKINNY_ROWS and k % 8 == 0 \
             and all(t.dtype == torch.bfloat16 and t.data_ptr() % 16 == 0 for t in tensors)
 
     def _stream(self) -> int:
@@ -537,7 +545,7 @@ class CudaKernels:
         up their barrier and flags are put back to zero, so that the next launch starts clean."""
         out = 0
         for name in ("hb_gemm_tcgen05_status", "hb_gemm_tcgen05_pair_status", "hb_attention_tcgen05_status",
-                     "hb_gemm_chain_status"):
+                     "hb_gemm_chain_status", "hb_gemm_tickets_status"):
             status = ctypes.c_uint(0)
             if getattr(self.lib, name)(ctypes.byref(status)):
                 raise KernelError(self.lib.hb_last_error().decode())
@@ -546,6 +554,7 @@ class CudaKernels:
         if out:
             self._chain_sync.zero_()
             self._chain_flags.zero_()
+            self._ticket_state.zero_()
         return out
 
     def swiglu_gate_up(self, out, x, weight) -> None:

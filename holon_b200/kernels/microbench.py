@@ -267,24 +267,22 @@ def chain(k, args) -> None:
             rows2 = k.linear_link(stream, act, w_down, gain, 1e-6, 0.0)
             k.linear(qkv, rows2, w_qkv)
             k.flush()
-        for chained, cooperative in ((False, True), (True, True), (True, False)):
-            k.chain, k.chain_cooperative = chained, cooperative
+        for chained, label in (("", "four launches"), ("tickets", "one launch, a ticket a tile"), ("ring", "one persistent kernel, a ring")):
+            k.chain = chained
             t = timed(layer, flush)
-            label = "four launches" if not chained else "one persistent kernel" + ("" if cooperative else ", plain launch")
             print(f"four products, rows {m}, {label:36s}: {t:7.1f} us  {moved / t / 1e6:5.2f} TB/s")
-        k.chain, k.chain_cooperative = True, True
         singles = (("o_proj+add+norm", lambda: k.linear_link(stream, o, w_o, gain, 1e-6, 0.0), w_o),
                    ("down+add+norm", lambda: k.linear_link(stream, act, w_down, gain, 1e-6, 0.0), w_down))
         for name, fn, w in singles:
-            for chained in (False, True):
+            for chained in ("", "tickets", "ring"):
                 k.chain = chained
 
                 def one(fn=fn):
                     fn()
                     k.flush()
                 t = timed(one, flush)
-                print(f"  {name:16s} rows {m} {'as a chain of one' if chained else 'its own kernel':18s}: {t:6.1f} us  {2 * w.numel() / t / 1e6:5.2f} TB/s")
-        k.chain = False
+                print(f"  {name:16s} rows {m} {(chained + ', alone') if chained else 'its own kernel':18s}: {t:6.1f} us  {2 * w.numel() / t / 1e6:5.2f} TB/s")
+        k.chain = ""
     print("status", k.tcgen05_status())
 
 

@@ -419,7 +419,7 @@ def test_residual_sum_and_norm_inside_the_products_around_them(K, hidden, wide, 
     products that take such rows (plain, SwiGLU, QKV with rotation), against the separate kernels: product,
     add_rmsnorm, product. The stream itself must come out the same to the bit. (Every product its own launch here;
     the same products as phases of one kernel: test_products_chained_in_one_kernel.)"""
-    monkeypatch.setattr(K, "chain", False)
+    monkeypatch.setattr(K, "chain", "")
     g = torch.Generator().manual_seed(hidden + m)
     dev = lambda t: t.to(DEV)                                          # noqa: E731
     x = dev((torch.randn(m, wide, generator=g) * 0.5).to(torch.bfloat16))
@@ -481,12 +481,14 @@ def test_residual_sum_and_norm_inside_the_products_around_them(K, hidden, wide, 
 @pytest.mark.parametrize("hidden,inter,heads,kv_heads,head_dim", [(4096, 12288, 32, 8, 128), (1024, 3072, 16, 8, 128),
                                                                   (96, 176, 6, 1, 48), (64, 128, 4, 2, 16), (200, 72, 2, 2, 24)])
 @pytest.mark.parametrize("m", [1, 7, 16])
-def test_products_chained_in_one_kernel(K, hidden, inter, heads, kv_heads, head_dim, m, monkeypatch):
+@pytest.mark.parametrize("kind", ["tickets", "ring"])
+def test_products_chained_in_one_kernel(K, hidden, inter, heads, kv_heads, head_dim, m, kind, monkeypatch):
     """A decode layer's products on the same few rows (attention output -> o_proj + residual + post norm -> gate/up with
-    SwiGLU -> down + residual + next input norm -> next QKV, twice over) queued and run as phases of one persistent
-    kernel, against the same products as launches of their own. The weights are cut into equal shares of chunks
-    whatever their shapes, so tiles are summed across CTAs: sums may differ in the last bits, never more; the odd
-    sizes leave CTAs without work and tiles with ragged ends."""
+    SwiGLU -> down + residual + next input norm -> next QKV, twice over) queued and run in one launch, against the same
+    products as launches of their own. "tickets": every CTA a tile of one of the products, in order, the arithmetic
+    that of the separate kernels: the same bits. "ring": one persistent kernel whose CTAs take equal shares of chunks
+    whatever the shapes, so tiles are summed across CTAs: sums may differ in the last bits, never more. The odd sizes
+    leave CTAs without work and tiles with ragged ends."""
     from holon_b200.parts.base import Scaled
     g = torch.Generator().manual_seed(hidden + 3 * m)
     dev = lambda t: t.to(DEV)                                          # noqa: E731
@@ -499,7 +501,7 @@ def test_products_chained_in_one_kernel(K, hidden, inter, heads, kv_heads, head_
     h0 = dev(torch.randn(m, hidden, generator=g))
     eps = 1e-6
 
-    def run(chain: bool):
+    def run(chain: str):
         monkeypatch.setattr(K, "chain", chain)
         h, outs, before = h0.clone(), [], (K.chain_launches, K.chain_phases)
         for layer, o in zip(layers, attn):
@@ -517,9 +519,13 @@ def test_products_chained_in_one_kernel(K, hidden, inter, heads, kv_heads, head_
         counted = (K.chain_launches - before[0], K.chain_phases - before[1])
         return h.cpu(), outs, counted
 
-    h_want, want, none = run(False)
-    h_got, got, counted = run(True)
+    h_want, want, none = run("")
+    h_got, got, counted = run(kind)
     assert none == (0, 0) and counted == (2, 8)
+    if kind == "tickets":
+        assert torch.equal(h_got, h_want)
+        for mine, theirs in zip(got, want):
+            assert all(torch.equal(a, b) for a, b in zip(mine, theirs))
     assert K.tcgen05_status() == 0
     assert torch.isfinite(h_got).all()
     # the stream: each product is rounded to bfloat16 before it is added, so a last-bit difference of a sum shows

@@ -160,14 +160,15 @@ def test_weights_stored_in_32_bits(tmp_path, dtype):
     compare(got, want, dtype)
 
 
-def test_products_chained_in_one_kernel_through_the_engine(model, monkeypatch):
-    """With HOLON_B200_CHAIN=1 the kernel table queues a decode step's consecutive products (o_proj, gate/up, down, the
-    next layer's QKV) and runs them as phases of one persistent kernel: the mixed trace (steps of up to 16 tokens take
-    that path, larger ones the usual one) must give the same logits as ever."""
+@pytest.mark.parametrize("kind", ["tickets", "ring"])
+def test_products_chained_in_one_kernel_through_the_engine(model, monkeypatch, kind):
+    """With HOLON_B200_CHAIN set the kernel table queues a decode step's consecutive products (o_proj, gate/up, down,
+    the next layer's QKV) and runs them in one launch: the mixed trace (steps of up to 16 tokens take that path, larger
+    ones the usual one) must give the same logits as ever."""
     from holon_b200.kernels import load_kernels
     folder, config, prompts, want = model
     kernels = load_kernels("cuda:0")
-    monkeypatch.setattr(kernels, "chain", True)
+    monkeypatch.setattr(kernels, "chain", kind)
     before = kernels.chain_launches
     r = Replayer(str(folder), "bfloat16", max_tokens=448)
     got = run(r, mixed_trace(prompts))
