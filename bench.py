@@ -276,8 +276,7 @@ def stream_run(arm: Arm, batch: int, context: int, steps: int, warmup: int, seed
             if began is None and len(first) == len(rids):
                 began = now
                 if clocks:
-                    clocks.start()
-                    clocks.mark()
+                    clocks.start()                                   # (every sample from here on lies in the decode part)
         clock = clocks.stop() if clocks else None
         assert began is not None and len(moments) == steps + warmup, (began, len(moments))
         if sampled:
