@@ -172,6 +172,7 @@ int hb_gemm_tcgen05_pair_width(int bn);             // tests: fix the tile width
 // completion event, and may write 0 to it. hb_status_selftest enqueues a wait of `polls` polls on a barrier nobody
 // arrives at (place 15): it runs out within microseconds and lets tests see what the host does then.
 int hb_status_word(unsigned int** host);
+int hb_status_word_device(unsigned int** device);   // the same word as the device addresses it (for a part's own kernel files)
 int hb_status_selftest(int polls, hb_stream stream);
 
 // The token each request sampled last, kept on the device by slot. feed: for every row r with from_last[r] != 0,

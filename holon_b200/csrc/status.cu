@@ -14,6 +14,7 @@ extern "C" int hb_gemm_tickets_status_mirror(unsigned int* word);
 HB_DEFINE_STATUS_MIRROR(hb_status_selftest_mirror)
 
 static unsigned int* g_word_host = nullptr;
+static unsigned int* g_word_device = nullptr;
 
 // The host address of the status word (made, and handed to the kernel files of the current device, at the first
 // call). 0 there: every wait so far ended; else (place << 28) | (block + 1) of a wait that gave up. The host may write
@@ -31,8 +32,18 @@ extern "C" int hb_status_word(unsigned int** host) {
             hb_status_selftest_mirror(device))
             return HB_ERR_CUDA;
         g_word_host = word;
+        g_word_device = device;
     }
     *host = g_word_host;
+    return 0;
+}
+
+// The same word's address as the device sees it, for kernel files outside this library (a part's own): they hand it
+// to their HB_DEFINE_STATUS_MIRROR function, and their waits report like every other.
+extern "C" int hb_status_word_device(unsigned int** device) {
+    unsigned int* host = nullptr;
+    if (int code = hb_status_word(&host)) return code;
+    *device = g_word_device;
     return 0;
 }
 

@@ -13,7 +13,7 @@ import os
 
 import torch
 
-from .build import library_path
+from .build import extension_path, library_path
 
 _CODES = {torch.float32: 0, torch.bfloat16: 1}
 
@@ -37,6 +37,27 @@ class _ChainPhase(ctypes.Structure):
         + [("next_offset", ctypes.c_float), ("eps_in", ctypes.c_float)]
 
 
+class Extension:
+    """The functions of a part's own CUDA library (`CudaKernels.extension`). `ext.call("fn", a, b, ...)` runs
+    `int fn(a, b, ..., stream)` on torch's current stream after whatever the table still has queued, and raises
+    `KernelError` with the library's text when it returns non-zero. `ptr`, `i32` and `check` are the table's own
+    helpers for arguments: a tensor's address (0 for None), the same with the dtype checked, and device and contiguity."""
+
+    def __init__(self, kernels: "CudaKernels", name: str, path, status_mirrors=()) -> None:
+        self.kernels, self.name, self.path = kernels, name, path
+        self.lib = ctypes.CDLL(str(path))
+        self._fn: dict = {}
+        self.ptr, self.i32, self.check = kernels._p, kernels._i32, kernels._check
+        for fn in status_mirrors:             # its bounded waits report into the word that the engine reads
+            word = ctypes.POINTER(ctypes.c_uint)()
+            with torch.cuda.device(kernels.device):
+                if kernels.lib.hb_status_word_device(ctypes.byref(word)) or getattr(self.lib, fn)(word):
+                    raise KernelError(f"{name}.{fn}: {kernels.lib.hb_last_error().decode()}")
+
+    def call(self, fn: str, *args) -> None:
+        self.kernels._call_in(self.lib, self._fn, fn, *args)
+
+
 class CudaKernels:
     name = "cuda sm_100a"
 
@@ -45,7 +66,8 @@ class CudaKernels:
         if self.device.type != "cuda":
             raise KernelError(f"the engine runs on a CUDA device; {self.device} is none")
         self.path = library_path()
-        self.lib = ctypes.CDLL(str(self.path))
+        self.lib = ctypes.CDLL(str(self.path), mode=ctypes.RTLD_GLOBAL)      # (extensions use its hb_set_error)
+        self._extensions: dict[str, Extension] = {}
         self.lib.hb_last_error.restype = ctypes.c_char_p
         self._fn = {}
         self._index = self.device.index if self.device.index is not None else torch.cuda.current_device()
@@ -122,6 +144,34 @@ class CudaKernels:
         self.launches += 1
         if code:
             raise KernelError(f"{name}: {self.lib.hb_last_error().decode()}")
+
+    def _call_in(self, lib, cache: dict, name: str, *args) -> None:
+        """`_call` for a function of another library (an extension's)."""
+        if self._pending:
+            self.flush()
+        fn = cache.get(name)
+        if fn is None:
+            try:
+                fn = cache[name] = getattr(lib, name)
+            except AttributeError:
+                raise KernelError(f"{name}: the extension's library exports no such function") from None
+            fn.restype = ctypes.c_int
+        code = fn(*args, ctypes.c_void_p(self._stream()))
+        self.launches += 1
+        if code:
+            raise KernelError(f"{name}: {self.lib.hb_last_error().decode() or f'returned {code}'}")
+
+    def extension(self, name: str, sources, build_dir=None, status_mirrors=()) -> Extension:
+        """A part's own CUDA files as a library beside this one: compiled on first use (kernels/build.py:
+        `extension_path`), loaded once per table. The part calls its functions through the `Extension` it gets; this
+        file, api.h and the main library stay as they are. `status_mirrors`: the names its files gave to
+        HB_DEFINE_STATUS_MIRROR (csrc/tcgen05.cuh), one per file with bounded waits; `status()` then shows a wait of
+        theirs that gave up, and the engine stops on it as on any other."""
+        ext = self._extensions.get(name)
+        if ext is None:
+            path = extension_path(name, sources, build_dir)
+            ext = self._extensions[name] = Extension(self, name, path, status_mirrors)
+        return ext
 
     # ---- products queued for one persistent kernel (decode steps)
     MAX_CHAIN = 8                              # phases a launch takes (csrc/gemm_chain.cu)

@@ -61,7 +61,9 @@ class Part:
             yield from child.loadables(f"{prefix}{name}.")
 
     def finalize(self) -> None:
-        """Called once after every parameter holds its tensor."""
+        """Called once after every parameter holds its tensor. What needs the tensors, the device or the kernel table
+        (derived tensors, a library of the part's own: `ctx.kernels.extension`) is done here, not in the constructor:
+        a model is also built on no device and without kernels, only to list its parameters."""
         for child in self._children.values():
             child.finalize()
 
