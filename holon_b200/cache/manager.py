@@ -9,9 +9,11 @@ request ends, or, in a group with a window, when every position in it lies befor
 (core/holon/core/state.py:398-418, 499-517). The last page of each pool's tensor is the null page: never handed
 out, it stands in every unused block-table cell (memory.py:49-54).
 
-With `prefix_cache` (and one group of full attention, no state of fixed size) whole pages of prompts are shared
-between requests through `prefix.PrefixIndex`: `admit(tokens)` starts a request on the pages of the longest known
-prefix of its tokens, `publish(slot, tokens)` enters the pages its computed tokens have filled.
+With `prefix_cache` whole pages of prompts are shared between requests through `prefix.PrefixIndex`, in every group
+at once: `admit(tokens)` starts a request on the pages of the longest known prefix of its tokens for which every
+group still has what the next token can read (a group with a window needs only the pages that reach into it),
+`publish(slot, tokens)` enters the pages its computed tokens have filled. A model with state of fixed size gets no
+index: such a state cannot be entered in the middle of a prompt without a copy of it taken there.
 
 Slots: a request holds one slot from admission to release; the slot is its row in every block table and in every
 per-request tensor (state.py:154, 183-186). Mixers may declare state of fixed size (`SlotState`); it is zeroed when
@@ -19,6 +21,7 @@ a request takes the slot.
 """
 from __future__ import annotations
 
+import functools
 import math
 
 import numpy as np
@@ -26,7 +29,7 @@ import torch
 
 from ..parts.base import PagedKV
 from .pages import OutOfPages, PagePool
-from .prefix import ROOT, PrefixIndex
+from .prefix import DEAD, ROOT, PrefixIndex
 
 
 class CacheGroup:
@@ -114,9 +117,9 @@ class CacheManager:
     def __init__(self, entries, page_size: int, max_seqs: int, max_model_len: int, dtype: torch.dtype, device,
                  state_memory: int | None = None, pages: int | None = None, prefix_cache: bool = False) -> None:
         """`entries`: the model's `CacheEntry` list. Give either `state_memory` (bytes for all pools together) or
-        `pages` (pages per pool). `prefix_cache`: share whole pages of equal prompt prefixes between requests; it
-        takes effect only for one group of full attention without state of fixed size (a window lets go of early
-        pages, and a fixed-size state cannot be entered in the middle of a prompt)."""
+        `pages` (pages per pool). `prefix_cache`: share whole pages of equal prompt prefixes between requests, in
+        all groups; it takes effect unless a part keeps state of fixed size (which cannot be entered in the middle of
+        a prompt)."""
         self.page_size, self.max_seqs, self.max_model_len = page_size, max_seqs, max_model_len
         self.dtype, self.device = dtype, torch.device(device)
         by_decl: dict[PagedKV, list[int]] = {}
@@ -151,9 +154,10 @@ class CacheManager:
                 self.slot_states[(e.entry, s.name)] = torch.zeros((max_seqs + 1, *s.shape),
                                                                   dtype=getattr(torch, s.dtype), device=device)
         self.prefix: PrefixIndex | None = None
-        if prefix_cache and len(self.groups) == 1 and self.groups[0].decl.window <= 0 and not self.slot_states:
-            self.prefix = PrefixIndex(page_size)
-            self.groups[0].pool.on_evict = self.prefix.evicted
+        if prefix_cache and self.groups and not self.slot_states:
+            self.prefix = PrefixIndex(page_size, [max(0, g.decl.window) for g in self.groups])
+            for g in self.groups:
+                g.pool.on_evict = functools.partial(self.prefix.evicted, g.index)
         self._chain_node = np.full(max_seqs + 1, ROOT, dtype=np.int64)    # per slot: the index node of its last known block
         self._chain_blocks = np.zeros(max_seqs + 1, dtype=np.int64)      # and how many blocks lead there
 
@@ -171,16 +175,17 @@ class CacheManager:
         for t in self.slot_states.values():
             t[slot].zero_()
         if self.prefix is not None and tokens is not None:
-            g = self.groups[0]
-            pages, node = self.prefix.match(tokens)
-            for i, page in enumerate(pages):
-                g.pool.share(page, slot)
-                g.table[slot, i] = page
-            if pages:
-                g.count[slot] = len(pages)
-                g.dirty.add(slot)
-                self.computed[slot] = len(pages) * self.page_size
-                self._chain_node[slot], self._chain_blocks[slot] = node, len(pages)
+            blocks, share, node = self.prefix.match(tokens)
+            if blocks:
+                for g, cells in zip(self.groups, share):
+                    for i, page in cells:
+                        g.pool.share(page, slot)
+                        g.table[slot, i] = page
+                    g.first[slot] = self.prefix.first_needed(g.index, blocks)     # (a window: the blocks before it are not held)
+                    g.count[slot] = blocks
+                    g.dirty.add(slot)
+                self.computed[slot] = blocks * self.page_size
+                self._chain_node[slot], self._chain_blocks[slot] = node, blocks
         return slot
 
     def publish(self, slot: int, tokens) -> None:
@@ -188,14 +193,15 @@ class CacheManager:
         request's tokens as far as the host knows them (a token still on the device is left for the next call)."""
         if self.prefix is None:
             return
-        g, p = self.groups[0], self.page_size
+        p = self.page_size
         known = min(len(tokens), int(self.computed[slot]))
         i, node = int(self._chain_blocks[slot]), int(self._chain_node[slot])
-        while (i + 1) * p <= known:
-            page = int(g.table[slot, i])
-            node, new = self.prefix.extend(node, tokens[i * p:(i + 1) * p], page)
-            if new:
-                g.pool.register(page)
+        while (i + 1) * p <= known and node != DEAD:
+            pages = [int(g.table[slot, i]) if i >= int(g.first[slot]) else None for g in self.groups]   # None: passed by the window
+            node, entered = self.prefix.extend(node, tokens[i * p:(i + 1) * p], pages)
+            for g, page, new in zip(self.groups, pages, entered):
+                if new:
+                    g.pool.register(page)
             i += 1
         self._chain_node[slot], self._chain_blocks[slot] = node, i
 
@@ -271,5 +277,6 @@ class CacheManager:
             assert len(held) + g.pool.available == g.pool.pages, "a page is neither available nor held"
             assert all(not g.pool.holders(p) for p in range(g.pool.pages) if p not in held), "a page is held by no table"
         if self.prefix is not None:
-            pool = self.groups[0].pool
-            assert all(pool.registered(p) for p in self.prefix.pages()), "the index names a page that is not registered"
+            for g in self.groups:
+                assert all(g.pool.registered(p) for p in self.prefix.pages(g.index)), \
+                    "the index names a page that is not registered"

@@ -193,18 +193,125 @@ def test_kept_pages_are_evicted_oldest_first_and_forgotten():
     assert m.reserve(t, 16) and len(g.pool._kept) == 4                # 4 pages: 3 free, then the one kept longest
     m.check()
     assert int(m.computed[m.admit(first)]) == 4                       # its leaf went first; the parent still serves
-    assert len(m.prefix) == 3 + 1 and m.prefix.match(second)[0] != []
+    assert len(m.prefix) == 3 + 1 and m.prefix.match(second)[0] > 0
     assert not m.reserve(t, 32) and m.reserve(t, 28) and len(g.pool._kept) == 0   # everything else is taken now
-    assert m.prefix.match(second)[0] == [] and len(m.prefix) == 1
+    assert m.prefix.match(second)[0] == 0 and len(m.prefix) == 1
     m.check()
 
 
-def test_no_prefix_index_where_pages_cannot_be_shared():
+def test_no_prefix_index_where_a_prompt_cannot_be_entered_in_the_middle():
     window = [CacheEntry(0, 0, PagedKV(2, 16), ()), CacheEntry(1, 1, PagedKV(2, 16, window=8), ())]
     state = [CacheEntry(0, 0, PagedKV(2, 16), (SlotState("sum", (4,), "float32"),))]
-    assert manager(window, prefix_cache=True).prefix is None
-    assert manager(state, prefix_cache=True).prefix is None
+    assert manager(window, prefix_cache=True).prefix is not None
+    assert manager(state, prefix_cache=True).prefix is None           # a state of fixed size has no copy to start from
     assert manager(prefix_cache=False).prefix is None and one_group().prefix is not None
+
+
+def full_and_window(window=6, **kw):
+    entries = [CacheEntry(0, 0, PagedKV(2, 16), ()), CacheEntry(1, 1, PagedKV(2, 16, window=window), ()),
+               CacheEntry(2, 2, PagedKV(2, 16), ())]
+    return manager(entries, prefix_cache=True, **kw)
+
+
+def walk(m, slot, tokens, upto, step=3):
+    """The request computes its tokens `step` at a time, publishing as it goes (as the engine does after every step)."""
+    at = int(m.computed[slot])
+    while at < upto:
+        at = min(upto, at + step)
+        assert m.reserve(slot, at)
+        m.advance(slot, at)
+        m.publish(slot, tokens)
+
+
+def test_prefixes_are_shared_in_every_group_and_a_window_needs_only_what_reaches_into_it():
+    """Two groups, one with a window of 6 on pages of 4: a request that starts after n shared blocks holds all n pages
+    in the full group and, in the other, only those that position 4 n can still see."""
+    m = full_and_window()
+    full, near = m.groups
+    assert near.decl.window == 6 and m.prefix.windows == (0, 6)
+    prompt = list(range(200, 223))                                    # 23 tokens: five whole pages
+    a = m.admit(prompt)
+    walk(m, a, prompt, 23)
+    m.check()
+    assert len(m.prefix) == 5 and int(near.first[a]) == 4             # the window has let go of blocks 0 to 3 ...
+    assert len(near.pool._kept) == 4 and len(full.pool._kept) == 0    # ... which are kept, not freed
+    b = m.admit(prompt + [1, 2])
+    assert int(m.computed[b]) == 20                                   # five blocks; the window sees positions 15 to 19
+    assert full.table[b, :5].tolist() == full.table[a, :5].tolist()
+    assert int(near.first[b]) == 3 and (near.table[b, :3] == near.null_page).all()
+    assert near.table[b, 4] == near.table[a, 4] and near.pool.holders(int(near.table[b, 3])) == {b}
+    assert len(near.pool._kept) == 3                                  # block 3 came out of the kept ones
+    m.check()
+    walk(m, b, prompt + [1, 2], 25)
+    m.check()
+    m.release(a)
+    m.release(b)
+    m.check()
+    assert all(g.pool.available == g.pool.pages for g in m.groups)
+    # the window's pool loses a page that the cut needs: the match falls back to a cut that needs none of the lost ones
+    lost = m.prefix._pages_of[m.prefix.match(prompt)[2]][1]           # the window group's page of block 4
+    m.prefix.evicted(1, lost)
+    near.pool._kept.pop(lost)
+    near.pool._registered.discard(lost)
+    near.pool._free.append(lost)
+    m.check()
+    c = m.admit(prompt + [1, 2])
+    assert int(m.computed[c]) == 16 and int(near.first[c]) == 2       # four blocks: positions 11 to 15 lie in blocks 2 and 3
+    d = m.admit(prompt[:21])
+    walk(m, d, prompt[:21], 21)                                       # block 4 again: its page fills the node's gap
+    assert m.prefix._pages_of[m.prefix.match(prompt)[2]][1] == int(near.table[d, 4])
+    e = m.admit(prompt + [5])
+    assert int(m.computed[e]) == 20
+    m.check()
+
+
+@pytest.mark.parametrize("seed", range(6))
+def test_random_traffic_with_shared_prefixes_in_two_groups(seed):
+    """As the test above with random traffic, with a full group and one with a window, in pools so small that kept pages
+    are evicted in one group while the other still has them."""
+    rng = random.Random(300 + seed)
+    window = rng.choice([3, 6, 9])
+    m = full_and_window(window=window, pages=rng.choice([16, 22, 30]), max_seqs=4)
+    families = [[rng.randrange(1000) for _ in range(40)] for _ in range(3)]
+    live: dict[int, tuple[list[int], int]] = {}
+    hits = 0
+    for _ in range(600):
+        op = rng.random()
+        if op < 0.3 and len(live) < 4:
+            tokens = families[rng.randrange(3)][:rng.choice([4, 9, 16, 23, 40])] + [rng.randrange(1000) for _ in range(rng.randrange(6))]
+            slot = m.admit(tokens)
+            hit = int(m.computed[slot])
+            assert hit % 4 == 0 and hit < len(tokens)
+            hits += hit
+            live[slot] = (tokens, hit)
+        elif op < 0.8 and live:
+            slot = rng.choice(list(live))
+            tokens, have = live[slot]
+            want = min(len(tokens), have + rng.choice([1, 2, 5, 17]))
+            if want > have and m.reserve(slot, want):
+                m.advance(slot, want)
+                m.publish(slot, tokens)
+                live[slot] = (tokens, want)
+        elif live:
+            slot = rng.choice(list(live))
+            m.release(slot)
+            del live[slot]
+        m.check()
+        for g in m.groups:
+            for slot, (tokens, have) in live.items():                  # every position the next token may read has a real page
+                lo = max(0, have - g.decl.window + 1) if g.decl.window else 0
+                assert all(p != g.null_page for p in g.table[slot, lo // 4: -(-have // 4)])
+            for page in range(g.pool.pages):                           # a page with two holders holds the same tokens for both
+                holders = sorted(g.pool.holders(page))
+                if len(holders) > 1:
+                    at = {g.table[s, :int(g.count[s])].tolist().index(page) for s in holders}
+                    assert len(at) == 1
+                    assert len({tuple(live[s][0][:(min(at) + 1) * 4]) for s in holders}) == 1
+    assert hits > 0
+    for slot in list(live):
+        m.release(slot)
+    m.check()
+    assert all(g.pool.available == g.pool.pages for g in m.groups)
 
 
 @pytest.mark.parametrize("seed", range(6))

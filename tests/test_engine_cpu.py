@@ -344,3 +344,52 @@ def test_the_engine_generates_what_the_reference_engine_generated(tmp_path, name
         assert engine.generate(work["prompts"], params) == work["tokens"]
         assert engine.stats()["mixed_steps"] > 0
         engine.built.cache.check()
+
+
+def test_prefix_cache_with_windowed_layers_beside_full_ones():
+    """A toy model with two cache groups (layers that see all keys, layers that see the last 10): with the prefix cache
+    requests start in the middle of their prompts in both groups, holding in the windowed group only the pages that
+    reach into the window, and generate what an engine without the prefix cache generates; also in a pool so small
+    that requests are preempted and kept pages evicted."""
+    from holon_b200.config import register_architecture, unregister_architecture
+    from holon_b200.weights import RandomSource
+    from test_gpu_toy_parts import window_recipe
+    register_architecture("ToyWindowPrefixForCausalLM", dict, window_recipe)
+    try:
+        config = {"architectures": ["ToyWindowPrefixForCausalLM"], "hidden": 32, "vocab": 61, "inter": 48, "head_dim": 16,
+                  "window": 10}
+        stem = random_prompt(61, 30, 3)
+        prompts = [stem + random_prompt(61, n, 50 + n) for n in (1, 6, 13)] + [stem[:13], stem]
+
+        def run(max_tokens=6, **kw):
+            args = dict(model="toy", device="cpu", dtype="float32", page_size=4, max_seqs=3, max_model_len=80,
+                        max_step_tokens=16, chunk_with_decode=8, state_memory=1 << 20)
+            args.update(kw)
+            engine = Engine(EngineConfig(**args), source=RandomSource(config, seed=8, dtype=torch.float32),
+                            kernels=RefKernels())
+            params = SamplingParams(temperature=0.8, max_tokens=max_tokens, seed=11)
+            out, cached = {}, {}
+            for round_ in range(2):
+                rids = [engine.add(p, params) for p in prompts]
+                while engine.has_work():
+                    for d in engine.step():
+                        out.setdefault((round_, d.rid), []).extend(d.token_ids)
+                        if d.cached_tokens is not None:
+                            cached[(round_, d.rid)] = d.cached_tokens
+                    engine.built.cache.check()
+                assert not engine.built.cache.live and len(rids) == len(prompts)
+            return engine, [out[k] for k in sorted(out)], cached
+
+        plain_engine, want, _ = run(prefix_cache=False)
+        assert len(plain_engine.built.cache.groups) == 2 and plain_engine.built.cache.prefix is None
+        engine, got, cached = run()
+        assert engine.built.cache.prefix is not None and engine.built.cache.prefix.windows == (10, 0)
+        assert got == want and any(len(set(t)) > 2 for t in got)
+        assert engine.stats()["prefix_hit_tokens"] > 0 and max(cached.values()) >= 28
+        assert all(c >= 12 for (r, _), c in cached.items() if r == 1)
+        per_page = sum(g.kv[:, 0].numel() * 4 for g in engine.built.cache.groups)
+        small, got_small, _ = run(max_tokens=30, state_memory=21 * per_page)
+        assert small.built.cache.pages == 20 and small.stats()["preemptions"] > 0 and small.stats()["prefix_hit_tokens"] > 0
+        assert got_small == run(max_tokens=30, prefix_cache=False)[1]
+    finally:
+        unregister_architecture("ToyWindowPrefixForCausalLM")

@@ -141,3 +141,35 @@ def test_windowed_layers_through_run_ahead_and_graphs(dtype):
         assert any(len(set(t)) > 5 for t in got)
     finally:
         unregister_architecture("ToyWindowEngineForCausalLM")
+
+
+def test_prefix_cache_with_windowed_layers_on_the_device():
+    """Two cache groups, one with a window, and prompts with an equal beginning, twice over, under run-ahead and graphs:
+    requests start in the middle of their prompts in both groups (in the windowed one on the pages that reach into the
+    window only) and generate what an engine without the prefix cache generates."""
+    register_architecture("ToyWindowPrefixEngineForCausalLM", dict, window_recipe)
+    try:
+        config = {"architectures": ["ToyWindowPrefixEngineForCausalLM"], "hidden": 64, "vocab": 113, "inter": 96,
+                  "head_dim": 16, "window": 18}
+        stem = prompts_of(113, (50,), 4)[0]
+        prompts = [stem + tail for tail in prompts_of(113, (1, 9, 20), 6)] + [stem[:27], stem]
+
+        def run(**kw):
+            args = dict(model="toy", dtype="float32", page_size=8, max_seqs=4, max_model_len=128, max_step_tokens=32,
+                        chunk_with_decode=8, state_memory=8 << 20, seed=1)
+            args.update(kw)
+            engine = Engine(EngineConfig(**args), source=RandomSource(config, seed=13, dtype=torch.float32))
+            params = [SamplingParams(temperature=1.0, max_tokens=24, seed=30 + i) for i in range(len(prompts))]
+            out = [engine.generate(prompts, params) for _ in range(2)]
+            engine.built.cache.check()
+            assert not engine.built.cache.live
+            return engine, out
+
+        engine, got = run()
+        prefix = engine.built.cache.prefix
+        assert prefix is not None and sorted(prefix.windows) == [0, 18]
+        assert engine.stats()["prefix_hit_tokens"] >= 5 * 24 and engine.stats()["graph_steps"] > 20
+        _, want = run(prefix_cache=False)
+        assert got == want and got[0] == got[1] and any(len(set(t)) > 3 for t in got[0])
+    finally:
+        unregister_architecture("ToyWindowPrefixEngineForCausalLM")
