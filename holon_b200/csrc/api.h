@@ -166,6 +166,23 @@ int hb_gemm_bf16_tcgen05_pair(void* out, int out_f32, const void* x, const void*
 int hb_gemm_tcgen05_pair_status(unsigned int* status);
 int hb_gemm_tcgen05_pair_width(int bn);             // tests: fix the tile width (0: chosen per launch)
 
+// bfloat16 products of 17 to 64 rows with the following work in their epilogue (csrc/gemm_mid.cu): weight tiles of
+// 256 rows on tcgen05, a tile's k range split over a thread-block cluster of `split` CTAs (0: chosen; 1 to 8) that
+// sum their partial results through distributed shared memory. mode 0 plain, 1 SwiGLU (w [2 inter, k], gate rows
+// first; out [m, inter]), 3 residual sum and next norm (h [m, n] float32 += product; out = bfloat16(h (next_weight +
+// next_offset)); ss_out [ceil(n / 256), 64] partial sums of squares of the new h). ss_in [parts_in, stride_in] (null:
+// none): x lacks its norm's row scale rsqrt(sum over parts / dim_in + eps_in). hb_qkv_rope_mid: the attention's first
+// product with q/k norm, rotation and cache write (arguments as hb_qkv_rope_skinny_linked).
+int hb_gemm_bf16_mid(void* out, int out_f32, const void* x, const void* w, int m, int n, int k, int mode, int inter,
+                     float* h, const void* next_weight, int next_weight_f32, float next_offset, float* ss_out,
+                     const float* ss_in, int parts_in, int stride_in, float eps_in, int dim_in, int split,
+                     hb_stream stream);
+int hb_qkv_rope_mid(void* q_out, const void* x, const void* w, int m, int k, const int32_t* positions, const float* table,
+                    int max_positions, const void* q_weight, const void* k_weight, int weight_f32, float eps, float offset,
+                    void* kv, const int32_t* write_index, int pages, int page_size, int heads, int kv_heads, int head_dim,
+                    const float* ss_in, int parts_in, int stride_in, float eps_in, int dim_in, int split, hb_stream stream);
+int hb_gemm_mid_status(unsigned int* status);
+
 // The waits inside the tcgen05 kernels are bounded; one that gives up records (place << 28) | (block + 1) in its
 // kernel file's status word (the *_status functions above read those, synchronising) and in one word of page-locked
 // host memory that hb_status_word hands out: the host reads it without a copy or a synchronisation, after a step's

@@ -11,6 +11,7 @@ extern "C" int hb_gemm_tcgen05_status_mirror(unsigned int* word);
 extern "C" int hb_gemm_tcgen05_pair_status_mirror(unsigned int* word);
 extern "C" int hb_gemm_chain_status_mirror(unsigned int* word);
 extern "C" int hb_gemm_tickets_status_mirror(unsigned int* word);
+extern "C" int hb_gemm_mid_status_mirror(unsigned int* word);
 HB_DEFINE_STATUS_MIRROR(hb_status_selftest_mirror)
 
 static unsigned int* g_word_host = nullptr;
@@ -28,7 +29,7 @@ extern "C" int hb_status_word(unsigned int** host) {
         HB_CUDA(cudaHostGetDevicePointer((void**)&device, word, 0));
         if (hb_attention_tcgen05_status_mirror(device) || hb_gemm_tcgen05_status_mirror(device) ||
             hb_gemm_tcgen05_pair_status_mirror(device) || hb_gemm_chain_status_mirror(device) ||
-            hb_gemm_tickets_status_mirror(device) ||
+            hb_gemm_tickets_status_mirror(device) || hb_gemm_mid_status_mirror(device) ||
             hb_status_selftest_mirror(device))
             return HB_ERR_CUDA;
         g_word_host = word;

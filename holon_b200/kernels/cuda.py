@@ -99,6 +99,11 @@ class CudaKernels:
         self.decode_cluster = os.environ.get("HOLON_B200_DECODE_CLUSTER", "1") != "0"   # splits of up to 16 merge in the kernel
         self.fused_qkv = os.environ.get("HOLON_B200_FUSED_QKV", "1") != "0"   # decode steps: norm, rotation, cache write in the product
         self.fused_norm = os.environ.get("HOLON_B200_FUSED_NORM", "1") != "0"   # decode steps: residual sum and next norm in the product before
+        # Steps of 17 to MID_ROWS rows: the products that have work fused behind them (q/k norm, rotation and cache write;
+        # SwiGLU; the residual sum and the next norm) run in csrc/gemm_mid.cu ("1"), or every product goes to the library
+        # and that work to kernels of its own ("0"). `mid_split`: tests force the cluster size (0: chosen per launch).
+        self.mid = os.environ.get("HOLON_B200_MID", "1") != "0"
+        self.mid_split = 0
         self.sms = torch.cuda.get_device_properties(self.device).multi_processor_count
         self.decode_ctas = None               # tests: a fixed number of CTAs for the balanced kernel
         self.prefill_tile = None              # tests, microbench: 128 or 256 queries a CTA of the tcgen05 prefill kernel
@@ -300,7 +305,7 @@ class CudaKernels:
         SKINNY_ROWS rows, another dtype, a head size other than 32, 64 or 128, a partial rotation or none."""
         scaled, x = (x, x.y) if hasattr(x, "ss") else (None, x)      # rows that lack their norm's scale (parts.base.Scaled)
         t, k = x.shape
-        if not self.fused_qkv or x.dtype != torch.bfloat16 or t > self.SKINNY_ROWS or k % 8 or table is None \
+        if not self.fused_qkv or x.dtype != torch.bfloat16 or t > (self.MID_ROWS if self.mid else self.SKINNY_ROWS) or k % 8 or table is None \
                 or head_dim not in (32, 64, 128) or rotary_dim != head_dim or (q_weight is None) != (k_weight is None):
             return False
         self._check(q_out, x, weight, positions, table, q_weight, k_weight, kv, write_index)
@@ -313,6 +318,16 @@ class CudaKernels:
             raise KernelError("qkv_rope: kv must be [pages, 2, kv_heads, page_size, head_dim], bfloat16")
         if q_weight is not None and q_weight.dtype != k_weight.dtype:
             raise KernelError("qkv_rope: the two norm weights must have one dtype")
+        if t > self.SKINNY_ROWS:
+            self._call("hb_qkv_rope_mid", self._p(q_out), self._p(x), self._p(weight), t, k,
+                       self._i32(positions, "positions"), self._p(table), table.shape[0], self._p(q_weight), self._p(k_weight),
+                       int(q_weight is not None and q_weight.dtype == torch.float32), ctypes.c_float(eps),
+                       ctypes.c_float(offset), self._p(kv), self._i32(write_index, "write_index"),
+                       kv.shape[0] if kv is not None else 0, kv.shape[3] if kv is not None else 1, heads, kv_heads, head_dim,
+                       self._p(scaled.ss) if scaled else None, scaled.ss.shape[0] if scaled else 0,
+                       scaled.ss.shape[1] if scaled else 0, ctypes.c_float(scaled.eps if scaled else 0.0),
+                       scaled.dim if scaled else 0, int(self.mid_split))
+            return True
         if self._pending and scaled is not None and self._chains(t, k, x, weight):
             # the product that made these rows is still queued: this one joins it as a plain product, so that the
             # weights of both stream through one kernel, and the norm, rotation and cache write run behind it
@@ -491,9 +506,9 @@ class CudaKernels:
     # ---- the residual sum and the next norm inside the product that ends a part (decode steps)
     def can_link(self, rows: int, hidden: int, norm) -> bool:
         """Whether a product of `rows` rows may add itself into the stream and leave `norm`'s rows unscaled for the
-        next product: both run in the weight-streaming kernel, which takes SKINNY_ROWS rows."""
+        next product: both run in the weight-streaming kernels, which take SKINNY_ROWS rows and, on clusters, MID_ROWS."""
         w = getattr(norm, "weight", None)
-        return self.fused_norm and 0 < rows <= self.SKINNY_ROWS and hidden % 8 == 0 and w is not None \
+        return self.fused_norm and 0 < rows <= (self.MID_ROWS if self.mid else self.SKINNY_ROWS) and hidden % 8 == 0 and w is not None \
             and w.tensor.dtype in (torch.bfloat16, torch.float32) and w.tensor.shape == (hidden,)
 
     def linear_link(self, h, x, weight, norm_weight, eps: float, offset: float):
@@ -504,10 +519,17 @@ class CudaKernels:
         m, k = x.shape
         n = weight.shape[0]
         if x.dtype != torch.bfloat16 or weight.dtype != torch.bfloat16 or h.dtype != torch.float32 or k % 8 \
-                or not 0 < m <= self.SKINNY_ROWS or tuple(h.shape) != (m, n) or weight.shape != (n, k):
+                or not 0 < m <= (self.MID_ROWS if self.mid else self.SKINNY_ROWS) or tuple(h.shape) != (m, n) \
+                or weight.shape != (n, k):
             return None
         self._check(h, x, weight, norm_weight)
         y = torch.empty((m, n), dtype=torch.bfloat16, device=self.device)
+        if m > self.SKINNY_ROWS:
+            ss = torch.empty((-(-n // 256), self.MID_ROWS), dtype=torch.float32, device=self.device)
+            self._call("hb_gemm_bf16_mid", self._p(y), 0, self._p(x), self._p(weight), m, n, k, 3, 0, self._p(h),
+                       self._p(norm_weight), int(norm_weight.dtype == torch.float32), ctypes.c_float(offset), self._p(ss),
+                       None, 0, 0, ctypes.c_float(0.0), 0, int(self.mid_split))
+            return Scaled(y, ss, float(eps), n)
         parts = -(-n // 16)
         ss = torch.empty((parts, 16), dtype=torch.float32, device=self.device)
         if self._chains(m, k, x, weight, y) and norm_weight.dtype in (torch.bfloat16, torch.float32):
@@ -523,8 +545,12 @@ class CudaKernels:
         y = x.y
         self._check(out, y, x.ss, weight)
         m, k = y.shape
-        if m > self.SKINNY_ROWS or k % 8 or y.dtype != torch.bfloat16 or weight.dtype != torch.bfloat16 or weight.shape[1] != k:
-            raise KernelError("a product of unscaled rows takes up to SKINNY_ROWS bfloat16 rows of a multiple of 8 columns")
+        if m > self.MID_ROWS or k % 8 or y.dtype != torch.bfloat16 or weight.dtype != torch.bfloat16 or weight.shape[1] != k:
+            raise KernelError("a product of unscaled rows takes up to MID_ROWS bfloat16 rows of a multiple of 8 columns")
+        if m > self.SKINNY_ROWS:
+            return self._call("hb_gemm_bf16_mid", self._p(out), int(out.dtype == torch.float32), self._p(y), self._p(weight),
+                              m, weight.shape[0], k, mode, inter, None, None, 0, ctypes.c_float(0.0), None, self._p(x.ss),
+                              x.ss.shape[0], x.ss.shape[1], ctypes.c_float(x.eps), x.dim, int(self.mid_split))
         if self._chains(m, k, y, weight) and out.dtype in (torch.bfloat16, torch.float32) and (mode == 0 or out.dtype == torch.bfloat16):
             self._queue(w=weight, x=x, out=out, mode=mode, n=weight.shape[0], inter=inter, scaled=x)
             return
@@ -562,6 +588,20 @@ class CudaKernels:
             torch.mm(x, weight.t(), out=out)
 
     SKINNY_ROWS = 16
+    MID_ROWS = 64                             # rows the clustered tcgen05 products take (csrc/gemm_mid.cu)
+
+    def linear_mid(self, out, x, weight, swiglu: bool = False, split: int = 0) -> None:
+        """The product (or SwiGLU's silu(gate) · up) of up to MID_ROWS bfloat16 rows on csrc/gemm_mid.cu, whatever the
+        table's own choice for these sizes would be (tests, microbench); `split`: the cluster size (0: chosen)."""
+        self._check(out, x, weight)
+        m, k = x.shape
+        n = weight.shape[0]
+        inter = n // 2 if swiglu else 0
+        if weight.shape != (n, k) or out.shape != (m, inter if swiglu else n) or x.dtype != torch.bfloat16 \
+                or weight.dtype != torch.bfloat16 or out.dtype not in (torch.bfloat16, torch.float32):
+            raise KernelError("linear_mid: bfloat16 x [m, k] and w [n, k]; out [m, n] (or [m, n / 2]) bfloat16 or float32")
+        self._call("hb_gemm_bf16_mid", self._p(out), int(out.dtype == torch.float32), self._p(x), self._p(weight), m, n, k,
+                   int(swiglu), inter, None, None, 0, ctypes.c_float(0.0), None, None, 0, 0, ctypes.c_float(0.0), 0, int(split))
 
     def linear_tcgen05(self, out, x, weight, swiglu: bool = False, pair: bool | None = None) -> None:
         """The product (or, with `swiglu`, SwiGLU's silu(gate) · up) on the hand-written tcgen05 / TMA / TMEM kernels:
@@ -595,7 +635,7 @@ class CudaKernels:
         up their barrier and flags are put back to zero, so that the next launch starts clean."""
         out = 0
         for name in ("hb_gemm_tcgen05_status", "hb_gemm_tcgen05_pair_status", "hb_attention_tcgen05_status",
-                     "hb_gemm_chain_status", "hb_gemm_tickets_status"):
+                     "hb_gemm_chain_status", "hb_gemm_tickets_status", "hb_gemm_mid_status"):
             status = ctypes.c_uint(0)
             if getattr(self.lib, name)(ctypes.byref(status)):
                 raise KernelError(self.lib.hb_last_error().decode())

@@ -134,6 +134,10 @@ def gemm(k, args) -> None:
             if m <= k.SKINNY_ROWS:
                 t_skinny = timed(lambda: k.linear(out, x, w), flush, runs)
                 line += f"  weight-streaming {t_skinny:7.1f} us ({rate(t_skinny)})"
+            if m <= k.MID_ROWS:
+                for split in (args.splits or [0]):
+                    t_mid = timed(lambda: k.linear_mid(out, x, w, split=split), flush, runs)
+                    line += f"  clustered split-k{f' ({split})' if split else ''} {t_mid:7.1f} us ({rate(t_mid)})"
             if name == "gate_up":
                 act = torch.empty(m, n // 2, device=k.device, dtype=torch.bfloat16)
                 t_fused = timed(lambda: k.linear_tcgen05(act, x, w, swiglu=True, pair=False), flush, runs)
@@ -143,6 +147,9 @@ def gemm(k, args) -> None:
                 if m <= k.SKINNY_ROWS:
                     t_sw = timed(lambda: k.swiglu_gate_up(act, x, w), flush, runs)
                     line += f"; weight-streaming with SwiGLU {t_sw:7.1f} us"
+                if m <= k.MID_ROWS:
+                    t_sw = timed(lambda: k.linear_mid(act, x, w, swiglu=True), flush, runs)
+                    line += f"; clustered split-k with SwiGLU {t_sw:7.1f} us"
             print(line)
     print("tcgen05 status", k.tcgen05_status())
 
