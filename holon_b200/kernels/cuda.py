@@ -99,11 +99,20 @@ class CudaKernels:
         self.decode_cluster = os.environ.get("HOLON_B200_DECODE_CLUSTER", "1") != "0"   # splits of up to 16 merge in the kernel
         self.fused_qkv = os.environ.get("HOLON_B200_FUSED_QKV", "1") != "0"   # decode steps: norm, rotation, cache write in the product
         self.fused_norm = os.environ.get("HOLON_B200_FUSED_NORM", "1") != "0"   # decode steps: residual sum and next norm in the product before
-        # Steps of 17 to MID_ROWS rows: the products that have work fused behind them (q/k norm, rotation and cache write;
-        # SwiGLU; the residual sum and the next norm) run in csrc/gemm_mid.cu ("1"), or every product goes to the library
-        # and that work to kernels of its own ("0"). `mid_split`: tests force the cluster size (0: chosen per launch).
-        self.mid = os.environ.get("HOLON_B200_MID", "1") != "0"
+        # Steps of 17 to MID_ROWS rows and csrc/gemm_mid.cu (HOLON_B200_MID): "0", the default: every product goes to the
+        # library and the work around it to kernels of its own; "swiglu": SwiGLU's product with its activation runs
+        # there (one CTA a tile); "all": so do the products with the q/k norm, rotation and cache write and with the
+        # residual sum and the next norm behind them (their k range is split over a cluster). Measured at Qwen3-8B sizes,
+        # 2,304 keys a row, a decode step of 64 / 32 / 17 rows: 7.31 / 5.26 / 4.45 ms with "0", 7.32 / 5.28 / 4.48 with
+        # "swiglu", 7.58 / 5.38 / 4.75 with "all": the kernel streams the weight at 5.2 to 6.3 TB/s, but every launch
+        # costs 3.5 us more than the library's (set-up, the cluster's barriers, 64 KB of partial sums a CTA through
+        # distributed shared memory), which is what the kernels it saves cost. `mid_split`: tests force the cluster
+        # size (0: chosen per launch).
+        self.mid_mode = os.environ.get("HOLON_B200_MID", "0")
+        if self.mid_mode not in ("0", "swiglu", "all"):
+            raise KernelError(f"HOLON_B200_MID must be 0, swiglu or all, not {self.mid_mode!r}")
         self.mid_split = 0
+        self.mid_launches = 0
         self.sms = torch.cuda.get_device_properties(self.device).multi_processor_count
         self.decode_ctas = None               # tests: a fixed number of CTAs for the balanced kernel
         self.prefill_tile = None              # tests, microbench: 128 or 256 queries a CTA of the tcgen05 prefill kernel
@@ -135,6 +144,11 @@ class CudaKernels:
         self._status_word = word
 
     # ------------------------------------------------------------------ plumbing
+    @property
+    def mid(self) -> bool:
+        """Whether steps of 17 to MID_ROWS rows keep their fused products (csrc/gemm_mid.cu)."""
+        return self.mid_mode == "all"
+
     def _call(self, name: str, *args) -> None:
         if self._pending:                      # what is queued comes first: this call may read what it writes
             self.flush()
@@ -319,6 +333,7 @@ class CudaKernels:
         if q_weight is not None and q_weight.dtype != k_weight.dtype:
             raise KernelError("qkv_rope: the two norm weights must have one dtype")
         if t > self.SKINNY_ROWS:
+            self.mid_launches += 1
             self._call("hb_qkv_rope_mid", self._p(q_out), self._p(x), self._p(weight), t, k,
                        self._i32(positions, "positions"), self._p(table), table.shape[0], self._p(q_weight), self._p(k_weight),
                        int(q_weight is not None and q_weight.dtype == torch.float32), ctypes.c_float(eps),
@@ -525,6 +540,7 @@ class CudaKernels:
         self._check(h, x, weight, norm_weight)
         y = torch.empty((m, n), dtype=torch.bfloat16, device=self.device)
         if m > self.SKINNY_ROWS:
+            self.mid_launches += 1
             ss = torch.empty((-(-n // 256), self.MID_ROWS), dtype=torch.float32, device=self.device)
             self._call("hb_gemm_bf16_mid", self._p(y), 0, self._p(x), self._p(weight), m, n, k, 3, 0, self._p(h),
                        self._p(norm_weight), int(norm_weight.dtype == torch.float32), ctypes.c_float(offset), self._p(ss),
@@ -548,6 +564,7 @@ class CudaKernels:
         if m > self.MID_ROWS or k % 8 or y.dtype != torch.bfloat16 or weight.dtype != torch.bfloat16 or weight.shape[1] != k:
             raise KernelError("a product of unscaled rows takes up to MID_ROWS bfloat16 rows of a multiple of 8 columns")
         if m > self.SKINNY_ROWS:
+            self.mid_launches += 1
             return self._call("hb_gemm_bf16_mid", self._p(out), int(out.dtype == torch.float32), self._p(y), self._p(weight),
                               m, weight.shape[0], k, mode, inter, None, None, 0, ctypes.c_float(0.0), None, self._p(x.ss),
                               x.ss.shape[0], x.ss.shape[1], ctypes.c_float(x.eps), x.dim, int(self.mid_split))
@@ -600,6 +617,7 @@ class CudaKernels:
         if weight.shape != (n, k) or out.shape != (m, inter if swiglu else n) or x.dtype != torch.bfloat16 \
                 or weight.dtype != torch.bfloat16 or out.dtype not in (torch.bfloat16, torch.float32):
             raise KernelError("linear_mid: bfloat16 x [m, k] and w [n, k]; out [m, n] (or [m, n / 2]) bfloat16 or float32")
+        self.mid_launches += 1
         self._call("hb_gemm_bf16_mid", self._p(out), int(out.dtype == torch.float32), self._p(x), self._p(weight), m, n, k,
                    int(swiglu), inter, None, None, 0, ctypes.c_float(0.0), None, None, 0, 0, ctypes.c_float(0.0), 0, int(split))
 
@@ -662,6 +680,8 @@ class CudaKernels:
         if x.dtype == torch.bfloat16 and m <= self.SKINNY_ROWS and k % 8 == 0:
             self._call("hb_gemm_bf16_skinny", self._p(out), 0, self._p(x), self._p(weight), m, 2 * inter, k, 1, inter)
             return
+        if x.dtype == torch.bfloat16 and m <= self.MID_ROWS and k % 8 == 0 and self.mid_mode != "0" and self.gemm != "cublas":
+            return self.linear_mid(out, x, weight, swiglu=True, split=self.mid_split)
         if x.dtype == torch.bfloat16 and k % 8 == 0 and self.gemm != "cublas":
             # Measured at 24576 x 4096 against the library's product plus the activation kernel: by CTA pairs 66 us
             # against 74 at 256 rows, 280 against 317 at 2,048, 555 against 627 at 4,096, but 1,226 against 1,202 at

@@ -406,10 +406,11 @@ def test_attention_finds_one_far_key(K, dtype, page):
 @pytest.mark.parametrize("heads,kv_heads,head_dim,hidden", [(32, 8, 128, 4096), (6, 1, 64, 104), (4, 4, 32, 64), (20, 2, 128, 320)])
 @pytest.mark.parametrize("m", [1, 8, 13, 17, 40, 64])
 @pytest.mark.parametrize("norm", ["bfloat16", "float32", None])
-def test_qkv_product_with_norm_rotation_and_cache_write(K, heads, kv_heads, head_dim, hidden, m, norm):
+def test_qkv_product_with_norm_rotation_and_cache_write(K, heads, kv_heads, head_dim, hidden, m, norm, monkeypatch):
     """The decode step's QKV product with q/k norm, rotation and cache write in its epilogue (up to 16 rows: a cluster
     of CTAs per head; 17 to 64: a cluster per 256 weight rows that shares the k range) against the product followed by
     the separate kernel: queries, and the pages that were written."""
+    monkeypatch.setattr(K, "mid_mode", "all")
     g = torch.Generator().manual_seed(heads + m)
     x = (torch.randn(m, hidden, generator=g) * 0.5).to(torch.bfloat16)
     w = (torch.randn((heads + 2 * kv_heads) * head_dim, hidden, generator=g) * 0.05).to(torch.bfloat16)
@@ -455,6 +456,7 @@ def test_residual_sum_and_norm_inside_the_products_around_them(K, hidden, wide, 
     then agrees to one rounding of the product. (Every product its own launch here; the same products as phases of one
     kernel: test_products_chained_in_one_kernel.)"""
     monkeypatch.setattr(K, "chain", "")
+    monkeypatch.setattr(K, "mid_mode", "all")
     g = torch.Generator().manual_seed(hidden + m)
     dev = lambda t: t.to(DEV)                                          # noqa: E731
     x = dev((torch.randn(m, wide, generator=g) * 0.5).to(torch.bfloat16))

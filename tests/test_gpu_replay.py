@@ -175,3 +175,24 @@ def test_products_chained_in_one_kernel_through_the_engine(model, monkeypatch, k
     assert kernels.chain_launches - before > 50 and not kernels._pending
     compare(got, want, "bfloat16")
     assert kernels.tcgen05_status() == 0
+
+
+def test_fused_products_of_17_to_64_rows_through_the_engine(model, monkeypatch):
+    """With HOLON_B200_MID=all steps of 17 to 64 tokens keep the q/k norm, rotation and cache write, SwiGLU and the
+    residual sum with the next norm inside their products (csrc/gemm_mid.cu): the mixed trace, whose steps bring 1 to
+    70 tokens, must give the same logits as ever."""
+    from holon_b200.kernels import load_kernels
+    folder, config, prompts, want = model
+    kernels = load_kernels("cuda:0")
+    monkeypatch.setattr(kernels, "mid_mode", "all")
+    before = kernels.mid_launches
+    r = Replayer(str(folder), "bfloat16", max_tokens=448)
+    steps = mixed_trace(prompts)
+    sizes = [sum(len(tokens) for _, tokens in entries) for entries, _ in steps]
+    assert any(16 < n <= 64 for n in sizes), sizes
+    got = run(r, steps)
+    # (per layer SwiGLU's product and the products that end the mixer and the feed-forward; the attention's first
+    # product too where the head size is one its epilogue takes)
+    assert kernels.mid_launches - before >= 2 * config["num_hidden_layers"] * sum(16 < n <= 64 for n in sizes)
+    compare(got, want, "bfloat16")
+    assert kernels.tcgen05_status() == 0
