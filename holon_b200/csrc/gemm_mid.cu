@@ -83,26 +83,36 @@ __global__ void __launch_bounds__(MD_THREADS, 1) gemm_mid_kernel(const __grid_co
     const int w0 = mode == 1 ? tile * 128 : tile * MD_BN;
     const int w1 = mode == 1 ? e.inter + tile * 128 : w0 + 128;      // gate rows and the up rows of the same columns
 
-    if (threadIdx.x == 0) {
+    // The producer thread makes the barriers itself and asks for its first stages at once: the weight is on its way
+    // while the rest of the CTA sets up (tensor memory, the barrier below).
+    const int share = (m + csize - 1) / csize;                        // this CTA's rows of the tile after the sum over the cluster
+    const int r0 = min(m, (int)rank * share), r1 = min(m, r0 + share), rows = r1 - r0;
+    auto load_stage = [&](int i) {
+        const int s = i % MD_STAGES, kb = kb0 + i;
+        const uint32_t a = base + s * MD_STAGE_BYTES, b = a + MD_A_BYTES;
+        mbar_expect_tx(full0 + 8 * s, MD_STAGE_BYTES);
+        tma_load_2d(a, &map_x, full0 + 8 * s, kb * MD_BK, 0);
+        tma_load_2d(b, &map_w, full0 + 8 * s, kb * MD_BK, w0);
+        tma_load_2d(b + MD_B_BYTES / 2, &map_w, full0 + 8 * s, kb * MD_BK, w1);
+    };
+    if (warp == 2 && lane == 0) {
+        asm volatile("prefetch.tensormap [%0];\n" ::"l"(&map_x) : "memory");
+        asm volatile("prefetch.tensormap [%0];\n" ::"l"(&map_w) : "memory");
         for (int s = 0; s < MD_STAGES; ++s) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, 1); }
         mbar_init(acc_full, 1);
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+        for (int i = 0; i < min(mine, MD_STAGES); ++i) load_stage(i);
     }
     if (warp == 3) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(slot), "r"(MD_BN) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
     }
-    // this CTA's rows of the tile after the sum over the cluster, and their scales
-    const int share = (m + csize - 1) / csize;
-    const int r0 = min(m, (int)rank * share), r1 = min(m, r0 + share), rows = r1 - r0;
-    if (threadIdx.x < rows) {
-        float sc = 1.f;
-        if (e.ss_in) {
-            float ss = 0.f;
-            for (int p = 0; p < e.parts_in; ++p) ss += e.ss_in[p * e.stride_in + r0 + threadIdx.x];
-            sc = rsqrtf(ss / (float)e.dim_in + e.eps_in);
-        }
-        scale[threadIdx.x] = sc;
+    // The scale of a row of x, asked for by the lane that will read that row out of tensor memory (long before it does).
+    float row_scale = 1.f;
+    if ((warp & 3) < 2 && e.ss_in != nullptr && (warp & 3) * 32 + lane < m) {
+        float ss = 0.f;
+        for (int p = 0; p < e.parts_in; ++p) ss += e.ss_in[p * e.stride_in + (warp & 3) * 32 + lane];
+        row_scale = rsqrtf(ss / (float)e.dim_in + e.eps_in);
     }
     tc_fence_before();
     __syncthreads();
@@ -113,14 +123,9 @@ __global__ void __launch_bounds__(MD_THREADS, 1) gemm_mid_kernel(const __grid_co
     // ---- the main loop: this CTA's k blocks of the tile
     if (warp == 2) {
         if (lane == 0) {
-            for (int i = 0; i < mine; ++i) {
-                const int s = i % MD_STAGES, kb = kb0 + i;
-                if (!mbar_wait(empty0 + 8 * s, ((i / MD_STAGES) & 1) ^ 1, 1)) break;
-                const uint32_t a = base + s * MD_STAGE_BYTES, b = a + MD_A_BYTES;
-                mbar_expect_tx(full0 + 8 * s, MD_STAGE_BYTES);
-                tma_load_2d(a, &map_x, full0 + 8 * s, kb * MD_BK, 0);
-                tma_load_2d(b, &map_w, full0 + 8 * s, kb * MD_BK, w0);
-                tma_load_2d(b + MD_B_BYTES / 2, &map_w, full0 + 8 * s, kb * MD_BK, w1);
+            for (int i = MD_STAGES; i < mine; ++i) {                  // (the first stages are on their way)
+                if (!mbar_wait(empty0 + 8 * (i % MD_STAGES), ((i / MD_STAGES) & 1) ^ 1, 1)) break;
+                load_stage(i);
             }
         }
     } else if (warp == 3) {
@@ -151,7 +156,8 @@ __global__ void __launch_bounds__(MD_THREADS, 1) gemm_mid_kernel(const __grid_co
             tc_fence_after();
         }
         float* to = csize == 1 ? res : partial;
-        const float sc = csize == 1 && row < rows ? scale[row] : 1.f;
+        const float sc = csize == 1 ? row_scale : 1.f;
+        if (hf == 0 && row >= r0 && row < r1) scale[row - r0] = row_scale;
         for (int c = hf * 2; c < hf * 2 + 2; ++c) {
             uint32_t r[32];
             if (mine > 0 && ok) {
@@ -169,8 +175,10 @@ __global__ void __launch_bounds__(MD_THREADS, 1) gemm_mid_kernel(const __grid_co
     tc_fence_before();
     __syncthreads();
     __syncwarp();
-    asm volatile("barrier.cluster.arrive.release.aligned;\n" ::: "memory");
-    asm volatile("barrier.cluster.wait.acquire.aligned;\n" ::: "memory");      // every CTA's partial sums are in its shared memory
+    if (csize > 1) {                                                            // (uniform over the cluster)
+        asm volatile("barrier.cluster.arrive.release.aligned;\n" ::: "memory");
+        asm volatile("barrier.cluster.wait.acquire.aligned;\n" ::: "memory");  // every CTA's partial sums are in its shared memory
+    }
     for (int f = threadIdx.x; csize > 1 && f < rows * (MD_BN / 4); f += MD_THREADS) {      // four columns a thread
         const int rl = f >> 6, c4 = (f & 63) * 4;
         const float* p = partial + (r0 + rl) * MD_PP + c4;
@@ -186,7 +194,7 @@ __global__ void __launch_bounds__(MD_THREADS, 1) gemm_mid_kernel(const __grid_co
         *(float4*)(res + rl * MD_PP + c4) = make_float4(v.x * sc, v.y * sc, v.z * sc, v.w * sc);
     }
     __syncwarp();
-    asm volatile("barrier.cluster.arrive.release.aligned;\n" ::: "memory");    // this CTA reads no other's shared memory any more
+    if (csize > 1) asm volatile("barrier.cluster.arrive.release.aligned;\n" ::: "memory");   // this CTA reads no other's shared memory any more
     __syncthreads();
 
     // ---- the epilogues: rows r0 .. r1 of the tile, 256 columns each, in res
@@ -304,7 +312,7 @@ __global__ void __launch_bounds__(MD_THREADS, 1) gemm_mid_kernel(const __grid_co
         }
     }
     __syncwarp();
-    asm volatile("barrier.cluster.wait.acquire.aligned;\n" ::: "memory");      // nobody leaves while its shared memory may be read
+    if (csize > 1) asm volatile("barrier.cluster.wait.acquire.aligned;\n" ::: "memory");     // nobody leaves while its shared memory may be read
     tc_fence_before();
     __syncthreads();
     if (warp == 3) {

@@ -99,18 +99,21 @@ class CudaKernels:
         self.decode_cluster = os.environ.get("HOLON_B200_DECODE_CLUSTER", "1") != "0"   # splits of up to 16 merge in the kernel
         self.fused_qkv = os.environ.get("HOLON_B200_FUSED_QKV", "1") != "0"   # decode steps: norm, rotation, cache write in the product
         self.fused_norm = os.environ.get("HOLON_B200_FUSED_NORM", "1") != "0"   # decode steps: residual sum and next norm in the product before
-        # Steps of 17 to MID_ROWS rows and csrc/gemm_mid.cu (HOLON_B200_MID): "0", the default: every product goes to the
-        # library and the work around it to kernels of its own; "swiglu": SwiGLU's product with its activation runs
-        # there (one CTA a tile); "all": so do the products with the q/k norm, rotation and cache write and with the
-        # residual sum and the next norm behind them (their k range is split over a cluster). Measured at Qwen3-8B sizes,
-        # 2,304 keys a row, a decode step of 64 / 32 / 17 rows: 7.31 / 5.26 / 4.45 ms with "0", 7.32 / 5.28 / 4.48 with
-        # "swiglu", 7.58 / 5.38 / 4.75 with "all": the kernel streams the weight at 5.2 to 6.3 TB/s, but every launch
-        # costs 3.5 us more than the library's (set-up, the cluster's barriers, 64 KB of partial sums a CTA through
-        # distributed shared memory), which is what the kernels it saves cost. `mid_split`: tests force the cluster
-        # size (0: chosen per launch).
-        self.mid_mode = os.environ.get("HOLON_B200_MID", "0")
-        if self.mid_mode not in ("0", "swiglu", "all"):
-            raise KernelError(f"HOLON_B200_MID must be 0, swiglu or all, not {self.mid_mode!r}")
+        # Where csrc/gemm_mid.cu (tcgen05, the k range split over a thread-block cluster) runs (HOLON_B200_MID). "auto", the
+        # default, for weights of 32 MB or more: steps of 9 to 16 rows send the attention's first product and SwiGLU's
+        # there (the mma.sync kernel reads x for a second tile of eight rows from 9 rows on; back to back in a graph at
+        # Qwen3-8B sizes, 16 rows: QKV 13.2 us against 15.6, gate/up level, but o_proj 10.9 against 9.5, and at 8 rows
+        # the mma.sync kernel wins everywhere by 2 us: a launch of this kernel costs 5 us before its first byte counts,
+        # the other 2), and steps of 17 to MID_ROWS rows SwiGLU's product (one CTA a tile, no sum over a cluster: level
+        # with the library's product, and the activation kernel is saved). "all": steps of 17 to MID_ROWS rows keep
+        # every fused product there, instead of the library's product and kernels of their own for the work around it;
+        # "swiglu": of those only SwiGLU's, whatever the weight's size. Measured, decode steps of 64 / 32 / 17 rows at
+        # 2,304 keys: 7.31 / 5.25 / 4.46 ms with the library alone, 7.24 / 5.24 / 4.45 with SwiGLU's product here,
+        # 7.48 / 5.28 / 4.48 with "all" (a clustered product costs 3 us more than the library's, which is what the
+        # kernels it saves cost). "0": never. `mid_split`: tests force the cluster size (0: chosen per launch).
+        self.mid_mode = os.environ.get("HOLON_B200_MID", "auto")
+        if self.mid_mode not in ("0", "auto", "swiglu", "all"):
+            raise KernelError(f"HOLON_B200_MID must be 0, auto, swiglu or all, not {self.mid_mode!r}")
         self.mid_split = 0
         self.mid_launches = 0
         self.sms = torch.cuda.get_device_properties(self.device).multi_processor_count
@@ -148,6 +151,18 @@ class CudaKernels:
     def mid(self) -> bool:
         """Whether steps of 17 to MID_ROWS rows keep their fused products (csrc/gemm_mid.cu)."""
         return self.mid_mode == "all"
+
+    MID_WEIGHT = 16 << 20                     # elements of a weight from which "auto" sends a product to csrc/gemm_mid.cu
+
+    def _mid_takes(self, m: int, weight, mode: int) -> bool:
+        """Whether the product of `m` rows with `weight` and the epilogue `mode` (1 SwiGLU, 2 q/k norm, rotation and
+        cache write) runs in csrc/gemm_mid.cu rather than in the kernel for up to SKINNY_ROWS rows."""
+        if self.mid_mode == "0" or m <= 8 or m > self.MID_ROWS or (self.chain and m <= self.SKINNY_ROWS):
+            return False                                   # (chained products are the mma.sync kernel's tiles)
+        large = weight.numel() >= self.MID_WEIGHT
+        if m <= self.SKINNY_ROWS:
+            return mode in (1, 2) and large
+        return self.mid_mode == "all" or (mode == 1 and (self.mid_mode == "swiglu" or large))
 
     def _call(self, name: str, *args) -> None:
         if self._pending:                      # what is queued comes first: this call may read what it writes
@@ -332,7 +347,7 @@ class CudaKernels:
             raise KernelError("qkv_rope: kv must be [pages, 2, kv_heads, page_size, head_dim], bfloat16")
         if q_weight is not None and q_weight.dtype != k_weight.dtype:
             raise KernelError("qkv_rope: the two norm weights must have one dtype")
-        if t > self.SKINNY_ROWS:
+        if t > self.SKINNY_ROWS or self._mid_takes(t, weight, 2):
             self.mid_launches += 1
             self._call("hb_qkv_rope_mid", self._p(q_out), self._p(x), self._p(weight), t, k,
                        self._i32(positions, "positions"), self._p(table), table.shape[0], self._p(q_weight), self._p(k_weight),
@@ -563,7 +578,7 @@ class CudaKernels:
         m, k = y.shape
         if m > self.MID_ROWS or k % 8 or y.dtype != torch.bfloat16 or weight.dtype != torch.bfloat16 or weight.shape[1] != k:
             raise KernelError("a product of unscaled rows takes up to MID_ROWS bfloat16 rows of a multiple of 8 columns")
-        if m > self.SKINNY_ROWS:
+        if m > self.SKINNY_ROWS or self._mid_takes(m, weight, mode):
             self.mid_launches += 1
             return self._call("hb_gemm_bf16_mid", self._p(out), int(out.dtype == torch.float32), self._p(y), self._p(weight),
                               m, weight.shape[0], k, mode, inter, None, None, 0, ctypes.c_float(0.0), None, self._p(x.ss),
@@ -677,11 +692,11 @@ class CudaKernels:
         inter = out.shape[1]
         if weight.shape != (2 * inter, k) or out.shape[0] != m or not (out.dtype == x.dtype == weight.dtype):
             raise KernelError("swiglu_gate_up: x [tokens, k], weight [2 inter, k], out [tokens, inter], one dtype")
+        if x.dtype == torch.bfloat16 and k % 8 == 0 and self._mid_takes(m, weight, 1):
+            return self.linear_mid(out, x, weight, swiglu=True, split=self.mid_split)
         if x.dtype == torch.bfloat16 and m <= self.SKINNY_ROWS and k % 8 == 0:
             self._call("hb_gemm_bf16_skinny", self._p(out), 0, self._p(x), self._p(weight), m, 2 * inter, k, 1, inter)
             return
-        if x.dtype == torch.bfloat16 and m <= self.MID_ROWS and k % 8 == 0 and self.mid_mode != "0" and self.gemm != "cublas":
-            return self.linear_mid(out, x, weight, swiglu=True, split=self.mid_split)
         if x.dtype == torch.bfloat16 and k % 8 == 0 and self.gemm != "cublas":
             # Measured at 24576 x 4096 against the library's product plus the activation kernel: by CTA pairs 66 us
             # against 74 at 256 rows, 280 against 317 at 2,048, 555 against 627 at 4,096, but 1,226 against 1,202 at

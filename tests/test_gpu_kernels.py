@@ -530,6 +530,7 @@ def test_products_chained_in_one_kernel(K, hidden, inter, heads, kv_heads, head_
     whatever the shapes, so tiles are summed across CTAs: sums may differ in the last bits, never more. The odd sizes
     leave CTAs without work and tiles with ragged ends."""
     from holon_b200.parts.base import Scaled
+    monkeypatch.setattr(K, "mid_mode", "0")                            # (the separate launches: the mma.sync kernel's too)
     g = torch.Generator().manual_seed(hidden + 3 * m)
     dev = lambda t: t.to(DEV)                                          # noqa: E731
     mat = lambda n, k: dev((torch.randn(n, k, generator=g) * 0.05).to(torch.bfloat16))   # noqa: E731
