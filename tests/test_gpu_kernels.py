@@ -38,11 +38,12 @@ def close(got, want, dtype, scale=1.0):
     assert diff <= tol, f"difference {diff} > {tol}"
 
 
-def test_embed(K):
+@pytest.mark.parametrize("hidden", [96, 100, 4096, 5128, 10])       # (multiples of 8 take 16 bytes a load, the others 2)
+def test_embed(K, hidden):
     for dtype in DTYPES:
-        table = rand(389, 96, dtype=dtype)
+        table = rand(389, hidden, dtype=dtype)
         ids = torch.tensor([0, 388, 5, 5, 77], dtype=torch.int32)
-        out, want = torch.empty(5, 96, device=DEV), torch.empty(5, 96)
+        out, want = torch.full((5, hidden), float("nan"), device=DEV), torch.empty(5, hidden)
         K.embed(out, table.to(DEV), ids.to(DEV))
         REF.embed(want, table, ids)
         assert torch.equal(out.cpu(), want)
