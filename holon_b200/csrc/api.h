@@ -130,6 +130,16 @@ int hb_qkv_rope_skinny_linked(void* q_out, const void* x, const void* w, int m, 
                               int weight_f32, float eps, float offset, void* kv, const int32_t* write_index, int pages,
                               int page_size, int heads, int kv_heads, int head_dim, const float* ss_in, int parts_in,
                               float eps_in, int dim_in, hb_stream stream);
+// The same two for up to 32 rows (four 8-row tiles of x a warp; meant for 17 to 32 rows and weights of a few MB, where a
+// product is its launch): ss_in and ss_out hold 32 tokens a part.
+int hb_gemm_bf16_skinny32(void* out, int out_f32, const void* x, const void* w, int m, int n, int k, int mode, int inter,
+                          float* h, const void* next_weight, int next_weight_f32, float next_offset, float* ss_out,
+                          const float* ss_in, int parts_in, float eps_in, int dim_in, hb_stream stream);
+int hb_qkv_rope_skinny32(void* q_out, const void* x, const void* w, int m, int k, const int32_t* positions,
+                         const float* table, int max_positions, const void* q_weight, const void* k_weight, int weight_f32,
+                         float eps, float offset, void* kv, const int32_t* write_index, int pages, int page_size, int heads,
+                         int kv_heads, int head_dim, const float* ss_in, int parts_in, float eps_in, int dim_in,
+                         hb_stream stream);
 
 // Several products of the same few rows, one after the other, as phases of ONE persistent kernel (csrc/gemm_chain.cu):
 // the weight stream keeps running across them. A phase is a product of hb_gemm_bf16_skinny_linked (modes 0, 1, 3, same

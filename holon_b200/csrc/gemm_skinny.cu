@@ -20,6 +20,10 @@
 // product that consumes those rows (any mode, `NormLink::ss_in`) adds the partial sums up in a fixed order and scales
 // its sums by rsqrt(mean + eps) per token: x · rstd · w == (x · w) · rstd, so the norm costs no kernel and no pass
 // over the stream of its own.
+// 17 to 32 rows run the same kernel with four 8-row tiles of x a warp (the *32 entry points): every CTA then reads
+// four times the rows of x for its 16 rows of w, which a weight of a few MB does not feel (such products are their
+// launch, and this one kernel stands for a product and the kernel after it) and a large one does; the kernel table
+// sends only small weights here. Their partial sums of squares lie 32 to a part instead of 16.
 #include "skinny.cuh"
 
 #define SK_WARPS 8
@@ -43,6 +47,7 @@ struct NormLink {                                  // the residual stream and th
     const float* ss_in;                            // any mode: [parts_in, 16] of the product that made x (null: x is normed)
     float next_offset, eps_in;
     int next_weight_f32, parts_in, dim_in;
+    int stride_in, stride_out;                     // tokens a part of ss_in / ss_out holds (16, or 32 for the 32-row kernels)
 };
 
 __device__ __forceinline__ float ld_peer_f32(const float* local, uint32_t rank) {
@@ -63,9 +68,11 @@ __global__ void __launch_bounds__(SK_WARPS * 32, MIN_CTAS) gemm_skinny_kernel(vo
                                                                     const bf16* __restrict__ x, const bf16* __restrict__ w,
                                                                     int m, int n, int k, int mode, int inter,
                                                                     const RopeEpilogue ep, const NormLink link) {
+    constexpr int TOKP = NT <= 2 ? 16 : NT * 8;          // tokens the per-token arrays hold
+    constexpr int SGROUPS = SK_WARPS * 32 / TOKP;        // threads that share a token's partial sums of squares
     __shared__ float red[SK_WARPS][MT * 16][NT * 8 + 1];
-    __shared__ float scale_part[16][17];
-    __shared__ float scale_in[16];                       // per token: what the rows of x still lack (1 without a link)
+    __shared__ float scale_part[SGROUPS][TOKP + 1];
+    __shared__ float scale_in[TOKP];                     // per token: what the rows of x still lack (1 without a link)
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, r = lane >> 2, c = lane & 3;
     int row0[MT];                                        // first weight row of each tile
     int limit[MT];                                       // rows below this exist
@@ -128,10 +135,10 @@ __global__ void __launch_bounds__(SK_WARPS * 32, MIN_CTAS) gemm_skinny_kernel(vo
                     mma16816(acc[a][b], wr[u][a][0].z, wr[u][a][1].z, wr[u][a][0].w, wr[u][a][1].w, xr[u][b].z, xr[u][b].w);
                 }
     }
-    float ss_mine = 0.f;                                 // token (thread & 15): every 16th partial sum, in ascending order
+    float ss_mine = 0.f;                                 // token (thread % TOKP): every SGROUPS-th partial sum, in ascending order
     if (link.ss_in)
-        for (int p2 = threadIdx.x >> 4; p2 < link.parts_in; p2 += 16) ss_mine += link.ss_in[p2 * 16 + (threadIdx.x & 15)];
-    scale_part[threadIdx.x >> 4][threadIdx.x & 15] = ss_mine;
+        for (int p2 = threadIdx.x / TOKP; p2 < link.parts_in; p2 += SGROUPS) ss_mine += link.ss_in[p2 * link.stride_in + threadIdx.x % TOKP];
+    scale_part[threadIdx.x / TOKP][threadIdx.x % TOKP] = ss_mine;
 #pragma unroll
     for (int a = 0; a < MT; ++a)
 #pragma unroll
@@ -142,10 +149,10 @@ __global__ void __launch_bounds__(SK_WARPS * 32, MIN_CTAS) gemm_skinny_kernel(vo
             red[warp][a * 16 + r + 8][b * 8 + c * 2 + 1] = acc[a][b][3];
         }
     __syncthreads();
-    if (threadIdx.x < 16) {
+    if (threadIdx.x < TOKP) {
         float total = 0.f;
 #pragma unroll
-        for (int j = 0; j < 16; ++j) total += scale_part[j][threadIdx.x];
+        for (int j = 0; j < SGROUPS; ++j) total += scale_part[j][threadIdx.x];
         scale_in[threadIdx.x] = link.ss_in ? rsqrtf(total / (float)link.dim_in + link.eps_in) : 1.f;
     }
     __syncthreads();
@@ -222,24 +229,27 @@ __global__ void __launch_bounds__(SK_WARPS * 32, MIN_CTAS) gemm_skinny_kernel(vo
         cluster_barrier_all();                                       // nobody leaves while its shared memory may be read
         return;
     }
-    if (MT == 1 && NT <= 2 && mode == 3) {                           // 16 columns x up to 16 tokens: one thread each
-        const int rr = threadIdx.x & 15, tok = threadIdx.x >> 4, col = row0[0] + rr;
-        const bool live = tok < m && col < n;
-        float hn = 0.f;
-        if (live) {
-            const float before = link.h[(size_t)tok * n + col];
-            const float wn = link.next_weight_f32 ? ((const float*)link.next_weight)[col] : to_f32(((const bf16*)link.next_weight)[col]);
-            float v = 0.f;
+    if (MT == 1 && mode == 3) {                                      // 16 columns x 16 tokens at a time: one thread each
+        const int rr = threadIdx.x & 15, col = row0[0] + rr;
 #pragma unroll
-            for (int wv = 0; wv < SK_WARPS; ++wv) v += red[wv][rr][tok];
-            hn = before + rounded<bf16>(v * scale_in[tok]);
-            link.h[(size_t)tok * n + col] = hn;
-            ((bf16*)out)[(size_t)tok * n + col] = __float2bfloat16_rn(hn * (wn + link.next_offset));
+        for (int tok = threadIdx.x >> 4; tok < TOKP; tok += 16) {
+            const bool live = tok < m && col < n;
+            float hn = 0.f;
+            if (live) {
+                const float before = link.h[(size_t)tok * n + col];
+                const float wn = link.next_weight_f32 ? ((const float*)link.next_weight)[col] : to_f32(((const bf16*)link.next_weight)[col]);
+                float v = 0.f;
+#pragma unroll
+                for (int wv = 0; wv < SK_WARPS; ++wv) v += red[wv][rr][tok];
+                hn = before + rounded<bf16>(v * scale_in[tok]);
+                link.h[(size_t)tok * n + col] = hn;
+                ((bf16*)out)[(size_t)tok * n + col] = __float2bfloat16_rn(hn * (wn + link.next_offset));
+            }
+            float sq = hn * hn;                                      // over the token's 16 columns: lanes 0-15 or 16-31
+#pragma unroll
+            for (int o = 8; o > 0; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
+            if (rr == 0) link.ss_out[blockIdx.x * link.stride_out + tok] = sq;   // (tokens beyond m: 0)
         }
-        float sq = hn * hn;                                          // over the token's 16 columns: lanes 0-15 or 16-31
-#pragma unroll
-        for (int o = 8; o > 0; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
-        if (rr == 0) link.ss_out[blockIdx.x * 16 + tok] = sq;        // (tokens beyond m: 0)
         return;
     }
     const int rows_out = mode == 1 ? HALF * 16 : MT * 16;
@@ -272,12 +282,11 @@ __global__ void __launch_bounds__(SK_WARPS * 32, MIN_CTAS) gemm_skinny_kernel(vo
 // ss_in (any mode; null: none): x lacks its norm's row scale, rsqrt(sum of ss_in [parts_in, 16] over parts / dim_in +
 // eps_in) per token; the product's sums are scaled by it.
 // m at most 16, k a multiple of 8, all pointers 16-byte aligned.
-extern "C" int hb_gemm_bf16_skinny_linked(void* out, int out_f32, const void* x, const void* w, int m, int n, int k,
-                                          int mode, int inter, float* h, const void* next_weight, int next_weight_f32,
-                                          float next_offset, float* ss_out, const float* ss_in, int parts_in,
-                                          float eps_in, int dim_in, hb_stream stream) {
+static int skinny_product(void* out, int out_f32, const void* x, const void* w, int m, int n, int k, int mode, int inter,
+                          float* h, const void* next_weight, int next_weight_f32, float next_offset, float* ss_out,
+                          const float* ss_in, int parts_in, float eps_in, int dim_in, int most, hb_stream stream) {
     if (m == 0) return 0;
-    if (m < 0 || m > 16) HB_REFUSE("gemm_bf16_skinny: %d rows; this kernel takes 1 to 16", m);
+    if (m < 0 || m > most) HB_REFUSE("gemm_bf16_skinny: %d rows; this kernel takes 1 to %d", m, most);
     if (k < 8 || k % 8) HB_REFUSE("gemm_bf16_skinny: k = %d is no multiple of 8", k);
     if ((((uintptr_t)out | (uintptr_t)x | (uintptr_t)w) % 16) != 0) HB_REFUSE("gemm_bf16_skinny: pointers must be 16-byte aligned");
     if (mode != 0 && mode != 1 && mode != 3) HB_REFUSE("gemm_bf16_skinny: mode %d", mode);
@@ -286,6 +295,7 @@ extern "C" int hb_gemm_bf16_skinny_linked(void* out, int out_f32, const void* x,
     NormLink link = {};
     link.h = h; link.next_weight = next_weight; link.ss_out = ss_out; link.ss_in = ss_in; link.next_offset = next_offset;
     link.eps_in = eps_in; link.next_weight_f32 = next_weight_f32; link.parts_in = parts_in; link.dim_in = dim_in;
+    link.stride_in = link.stride_out = most;             // (16 tokens a part, or 32: both sides of a link run the same kernels)
     cudaStream_t s = (cudaStream_t)stream;
     static int sms = 0;
     if (sms == 0) {
@@ -295,7 +305,15 @@ extern "C" int hb_gemm_bf16_skinny_linked(void* out, int out_f32, const void* x,
     }
     const int nt = m <= 8 ? 1 : 2;
 #define HB_SK_ARGS(md, it) out, out_f32, (const bf16*)x, (const bf16*)w, m, n, k, md, it, RopeEpilogue{}, link
-    if (mode == 1) {
+    if (most > 16) {                                     // the 32-row kernels: four tiles of x a warp
+        if (mode == 1) {
+            if (inter < 1) HB_REFUSE("gemm_bf16_skinny: inter = %d", inter);
+            gemm_skinny_kernel<2, 4, 2, 2><<<(inter + 15) / 16, SK_WARPS * 32, 0, s>>>(HB_SK_ARGS(1, inter));
+        } else {
+            if (n < 1) HB_REFUSE("gemm_bf16_skinny: n = %d", n);
+            gemm_skinny_kernel<1, 4, 4, 2><<<(n + 15) / 16, SK_WARPS * 32, 0, s>>>(HB_SK_ARGS(mode, 0));
+        }
+    } else if (mode == 1) {
         if (inter < 1) HB_REFUSE("gemm_bf16_skinny: inter = %d", inter);
         const int grid = (inter + 15) / 16;
         if (nt == 1) gemm_skinny_kernel<2, 1, 4, 2><<<grid, SK_WARPS * 32, 0, s>>>(HB_SK_ARGS(1, inter));
@@ -314,6 +332,24 @@ extern "C" int hb_gemm_bf16_skinny_linked(void* out, int out_f32, const void* x,
 #undef HB_SK_ARGS
     HB_LAUNCH_CHECK("gemm_bf16_skinny");
     return 0;
+}
+
+extern "C" int hb_gemm_bf16_skinny_linked(void* out, int out_f32, const void* x, const void* w, int m, int n, int k,
+                                          int mode, int inter, float* h, const void* next_weight, int next_weight_f32,
+                                          float next_offset, float* ss_out, const float* ss_in, int parts_in,
+                                          float eps_in, int dim_in, hb_stream stream) {
+    return skinny_product(out, out_f32, x, w, m, n, k, mode, inter, h, next_weight, next_weight_f32, next_offset, ss_out,
+                          ss_in, parts_in, eps_in, dim_in, 16, stream);
+}
+
+// The same for up to 32 rows (meant for 17 to 32, and for weights of a few MB: see the head of this file); ss_in and
+// ss_out hold 32 tokens a part.
+extern "C" int hb_gemm_bf16_skinny32(void* out, int out_f32, const void* x, const void* w, int m, int n, int k, int mode,
+                                     int inter, float* h, const void* next_weight, int next_weight_f32, float next_offset,
+                                     float* ss_out, const float* ss_in, int parts_in, float eps_in, int dim_in,
+                                     hb_stream stream) {
+    return skinny_product(out, out_f32, x, w, m, n, k, mode, inter, h, next_weight, next_weight_f32, next_offset, ss_out,
+                          ss_in, parts_in, eps_in, dim_in, 32, stream);
 }
 
 extern "C" int hb_gemm_bf16_skinny(void* out, int out_f32, const void* x, const void* w, int m, int n, int k, int mode,
@@ -344,13 +380,12 @@ static int launch_head_clusters(Kernel kernel, int grid, int per_head, cudaStrea
 // values go to kv [pages, 2, kv_heads, page_size, head_dim] at write_index (kv null: they are dropped). head_dim 32, 64
 // or 128 with the whole head rotated; weights of the norms bfloat16 or float32, or null for no norm.
 // ss_in, parts_in, eps_in, dim_in: as for hb_gemm_bf16_skinny_linked (x lacks its norm's row scale).
-extern "C" int hb_qkv_rope_skinny_linked(void* q_out, const void* x, const void* w, int m, int k, const int32_t* positions,
-                                         const float* table, int max_positions, const void* q_weight, const void* k_weight,
-                                         int weight_f32, float eps, float offset, void* kv, const int32_t* write_index,
-                                         int pages, int page_size, int heads, int kv_heads, int head_dim,
-                                         const float* ss_in, int parts_in, float eps_in, int dim_in, hb_stream stream) {
+static int skinny_qkv(void* q_out, const void* x, const void* w, int m, int k, const int32_t* positions, const float* table,
+                      int max_positions, const void* q_weight, const void* k_weight, int weight_f32, float eps, float offset,
+                      void* kv, const int32_t* write_index, int pages, int page_size, int heads, int kv_heads, int head_dim,
+                      const float* ss_in, int parts_in, float eps_in, int dim_in, int most, hb_stream stream) {
     if (m == 0) return 0;
-    if (m < 0 || m > 16) HB_REFUSE("qkv_rope_skinny: %d rows; this kernel takes 1 to 16", m);
+    if (m < 0 || m > most) HB_REFUSE("qkv_rope_skinny: %d rows; this kernel takes 1 to %d", m, most);
     if (k < 8 || k % 8) HB_REFUSE("qkv_rope_skinny: k = %d is no multiple of 8", k);
     if (head_dim != 32 && head_dim != 64 && head_dim != 128) HB_REFUSE("qkv_rope_skinny: head_dim %d (32, 64 or 128)", head_dim);
     if (heads < 1 || kv_heads < 1) HB_REFUSE("qkv_rope_skinny: %d heads, %d kv heads", heads, kv_heads);
@@ -360,6 +395,7 @@ extern "C" int hb_qkv_rope_skinny_linked(void* q_out, const void* x, const void*
     if (ss_in && (parts_in < 1 || dim_in < 1)) HB_REFUSE("qkv_rope_skinny: %d partial sums over %d columns", parts_in, dim_in);
     NormLink link = {};
     link.ss_in = ss_in; link.parts_in = parts_in; link.eps_in = eps_in; link.dim_in = dim_in;
+    link.stride_in = link.stride_out = most;
     static int sms = 0;
     if (sms == 0) {
         int device = 0;
@@ -373,11 +409,32 @@ extern "C" int hb_qkv_rope_skinny_linked(void* q_out, const void* x, const void*
     ep.kv_heads = kv_heads; ep.head_dim = head_dim;
     const int per_head = head_dim / 16, n = (heads + 2 * kv_heads) * head_dim, grid = n / 16;
     cudaStream_t s = (cudaStream_t)stream;
+    if (most > 16)
+        return launch_head_clusters(gemm_skinny_kernel<1, 4, 4, 2>, grid, per_head, s, nullptr, (const bf16*)x, (const bf16*)w, m, n, k, ep, link);
     if (m <= 8 && grid > 2 * sms && grid <= 3 * sms)
         return launch_head_clusters(gemm_skinny_kernel<1, 1, 4, 3>, grid, per_head, s, nullptr, (const bf16*)x, (const bf16*)w, m, n, k, ep, link);
     if (m <= 8)
         return launch_head_clusters(gemm_skinny_kernel<1, 1, 8, 2>, grid, per_head, s, nullptr, (const bf16*)x, (const bf16*)w, m, n, k, ep, link);
     return launch_head_clusters(gemm_skinny_kernel<1, 2, 8, 2>, grid, per_head, s, nullptr, (const bf16*)x, (const bf16*)w, m, n, k, ep, link);
+}
+
+extern "C" int hb_qkv_rope_skinny_linked(void* q_out, const void* x, const void* w, int m, int k, const int32_t* positions,
+                                         const float* table, int max_positions, const void* q_weight, const void* k_weight,
+                                         int weight_f32, float eps, float offset, void* kv, const int32_t* write_index,
+                                         int pages, int page_size, int heads, int kv_heads, int head_dim,
+                                         const float* ss_in, int parts_in, float eps_in, int dim_in, hb_stream stream) {
+    return skinny_qkv(q_out, x, w, m, k, positions, table, max_positions, q_weight, k_weight, weight_f32, eps, offset, kv,
+                      write_index, pages, page_size, heads, kv_heads, head_dim, ss_in, parts_in, eps_in, dim_in, 16, stream);
+}
+
+// The same for up to 32 tokens; ss_in holds 32 tokens a part.
+extern "C" int hb_qkv_rope_skinny32(void* q_out, const void* x, const void* w, int m, int k, const int32_t* positions,
+                                    const float* table, int max_positions, const void* q_weight, const void* k_weight,
+                                    int weight_f32, float eps, float offset, void* kv, const int32_t* write_index,
+                                    int pages, int page_size, int heads, int kv_heads, int head_dim, const float* ss_in,
+                                    int parts_in, float eps_in, int dim_in, hb_stream stream) {
+    return skinny_qkv(q_out, x, w, m, k, positions, table, max_positions, q_weight, k_weight, weight_f32, eps, offset, kv,
+                      write_index, pages, page_size, heads, kv_heads, head_dim, ss_in, parts_in, eps_in, dim_in, 32, stream);
 }
 
 extern "C" int hb_qkv_rope_skinny(void* q_out, const void* x, const void* w, int m, int k, const int32_t* positions,

@@ -116,6 +116,10 @@ class CudaKernels:
             raise KernelError(f"HOLON_B200_MID must be 0, auto, swiglu or all, not {self.mid_mode!r}")
         self.mid_split = 0
         self.mid_launches = 0
+        # Steps of 17 to WIDE_ROWS rows and weights below MID_WEIGHT elements (small models, where a kernel is its launch):
+        # the mma.sync kernel with four tiles of x a warp keeps the fused epilogues ("1"), or the library multiplies and
+        # kernels of their own do the rest ("0").
+        self.skinny32 = os.environ.get("HOLON_B200_SKINNY32", "1") != "0"
         self.sms = torch.cuda.get_device_properties(self.device).multi_processor_count
         self.decode_ctas = None               # tests: a fixed number of CTAs for the balanced kernel
         self.prefill_tile = None              # tests, microbench: 128 or 256 queries a CTA of the tcgen05 prefill kernel
@@ -151,6 +155,14 @@ class CudaKernels:
     def mid(self) -> bool:
         """Whether steps of 17 to MID_ROWS rows keep their fused products (csrc/gemm_mid.cu)."""
         return self.mid_mode == "all"
+
+    WIDE_ROWS = 32                            # rows the mma.sync kernel takes with four tiles of x a warp
+
+    def _wide_takes(self, m: int, weight, stride: int | None = None) -> bool:
+        """Whether a product of 17 to WIDE_ROWS rows with a small `weight` runs in the 32-row mma.sync kernel (`stride`:
+        the tokens a part of its rows' partial sums holds, if the rows are parts.base.Scaled: that kernel reads 32)."""
+        return self.skinny32 and self.SKINNY_ROWS < m <= self.WIDE_ROWS and weight.numel() < self.MID_WEIGHT \
+            and stride in (None, self.WIDE_ROWS) and not (self.mid_mode == "all" and stride is None)
 
     MID_WEIGHT = 16 << 20                     # elements of a weight from which "auto" sends a product to csrc/gemm_mid.cu
 
@@ -334,7 +346,8 @@ class CudaKernels:
         SKINNY_ROWS rows, another dtype, a head size other than 32, 64 or 128, a partial rotation or none."""
         scaled, x = (x, x.y) if hasattr(x, "ss") else (None, x)      # rows that lack their norm's scale (parts.base.Scaled)
         t, k = x.shape
-        if not self.fused_qkv or x.dtype != torch.bfloat16 or t > (self.MID_ROWS if self.mid else self.SKINNY_ROWS) or k % 8 or table is None \
+        wide = x.dtype == torch.bfloat16 and self._wide_takes(t, weight, scaled.ss.shape[1] if scaled else None)
+        if not self.fused_qkv or x.dtype != torch.bfloat16 or (t > (self.MID_ROWS if self.mid else self.SKINNY_ROWS) and not wide) or k % 8 or table is None \
                 or head_dim not in (32, 64, 128) or rotary_dim != head_dim or (q_weight is None) != (k_weight is None):
             return False
         self._check(q_out, x, weight, positions, table, q_weight, k_weight, kv, write_index)
@@ -347,6 +360,15 @@ class CudaKernels:
             raise KernelError("qkv_rope: kv must be [pages, 2, kv_heads, page_size, head_dim], bfloat16")
         if q_weight is not None and q_weight.dtype != k_weight.dtype:
             raise KernelError("qkv_rope: the two norm weights must have one dtype")
+        if wide:
+            self._call("hb_qkv_rope_skinny32", self._p(q_out), self._p(x), self._p(weight), t, k,
+                       self._i32(positions, "positions"), self._p(table), table.shape[0], self._p(q_weight), self._p(k_weight),
+                       int(q_weight is not None and q_weight.dtype == torch.float32), ctypes.c_float(eps),
+                       ctypes.c_float(offset), self._p(kv), self._i32(write_index, "write_index"),
+                       kv.shape[0] if kv is not None else 0, kv.shape[3] if kv is not None else 1, heads, kv_heads, head_dim,
+                       self._p(scaled.ss) if scaled else None, scaled.ss.shape[0] if scaled else 0,
+                       ctypes.c_float(scaled.eps if scaled else 0.0), scaled.dim if scaled else 0)
+            return True
         if t > self.SKINNY_ROWS or self._mid_takes(t, weight, 2):
             self.mid_launches += 1
             self._call("hb_qkv_rope_mid", self._p(q_out), self._p(x), self._p(weight), t, k,
@@ -538,7 +560,8 @@ class CudaKernels:
         """Whether a product of `rows` rows may add itself into the stream and leave `norm`'s rows unscaled for the
         next product: both run in the weight-streaming kernels, which take SKINNY_ROWS rows and, on clusters, MID_ROWS."""
         w = getattr(norm, "weight", None)
-        return self.fused_norm and 0 < rows <= (self.MID_ROWS if self.mid else self.SKINNY_ROWS) and hidden % 8 == 0 and w is not None \
+        most = self.MID_ROWS if self.mid else self.WIDE_ROWS if self.skinny32 else self.SKINNY_ROWS
+        return self.fused_norm and 0 < rows <= most and hidden % 8 == 0 and w is not None \
             and w.tensor.dtype in (torch.bfloat16, torch.float32) and w.tensor.shape == (hidden,)
 
     def linear_link(self, h, x, weight, norm_weight, eps: float, offset: float):
@@ -548,12 +571,19 @@ class CudaKernels:
         from ..parts.base import Scaled
         m, k = x.shape
         n = weight.shape[0]
+        wide = self._wide_takes(m, weight)
         if x.dtype != torch.bfloat16 or weight.dtype != torch.bfloat16 or h.dtype != torch.float32 or k % 8 \
-                or not 0 < m <= (self.MID_ROWS if self.mid else self.SKINNY_ROWS) or tuple(h.shape) != (m, n) \
+                or not (0 < m <= (self.MID_ROWS if self.mid else self.SKINNY_ROWS) or wide) or tuple(h.shape) != (m, n) \
                 or weight.shape != (n, k):
             return None
         self._check(h, x, weight, norm_weight)
         y = torch.empty((m, n), dtype=torch.bfloat16, device=self.device)
+        if wide:
+            ss = torch.empty((-(-n // 16), self.WIDE_ROWS), dtype=torch.float32, device=self.device)
+            self._call("hb_gemm_bf16_skinny32", self._p(y), 0, self._p(x), self._p(weight), m, n, k, 3, 0, self._p(h),
+                       self._p(norm_weight), int(norm_weight.dtype == torch.float32), ctypes.c_float(offset), self._p(ss),
+                       None, 0, ctypes.c_float(0.0), 0)
+            return Scaled(y, ss, float(eps), n)
         if m > self.SKINNY_ROWS:
             self.mid_launches += 1
             ss = torch.empty((-(-n // 256), self.MID_ROWS), dtype=torch.float32, device=self.device)
@@ -578,6 +608,10 @@ class CudaKernels:
         m, k = y.shape
         if m > self.MID_ROWS or k % 8 or y.dtype != torch.bfloat16 or weight.dtype != torch.bfloat16 or weight.shape[1] != k:
             raise KernelError("a product of unscaled rows takes up to MID_ROWS bfloat16 rows of a multiple of 8 columns")
+        if self._wide_takes(m, weight, x.ss.shape[1]):
+            return self._call("hb_gemm_bf16_skinny32", self._p(out), int(out.dtype == torch.float32), self._p(y),
+                              self._p(weight), m, weight.shape[0], k, mode, inter, None, None, 0, ctypes.c_float(0.0), None,
+                              self._p(x.ss), x.ss.shape[0], ctypes.c_float(x.eps), x.dim)
         if m > self.SKINNY_ROWS or self._mid_takes(m, weight, mode):
             self.mid_launches += 1
             return self._call("hb_gemm_bf16_mid", self._p(out), int(out.dtype == torch.float32), self._p(y), self._p(weight),
@@ -692,6 +726,9 @@ class CudaKernels:
         inter = out.shape[1]
         if weight.shape != (2 * inter, k) or out.shape[0] != m or not (out.dtype == x.dtype == weight.dtype):
             raise KernelError("swiglu_gate_up: x [tokens, k], weight [2 inter, k], out [tokens, inter], one dtype")
+        if x.dtype == torch.bfloat16 and k % 8 == 0 and self._wide_takes(m, weight):
+            return self._call("hb_gemm_bf16_skinny32", self._p(out), 0, self._p(x), self._p(weight), m, 2 * inter, k, 1, inter,
+                              None, None, 0, ctypes.c_float(0.0), None, None, 0, ctypes.c_float(0.0), 0)
         if x.dtype == torch.bfloat16 and k % 8 == 0 and self._mid_takes(m, weight, 1):
             return self.linear_mid(out, x, weight, swiglu=True, split=self.mid_split)
         if x.dtype == torch.bfloat16 and m <= self.SKINNY_ROWS and k % 8 == 0:

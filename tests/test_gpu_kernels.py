@@ -407,11 +407,17 @@ def test_attention_finds_one_far_key(K, dtype, page):
 @pytest.mark.parametrize("heads,kv_heads,head_dim,hidden", [(32, 8, 128, 4096), (6, 1, 64, 104), (4, 4, 32, 64), (20, 2, 128, 320)])
 @pytest.mark.parametrize("m", [1, 8, 13, 17, 40, 64])
 @pytest.mark.parametrize("norm", ["bfloat16", "float32", None])
-def test_qkv_product_with_norm_rotation_and_cache_write(K, heads, kv_heads, head_dim, hidden, m, norm, monkeypatch):
+@pytest.mark.parametrize("wide", [False, True])
+def test_qkv_product_with_norm_rotation_and_cache_write(K, heads, kv_heads, head_dim, hidden, m, norm, wide, monkeypatch):
     """The decode step's QKV product with q/k norm, rotation and cache write in its epilogue (up to 16 rows: a cluster
     of CTAs per head; 17 to 64: a cluster per 256 weight rows that shares the k range) against the product followed by
-    the separate kernel: queries, and the pages that were written."""
-    monkeypatch.setattr(K, "mid_mode", "all")
+    the separate kernel: queries, and the pages that were written. `wide`: 17 to 32 rows through the mma.sync kernel
+    with four tiles of x a warp (weights of a few MB) instead."""
+    if wide and not 16 < m <= 32:
+        pytest.skip("the 32-row kernels take 17 to 32 rows")
+    monkeypatch.setattr(K, "mid_mode", "0" if wide else "all")
+    monkeypatch.setattr(K, "skinny32", wide)
+    monkeypatch.setattr(K, "MID_WEIGHT", 1 << 40 if wide else K.MID_WEIGHT)   # (whatever the weight's size)
     g = torch.Generator().manual_seed(heads + m)
     x = (torch.randn(m, hidden, generator=g) * 0.5).to(torch.bfloat16)
     w = (torch.randn((heads + 2 * kv_heads) * head_dim, hidden, generator=g) * 0.05).to(torch.bfloat16)
@@ -447,17 +453,22 @@ def test_qkv_product_with_norm_rotation_and_cache_write(K, heads, kv_heads, head
 
 
 @pytest.mark.parametrize("hidden,wide", [(4096, 4096), (96, 192), (200, 72), (1024, 3072)])
-@pytest.mark.parametrize("m", [1, 8, 16, 17, 33, 64])
+@pytest.mark.parametrize("m", [1, 8, 16, 17, 32, 33, 64])
 @pytest.mark.parametrize("norm", ["bfloat16", "float32"])
-def test_residual_sum_and_norm_inside_the_products_around_them(K, hidden, wide, m, norm, monkeypatch):
+@pytest.mark.parametrize("rows32", [False, True])
+def test_residual_sum_and_norm_inside_the_products_around_them(K, hidden, wide, m, norm, rows32, monkeypatch):
     """A product that adds itself into the 32-bit stream and leaves the next norm's rows unscaled, and the three
     products that take such rows (plain, SwiGLU, QKV with rotation), against the separate kernels: product,
     add_rmsnorm, product. Up to 16 rows the stream itself must come out the same to the bit (both ways sum in the
     same order); from 17 rows on the separate product is the library's, whose sums may round another way: the stream
     then agrees to one rounding of the product. (Every product its own launch here; the same products as phases of one
     kernel: test_products_chained_in_one_kernel.)"""
+    if rows32 and not 16 < m <= 32:
+        pytest.skip("the 32-row kernels take 17 to 32 rows")
     monkeypatch.setattr(K, "chain", "")
-    monkeypatch.setattr(K, "mid_mode", "all")
+    monkeypatch.setattr(K, "mid_mode", "0" if rows32 else "all")       # rows32: the mma.sync kernel with four tiles of x a warp
+    monkeypatch.setattr(K, "skinny32", rows32)
+    monkeypatch.setattr(K, "MID_WEIGHT", 1 << 40 if rows32 else K.MID_WEIGHT)  # (whatever the weight's size)
     g = torch.Generator().manual_seed(hidden + m)
     dev = lambda t: t.to(DEV)                                          # noqa: E731
     x = dev((torch.randn(m, wide, generator=g) * 0.5).to(torch.bfloat16))
@@ -466,7 +477,7 @@ def test_residual_sum_and_norm_inside_the_products_around_them(K, hidden, wide, 
     gain = dev((1 + 0.1 * torch.randn(hidden, generator=g)).to(getattr(torch, norm)))
     eps, offset = 1e-5, 0.25
     norm_part = types.SimpleNamespace(weight=types.SimpleNamespace(tensor=gain))
-    assert K.can_link(m, hidden, norm_part) and not K.can_link(65, hidden, norm_part)
+    assert K.can_link(m, hidden, norm_part) and not K.can_link(33 if rows32 else 65, hidden, norm_part)
     # the separate kernels
     delta = torch.empty(m, hidden, dtype=torch.bfloat16, device=DEV)
     K.linear(delta, x, w)
@@ -479,7 +490,7 @@ def test_residual_sum_and_norm_inside_the_products_around_them(K, hidden, wide, 
     if m <= 16:
         assert rows.ss.shape == (-(-hidden // 16), 16) and torch.equal(h_got, h_want) and (rows.ss[:, m:] == 0).all()
     else:
-        assert rows.ss.shape == (-(-hidden // 256), 64)
+        assert rows.ss.shape == ((-(-hidden // 16), 32) if rows32 else (-(-hidden // 256), 64))
         assert (h_got - h_want).abs().max() <= 2.0 ** -7 * float(delta.float().abs().max())
     ss = rows.ss.double().sum(0)[:m].cpu()
     assert torch.allclose(ss, h_got.double().pow(2).sum(-1).cpu(), rtol=1e-5)
