@@ -405,16 +405,14 @@ def test_attention_finds_one_far_key(K, dtype, page):
 
 
 @pytest.mark.parametrize("heads,kv_heads,head_dim,hidden", [(32, 8, 128, 4096), (6, 1, 64, 104), (4, 4, 32, 64), (20, 2, 128, 320)])
-@pytest.mark.parametrize("m", [1, 8, 13, 17, 40, 64])
+@pytest.mark.parametrize("m,wide", [(1, False), (8, False), (13, False), (17, False), (40, False), (64, False),
+                                    (17, True), (32, True)])
 @pytest.mark.parametrize("norm", ["bfloat16", "float32", None])
-@pytest.mark.parametrize("wide", [False, True])
 def test_qkv_product_with_norm_rotation_and_cache_write(K, heads, kv_heads, head_dim, hidden, m, norm, wide, monkeypatch):
     """The decode step's QKV product with q/k norm, rotation and cache write in its epilogue (up to 16 rows: a cluster
     of CTAs per head; 17 to 64: a cluster per 256 weight rows that shares the k range) against the product followed by
     the separate kernel: queries, and the pages that were written. `wide`: 17 to 32 rows through the mma.sync kernel
     with four tiles of x a warp (weights of a few MB) instead."""
-    if wide and not 16 < m <= 32:
-        pytest.skip("the 32-row kernels take 17 to 32 rows")
     monkeypatch.setattr(K, "mid_mode", "0" if wide else "all")
     monkeypatch.setattr(K, "skinny32", wide)
     monkeypatch.setattr(K, "MID_WEIGHT", 1 << 40 if wide else K.MID_WEIGHT)   # (whatever the weight's size)
@@ -453,9 +451,9 @@ def test_qkv_product_with_norm_rotation_and_cache_write(K, heads, kv_heads, head
 
 
 @pytest.mark.parametrize("hidden,wide", [(4096, 4096), (96, 192), (200, 72), (1024, 3072)])
-@pytest.mark.parametrize("m", [1, 8, 16, 17, 32, 33, 64])
+@pytest.mark.parametrize("m,rows32", [(1, False), (8, False), (16, False), (17, False), (32, False), (33, False),
+                                      (64, False), (17, True), (32, True)])
 @pytest.mark.parametrize("norm", ["bfloat16", "float32"])
-@pytest.mark.parametrize("rows32", [False, True])
 def test_residual_sum_and_norm_inside_the_products_around_them(K, hidden, wide, m, norm, rows32, monkeypatch):
     """A product that adds itself into the 32-bit stream and leaves the next norm's rows unscaled, and the three
     products that take such rows (plain, SwiGLU, QKV with rotation), against the separate kernels: product,
@@ -463,8 +461,6 @@ def test_residual_sum_and_norm_inside_the_products_around_them(K, hidden, wide, 
     same order); from 17 rows on the separate product is the library's, whose sums may round another way: the stream
     then agrees to one rounding of the product. (Every product its own launch here; the same products as phases of one
     kernel: test_products_chained_in_one_kernel.)"""
-    if rows32 and not 16 < m <= 32:
-        pytest.skip("the 32-row kernels take 17 to 32 rows")
     monkeypatch.setattr(K, "chain", "")
     monkeypatch.setattr(K, "mid_mode", "0" if rows32 else "all")       # rows32: the mma.sync kernel with four tiles of x a warp
     monkeypatch.setattr(K, "skinny32", rows32)
