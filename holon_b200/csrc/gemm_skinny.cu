@@ -111,6 +111,31 @@ __global__ void __launch_bounds__(SK_WARPS * 32, MIN_CTAS) gemm_skinny_kernel(vo
 #pragma unroll
         for (int b = 0; b < NT; ++b) acc[a][b][0] = acc[a][b][1] = acc[a][b][2] = acc[a][b][3] = 0.f;
 
+    // Mode 2 with at most 16 tokens: what this thread's element of the epilogue reads from global memory (its token's
+    // position, then the cosine and sine there; the norm weights of its column and of its partner; where the cache is
+    // written) is asked for here, ahead of the weights: at the end of the CTA each would be a trip to the L2 in a row
+    // (0.2 to 0.3 us a launch, measured back to back in a graph).
+    float pf_cs = 1.f, pf_sn = 0.f, pf_w = 1.f, pf_wo = 1.f;
+    int pf_write = -1;
+    if (MT == 1 && NT <= 2 && mode == 2 && threadIdx.x < 16 * m) {
+        const int per_head = ep.head_dim >> 4, rank = blockIdx.x % per_head, item = blockIdx.x / per_head;
+        const int tok = threadIdx.x >> 4, col = rank * 16 + (threadIdx.x & 15), half = ep.head_dim >> 1;
+        const bool is_q = item < ep.heads, is_v = item >= ep.heads + ep.kv_heads;
+        const void* weight = is_q ? ep.q_weight : ep.k_weight;
+        if (!is_v) {
+            const int pair = col < half ? col : col - half, pcol = col < half ? col + half : col - half;
+            if (weight) {
+                pf_w = ep.weight_f32 ? ((const float*)weight)[col] : to_f32(((const bf16*)weight)[col]);
+                pf_wo = ep.weight_f32 ? ((const float*)weight)[pcol] : to_f32(((const bf16*)weight)[pcol]);
+            }
+            int pos = ep.positions[tok];
+            pos = pos < 0 ? 0 : (pos >= ep.max_positions ? ep.max_positions - 1 : pos);
+            pf_cs = ep.table[(size_t)pos * ep.head_dim + pair];
+            pf_sn = ep.table[(size_t)pos * ep.head_dim + half + pair];
+        }
+        if (!is_q && ep.kv) pf_write = ep.write_index[tok];
+    }
+
     const int blocks = (k + 31) >> 5;                    // 32-wide k blocks; warp w takes w, w + 8, ...
     for (int kb = warp; kb < blocks; kb += SK_WARPS * SK_UNROLL) {
         uint4 wr[SK_UNROLL][MT][2], xr[SK_UNROLL][NT];
@@ -193,23 +218,27 @@ __global__ void __launch_bounds__(SK_WARPS * 32, MIN_CTAS) gemm_skinny_kernel(vo
         for (int i = threadIdx.x; i < 16 * m; i += SK_WARPS * 32) {
             const int rr = i & 15, tok = i >> 4, col = rank * 16 + rr;          // column inside the head
             const int pair = col < half ? col : col - half, pcol = col < half ? col + half : col - half;
-            float y = res[tok][rr], other = 0.f, w_mine = 1.f, w_other = 1.f, cs = 1.f, sn = 0.f;
-            if (!is_v) {                                             // everything is asked for before anything is used
-                other = ld_peer_f32(&res[tok][rr], rank ^ (per_head >> 1));     // the column half a head away
-                if (weight) {
-                    w_mine = ep.weight_f32 ? ((const float*)weight)[col] : to_f32(((const bf16*)weight)[col]);
-                    w_other = ep.weight_f32 ? ((const float*)weight)[pcol] : to_f32(((const bf16*)weight)[pcol]);
+            float y = res[tok][rr], other = 0.f, w_mine = pf_w, w_other = pf_wo, cs = pf_cs, sn = pf_sn;
+            int w = pf_write;
+            if (!is_v) other = ld_peer_f32(&res[tok][rr], rank ^ (per_head >> 1));   // the column half a head away
+            if (NT > 2) {                                            // (more tokens than threads: nothing was asked for ahead)
+                w_mine = w_other = 1.f; cs = 1.f; sn = 0.f; w = -1;
+                if (!is_v) {
+                    if (weight) {
+                        w_mine = ep.weight_f32 ? ((const float*)weight)[col] : to_f32(((const bf16*)weight)[col]);
+                        w_other = ep.weight_f32 ? ((const float*)weight)[pcol] : to_f32(((const bf16*)weight)[pcol]);
+                    }
+                    int pos = ep.positions[tok];
+                    pos = pos < 0 ? 0 : (pos >= ep.max_positions ? ep.max_positions - 1 : pos);
+                    cs = ep.table[(size_t)pos * ep.head_dim + pair];
+                    sn = ep.table[(size_t)pos * ep.head_dim + half + pair];
                 }
-                int pos = ep.positions[tok];
-                pos = pos < 0 ? 0 : (pos >= ep.max_positions ? ep.max_positions - 1 : pos);
-                cs = ep.table[(size_t)pos * ep.head_dim + pair];
-                sn = ep.table[(size_t)pos * ep.head_dim + half + pair];
+                if (!is_q && ep.kv) w = ep.write_index[tok];
             }
             bf16* dst = nullptr;
             if (is_q) {
                 dst = ep.q_out + ((size_t)tok * ep.heads + item) * ep.head_dim + col;
             } else if (ep.kv) {
-                const int w = ep.write_index[tok];
                 const int page = w >= 0 ? w / ep.page_size : -1, off = w >= 0 ? w % ep.page_size : 0;
                 const int head = item - ep.heads - (is_v ? ep.kv_heads : 0);
                 if (page >= 0 && page < ep.pages)
