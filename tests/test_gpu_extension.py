@@ -6,7 +6,6 @@ table's error with the kernel's own text; and a bounded wait inside the part's k
 engine's status word like a wait of the engine's own kernels."""
 from __future__ import annotations
 
-import ctypes
 import pathlib
 
 import pytest
