@@ -174,7 +174,7 @@ class CudaKernels:
         large = weight.numel() >= self.MID_WEIGHT
         if m <= self.SKINNY_ROWS:
             return mode in (1, 2) and large
-        return self.mid_mode == "all" or (mode == 1 and (self.mid_mode == "swiglu" or large))
+        return self.mid_mode == "all" or (mode == 1 and (self.mid_mode == "swiglu" or (large and self.gemm != "cublas")))
 
     def _call(self, name: str, *args) -> None:
         if self._pending:                      # what is queued comes first: this call may read what it writes
