@@ -57,9 +57,24 @@ __global__ void __launch_bounds__(SAMPLE_THREADS) sample_kernel(
     // ---- the largest logit and its first index
     float best = -INFINITY;
     int arg = vocab;
-    for (int i = tid; i < vocab; i += SAMPLE_THREADS) {
-        const float v = x[i];
-        if (v > best) { best = v; arg = i; }
+    if ((vocab & 3) == 0 && (((uintptr_t)x) & 15) == 0) {           // four logits a load, two loads in flight a thread
+        const float4* x4 = (const float4*)x;
+        const int pieces = vocab >> 2;
+        for (int i0 = tid; i0 < pieces; i0 += 2 * SAMPLE_THREADS) {
+            const int i1 = i0 + SAMPLE_THREADS;
+            const float4 a = x4[i0];
+            const float4 b = i1 < pieces ? x4[i1] : make_float4(-INFINITY, -INFINITY, -INFINITY, -INFINITY);
+            const float va[4] = {a.x, a.y, a.z, a.w}, vb[4] = {b.x, b.y, b.z, b.w};
+#pragma unroll
+            for (int e = 0; e < 4; ++e) if (va[e] > best) { best = va[e]; arg = i0 * 4 + e; }   // (ascending indices: the first of equals)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) if (vb[e] > best) { best = vb[e]; arg = i1 * 4 + e; }
+        }
+    } else {
+        for (int i = tid; i < vocab; i += SAMPLE_THREADS) {
+            const float v = x[i];
+            if (v > best) { best = v; arg = i; }
+        }
     }
     const float top = block_max(best, scratch);
     int cand = best == top ? arg : vocab;
