@@ -107,18 +107,28 @@ __global__ void __launch_bounds__(MD_THREADS, 1) gemm_mid_kernel(const __grid_co
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(slot), "r"(MD_BN) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
     }
-    // The scale of a row of x, asked for by the lane that will read that row out of tensor memory (long before it does).
-    float row_scale = 1.f;
-    if ((warp & 3) < 2 && e.ss_in != nullptr && (warp & 3) * 32 + lane < m) {
-        float ss = 0.f;
-        for (int p = 0; p < e.parts_in; ++p) ss += e.ss_in[p * e.stride_in + (warp & 3) * 32 + lane];
-        row_scale = rsqrtf(ss / (float)e.dim_in + e.eps_in);
-    }
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
     uint32_t tmem;
     asm volatile("ld.shared.b32 %0, [%1];\n" : "=r"(tmem) : "r"(slot));
+
+    // The scales of the rows of x, by the fourteen warps that neither load nor issue, while those two work: a warp a
+    // row, a lane every 32nd part, summed over the warp in a fixed order. (One lane a row, all parts in turn, before the
+    // barrier above held the first MMA back by the whole walk: 8 us at 16 rows and 256 parts.)
+    if (warp != 2 && warp != 3) {
+        if (e.ss_in != nullptr) {
+            for (int row = warp < 2 ? warp : warp - 2; row < m; row += MD_THREADS / 32 - 2) {
+                float ss = 0.f;
+                for (int p = lane; p < e.parts_in; p += 32) ss += e.ss_in[p * e.stride_in + row];
+                ss = warp_sum(ss);
+                if (lane == 0) scale[row] = rsqrtf(ss / (float)e.dim_in + e.eps_in);
+            }
+        } else if (threadIdx.x < MD_ROWS) {
+            scale[threadIdx.x] = 1.f;
+        }
+        asm volatile("bar.sync 1, %0;\n" ::"n"(MD_THREADS - 64) : "memory");    // (the fourteen warps: the scales are there)
+    }
 
     // ---- the main loop: this CTA's k blocks of the tile
     if (warp == 2) {
@@ -156,8 +166,7 @@ __global__ void __launch_bounds__(MD_THREADS, 1) gemm_mid_kernel(const __grid_co
             tc_fence_after();
         }
         float* to = csize == 1 ? res : partial;
-        const float sc = csize == 1 ? row_scale : 1.f;
-        if (hf == 0 && row >= r0 && row < r1) scale[row - r0] = row_scale;
+        const float sc = csize == 1 && row < m ? scale[row] : 1.f;
         for (int c = hf * 2; c < hf * 2 + 2; ++c) {
             uint32_t r[32];
             if (mine > 0 && ok) {
@@ -190,7 +199,7 @@ __global__ void __launch_bounds__(MD_THREADS, 1) gemm_mid_kernel(const __grid_co
 #pragma unroll
         for (int r2 = 1; r2 < 8; ++r2)
             if (r2 < csize) { v.x += part[r2].x; v.y += part[r2].y; v.z += part[r2].z; v.w += part[r2].w; }
-        const float sc = scale[rl];
+        const float sc = scale[r0 + rl];
         *(float4*)(res + rl * MD_PP + c4) = make_float4(v.x * sc, v.y * sc, v.z * sc, v.w * sc);
     }
     __syncwarp();

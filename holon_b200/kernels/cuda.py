@@ -100,22 +100,26 @@ class CudaKernels:
         self.fused_qkv = os.environ.get("HOLON_B200_FUSED_QKV", "1") != "0"   # decode steps: norm, rotation, cache write in the product
         self.fused_norm = os.environ.get("HOLON_B200_FUSED_NORM", "1") != "0"   # decode steps: residual sum and next norm in the product before
         # Where csrc/gemm_mid.cu (tcgen05, the k range split over a thread-block cluster) runs (HOLON_B200_MID). "auto", the
-        # default, for weights of 32 MB or more: steps of 9 to 16 rows send the attention's first product and SwiGLU's
-        # there (the mma.sync kernel reads x for a second tile of eight rows from 9 rows on; back to back in a graph at
-        # Qwen3-8B sizes, 16 rows: QKV 13.2 us against 15.6, gate/up level, but o_proj 10.9 against 9.5, and at 8 rows
-        # the mma.sync kernel wins everywhere by 2 us: a launch of this kernel costs 5 us before its first byte counts,
-        # the other 2), and steps of 17 to MID_ROWS rows SwiGLU's product (one CTA a tile, no sum over a cluster: level
-        # with the library's product, and the activation kernel is saved). "all": steps of 17 to MID_ROWS rows keep
-        # every fused product there, instead of the library's product and kernels of their own for the work around it;
-        # "swiglu": of those only SwiGLU's, whatever the weight's size. Measured, decode steps of 64 / 32 / 17 rows at
-        # 2,304 keys: 7.31 / 5.25 / 4.46 ms with the library alone, 7.24 / 5.24 / 4.45 with SwiGLU's product here,
-        # 7.48 / 5.28 / 4.48 with "all" (a clustered product costs 3 us more than the library's, which is what the
-        # kernels it saves cost). "0": never. `mid_split`: tests force the cluster size (0: chosen per launch).
+        # default, for weights of 32 MB or more: SwiGLU's product at up to MID_ROWS rows (one CTA a tile, no sum over a
+        # cluster; its idle warps add up the row scales while the weights stream, which costs the mma.sync kernel a trip
+        # to the L2 at the end of every CTA: back to back in a graph on rows that lack their norm's scale, Qwen3-8B
+        # sizes, 36.3 us against 38.0 at 8 rows, 36.3 against 37.4 at 1, 36.5 against 42.3 at 16; from 17 rows level
+        # with the library's product, and the activation kernel is saved), and the attention's first product at 9 to
+        # 16 rows (14.4 us against 15.1 at 16 rows: the mma.sync kernel reads x for a second tile of eight rows there;
+        # at 8 rows it is 13.9 against 14.1 the other way). o_proj and down stay with the mma.sync kernel up to 16 rows
+        # (8.5 and 18.6 us against 10.3 and 20.6: a launch of this kernel costs 5 us before its first byte counts, the
+        # other 2). "all": steps of 17 to MID_ROWS rows keep every fused product there, instead of the library's
+        # product and kernels of their own for the work around it; "swiglu": of those only SwiGLU's, whatever the
+        # weight's size. Measured, decode steps of 64 / 32 / 17 rows at 2,304 keys: 7.31 / 5.25 / 4.46 ms with the library
+        # alone, 7.24 / 5.24 / 4.45 with SwiGLU's product here, 7.48 / 5.28 / 4.48 with "all" (a clustered product costs
+        # 3 us more than the library's, which is what the kernels it saves cost). "0": never. `mid_split`: tests force
+        # the cluster size (0: chosen per launch).
         self.mid_mode = os.environ.get("HOLON_B200_MID", "auto")
         if self.mid_mode not in ("0", "auto", "swiglu", "all"):
             raise KernelError(f"HOLON_B200_MID must be 0, auto, swiglu or all, not {self.mid_mode!r}")
         self.mid_split = 0
         self.mid_launches = 0
+        self.mid_min_rows = int(os.environ.get("HOLON_B200_MID_MIN_ROWS", "9"))   # the attention's first product: fewer rows stay with the mma.sync kernel
         # Steps of 17 to WIDE_ROWS rows and weights below MID_WEIGHT elements (small models, where a kernel is its launch):
         # the mma.sync kernel with four tiles of x a warp keeps the fused epilogues ("1"), or the library multiplies and
         # kernels of their own do the rest ("0").
@@ -169,11 +173,11 @@ class CudaKernels:
     def _mid_takes(self, m: int, weight, mode: int) -> bool:
         """Whether the product of `m` rows with `weight` and the epilogue `mode` (1 SwiGLU, 2 q/k norm, rotation and
         cache write) runs in csrc/gemm_mid.cu rather than in the kernel for up to SKINNY_ROWS rows."""
-        if self.mid_mode == "0" or m <= 8 or m > self.MID_ROWS or (self.chain and m <= self.SKINNY_ROWS):
+        if self.mid_mode == "0" or m > self.MID_ROWS or (self.chain and m <= self.SKINNY_ROWS):
             return False                                   # (chained products are the mma.sync kernel's tiles)
         large = weight.numel() >= self.MID_WEIGHT
-        if m <= self.SKINNY_ROWS:
-            return mode in (1, 2) and large
+        if m <= self.SKINNY_ROWS:                          # SwiGLU's at any number of rows, the attention's first from 9 on
+            return large and (mode == 1 or (mode == 2 and m >= self.mid_min_rows))
         return self.mid_mode == "all" or (mode == 1 and (self.mid_mode == "swiglu" or (large and self.gemm != "cublas")))
 
     def _call(self, name: str, *args) -> None:

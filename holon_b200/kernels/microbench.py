@@ -3,6 +3,11 @@
     python -m holon_b200.kernels.microbench decode_attention [--rows 8 64 1] [--context 8192] [--splits 4 6 13]
     python -m holon_b200.kernels.microbench gemm [--rows 2048] [--shapes qkv o gate_up down]
     python -m holon_b200.kernels.microbench prefill_attention [--rows 2048] [--context 2048]
+    python -m holon_b200.kernels.microbench layer [--rows 8 1 16 64] [--context 8192]
+
+`layer` times the kernels of a decode layer the way a step runs them: back to back inside a CUDA graph, each launch
+on weights (or a cache) other than the launch before, several hundred MB in turn, so that nothing comes from the L2
+and nothing of the host's pace or of an event's own cost is in the number.
 
 Sizes default to Qwen3-8B's (32 query and 8 KV heads of 128, hidden 4096, intermediate 12288). `layer_table` times
 every kernel of one decode layer and of one prefill layer the same way and sets each time against the bytes or the
@@ -293,9 +298,94 @@ def chain(k, args) -> None:
     print("status", k.tcgen05_status())
 
 
+def in_graph(calls, reps: int = 12) -> float:
+    """Microseconds a call of `calls` takes on average when `reps` rounds of them run back to back in a CUDA graph
+    (the fastest of five replays)."""
+    for fn in calls:
+        fn()
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        for _ in range(reps):
+            for fn in calls:
+                fn()
+    graph.replay()
+    torch.cuda.synchronize()
+    best = float("inf")
+    for _ in range(5):
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        graph.replay()
+        end.record()
+        torch.cuda.synchronize()
+        best = min(best, start.elapsed_time(end) * 1e3 / (reps * len(calls)))
+    return best
+
+
+def layer(k, args) -> None:
+    """The kernels of one decode layer at Qwen3-8B sizes, each back to back in a graph: the four products plain, and
+    as the engine runs them (the attention's first with q/k norm, rotation and cache write; the mixer's and the
+    feed-forward's last with the residual sum and the next norm; SwiGLU's on rows that lack their norm's scale), and
+    the attention over `--context` keys. The bytes a kernel must read over the copy bandwidth stand beside each time."""
+    from ..parts.base import Scaled
+    heads, kvh, d, hidden, inter, page = 32, 8, 128, 4096, 12288, 64
+    dev, bf = k.device, torch.bfloat16
+    rand = lambda *shape: torch.randn(*shape, device=dev, dtype=bf) * 0.02   # noqa: E731
+    inv = 1.0 / (1e6 ** (torch.arange(0, d, 2, dtype=torch.float32) / d))
+    angle = torch.arange(args.context + 1, dtype=torch.float32)[:, None] * inv[None, :]
+    table = torch.cat((angle.cos(), angle.sin()), dim=-1).contiguous().to(dev)
+    gain_d, gain_h = torch.ones(d, device=dev, dtype=bf), torch.ones(hidden, device=dev, dtype=bf)
+    ideal = lambda numel: 2 * numel / 6.55e6                            # noqa: E731  (us at 6.55 TB/s)
+    for m in args.rows:
+        x, act, attn = rand(m, hidden) * 50, rand(m, inter) * 50, rand(m, heads * d) * 50
+        positions = torch.randint(0, args.context, (m,), dtype=torch.int32, device=dev)
+        cache = torch.zeros(64, 2, kvh, page, d, device=dev, dtype=bf)
+        write = torch.randperm(64 * page)[:m].to(torch.int32).to(dev)
+        q = torch.empty(m, heads, d, device=dev, dtype=bf)
+        h = torch.randn(m, hidden, device=dev)
+        unscaled = Scaled(x, torch.rand(hidden // 16, 16, device=dev), 1e-6, hidden) if m <= k.SKINNY_ROWS else None
+        shapes = {"qkv": ((heads + 2 * kvh) * d, hidden), "o": (hidden, heads * d), "gate_up": (2 * inter, hidden), "down": (hidden, inter)}
+        for name, (n, kk) in shapes.items():
+            ws = [rand(n, kk) for _ in range(4 if n * kk < 60e6 else 2)]
+            src = {"qkv": x, "o": attn, "gate_up": x, "down": act}[name]
+            out = torch.empty(m, n // 2 if name == "gate_up" else n, device=dev, dtype=bf)
+            if name == "gate_up":
+                plain = in_graph([(lambda w=w: k.swiglu_gate_up(out, src, w)) for w in ws])
+                fused = in_graph([(lambda w=w: k.swiglu_gate_up(out, unscaled, w)) for w in ws]) if unscaled else None
+                what = "with SwiGLU", "the same on rows that lack their norm's scale"
+            elif name == "qkv":
+                plain = in_graph([(lambda w=w: k.linear(out, src, w)) for w in ws])
+                rope = lambda rows, w: k.qkv_rope(q, rows, w, positions, table, d, gain_d, gain_d, 1e-6, 0.0, cache, write, heads, kvh, d)   # noqa: E731
+                fused = in_graph([(lambda w=w: rope(src, w)) for w in ws]) if rope(src, ws[0]) else None
+                what = "plain", "with q/k norm, rotation and cache write"
+                if fused is not None and unscaled is not None:
+                    late = in_graph([(lambda w=w: rope(unscaled, w)) for w in ws])
+                    what = what[0], what[1] + f" (on rows that lack their norm's scale {late:6.2f} us)"
+            else:
+                plain = in_graph([(lambda w=w: k.linear(out, src, w)) for w in ws])
+                fused = in_graph([(lambda w=w: k.linear_link(h, src, w, gain_h, 1e-6, 0.0)) for w in ws]) \
+                    if k.linear_link(h, src, ws[0], gain_h, 1e-6, 0.0) is not None else None
+                what = "plain", "with the residual sum and the next norm"
+            line = f"rows {m:3d} {name:8s} {what[0]}: {plain:6.2f} us"
+            if fused is not None:
+                line += f"; {what[1]}: {fused:6.2f} us"
+            print(line + f"  (the weight at the copy bandwidth: {ideal(n * kk):5.1f} us)")
+            del ws
+        per = -(-args.context // page)
+        caches = [torch.randn(m * per + 1, 2, kvh, page, d, device=dev, dtype=bf) for _ in range(max(2, min(8, int(400e6 // (m * per * page * kvh * d * 4)) + 1)))]
+        blocks = torch.arange(m * per, device=dev, dtype=torch.int32).view(m, per).contiguous()
+        ar = torch.arange(m + 1, device=dev, dtype=torch.int32)
+        batch = Rows(ar[:m].contiguous(), ar, torch.full((m,), args.context, device=dev, dtype=torch.int32), m, m, m, 1, args.context)
+        o = torch.empty_like(q)
+        t = in_graph([(lambda c=c: k.paged_attention(o, q, c, blocks, batch, 1 / math.sqrt(d), 0)) for c in caches])
+        print(f"rows {m:3d} attention over {args.context} keys: {t:6.2f} us  (its cache at the copy bandwidth: {ideal(m * args.context * kvh * d * 2):5.1f} us)")
+        del caches
+    print("status", k.tcgen05_status())
+
+
 def main() -> None:
     ap = argparse.ArgumentParser(description=__doc__.split("\n\n")[0])
-    ap.add_argument("what", choices=("decode_attention", "gemm", "prefill_attention", "chain"))
+    ap.add_argument("what", choices=("decode_attention", "gemm", "prefill_attention", "chain", "layer"))
     ap.add_argument("--rows", type=int, nargs="*", default=None)
     ap.add_argument("--context", type=int, default=8192)
     ap.add_argument("--splits", type=int, nargs="*", default=None)
@@ -311,6 +401,9 @@ def main() -> None:
         elif args.what == "chain":
             args.rows = args.rows or [1, 8, 16]
             chain(k, args)
+        elif args.what == "layer":
+            args.rows = args.rows or [8, 1, 16, 64]
+            layer(k, args)
         elif args.what == "prefill_attention":
             args.rows = args.rows or [2048]
             prefill_attention(k, args)
