@@ -176,7 +176,7 @@ int hb_gemm_bf16_tcgen05_pair(void* out, int out_f32, const void* x, const void*
 int hb_gemm_tcgen05_pair_status(unsigned int* status);
 int hb_gemm_tcgen05_pair_width(int bn);             // tests: fix the tile width (0: chosen per launch)
 
-// bfloat16 products of 17 to 64 rows with the following work in their epilogue (csrc/gemm_mid.cu): weight tiles of
+// bfloat16 products of 1 to 64 rows with the following work in their epilogue (csrc/gemm_mid.cu): weight tiles of
 // 256 rows on tcgen05, a tile's k range split over a thread-block cluster of `split` CTAs (0: chosen; 1 to 8) that
 // sum their partial results through distributed shared memory. mode 0 plain, 1 SwiGLU (w [2 inter, k], gate rows
 // first; out [m, inter]), 3 residual sum and next norm (h [m, n] float32 += product; out = bfloat16(h (next_weight +

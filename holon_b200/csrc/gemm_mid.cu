@@ -1,5 +1,7 @@
-// bfloat16 products of 17 to 64 rows (decode steps of many requests): out[m, n] = sum_k x[m, k] * w[n, k], bound by
-// reading w once, with the work that follows the product in its epilogue, as in the kernel for up to 16 rows.
+// bfloat16 products of up to 64 rows (decode steps): out[m, n] = sum_k x[m, k] * w[n, k], bound by reading w once, with
+// the work that follows the product in its epilogue, as in the mma.sync kernel for up to 16 rows. The kernel table sends
+// SwiGLU's product here at every number of rows, the attention's first from 9 rows on, and from 17 rows on whatever
+// HOLON_B200_MID says.
 //
 // The weight is the N side of tcgen05.mma: a tile is 256 rows of w (8 KB of weights an MMA of 16 k values, so the one
 // issuing thread keeps up with the memory) against the rows of x on the M side (a box of 64 rows; the MMA's other 64
