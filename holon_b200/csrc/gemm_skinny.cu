@@ -57,6 +57,11 @@ __device__ __forceinline__ float ld_peer_f32(const float* local, uint32_t rank) 
     asm volatile("ld.shared::cluster.f32 %0, [%1];\n" : "=f"(v) : "r"(remote) : "memory");
     return v;
 }
+__device__ __forceinline__ void st_peer_f32(float* local, uint32_t rank, float v) {
+    uint32_t remote;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;\n" : "=r"(remote) : "r"((uint32_t)__cvta_generic_to_shared(local)), "r"(rank));
+    asm volatile("st.shared::cluster.f32 [%0], %1;\n" ::"r"(remote), "f"(v) : "memory");
+}
 __device__ __forceinline__ void cluster_barrier_all() {
     asm volatile("barrier.cluster.arrive.release.aligned;\n" ::: "memory");
     asm volatile("barrier.cluster.wait.acquire.aligned;\n" ::: "memory");
@@ -74,6 +79,8 @@ __global__ void __launch_bounds__(SK_WARPS * 32, MIN_CTAS) gemm_skinny_kernel(vo
     __shared__ float scale_part[SGROUPS][TOKP + 1];
     __shared__ float scale_in[TOKP];                     // per token: what the rows of x still lack (1 without a link)
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, r = lane >> 2, c = lane & 3;
+    if (MT == 1 && mode == 2 && (int)(blockIdx.x / (ep.head_dim >> 4)) < ep.heads + ep.kv_heads)   // a head that is normed and rotated:
+        asm volatile("barrier.cluster.arrive.release.aligned;\n" ::: "memory");   // its CTAs say that they run (waited for in the epilogue)
     int row0[MT];                                        // first weight row of each tile
     int limit[MT];                                       // rows below this exist
     constexpr int HALF = MT > 1 ? MT / 2 : 1;           // mode 1: the CTA's gate tiles, then as many up tiles
@@ -182,36 +189,45 @@ __global__ void __launch_bounds__(SK_WARPS * 32, MIN_CTAS) gemm_skinny_kernel(vo
     }
     __syncthreads();
     if (MT == 1 && mode == 2) {
+        // The CTAs of a head hand one another what they need by writing it into the others' shared memory (the head's
+        // sums of squares to every CTA, the rotation partner's columns to the CTA half a head away), then meet at one
+        // cluster barrier; nobody reads another's memory, so nobody waits for the others before it leaves. (The CTAs of a
+        // cluster are known to run once the barrier of the kernel's first lines has completed.)
         __shared__ float res[NT * 8][16];                            // the product, rounded as the separate kernel's input is
-        __shared__ float psum[NT * 8];                               // this CTA's share of each token's sum of squares
+        __shared__ float other_s[NT * 8][16];                        // the same of the CTA half a head away, written by it
+        __shared__ float psum_all[8][NT * 8];                        // per CTA of the head: its share of each token's sum of squares
         const int per_head = ep.head_dim >> 4, rank = blockIdx.x % per_head, item = blockIdx.x / per_head;
         const bool is_q = item < ep.heads, is_v = item >= ep.heads + ep.kv_heads;
+        const void* weight = is_q ? ep.q_weight : ep.k_weight;
+        if (!is_v) asm volatile("barrier.cluster.wait.acquire.aligned;\n" ::: "memory");   // (the first lines' arrival: long complete)
         for (int i = threadIdx.x; i < 16 * m; i += SK_WARPS * 32) {
             const int rr = i & 15, tok = i >> 4;
             float v = 0.f;
 #pragma unroll
             for (int wv = 0; wv < SK_WARPS; ++wv) v += red[wv][rr][tok];
-            res[tok][rr] = rounded<bf16>(v * scale_in[tok]);
+            v = rounded<bf16>(v * scale_in[tok]);
+            res[tok][rr] = v;
+            if (!is_v) st_peer_f32(&other_s[tok][rr], rank ^ (per_head >> 1), v);
         }
         __syncthreads();
-        if (threadIdx.x < m) {
+        if (threadIdx.x < m && weight && !is_v) {
             float ss = 0.f;
 #pragma unroll
             for (int j = 0; j < 16; ++j) ss += res[threadIdx.x][j] * res[threadIdx.x][j];
-            psum[threadIdx.x] = ss;
+#pragma unroll
+            for (int p2 = 0; p2 < 8; ++p2)
+                if (p2 < per_head) st_peer_f32(&psum_all[rank][threadIdx.x], p2, ss);
         }
-        __syncthreads();
-        __syncwarp();
-        cluster_barrier_all();                                       // every CTA of the head has its 16 columns ready
-        const void* weight = is_q ? ep.q_weight : ep.k_weight;
+        if (!is_v) {                                                 // (the same for every CTA of a head)
+            __syncwarp();
+            cluster_barrier_all();                                   // what the others wrote here is here
+        }
         const int half = ep.head_dim >> 1;
         __shared__ float rstd_s[NT * 8];
         if (threadIdx.x < m && weight && !is_v) {                    // the head's sum of squares, in the order of its CTAs
-            float part[8], ss = 0.f;
+            float ss = 0.f;
 #pragma unroll
-            for (int p2 = 0; p2 < 8; ++p2) part[p2] = p2 < per_head ? ld_peer_f32(&psum[threadIdx.x], p2) : 0.f;
-#pragma unroll
-            for (int p2 = 0; p2 < 8; ++p2) ss += part[p2];
+            for (int p2 = 0; p2 < 8; ++p2) ss += p2 < per_head ? psum_all[p2][threadIdx.x] : 0.f;
             rstd_s[threadIdx.x] = rsqrtf(ss / (float)ep.head_dim + ep.eps);
         }
         __syncthreads();
@@ -220,7 +236,7 @@ __global__ void __launch_bounds__(SK_WARPS * 32, MIN_CTAS) gemm_skinny_kernel(vo
             const int pair = col < half ? col : col - half, pcol = col < half ? col + half : col - half;
             float y = res[tok][rr], other = 0.f, w_mine = pf_w, w_other = pf_wo, cs = pf_cs, sn = pf_sn;
             int w = pf_write;
-            if (!is_v) other = ld_peer_f32(&res[tok][rr], rank ^ (per_head >> 1));   // the column half a head away
+            if (!is_v) other = other_s[tok][rr];                      // the column half a head away
             if (NT > 2) {                                            // (more tokens than threads: nothing was asked for ahead)
                 w_mine = w_other = 1.f; cs = 1.f; sn = 0.f; w = -1;
                 if (!is_v) {
@@ -254,8 +270,6 @@ __global__ void __launch_bounds__(SK_WARPS * 32, MIN_CTAS) gemm_skinny_kernel(vo
             }
             if (dst) *dst = __float2bfloat16_rn(y);
         }
-        __syncwarp();
-        cluster_barrier_all();                                       // nobody leaves while its shared memory may be read
         return;
     }
     if (MT == 1 && mode == 3) {                                      // 16 columns x 16 tokens at a time: one thread each
