@@ -366,6 +366,18 @@ __device__ __forceinline__ void cluster_barrier() {
     asm volatile("barrier.cluster.wait.acquire.aligned;\n" ::: "memory");
 }
 
+#define CL_RECV_BYTES 4096
+template <int D_PAD, int STAGES> __host__ __device__ constexpr size_t decode_walk_bytes() {
+    constexpr size_t tiles = (size_t)(16 + 2 * STAGES * TILE_N) * D_PAD * sizeof(bf16);
+    constexpr size_t merge = 16 * D_PAD * sizeof(bf16) + (size_t)(4 * 16 * D_PAD + 4 * 16 * 2 + 16 * D_PAD + 16 * 2) * sizeof(float);
+    return tiles > merge ? tiles : merge;
+}
+__device__ __forceinline__ void st_cluster_f32(const float* local, uint32_t rank, float v) {
+    uint32_t remote;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;\n" : "=r"(remote) : "r"(smem_u32(local)), "r"(rank));
+    asm volatile("st.shared::cluster.f32 [%0], %1;\n" ::"r"(remote), "f"(v) : "memory");
+}
+
 template <int D_PAD, int STAGES>
 __global__ void __launch_bounds__(128) decode_cluster_kernel(
         bf16* __restrict__ out, const bf16* __restrict__ q, const bf16* __restrict__ kv,
@@ -373,6 +385,7 @@ __global__ void __launch_bounds__(128) decode_cluster_kernel(
         const int32_t* __restrict__ query_start, const int32_t* __restrict__ kv_len, int heads, int kv_heads,
         int head_dim, int pages, int page_size, int page_shift, float scale_log2, int window, int splits) {
     extern __shared__ __align__(128) unsigned char smem_raw[];
+    asm volatile("barrier.cluster.arrive.release.aligned;\n" ::: "memory");   // (this CTA runs: waited for before anybody writes here)
     const int b = blockIdx.x, split = blockIdx.z;                   // the cluster is the z direction: split = rank in it
     const int group = heads / kv_heads, m_tiles = (group + 15) / 16;
     const int hk = blockIdx.y / m_tiles, mt = blockIdx.y % m_tiles;
@@ -386,10 +399,46 @@ __global__ void __launch_bounds__(128) decode_cluster_kernel(
     decode_walk<D_PAD, STAGES>(smem_raw, out, nullptr, nullptr, 0, -1, q, kv, block_table + (size_t)row_slot[b] * table_stride,
                                t, heads, kv_heads, head_dim, pages, page_size, page_shift, scale_log2, hk, group, g0, g,
                                first, last, lo, n);
+    const int total = g * head_dim, share = (total + splits - 1) / splits;
     __syncwarp();
+    asm volatile("barrier.cluster.wait.acquire.aligned;\n" ::: "memory");     // every CTA of the cluster runs
+    if ((size_t)(splits * share + splits * g * 2) * sizeof(float) <= CL_RECV_BYTES) {   // (the same for every CTA of the launch)
+        // Every CTA writes, for each of the others, the share of its sums that the other combines (and its maxima and row
+        // sums) into the other's shared memory, behind the walk's; after one barrier each combines what lies in its own
+        // memory, in the order of the splits, and leaves: no CTA reads another's memory, none waits for the others' reads.
+        const float* mine = (const float*)(smem_raw + 16 * D_PAD * 2) + 4 * 16 * D_PAD + 4 * 16 * 2;   // [16][D_PAD], then [16][2]
+        float* recv_o = (float*)(smem_raw + decode_walk_bytes<D_PAD, STAGES>());                      // [splits][share]
+        float* recv_ml = recv_o + splits * share;                                                    // [splits][g][2]
+        for (int e = threadIdx.x; e < total; e += 128) {
+            const int peer = e / share, r = e / head_dim, d = e - r * head_dim;
+            st_cluster_f32(recv_o + split * share + (e - peer * share), peer, mine[r * D_PAD + d]);
+        }
+        for (int i = threadIdx.x; i < splits * g; i += 128) {
+            const int peer = i / g, r = i - peer * g;
+            st_cluster_f32(recv_ml + (split * g + r) * 2, peer, mine[16 * D_PAD + r * 2]);
+            st_cluster_f32(recv_ml + (split * g + r) * 2 + 1, peer, mine[16 * D_PAD + r * 2 + 1]);
+        }
+        __syncwarp();
+        cluster_barrier();
+        for (int i = threadIdx.x; i < share; i += 128) {
+            const int e = split * share + i;
+            if (e >= total) break;
+            const int r = e / head_dim, d = e % head_dim;
+            float mm = -INFINITY;
+            for (int s2 = 0; s2 < splits; ++s2) mm = fmaxf(mm, recv_ml[(s2 * g + r) * 2]);
+            float acc = 0.f, l = 0.f;
+            for (int s2 = 0; s2 < splits; ++s2) {                   // in the order of the splits
+                const float ms = recv_ml[(s2 * g + r) * 2];
+                const float fs = ms == -INFINITY ? 0.f : ex2(ms - mm);
+                acc += fs * recv_o[s2 * share + i];
+                l += fs * recv_ml[(s2 * g + r) * 2 + 1];
+            }
+            out[((size_t)t * heads + hk * group + g0 + r) * head_dim + d] = __float2bfloat16_rn(l > 0.f ? acc / l : 0.f);
+        }
+        return;
+    }
     cluster_barrier();                                              // every split's sums are in its shared memory
     const uint32_t stage = smem_u32(smem_raw) + 16 * D_PAD * 2 + (4 * 16 * D_PAD + 4 * 16 * 2) * 4;
-    const int total = g * head_dim, share = (total + splits - 1) / splits;
     for (int i = threadIdx.x; i < share; i += 128) {
         const int e = split * share + i;
         if (e >= total) break;
@@ -467,6 +516,8 @@ template <int D_PAD> static size_t decode_smem(int stages) {
     const size_t merge = 16 * D_PAD * sizeof(bf16) + (size_t)(4 * 16 * D_PAD + 4 * 16 * 2 + 16 * D_PAD + 16 * 2) * sizeof(float);
     return tiles > merge ? tiles : merge;
 }
+// The cluster kernel's shared memory: the walk's, and behind it what the other CTAs of the cluster write here.
+template <int D_PAD> static size_t decode_cluster_smem(int stages) { return decode_smem<D_PAD>(stages) + CL_RECV_BYTES; }
 
 template <int D_PAD, int STAGES>
 static int launch_decode(bf16* out, float* part_o, float* part_ml, const bf16* q, const bf16* kv,
@@ -496,7 +547,7 @@ static int decode_cluster_capacity(int splits) {
     static int known[17] = {};                                       // per size: 0 unknown, else capacity + 1
     if (known[splits] == 0) {
         auto kernel = decode_cluster_kernel<D_PAD, STAGES>;
-        const size_t smem = decode_smem<D_PAD>(STAGES);
+        const size_t smem = decode_cluster_smem<D_PAD>(STAGES);
         bool ok = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) == cudaSuccess;
         if (ok && splits > 8)
             ok = cudaFuncSetAttribute(kernel, cudaFuncAttributeNonPortableClusterSizeAllowed, 1) == cudaSuccess;
@@ -531,7 +582,7 @@ static int launch_decode_cluster(bf16* out, const bf16* q, const bf16* kv, const
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(rows, kv_heads * m_tiles, splits);
     cfg.blockDim = dim3(128);
-    cfg.dynamicSmemBytes = decode_smem<D_PAD>(STAGES);
+    cfg.dynamicSmemBytes = decode_cluster_smem<D_PAD>(STAGES);
     cfg.stream = s;
     cudaLaunchAttribute attr = {};
     attr.id = cudaLaunchAttributeClusterDimension;
