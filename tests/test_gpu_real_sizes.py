@@ -135,3 +135,52 @@ def test_mixed_steps_at_real_sizes(mixed_case, dtype):
     assert at == {rid: len(ids) for rid, ids in p.items()} and not b.cache.live
     compare(got, want, dtype)
     assert b.ctx.kernels.tcgen05_status() == 0
+
+
+@pytest.fixture(scope="module")
+def rows_case():
+    source = Held(CONFIG, seed=2)
+    prompts = {f"r{i}": random_prompt(CONFIG["vocab_size"], 70, 60 + i) for i in range(4)}
+    weights = {k: v.float() for k, v in source.kept.items()}
+    want = {}
+    for rid, ids in prompts.items():
+        exact = plain.forward(CONFIG, weights, ids)
+        with plain.rounding(torch.bfloat16):
+            want[rid] = (exact, plain.forward(CONFIG, weights, ids))
+    del weights
+    return source, prompts, want
+
+
+def test_steps_on_both_sides_of_every_row_limit_at_real_sizes(rows_case):
+    """The products change kernels with the number of rows a step brings (up to 8 and up to 16: the mma.sync kernel with
+    one and two tiles of x; SwiGLU's on the clustered tcgen05 kernel up to 64, the attention's first from 9 to 16; from
+    17 the library, from 65 for every product): steps of 65, 64, 33, 32, 17, 16, 9 and 8 tokens at the production layer
+    sizes, decode rows beside prompt portions, against the plain implementation."""
+    from replay_tools import compare
+    source, p, want = rows_case
+    b = build(source, dtype="bfloat16", device="cuda:0", page_size=64, max_seqs=4, max_model_len=128, max_step_tokens=128,
+              pages=9)
+    trace = [[("r0", 65)], [("r1", 64)], [("r0", 1), ("r2", 32)], [("r0", 1), ("r1", 1), ("r3", 30)],
+             [("r0", 1), ("r1", 1), ("r2", 15)], [("r0", 1), ("r1", 1), ("r3", 14)], [("r0", 1), ("r1", 1), ("r2", 7)],
+             [("r1", 1), ("r2", 7)], [("r1", 1), ("r2", 9), ("r3", 26)]]
+    assert [sum(n for _, n in step) for step in trace] == [65, 64, 33, 32, 17, 16, 9, 8, 36]
+    kernels = b.ctx.kernels
+    before = kernels.mid_launches
+    slots, at, got = {}, {rid: 0 for rid in p}, {}
+    for step in trace:
+        entries = []
+        for rid, n in step:
+            if rid not in slots:
+                slots[rid] = b.cache.admit()
+            assert b.cache.reserve(slots[rid], at[rid] + n)
+            entries.append(StepEntry(slots[rid], p[rid][at[rid]:at[rid] + n], at[rid], range(n)))
+        logits = b.runner.step(entries).float().cpu()
+        k = 0
+        for rid, n in step:
+            for _ in range(n):
+                got[(rid, at[rid])] = logits[k]
+                at[rid], k = at[rid] + 1, k + 1
+    assert at == {rid: 70 for rid in p}
+    assert kernels.mid_launches - before >= 2 * 8          # (SwiGLU's product of the eight steps of up to 64 rows, two layers)
+    compare(got, want, "bfloat16")
+    assert kernels.tcgen05_status() == 0
